@@ -1,0 +1,113 @@
+/* C ABI of the B200 binarised-network library (libtcbnn_b200.so).
+ *
+ * Every entry point takes plain pointers and sizes.  Unless a name ends in _host, pointers
+ * are DEVICE pointers on the current CUDA device and the work is queued on `stream`
+ * (a cudaStream_t passed as void*; NULL = default stream) without synchronising.
+ * Return value: 0 on success, non-zero on error (tcbnn_last_error() gives the text).
+ * Nothing here falls back to the CPU: without a usable CUDA device the calls fail.
+ *
+ * Bit format, shared by all tensors: element e of a row sits in 32-bit word e/32 at bit
+ * (31 - e%32) -- the order __brev(__ballot_sync()) produces in the reference packers
+ * (param.h:60).  bit 1 = +1, bit 0 = -1, pad bits are 0.
+ *   FC activations / weights : [rows][ld] words, ld a multiple of 4 (16-byte rows)
+ *   conv activations         : NHWC [B][H][W][Cw] words, Cw = ceil(C/32)
+ *   conv filters             : [O][R*S][Cw] words
+ *   residuals / accumulators : NHWC int32 [B][P][Q][O]
+ * Citations name the reference interface each entry point stands in for
+ * (file:line inside pnnl/TCBNN).
+ */
+#ifndef TCBNN_B200_H
+#define TCBNN_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int tcbnn_version(void);
+const char* tcbnn_last_error(void);
+
+/* fp32 [rows][cols] -> bit rows, bit = (x >= 0).  In128LayerFMT, kernel.cuh:153-172. */
+int tcbnn_pack_rows(const float* x, int rows, int cols, int ld_words, uint32_t* out, void* stream);
+/* bit rows -> +-1 fp32.  UnPackFcOutput128FMT param.h:87-104, UnpackConvOutput32FMT :661-688. */
+int tcbnn_unpack_rows(const uint32_t* in, int rows, int cols, int ld_words, float* out,
+                      void* stream);
+/* fp32 W[K][N] -> bit rows [N][ld_words] over K.  PackFcWeight128FMT, param.h:44-63. */
+int tcbnn_pack_fc_weight(const float* W, int K, int N, int ld_words, uint32_t* out, void* stream);
+/* fp32 F[R*S][C][O] -> bits [O][R*S][Cw].  PackFiltersByInChannels128FMT, param.h:560-581. */
+int tcbnn_pack_conv_filter(const float* F, int RS, int C, int O, uint32_t* out, void* stream);
+/* fp32 F[R*S][3][O] -> [R*S][3][Ow] words over O.  PackFiltersByOutChannels32, param.h:613-632. */
+int tcbnn_pack_inconv_filter(const float* F, int RS, int O, uint32_t* out, void* stream);
+
+/* Scratch a GEMM-family call can use to split K when M x N alone leaves SMs idle.
+ * Passing NULL / 0 is always allowed (no split). */
+size_t tcbnn_gemm_workspace_bytes(int M, int N, int K);
+
+/* C[m][n] = K - 2*popc(A[m] xor B[n]), int32 [M][ldc].
+ * BMMA / BMMAS_new, bmm/tensorcore_kernel.cu:138-356 (C = K - 2*acc at :331). */
+int tcbnn_bgemm(const uint32_t* A, const uint32_t* B, int M, int N, int K, int lda, int ldb,
+                int32_t* C, int ldc, void* workspace, size_t workspace_bytes, void* stream);
+/* Hidden FC layer: bit[m][n] = ((float)K - 2*(float)popc >= thr[n]).
+ * Fc128LayerFMT, kernel.cuh:174-226.  out: bit rows [M][ldo]; words past N/32 untouched. */
+int tcbnn_fc_layer(const uint32_t* A, const uint32_t* W, const float* thr, int M, int K, int N,
+                   int lda, int ldw, uint32_t* out, int ldo, void* workspace,
+                   size_t workspace_bytes, void* stream);
+/* Output layer: out[m][n] = fma((float)(K - 2*popc), scale[n], bias[n]), fp32 [M][ldo].
+ * Out128LayerFMT, kernel.cuh:230-280. */
+int tcbnn_out_layer(const uint32_t* A, const uint32_t* W, const float* scale, const float* bias,
+                    int M, int K, int N, int lda, int ldw, float* out, int ldo, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* Geometry of a conv layer.  Fill the input fields, call tcbnn_conv_shape() for the rest. */
+typedef struct tcbnn_conv_desc {
+    int B, H, W, C, O, R, S;
+    int stride_h, stride_w;
+    int padding;            /* 1: "same"-style padding with the reference's arithmetic */
+    int pool;               /* 1 or 2 (non-overlapping pool x pool OR-pooling) */
+    /* derived */
+    int pad_h, pad_w, OH, OW;
+} tcbnn_conv_desc;
+/* pad / output-size arithmetic of InConv128LayerParam and Conv128LayerParam
+ * (param.h:719-728, 897-906).  Host-only, no device needed. */
+int tcbnn_conv_shape(tcbnn_conv_desc* d);
+
+/* Bytes of the prepared-filter blob for a binary conv layer, and its construction from
+ * filter bits [O][R*S][Cw] (tcbnn_pack_conv_filter output).  The blob is opaque device
+ * memory owned by the caller; preparation happens once per layer, like the filter packing
+ * in Conv128LayerParam::initialize (param.h:944-985). */
+size_t tcbnn_conv_prepared_bytes(const tcbnn_conv_desc* d);
+int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, void* prepared,
+                       void* stream);
+
+/* Binary conv layer with threshold / OR-pool / residual / repack fused.
+ * Conv128LayerFMT, kernel.cuh:676-827.
+ *   in   [B][H][W][Cw]; out: image b at out + b*out_image_stride words, [OH][OW][Ow]
+ *        (out_image_stride > OH*OW*Ow lets the next FC layer see padded rows: ahead_fc)
+ *   res_in  (optional) int32 [B][P or 2P][Q or 2Q][res_in_ch]; injected for
+ *           o < residual_channels; residual_pool takes the max over the 2x2 window
+ *   res_out (optional) int32 [B][P][Q][O]: value after injection (save_residual)
+ *   acc_out (optional) int32 [B][P][Q][O]: value before injection (for checking)       */
+int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
+                     const float* thr, const int32_t* res_in, int res_in_ch,
+                     int residual_channels, int residual_pool, uint32_t* out,
+                     long long out_image_stride, int32_t* res_out, int32_t* acc_out,
+                     void* stream);
+
+/* First layer on fp32 NCHW input [B][3][H][W] (d->C must be 3).
+ * InConv128LayerFMT, kernel.cuh:578-672.  filter_bits from tcbnn_pack_inconv_filter.
+ * res_out: (int)acc, truncated toward zero; acc_out (optional): fp32 sums. */
+int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t* filter_bits,
+                       const float* thr, uint32_t* out, long long out_image_stride,
+                       int32_t* res_out, float* acc_out, void* stream);
+
+/* Issue-rate probe of the warp-level MMA forms on all SMs: kind 0 = b1 and.popc m16n8k256,
+ * 1 = b1 xor.popc m16n8k256, 2 = s8 m16n8k32.  Returns tera-ops/s (2*m*n*k per MMA) in *tops.
+ * Synchronises the device.  The reference's counterpart is the WMMA latency probe
+ * bmm/bmma_op_test/main_test.cu:35-220 and its TOPS formula at :368. */
+int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

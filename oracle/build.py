@@ -1,0 +1,71 @@
+"""Build the CPU oracle (test infrastructure) and, when the reference tree is present,
+the reference's own host popcount functions into oracle/_ref/.
+
+    python oracle/build.py [--native] [--ref-root /path/to/TCBNN]
+
+liboracle.so        : oracle/tcbnn_oracle.cpp, x86-64-v3 so the file also runs on other hosts
+liboracle_native.so : same source with -march=native (built on the machine that times it)
+_ref/libref_bmm.so  : BMMAcpu / WMMABOOLCPU compiled from the reference's source files where
+                      they lie (never copied); skipped when the tree is absent.
+"""
+import argparse
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        raise RuntimeError("build failed: " + cmd[0])
+
+
+def _stale(target, sources):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def build_oracle(native=False):
+    src = os.path.join(HERE, "tcbnn_oracle.cpp")
+    out = os.path.join(HERE, "liboracle_native.so" if native else "liboracle.so")
+    if _stale(out, [src]):
+        march = "-march=native" if native else "-march=x86-64-v3"
+        _run(["g++", "-O3", march, "-fopenmp", "-shared", "-fPIC", "-std=c++17", "-o", out, src])
+    return out
+
+
+def build_ref(ref_root="/root/reference"):
+    tc = os.path.join(ref_root, "bmm", "tensorcore_kernel.cu")
+    mt = os.path.join(ref_root, "bmm", "bmma_op_test", "main_test.cu")
+    if not (os.path.exists(tc) and os.path.exists(mt)):
+        return None
+    outdir = os.path.join(HERE, "_ref")
+    os.makedirs(outdir, exist_ok=True)
+    out = os.path.join(outdir, "libref_bmm.so")
+    wrap = os.path.join(HERE, "ref_wrap.cu")
+    if _stale(out, [wrap, tc, mt]):
+        objs = []
+        for which, src in ((1, tc), (2, mt)):
+            obj = os.path.join(outdir, "ref_wrap_%d.o" % which)
+            _run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-w",
+                  "-Xcompiler", "-fPIC", "-DWHICH=%d" % which, '-DREF_SRC="%s"' % src,
+                  "-c", "-o", obj, wrap])
+            objs.append(obj)
+        _run(["nvcc", "-shared", "-o", out] + objs)
+    return out
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--native", action="store_true")
+    ap.add_argument("--ref-root", default="/root/reference")
+    a = ap.parse_args()
+    print(build_oracle(False))
+    if a.native:
+        print(build_oracle(True))
+    print(build_ref(a.ref_root))

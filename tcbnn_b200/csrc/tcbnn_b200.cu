@@ -1,0 +1,410 @@
+// libtcbnn_b200.so: kernels and C ABI of the binarised-network hot path (see
+// include/tcbnn_b200.h for the contract of each entry point).
+#include "../../include/tcbnn_b200.h"
+#include "bnn_layers.cuh"
+#include <cstdio>
+#include <cstdarg>
+#include <cstring>
+
+using namespace tcbnn;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+#define CUDA_TRY(expr)                                                              \
+    do {                                                                            \
+        cudaError_t e_ = (expr);                                                    \
+        if (e_ != cudaSuccess)                                                      \
+            return fail("%s failed: %s", #expr, cudaGetErrorString(e_));            \
+    } while (0)
+
+int sm_count(int* sms) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail("no CUDA device: %s", cudaGetErrorString(e));
+    static int cache[64] = {0};
+    if (dev < 64 && cache[dev]) { *sms = cache[dev]; return 0; }
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || n <= 0) return fail("cannot query SM count: %s", cudaGetErrorString(e));
+    if (dev < 64) cache[dev] = n;
+    *sms = n;
+    return 0;
+}
+
+constexpr int kThreads = 256;          // 8 warps per CTA
+constexpr int kCtasPerSm = 2;          // 16 resident warps per SM, up to 128 registers each
+
+// grid for `tasks` warp-sized tasks on a persistent warp-strided loop
+int warp_grid(long long tasks, int sms) {
+    long long ctas = (tasks + (kThreads / 32) - 1) / (kThreads / 32);
+    long long cap = (long long)kCtasPerSm * sms;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    return (int)ctas;
+}
+
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) k_gemm(GemmArgs g) { gemm_layer(g); }
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) k_gemm_finish(GemmArgs g) { gemm_splitk_finish(g); }
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) k_conv(ConvArgs c) { conv_layer(c); }
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) k_inconv(InConvArgs c) { inconv_layer(c); }
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+k_pack_rows(const float* x, int rows, int cols, int ld, uint32_t* out) {
+    pack_rows(x, rows, cols, ld, out);
+}
+__global__ void k_unpack_rows(const uint32_t* in, int rows, int cols, int ld, float* out) {
+    unpack_rows(in, rows, cols, ld, out);
+}
+__global__ void k_pack_fc_weight(const float* W, int K, int N, int ld, uint32_t* out) {
+    pack_fc_weight(W, K, N, ld, out);
+}
+__global__ void k_pack_conv_filter(const float* F, int RS, int C, int O, uint32_t* out) {
+    pack_conv_filter(F, RS, C, O, out);
+}
+__global__ void k_pack_inconv_filter(const float* F, int RS, int O, uint32_t* out) {
+    pack_inconv_filter(F, RS, O, out);
+}
+__global__ void k_conv_prepare(const uint32_t* fbits, int O, int R, int S, int Cw, int W_in, int KP,
+                               uint32_t* wq, uint32_t* ktab, int* pwt, int* pwtot) {
+    conv_prepare(fbits, O, R, S, Cw, W_in, KP, wq, ktab, pwt, pwtot);
+}
+
+int launch_check(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail("%s launch failed: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+int elementwise_grid(long long n, int sms) {
+    long long b = (n + 255) / 256;
+    long long cap = 8LL * sms;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+// ---- split-K policy ---------------------------------------------------------------------
+int gemm_splits(int M, int N, int K, int sms) {
+    const long long tiles = (long long)((M + 31) / 32) * ((N + 31) / 32);
+    const long long slots = (long long)sms * kCtasPerSm * (kThreads / 32);
+    const int KP = (K + 63) / 64;
+    if (tiles * 2 > slots || KP < 32) return 1;
+    long long s = (slots + tiles - 1) / tiles;
+    if (s > KP / 8) s = KP / 8;
+    if (s > 32) s = 32;
+    return s < 1 ? 1 : (int)s;
+}
+
+int run_gemm(GemmArgs g, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (g.M <= 0 || g.N <= 0 || g.K <= 0) return fail("gemm: M, N, K must be positive");
+    if ((g.lda & 1) || (g.ldw & 1)) return fail("gemm: lda and ldw must be even (64-bit loads)");
+    if (g.lda * 32 < g.K || g.ldw * 32 < g.K) return fail("gemm: leading dimension shorter than K");
+    if ((long long)g.M * g.lda >= (1LL << 31) || (long long)g.N * g.ldw >= (1LL << 31))
+        return fail("gemm: operand larger than 2^31 words");
+    if (((uintptr_t)g.A & 7) || ((uintptr_t)g.W & 7)) return fail("gemm: operands must be 8-byte aligned");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    int splits = gemm_splits(g.M, g.N, g.K, sms);
+    const size_t need = (size_t)splits * g.M * g.N * sizeof(int32_t);
+    if (splits > 1 && (workspace == nullptr || workspace_bytes < need)) splits = 1;
+    const long long tiles = (long long)((g.M + 31) / 32) * ((g.N + 31) / 32);
+    if (splits == 1) {
+        g.splits = 1;
+        g.partial = nullptr;
+        k_gemm<<<warp_grid(tiles, sms), kThreads, 0, st>>>(g);
+        return launch_check("gemm");
+    }
+    GemmArgs p = g;
+    p.mode = GEMM_PARTIAL;
+    p.splits = splits;
+    p.partial = (int32_t*)workspace;
+    k_gemm<<<warp_grid(tiles * splits, sms), kThreads, 0, st>>>(p);
+    if (launch_check("gemm split-K")) return 1;
+    g.splits = splits;
+    g.partial = (int32_t*)workspace;
+    k_gemm_finish<<<warp_grid((long long)g.M * ((g.N + 31) / 32), sms), kThreads, 0, st>>>(g);
+    return launch_check("gemm split-K finish");
+}
+
+// ---- prepared conv filter blob ------------------------------------------------------------
+struct PreparedLayout {
+    int KP;               // 64-bit pairs per filter row, multiple of 4
+    size_t off_wq, off_ktab, off_pwt, off_pwtot, bytes;
+};
+
+int conv_check(const tcbnn_conv_desc* d, bool binary) {
+    if (!d) return fail("conv: null descriptor");
+    if (d->B <= 0 || d->H <= 0 || d->W <= 0 || d->C <= 0 || d->O <= 0 || d->R <= 0 || d->S <= 0)
+        return fail("conv: sizes must be positive");
+    if (d->R > 15 || d->S > 15) return fail("conv: filter larger than 15x15 is not supported");
+    if (d->stride_h <= 0 || d->stride_w <= 0) return fail("conv: stride must be positive");
+    if (d->pool != 1 && d->pool != 2) return fail("conv: pool must be 1 or 2");
+    if (binary && (((d->C + 31) / 32) & 1))
+        return fail("conv: input channels must fill an even number of 32-bit words (C=%d)", d->C);
+    if (!binary && d->C != 3) return fail("inconv: input channels must be 3");
+    if (!binary && d->O > 128) return fail("inconv: more than 128 output channels not supported");
+    if (d->OH <= 0 || d->OW <= 0) return fail("conv: call tcbnn_conv_shape first");
+    const long long in_words = (long long)d->B * d->H * d->W * ((d->C + 31) / 32);
+    if (binary && in_words >= (1LL << 31)) return fail("conv: input larger than 2^31 words");
+    if ((long long)d->B * d->OH * d->OW * d->pool * d->pool >= (1LL << 31))
+        return fail("conv: more than 2^31 output pixels");
+    return 0;
+}
+
+PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
+    PreparedLayout L;
+    const int Cw = (d->C + 31) / 32;
+    const int words = d->R * d->S * Cw;
+    L.KP = ((words + 7) / 8) * 4;
+    size_t o = 0;
+    L.off_wq = o;    o += (size_t)d->O * 2 * L.KP * 4;  o = (o + 255) & ~(size_t)255;
+    L.off_ktab = o;  o += (size_t)L.KP * 4;             o = (o + 255) & ~(size_t)255;
+    L.off_pwt = o;   o += (size_t)d->R * d->S * d->O * 4; o = (o + 255) & ~(size_t)255;
+    L.off_pwtot = o; o += (size_t)d->O * 4;             o = (o + 255) & ~(size_t)255;
+    L.bytes = o;
+    return L;
+}
+
+// ---- MMA issue-rate probe ----------------------------------------------------------------
+template <int KIND>
+__global__ void k_mma_peak(int iters, unsigned seed, int* sink) {
+    unsigned a[4], b[2];
+    int c[8][4];
+    for (int i = 0; i < 4; i++) a[i] = seed * (threadIdx.x + i + 1);
+    for (int i = 0; i < 2; i++) b[i] = seed * (threadIdx.x * 7 + i + 3);
+    for (int j = 0; j < 8; j++)
+        for (int i = 0; i < 4; i++) c[j][i] = 0;
+    for (int it = 0; it < iters; it++) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (KIND == 0) mma_b1_and(c[j], a[0], a[1], a[2], a[3], b[0], b[1]);
+            if (KIND == 1)
+                asm volatile(
+                    "mma.sync.aligned.m16n8k256.row.col.s32.b1.b1.s32.xor.popc "
+                    "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                    : "+r"(c[j][0]), "+r"(c[j][1]), "+r"(c[j][2]), "+r"(c[j][3])
+                    : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+            if (KIND == 2)
+                asm volatile(
+                    "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 "
+                    "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                    : "+r"(c[j][0]), "+r"(c[j][1]), "+r"(c[j][2]), "+r"(c[j][3])
+                    : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+        }
+    }
+    int s = 0;
+    for (int j = 0; j < 8; j++)
+        for (int i = 0; i < 4; i++) s += c[j][i];
+    if (s == 0x7fffffff) sink[0] = s;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tcbnn_version(void) { return 100; }
+const char* tcbnn_last_error(void) { return g_err; }
+
+int tcbnn_pack_rows(const float* x, int rows, int cols, int ld_words, uint32_t* out, void* stream) {
+    if (rows <= 0 || cols <= 0) return fail("pack_rows: empty input");
+    if ((ld_words & 3) || ld_words * 32 < cols) return fail("pack_rows: ld_words must be a multiple of 4 and cover cols");
+    if ((uintptr_t)out & 15) return fail("pack_rows: output must be 16-byte aligned");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_pack_rows<<<warp_grid((long long)rows * (ld_words / 4), sms), kThreads, 0, (cudaStream_t)stream>>>(
+        x, rows, cols, ld_words, out);
+    return launch_check("pack_rows");
+}
+
+int tcbnn_unpack_rows(const uint32_t* in, int rows, int cols, int ld_words, float* out, void* stream) {
+    if (rows <= 0 || cols <= 0) return fail("unpack_rows: empty input");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_unpack_rows<<<elementwise_grid((long long)rows * cols, sms), 256, 0, (cudaStream_t)stream>>>(
+        in, rows, cols, ld_words, out);
+    return launch_check("unpack_rows");
+}
+
+int tcbnn_pack_fc_weight(const float* W, int K, int N, int ld_words, uint32_t* out, void* stream) {
+    if (K <= 0 || N <= 0 || ld_words * 32 < K) return fail("pack_fc_weight: bad sizes");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_pack_fc_weight<<<elementwise_grid((long long)N * ld_words, sms), 256, 0, (cudaStream_t)stream>>>(
+        W, K, N, ld_words, out);
+    return launch_check("pack_fc_weight");
+}
+
+int tcbnn_pack_conv_filter(const float* F, int RS, int C, int O, uint32_t* out, void* stream) {
+    if (RS <= 0 || C <= 0 || O <= 0) return fail("pack_conv_filter: bad sizes");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_pack_conv_filter<<<elementwise_grid((long long)O * RS * ((C + 31) / 32), sms), 256, 0,
+                         (cudaStream_t)stream>>>(F, RS, C, O, out);
+    return launch_check("pack_conv_filter");
+}
+
+int tcbnn_pack_inconv_filter(const float* F, int RS, int O, uint32_t* out, void* stream) {
+    if (RS <= 0 || O <= 0) return fail("pack_inconv_filter: bad sizes");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_pack_inconv_filter<<<elementwise_grid((long long)RS * 3 * ((O + 31) / 32), sms), 256, 0,
+                           (cudaStream_t)stream>>>(F, RS, O, out);
+    return launch_check("pack_inconv_filter");
+}
+
+size_t tcbnn_gemm_workspace_bytes(int M, int N, int K) {
+    int sms;
+    if (M <= 0 || N <= 0 || K <= 0 || sm_count(&sms)) return 0;
+    const int s = gemm_splits(M, N, K, sms);
+    return s > 1 ? (size_t)s * M * N * sizeof(int32_t) : 0;
+}
+
+int tcbnn_bgemm(const uint32_t* A, const uint32_t* B, int M, int N, int K, int lda, int ldb,
+                int32_t* C, int ldc, void* workspace, size_t workspace_bytes, void* stream) {
+    if (ldc < N) return fail("bgemm: ldc < N");
+    GemmArgs g{A, B, M, N, K, lda, ldb, GEMM_INT32, C, ldc, nullptr, nullptr, 1, nullptr};
+    return run_gemm(g, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int tcbnn_fc_layer(const uint32_t* A, const uint32_t* W, const float* thr, int M, int K, int N,
+                   int lda, int ldw, uint32_t* out, int ldo, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+    if (ldo * 32 < N) return fail("fc_layer: ldo too small");
+    GemmArgs g{A, W, M, N, K, lda, ldw, GEMM_FC_BITS, out, ldo, thr, nullptr, 1, nullptr};
+    return run_gemm(g, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int tcbnn_out_layer(const uint32_t* A, const uint32_t* W, const float* scale, const float* bias,
+                    int M, int K, int N, int lda, int ldw, float* out, int ldo, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+    if (ldo < N) return fail("out_layer: ldo < N");
+    GemmArgs g{A, W, M, N, K, lda, ldw, GEMM_OUT_AFFINE, out, ldo, scale, bias, 1, nullptr};
+    return run_gemm(g, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int tcbnn_conv_shape(tcbnn_conv_desc* d) {
+    if (!d) return fail("conv_shape: null descriptor");
+    if (d->H <= 0 || d->W <= 0 || d->R <= 0 || d->S <= 0 || d->stride_h <= 0 || d->stride_w <= 0 ||
+        d->pool <= 0)
+        return fail("conv_shape: sizes must be positive");
+    const int H = d->H, W = d->W, sh = d->stride_h, sw = d->stride_w;
+    d->pad_h = d->padding ? ((((H + sh - (H % sh)) / sh - 1) * sh + d->R - H) / 2) : 0;
+    d->pad_w = d->padding ? ((((W + sw - (W % sw)) / sw - 1) * sw + d->S - W) / 2) : 0;
+    const int bh = d->padding ? (H + sh - 1) / sh : ((H - d->R) / sh + 1);
+    const int bw = d->padding ? (W + sw - 1) / sw : ((W - d->S) / sw + 1);
+    d->OH = (bh + d->pool - 1) / d->pool;
+    d->OW = (bw + d->pool - 1) / d->pool;
+    return 0;
+}
+
+size_t tcbnn_conv_prepared_bytes(const tcbnn_conv_desc* d) {
+    if (conv_check(d, true)) return 0;
+    return prepared_layout(d).bytes;
+}
+
+int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, void* prepared,
+                       void* stream) {
+    if (conv_check(d, true)) return 1;
+    if ((uintptr_t)prepared & 255) return fail("conv_prepare: blob must be 256-byte aligned");
+    const PreparedLayout L = prepared_layout(d);
+    char* p = (char*)prepared;
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_conv_prepare<<<elementwise_grid((long long)d->O * 2 * L.KP, sms), 256, 0, (cudaStream_t)stream>>>(
+        filter_bits, d->O, d->R, d->S, (d->C + 31) / 32, d->W, L.KP, (uint32_t*)(p + L.off_wq),
+        (uint32_t*)(p + L.off_ktab), (int*)(p + L.off_pwt), (int*)(p + L.off_pwtot));
+    return launch_check("conv_prepare");
+}
+
+int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
+                     const float* thr, const int32_t* res_in, int res_in_ch,
+                     int residual_channels, int residual_pool, uint32_t* out,
+                     long long out_image_stride, int32_t* res_out, int32_t* acc_out, void* stream) {
+    if (conv_check(d, true)) return 1;
+    const int Ow = (d->O + 31) / 32;
+    if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("conv_layer: out_image_stride too small");
+    if ((res_out || res_in) && d->pool != 1) return fail("conv_layer: residuals need pool == 1");
+    if (res_in && (res_in_ch <= 0 || residual_channels <= 0)) return fail("conv_layer: residual channel counts must be positive");
+    if ((uintptr_t)in & 7) return fail("conv_layer: input must be 8-byte aligned");
+    const PreparedLayout L = prepared_layout(d);
+    const char* p = (const char*)prepared;
+    ConvArgs c;
+    c.in = in;
+    c.wq = (const uint32_t*)(p + L.off_wq);
+    c.ktab = (const uint32_t*)(p + L.off_ktab);
+    c.pwt = (const int*)(p + L.off_pwt);
+    c.pwtot = (const int*)(p + L.off_pwtot);
+    c.thr = thr;
+    c.B = d->B; c.H = d->H; c.W = d->W; c.C = d->C; c.Cw = (d->C + 31) / 32; c.O = d->O;
+    c.R = d->R; c.S = d->S; c.sh = d->stride_h; c.sw = d->stride_w;
+    c.pad_h = d->pad_h; c.pad_w = d->pad_w; c.pool = d->pool; c.OH = d->OH; c.OW = d->OW;
+    c.KP = L.KP;
+    c.res_in = res_in; c.res_in_ch = res_in_ch; c.residual_channels = residual_channels;
+    c.residual_pool = residual_pool;
+    c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out; c.acc_out = acc_out;
+    int sms;
+    if (sm_count(&sms)) return 1;
+    const long long rows = (long long)d->B * d->OH * d->OW * d->pool * d->pool;
+    const long long tasks = ((rows + 31) / 32) * Ow;
+    k_conv<<<warp_grid(tasks, sms), kThreads, 0, (cudaStream_t)stream>>>(c);
+    return launch_check("conv_layer");
+}
+
+int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t* filter_bits,
+                       const float* thr, uint32_t* out, long long out_image_stride,
+                       int32_t* res_out, float* acc_out, void* stream) {
+    if (conv_check(d, false)) return 1;
+    const int Ow = (d->O + 31) / 32;
+    if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("inconv_layer: out_image_stride too small");
+    InConvArgs c;
+    c.x = x; c.fbits = filter_bits; c.thr = thr;
+    c.B = d->B; c.H = d->H; c.W = d->W; c.O = d->O; c.R = d->R; c.S = d->S;
+    c.sh = d->stride_h; c.sw = d->stride_w; c.pad_h = d->pad_h; c.pad_w = d->pad_w;
+    c.pool = d->pool; c.OH = d->OH; c.OW = d->OW;
+    c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out; c.acc_out = acc_out;
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_inconv<<<warp_grid((long long)d->B * d->OH * d->OW, sms), kThreads, 0, (cudaStream_t)stream>>>(c);
+    return launch_check("inconv_layer");
+}
+
+int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
+    if (!tops || iters <= 0 || warps_per_sm <= 0 || kind < 0 || kind > 2) return fail("mma_peak: bad arguments");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    int* sink = nullptr;
+    CUDA_TRY(cudaMalloc(&sink, 4));
+    const int threads = 256, ctas = sms * warps_per_sm * 32 / threads;
+    cudaEvent_t e0, e1;
+    CUDA_TRY(cudaEventCreate(&e0));
+    CUDA_TRY(cudaEventCreate(&e1));
+    float best = 1e30f;
+    for (int rep = 0; rep < 4; rep++) {
+        cudaEventRecord(e0);
+        if (kind == 0) k_mma_peak<0><<<ctas, threads>>>(iters, 1u, sink);
+        if (kind == 1) k_mma_peak<1><<<ctas, threads>>>(iters, 1u, sink);
+        if (kind == 2) k_mma_peak<2><<<ctas, threads>>>(iters, 1u, sink);
+        cudaEventRecord(e1);
+        CUDA_TRY(cudaEventSynchronize(e1));
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep > 0 && ms < best) best = ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(sink);
+    const double ops = (kind == 2 ? 2.0 * 16 * 8 * 32 : 2.0 * 16 * 8 * 256);
+    *tops = (double)ctas * (threads / 32) * iters * 8 * ops / (best * 1e-3) / 1e12;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,174 @@
+"""Torch-tensor front end of the C ABI: device memory and streams come from torch, every
+computation is a call into libtcbnn_b200.so.  Bit tensors are torch.int32 (same bytes as the
+library's uint32 words)."""
+import ctypes as C
+
+import torch
+
+from . import lib as _l
+from .lib import ConvDesc
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _l.TcbnnError("tcbnn_b200 ops need CUDA tensors (no CPU path exists)")
+        if t is not None and not t.is_contiguous():
+            raise _l.TcbnnError("tcbnn_b200 ops need contiguous tensors")
+
+
+def step128_words(k):
+    """Words per bit row padded to 128 bits (STEP128(k)*4, utility.h:38)."""
+    return ((k + 127) // 128) * 4
+
+
+def pack_rows(x, ld_words=None):
+    _need_cuda(x)
+    rows, cols = x.shape
+    ld = ld_words or step128_words(cols)
+    out = torch.empty((rows, ld), dtype=torch.int32, device=x.device)
+    _l.call("tcbnn_pack_rows", _ptr(x), rows, cols, ld, _ptr(out), _stream())
+    return out
+
+
+def unpack_rows(bits, cols):
+    _need_cuda(bits)
+    rows, ld = bits.shape
+    out = torch.empty((rows, cols), dtype=torch.float32, device=bits.device)
+    _l.call("tcbnn_unpack_rows", _ptr(bits), rows, cols, ld, _ptr(out), _stream())
+    return out
+
+
+def pack_fc_weight(W, ld_words=None):
+    _need_cuda(W)
+    K, N = W.shape
+    ld = ld_words or step128_words(K)
+    out = torch.empty((N, ld), dtype=torch.int32, device=W.device)
+    _l.call("tcbnn_pack_fc_weight", _ptr(W), K, N, ld, _ptr(out), _stream())
+    return out
+
+
+def pack_conv_filter(F):
+    """F: fp32 [R*S][C][O] -> bits [O][R*S][Cw]."""
+    _need_cuda(F)
+    RS, Cc, O = F.shape
+    out = torch.empty((O, RS, (Cc + 31) // 32), dtype=torch.int32, device=F.device)
+    _l.call("tcbnn_pack_conv_filter", _ptr(F), RS, Cc, O, _ptr(out), _stream())
+    return out
+
+
+def pack_inconv_filter(F):
+    """F: fp32 [R*S][3][O] -> [R*S][3][Ow] words."""
+    _need_cuda(F)
+    RS, Cc, O = F.shape
+    assert Cc == 3
+    out = torch.empty((RS, 3, (O + 31) // 32), dtype=torch.int32, device=F.device)
+    _l.call("tcbnn_pack_inconv_filter", _ptr(F), RS, O, _ptr(out), _stream())
+    return out
+
+
+def gemm_workspace(M, N, K, device):
+    n = _l.load().tcbnn_gemm_workspace_bytes(M, N, K)
+    return torch.empty((max(n, 4) // 4,), dtype=torch.int32, device=device) if n else None
+
+
+def _ws(ws):
+    return (_ptr(ws), C.c_size_t(ws.numel() * 4 if ws is not None else 0))
+
+
+def bgemm(A, B, K, out=None, workspace=None):
+    _need_cuda(A, B)
+    M, lda = A.shape
+    N, ldb = B.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.int32, device=A.device)
+    _l.call("tcbnn_bgemm", _ptr(A), _ptr(B), M, N, K, lda, ldb, _ptr(out), out.shape[1],
+            *_ws(workspace), _stream())
+    return out
+
+
+def fc_layer(A, W, thr, K, out=None, workspace=None):
+    _need_cuda(A, W, thr)
+    M, lda = A.shape
+    N, ldw = W.shape
+    if out is None:
+        out = torch.zeros((M, step128_words(N)), dtype=torch.int32, device=A.device)
+    _l.call("tcbnn_fc_layer", _ptr(A), _ptr(W), _ptr(thr), M, K, N, lda, ldw, _ptr(out),
+            out.shape[1], *_ws(workspace), _stream())
+    return out
+
+
+def out_layer(A, W, scale, bias, K, out=None, workspace=None):
+    _need_cuda(A, W, scale, bias)
+    M, lda = A.shape
+    N, ldw = W.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    _l.call("tcbnn_out_layer", _ptr(A), _ptr(W), _ptr(scale), _ptr(bias), M, K, N, lda, ldw,
+            _ptr(out), out.shape[1], *_ws(workspace), _stream())
+    return out
+
+
+def conv_desc(B, H, W, Cc, O, R, S, stride_h=1, stride_w=1, padding=True, pool=1):
+    d = ConvDesc(B=B, H=H, W=W, C=Cc, O=O, R=R, S=S, stride_h=stride_h, stride_w=stride_w,
+                 padding=int(bool(padding)), pool=pool)
+    _l.call("tcbnn_conv_shape", C.byref(d))
+    return d
+
+
+def conv_prepare(d, filter_bits):
+    _need_cuda(filter_bits)
+    n = _l.load().tcbnn_conv_prepared_bytes(C.byref(d))
+    if n == 0:
+        raise _l.TcbnnError(_l.load().tcbnn_last_error().decode())
+    blob = torch.empty((n,), dtype=torch.uint8, device=filter_bits.device)
+    _l.call("tcbnn_conv_prepare", C.byref(d), _ptr(filter_bits), _ptr(blob), _stream())
+    return blob
+
+
+def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_pool=False,
+               out=None, out_image_stride=None, save_residual=False, want_acc=False):
+    """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out)."""
+    _need_cuda(x, prepared, thr, res_in)
+    Ow = (d.O + 31) // 32
+    stride = out_image_stride or d.OH * d.OW * Ow
+    if out is None:
+        out = torch.zeros((d.B, stride), dtype=torch.int32, device=x.device)
+    P, Q = d.pool * d.OH, d.pool * d.OW
+    res_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if save_residual else None
+    acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if want_acc else None
+    res_in_ch = res_in.shape[-1] if res_in is not None else 0
+    _l.call("tcbnn_conv_layer", C.byref(d), _ptr(x), _ptr(prepared), _ptr(thr), _ptr(res_in),
+            res_in_ch, residual_channels, int(bool(residual_pool)), _ptr(out),
+            C.c_longlong(stride), _ptr(res_out), _ptr(acc_out), _stream())
+    return out, res_out, acc_out
+
+
+def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_residual=False,
+                 want_acc=False):
+    """x: fp32 [B][3][H][W].  Returns (out_bits, res_out, acc_out)."""
+    _need_cuda(x, filter_bits, thr)
+    Ow = (d.O + 31) // 32
+    stride = out_image_stride or d.OH * d.OW * Ow
+    if out is None:
+        out = torch.zeros((d.B, stride), dtype=torch.int32, device=x.device)
+    P, Q = d.pool * d.OH, d.pool * d.OW
+    res_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if save_residual else None
+    acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.float32, device=x.device) if want_acc else None
+    _l.call("tcbnn_inconv_layer", C.byref(d), _ptr(x), _ptr(filter_bits), _ptr(thr), _ptr(out),
+            C.c_longlong(stride), _ptr(res_out), _ptr(acc_out), _stream())
+    return out, res_out, acc_out
+
+
+def mma_peak(kind, warps_per_sm=32, iters=4000):
+    t = C.c_double(0)
+    _l.call("tcbnn_mma_peak", kind, warps_per_sm, iters, C.byref(t))
+    return t.value

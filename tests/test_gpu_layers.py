@@ -1,0 +1,179 @@
+"""GPU parity: every C-ABI entry point against the CPU oracle on the same seeded inputs.
+Bit-exact for packed tensors and int32 values; fp32 logits within 1e-5 relative."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as orc
+import util
+from tcbnn_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, cuda):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint32:
+        a = a.view(np.int32)
+    return torch.from_numpy(a).to(cuda)
+
+
+def host_u32(t):
+    return t.cpu().numpy().view(np.uint32)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (5, 70), (64, 784), (33, 1000), (8, 4096)])
+def test_pack_unpack_rows(cuda, rows, cols):
+    g = util.rng(rows * 7 + cols)
+    x = g.standard_normal((rows, cols)).astype(np.float32)
+    x[0, 0] = 0.0
+    bits = ops.pack_rows(dev(x, cuda))
+    assert np.array_equal(host_u32(bits), orc.pack_rows(x))
+    back = ops.unpack_rows(bits, cols).cpu().numpy()
+    assert np.array_equal(back, orc.unpack_rows(orc.pack_rows(x), cols))
+
+
+def test_pack_weights_and_filters(cuda):
+    g = util.rng(3)
+    W = g.standard_normal((200, 37)).astype(np.float32)
+    assert np.array_equal(host_u32(ops.pack_fc_weight(dev(W, cuda))), orc.pack_fc_weight(W))
+    F = g.standard_normal((9, 192, 40)).astype(np.float32)
+    assert np.array_equal(host_u32(ops.pack_conv_filter(dev(F, cuda))), orc.pack_conv_filter(F))
+
+
+GEMM_SHAPES = [(8, 8, 128), (32, 32, 256), (33, 17, 200), (100, 70, 784), (256, 128, 4096),
+               (64, 10, 1024), (40, 1000, 512), (1024, 1024, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("split", [False, True])
+def test_bgemm_fc_out(cuda, M, N, K, split):
+    g = util.rng(M + 3 * N + 7 * K)
+    ld = orc.step128_words(K)
+    A = util.mask_row_pad(util.rand_words(g, (M, ld)), K)
+    W = util.mask_row_pad(util.rand_words(g, (N, ld)), K)
+    thr = (g.standard_normal(N) * np.sqrt(K)).astype(np.float32)
+    scale = g.standard_normal(N).astype(np.float32)
+    bias = g.standard_normal(N).astype(np.float32)
+    dA, dW = dev(A, cuda), dev(W, cuda)
+    ws = None
+    if split:
+        # force a split by handing over a generous workspace; small shapes may still not split
+        ws = torch.empty((32 * M * N,), dtype=torch.int32, device=cuda)
+    Cg = ops.bgemm(dA, dW, K, workspace=ws).cpu().numpy()
+    assert np.array_equal(Cg, orc.bgemm(A, W, K))
+    bits = ops.fc_layer(dA, dW, dev(thr, cuda), K, workspace=ws)
+    assert np.array_equal(host_u32(bits), orc.fc_layer(A, W, thr, K))
+    out = ops.out_layer(dA, dW, dev(scale, cuda), dev(bias, cuda), K, workspace=ws).cpu().numpy()
+    ref = orc.out_layer(A, W, scale, bias, K)
+    np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_kat_srand4(cuda):
+    """The reference's seeded known-answer recipe, through the GPU path."""
+    import os
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "wmma_kat_srand4.npz"))
+    for t in sorted(k[2:] for k in z.files if k.startswith("A_")):
+        m, n, k = (int(v) for v in t.split("x"))
+        ld = orc.step128_words(k)
+        A = np.zeros((m, ld), np.uint32); A[:, :k // 32] = z["A_" + t]
+        B = np.zeros((n, ld), np.uint32); B[:, :k // 32] = z["B_" + t]
+        Cg = ops.bgemm(dev(A, cuda), dev(B, cuda), k).cpu().numpy()      # K - 2*popc
+        popc = (k - Cg) // 2
+        assert np.array_equal(popc + z["C_" + t], z["D_" + t]), t
+
+
+CONV_CASES = [
+    # B, H, W, C, O, R, S, sh, sw, padding, pool, residual
+    (2, 6, 6, 64, 32, 3, 3, 1, 1, True, 1, None),
+    (3, 8, 8, 64, 64, 3, 3, 1, 1, True, 2, None),
+    (1, 9, 7, 128, 40, 3, 3, 2, 2, True, 1, None),
+    (2, 6, 6, 64, 64, 3, 3, 1, 1, True, 1, "plain"),
+    (2, 4, 4, 64, 128, 3, 3, 1, 1, True, 1, "pool"),
+    (1, 7, 7, 64, 32, 5, 5, 1, 1, True, 1, None),
+    (1, 8, 8, 64, 32, 3, 3, 1, 1, False, 1, None),
+    (5, 14, 14, 256, 256, 3, 3, 1, 1, True, 1, "plain"),
+    (4, 14, 14, 128, 256, 3, 3, 2, 2, True, 1, None),
+    (3, 7, 7, 512, 512, 3, 3, 1, 1, True, 1, "plain"),
+    (2, 13, 13, 192, 384, 3, 3, 1, 1, True, 1, None),
+    (2, 28, 28, 64, 192, 5, 5, 1, 1, True, 2, None),
+    (2, 9, 9, 64, 64, 3, 3, 1, 1, True, 2, None),
+    (8, 56, 56, 64, 64, 3, 3, 1, 1, True, 1, "plain"),
+    (4, 32, 32, 128, 128, 3, 3, 1, 1, True, 2, None),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv_layer(cuda, case):
+    B, H, W, C, O, R, S, sh, sw, padding, pool, resmode = case
+    g = util.rng(hash(case[:9]) & 0xFFFF)
+    Cw = (C + 31) // 32
+    x = util.rand_words(g, (B, H, W, Cw))
+    f = util.rand_words(g, (O, R * S, Cw))
+    thr = (g.standard_normal(O) * np.sqrt(C * R * S) * 0.5).astype(np.float32)
+    pad_h, pad_w, OH, OW = util.conv_shape(H, W, R, S, sh, sw, padding, pool)
+    res_in, rc, rpool = None, 0, False
+    if resmode == "plain":
+        res_in = g.integers(-300, 300, size=(B, OH, OW, max(32, O // 2))).astype(np.int32)
+        rc = O
+    elif resmode == "pool":
+        res_in = g.integers(-300, 300, size=(B, 2 * OH, 2 * OW, O // 2)).astype(np.int32)
+        rc, rpool = O // 2, True
+    Ow = (O + 31) // 32
+    stride = OH * OW * Ow + 4            # padded image stride, like an ahead_fc layer
+    eo, er, ea = orc.conv_layer(x, f, thr, C, R, S, sh, sw, padding, pool, res_in=res_in,
+                                residual_channels=rc, residual_pool=rpool, out_image_stride=stride,
+                                save_residual=(pool == 1), want_acc=True)
+    d = ops.conv_desc(B, H, W, C, O, R, S, sh, sw, padding, pool)
+    assert (d.pad_h, d.pad_w, d.OH, d.OW) == (pad_h, pad_w, OH, OW)
+    prep = ops.conv_prepare(d, dev(f, cuda))
+    go, gr, ga = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda),
+                                res_in=dev(res_in, cuda) if res_in is not None else None,
+                                residual_channels=rc, residual_pool=rpool, out_image_stride=stride,
+                                save_residual=(pool == 1), want_acc=True)
+    assert np.array_equal(ga.cpu().numpy(), ea)
+    if pool == 1:
+        assert np.array_equal(gr.cpu().numpy(), er)
+    assert np.array_equal(host_u32(go), eo)
+    # running the layer again on the same buffers gives the same bits (stores, not ORs)
+    go2, _, _ = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda),
+                               res_in=dev(res_in, cuda) if res_in is not None else None,
+                               residual_channels=rc, residual_pool=rpool, out=go,
+                               out_image_stride=stride)
+    assert np.array_equal(host_u32(go2), eo)
+
+
+INCONV_CASES = [
+    (2, 9, 9, 40, 3, 3, 2, 2, 1),
+    (2, 32, 32, 128, 3, 3, 1, 1, 1),
+    (2, 64, 64, 64, 7, 7, 4, 4, 1),
+    (1, 48, 48, 64, 11, 11, 4, 4, 2),
+]
+
+
+@pytest.mark.parametrize("case", INCONV_CASES)
+def test_inconv_layer(cuda, case):
+    B, H, W, O, R, S, sh, sw, pool = case
+    g = util.rng(sum(case))
+    x = g.standard_normal((B, 3, H, W)).astype(np.float32)
+    F = g.standard_normal((R * S, 3, O)).astype(np.float32)
+    thr = (g.standard_normal(O) * 3).astype(np.float32)
+    eo, er, ea = orc.inconv_layer(x, F, thr, R, S, sh, sw, True, pool, save_residual=True, want_acc=True)
+    d = ops.conv_desc(B, H, W, 3, O, R, S, sh, sw, True, pool)
+    fb = ops.pack_inconv_filter(dev(F, cuda))
+    go, gr, ga = ops.inconv_layer(d, dev(x, cuda), fb, dev(thr, cuda), save_residual=True, want_acc=True)
+    assert np.array_equal(ga.cpu().numpy(), ea)          # fp32 sums bit-exact (same add order)
+    assert np.array_equal(gr.cpu().numpy(), er)
+    assert np.array_equal(host_u32(go), eo)
+
+
+def test_bad_arguments_are_rejected(cuda):
+    from tcbnn_b200.lib import TcbnnError
+    A = torch.zeros((8, 3), dtype=torch.int32, device=cuda)      # odd leading dimension
+    with pytest.raises(TcbnnError):
+        ops.bgemm(A, A, 96)
+    with pytest.raises(TcbnnError):
+        ops.conv_desc(1, 8, 8, 64, 64, 3, 3, pool=0)
+    d = ops.conv_desc(1, 8, 8, 32, 64, 3, 3)                     # odd word count per pixel
+    with pytest.raises(TcbnnError):
+        ops.conv_prepare(d, torch.zeros((64, 9, 1), dtype=torch.int32, device=cuda))
