@@ -1,0 +1,186 @@
+"""Network topologies of the reference drivers as data, seeded synthetic weights and inputs,
+and the GPU runner that chains the layer objects.
+
+A topology is a list of layer specs (dicts).  The same list drives the GPU runner here and the
+CPU oracle runner used by the tests, so both sides execute the identical network.
+
+Topologies follow the reference drivers, not the textbook networks:
+  * resnet18   : imagenet_resnet.cu:223-325 -- 7x7 stride-4 first layer (56x56x64, residual
+                 saved), 16 binary 3x3 convs in 8 basic blocks (64/128/256/512; stride 2 at the
+                 start of stages 2-4), every second conv adds the previous block's integer
+                 residual (2x2 max-pooled when the stage changes), FC 25088->512, out 512->1000.
+  * vgg_cifar  : cifar10_vgg.cu:162-199 -- conv 3->128, 128->128+pool, ->256, 256+pool, ->512,
+                 512+pool (feeds FC), FC 8192->1024->1024, out ->10.
+  * mlp        : mnist_mlp.cu:112-126 -- 784 -> 1024 -> 1024 -> 1024 -> 10.
+"""
+import numpy as np
+
+from . import param
+
+
+def resnet18_spec(batch, image=224, classes=1000):
+    L = [dict(type="inconv", name="Conv1", H=image, W=image, R=7, S=7, C=3, O=64,
+              stride=4, pool=1, save_residual=True)]
+
+    def conv(name, C, O, stride=1, **kw):
+        L.append(dict(type="conv", name=name, C=C, O=O, R=3, S=3, stride=stride, pool=1, **kw))
+
+    # stage 1
+    conv("L1B1C1", 64, 64)
+    conv("L1B1C2", 64, 64, save_residual=True, inject=0, residual_channels=64)
+    conv("L1B2C1", 64, 64)
+    conv("L1B2C2", 64, 64, save_residual=True, inject=2, residual_channels=128)
+    # stage 2
+    conv("L2B1C1", 64, 128, stride=2)
+    conv("L2B1C2", 128, 128, save_residual=True, inject=4, residual_channels=128, residual_pool=True)
+    conv("L2B2C1", 128, 128)
+    conv("L2B2C2", 128, 128, save_residual=True, inject=6, residual_channels=128)
+    # stage 3
+    conv("L3B1C1", 128, 256, stride=2)
+    conv("L3B1C2", 256, 256, save_residual=True, inject=8, residual_channels=128, residual_pool=True)
+    conv("L3B2C1", 256, 256)
+    conv("L3B2C2", 256, 256, save_residual=True, inject=10, residual_channels=256)
+    # stage 4
+    conv("L4B1C1", 256, 512, stride=2)
+    conv("L4B1C2", 512, 512, save_residual=True, inject=12, residual_channels=256, residual_pool=True)
+    conv("L4B2C1", 512, 512)
+    conv("L4B2C2", 512, 512, ahead_fc=True, inject=14, residual_channels=512)
+    L.append(dict(type="fc", name="Fc1", N=512))
+    L.append(dict(type="out", name="Fout", N=classes))
+    return dict(name="resnet18", batch=batch, layers=L)
+
+
+def vgg_cifar_spec(batch, image=32, classes=10):
+    L = [dict(type="inconv", name="Conv1", H=image, W=image, R=3, S=3, C=3, O=128, stride=1, pool=1)]
+    for name, C, O, pool, afc in [("Conv2", 128, 128, 2, False), ("Conv3", 128, 256, 1, False),
+                                  ("Conv4", 256, 256, 2, False), ("Conv5", 256, 512, 1, False),
+                                  ("Conv6", 512, 512, 2, True)]:
+        L.append(dict(type="conv", name=name, C=C, O=O, R=3, S=3, stride=1, pool=pool, ahead_fc=afc))
+    L += [dict(type="fc", name="Fc1", N=1024), dict(type="fc", name="Fc2", N=1024),
+          dict(type="out", name="Fout", N=classes)]
+    return dict(name="vgg_cifar", batch=batch, layers=L)
+
+
+def mlp_spec(batch, features=784, hidden=1024, classes=10):
+    L = [dict(type="in", name="Fin", K=features),
+         dict(type="fc", name="Fc1", N=hidden), dict(type="fc", name="Fc2", N=hidden),
+         dict(type="fc", name="Fc3", N=hidden), dict(type="out", name="Fout", N=classes)]
+    return dict(name="mlp", batch=batch, layers=L)
+
+
+def layer_shapes(spec):
+    """Resolve H/W/K of every layer by walking the chain; returns a list of dicts with the
+    resolved fields added (H, W, OH, OW, K)."""
+    out = []
+    H = W = Cprev = K = None
+    for l in spec["layers"]:
+        l = dict(l)
+        t = l["type"]
+        if t == "in":
+            K = l["K"]
+        elif t in ("inconv", "conv"):
+            if t == "inconv":
+                H, W = l["H"], l["W"]
+            else:
+                l["H"], l["W"] = H, W
+            s, p, R = l["stride"], l["pool"], l["R"]
+            bh = (H + s - 1) // s
+            bw = (W + s - 1) // s
+            l["OH"], l["OW"] = (bh + p - 1) // p, (bw + p - 1) // p
+            H, W, Cprev = l["OH"], l["OW"], l["O"]
+            K = H * W * Cprev
+        elif t in ("fc", "out"):
+            l["K"] = K
+            K = l["N"]
+        out.append(l)
+    return out
+
+
+def synthetic_weights(spec, seed):
+    """Arrays in launch_array order (utility.h:188-196): per conv layer filter[R*S][C][O] then
+    thresholds[O]; per FC weight[K][N] then thresholds[N]; output layer weight, scale, bias.
+    Weights are +-1 (Bernoulli 0.5), thresholds N(0, sqrt(fan_in)); the first layer's
+    thresholds are scaled to its fp32 input range."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    arrays = []
+
+    def pm1(shape):
+        return (g.integers(0, 2, size=shape, dtype=np.int8).astype(np.float32) * 2 - 1)
+
+    for l in layer_shapes(spec):
+        t = l["type"]
+        if t == "inconv":
+            arrays.append(pm1((l["R"] * l["S"], 3, l["O"])))
+            arrays.append((g.standard_normal(l["O"]) * np.sqrt(3 * l["R"] * l["S"])).astype(np.float32))
+        elif t == "conv":
+            fan = l["C"] * l["R"] * l["S"]
+            arrays.append(pm1((l["R"] * l["S"], l["C"], l["O"])))
+            arrays.append((g.standard_normal(l["O"]) * np.sqrt(fan)).astype(np.float32))
+        elif t == "fc":
+            arrays.append(pm1((l["K"], l["N"])))
+            arrays.append((g.standard_normal(l["N"]) * np.sqrt(l["K"])).astype(np.float32))
+        elif t == "out":
+            arrays.append(pm1((l["K"], l["N"])))
+            arrays.append((g.standard_normal(l["N"]) * 0.1 + 1.0).astype(np.float32))
+            arrays.append(g.standard_normal(l["N"]).astype(np.float32))
+    return arrays
+
+
+def synthetic_input(spec, seed, batch=None):
+    """Seeded stand-in for the datasets, with the value ranges the reference readers produce:
+    images are uint8 uniform, scaled to [0,1] and normalised per channel (data.cpp:295-315,
+    534-542); MLP features are uniform[0,1) minus 0.5 because In128 binarises at 0."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    B = batch or spec["batch"]
+    first = spec["layers"][0]
+    if first["type"] == "in":
+        return (g.random((B, first["K"]), dtype=np.float32) - np.float32(0.5))
+    u8 = g.integers(0, 256, size=(B, 3, first["H"], first["W"]), dtype=np.uint8)
+    mean = np.array([0.485, 0.456, 0.406], dtype=np.float32).reshape(1, 3, 1, 1)
+    std = np.array([0.229, 0.224, 0.225], dtype=np.float32).reshape(1, 3, 1, 1)
+    return ((u8.astype(np.float32) / np.float32(255.0)) - mean) / std
+
+
+class Network:
+    """Chain of layer objects built from a spec, the way the reference drivers build theirs
+    (new XLayerParam(...) ; initialize(config, prev->get_output_gpu(), residual))."""
+
+    def __init__(self, spec, weights, input_host):
+        self.spec = spec
+        B = spec["batch"]
+        cfg = weights if hasattr(weights, "read") else param.ArrayConfig(weights)
+        self.layers = []
+        prev = None
+        for l in layer_shapes(spec):
+            t = l["type"]
+            if t == "in":
+                obj = param.In128LayerParam(l["name"], B, l["K"]).initialize(input_host)
+            elif t == "inconv":
+                obj = param.InConv128LayerParam(l["name"], l["H"], l["W"], l["R"], l["S"], 3, l["O"], B,
+                                                l["stride"], l["stride"], True, l["pool"], l["pool"],
+                                                l.get("save_residual", False)).initialize(input_host, cfg)
+            elif t == "conv":
+                inj = l.get("inject")
+                obj = param.Conv128LayerParam(l["name"], l["H"], l["W"], l["R"], l["S"], l["C"], l["O"], B,
+                                              l["stride"], l["stride"], True, l["pool"], l["pool"],
+                                              l.get("ahead_fc", False), l.get("save_residual", False),
+                                              inj is not None, l.get("residual_channels", 0),
+                                              l.get("residual_pool", False))
+                res = self.layers[inj].get_output_residual_gpu() if inj is not None else None
+                obj.initialize(cfg, prev.get_output_gpu(), res)
+            elif t == "fc":
+                obj = param.Fc128LayerParam(l["name"], B, l["K"], l["N"]).initialize(cfg, prev.get_output_gpu())
+            elif t == "out":
+                obj = param.Out128LayerParam(l["name"], B, l["K"], l["N"]).initialize(cfg, prev.get_output_gpu())
+            else:
+                raise ValueError(t)
+            self.layers.append(obj)
+            prev = obj
+
+    def set_input(self, x):
+        self.layers[0].set_input(x)
+
+    def forward(self):
+        for l in self.layers:
+            l.forward()
+        return self.layers[-1].get_output_gpu()

@@ -135,7 +135,8 @@ def conv_prepare(d, filter_bits):
 
 
 def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_pool=False,
-               out=None, out_image_stride=None, save_residual=False, want_acc=False):
+               out=None, out_image_stride=None, save_residual=False, want_acc=False,
+               res_out_buf=None):
     """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out)."""
     _need_cuda(x, prepared, thr, res_in)
     Ow = (d.O + 31) // 32
@@ -143,7 +144,9 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
     if out is None:
         out = torch.zeros((d.B, stride), dtype=torch.int32, device=x.device)
     P, Q = d.pool * d.OH, d.pool * d.OW
-    res_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if save_residual else None
+    res_out = res_out_buf
+    if res_out is None and save_residual:
+        res_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device)
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if want_acc else None
     res_in_ch = res_in.shape[-1] if res_in is not None else 0
     _l.call("tcbnn_conv_layer", C.byref(d), _ptr(x), _ptr(prepared), _ptr(thr), _ptr(res_in),

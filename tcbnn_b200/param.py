@@ -1,0 +1,311 @@
+"""Host-side layer objects with the names, constructor arguments and method names of the
+reference's param.h classes (In128/Fc128/Out128/InConv128/Conv128 LayerParam), built on the
+C ABI.  Differences that follow from the B200 design, not from the interface:
+
+  * activations stay NHWC bit-packed (no HWNC 8x128 tiling) and residuals are unpadded NHWC
+    int32, so get_output_gpu() hands the next layer an opaque device tensor exactly as the
+    reference hands over an opaque uin32* (param.h:986);
+  * every layer is a separate launch on the current stream (forward()), outputs are written
+    with stores, so a layer object can be run any number of times;
+  * weights come from a `config` object with read(n) -> n floats in the order launch_array
+    consumes them (utility.h:188-196): filter/weight first, then thresholds.
+"""
+import numpy as np
+import torch
+
+from . import ops
+
+
+class ArrayConfig:
+    """In-memory stand-in for the reference's text weight file: read(n) returns the next n
+    float32 values."""
+
+    def __init__(self, arrays):
+        if isinstance(arrays, np.ndarray):
+            arrays = [arrays]
+        self._arrays = [np.ascontiguousarray(a, dtype=np.float32).ravel() for a in arrays]
+        self._i = 0
+        self._off = 0
+
+    def read(self, n):
+        out = np.empty(n, dtype=np.float32)
+        got = 0
+        while got < n:
+            if self._i >= len(self._arrays):
+                raise ValueError("weight stream exhausted (launch_array would read past EOF)")
+            a = self._arrays[self._i]
+            take = min(n - got, a.size - self._off)
+            out[got:got + take] = a[self._off:self._off + take]
+            got += take
+            self._off += take
+            if self._off == a.size:
+                self._i += 1
+                self._off = 0
+        return out
+
+
+class TextConfig(ArrayConfig):
+    """Whitespace-separated floats, the reference's file format (fscanf "%f")."""
+
+    def __init__(self, path):
+        super().__init__(np.loadtxt(path, dtype=np.float32).ravel())
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        raise RuntimeError("tcbnn_b200 needs a CUDA device; there is no CPU path")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+class In128LayerParam:
+    """param.h:115-222.  fp32 [input_height][input_width] -> bit rows."""
+
+    def __init__(self, name, input_height, input_width):
+        self.name = name
+        self.input_height = self.output_height = input_height
+        self.input_width = self.output_width = input_width
+        self.input_gpu = self.output_gpu = None
+
+    def initialize(self, input):
+        dev = _dev()
+        self.input_gpu = torch.empty((self.input_height, self.input_width), dtype=torch.float32, device=dev)
+        self.set_input(input)
+        self.output_gpu = torch.zeros((self.input_height, ops.step128_words(self.input_width)),
+                                      dtype=torch.int32, device=dev)
+        return self
+
+    def set_input(self, input):
+        src = input if torch.is_tensor(input) else torch.from_numpy(np.ascontiguousarray(input, dtype=np.float32))
+        self.input_gpu.copy_(src.reshape(self.input_height, self.input_width), non_blocking=True)
+
+    def forward(self):
+        ops._l.call("tcbnn_pack_rows", ops._ptr(self.input_gpu), self.input_height, self.input_width,
+                    self.output_gpu.shape[1], ops._ptr(self.output_gpu), ops._stream())
+
+    def get_output_gpu(self):
+        return self.output_gpu
+
+    def download_output(self):
+        return self.output_gpu.cpu().numpy().view(np.uint32)
+
+    def download_full_output(self):
+        return ops.unpack_rows(self.output_gpu, self.output_width).cpu().numpy()
+
+
+class Fc128LayerParam:
+    """param.h:224-385.  Hidden FC layer: bit GEMM + threshold + repack."""
+
+    def __init__(self, name, input_height, input_width, weight_width):
+        self.name = name
+        self.input_height = self.output_height = input_height
+        self.input_width = self.weight_height = input_width
+        self.weight_width = self.output_width = self.bn_width = weight_width
+        self.weight_gpu = self.bn_gpu = self.input_gpu = self.output_gpu = None
+
+    def initialize(self, config, prev_layer_gpu):
+        dev = _dev()
+        K, N = self.weight_height, self.weight_width
+        w = torch.from_numpy(config.read(K * N).reshape(K, N)).to(dev)
+        self.weight_gpu = ops.pack_fc_weight(w)
+        self.bn = config.read(N)
+        self.bn_gpu = torch.from_numpy(self.bn).to(dev)
+        self.output_gpu = torch.zeros((self.input_height, ops.step128_words(N)), dtype=torch.int32, device=dev)
+        self.workspace = ops.gemm_workspace(self.input_height, N, K, dev)
+        self.set_input_gpu(prev_layer_gpu)
+        return self
+
+    def set_input_gpu(self, t):
+        M, K = self.input_height, self.input_width
+        t = t.reshape(M, -1)
+        if t.shape[1] * 32 < K or t.shape[1] % 2:
+            raise ValueError("%s: input rows of %d words do not cover K=%d" % (self.name, t.shape[1], K))
+        self.input_gpu = t
+
+    def forward(self):
+        ops.fc_layer(self.input_gpu, self.weight_gpu, self.bn_gpu, self.input_width,
+                     out=self.output_gpu, workspace=self.workspace)
+
+    def get_output_gpu(self):
+        return self.output_gpu
+
+    def download_output(self):
+        return self.output_gpu.cpu().numpy().view(np.uint32)
+
+    def download_full_output(self):
+        return ops.unpack_rows(self.output_gpu, self.output_width).cpu().numpy()
+
+
+class Out128LayerParam:
+    """param.h:388-531.  Output layer: bit GEMM + per-class scale and bias -> fp32 logits."""
+
+    def __init__(self, name, input_height, input_width, weight_width):
+        self.name = name
+        self.input_height = self.output_height = input_height
+        self.input_width = self.weight_height = input_width
+        self.weight_width = self.output_width = weight_width
+        self.weight_gpu = self.input_gpu = self.output_gpu = None
+
+    def initialize(self, config, prev_layer_gpu):
+        dev = _dev()
+        K, N = self.weight_height, self.weight_width
+        w = torch.from_numpy(config.read(K * N).reshape(K, N)).to(dev)
+        self.weight_gpu = ops.pack_fc_weight(w)
+        self.bn_scale = config.read(N)
+        self.bn_bias = config.read(N)
+        self.bn_scale_gpu = torch.from_numpy(self.bn_scale).to(dev)
+        self.bn_bias_gpu = torch.from_numpy(self.bn_bias).to(dev)
+        self.output_gpu = torch.zeros((self.input_height, N), dtype=torch.float32, device=dev)
+        self.workspace = ops.gemm_workspace(self.input_height, N, K, dev)
+        self.input_gpu = prev_layer_gpu.reshape(self.input_height, -1)
+        return self
+
+    def forward(self):
+        ops.out_layer(self.input_gpu, self.weight_gpu, self.bn_scale_gpu, self.bn_bias_gpu,
+                      self.input_width, out=self.output_gpu, workspace=self.workspace)
+
+    def get_output_gpu(self):
+        return self.output_gpu
+
+    def download_output(self):
+        return self.output_gpu.cpu().numpy()
+
+
+class InConv128LayerParam:
+    """param.h:701-870.  First conv layer on fp32 NCHW images."""
+
+    def __init__(self, name, input_height, input_width, filter_height, filter_width,
+                 input_channels, output_channels, batch, stride_height=1, stride_width=1,
+                 padding=True, pool_height=1, pool_width=1, save_residual=False):
+        if pool_height != pool_width:
+            raise ValueError("only square pooling windows are supported")
+        self.name = name
+        self.input_height, self.input_width = input_height, input_width
+        self.filter_height, self.filter_width = filter_height, filter_width
+        self.input_channels, self.output_channels, self.batch = input_channels, output_channels, batch
+        self.stride_height, self.stride_width, self.padding = stride_height, stride_width, padding
+        self.pool_height, self.pool_width, self.save_residual = pool_height, pool_width, save_residual
+        self.desc = ops.conv_desc(batch, input_height, input_width, input_channels, output_channels,
+                                  filter_height, filter_width, stride_height, stride_width, padding,
+                                  pool_height)
+        self.pad_h, self.pad_w = self.desc.pad_h, self.desc.pad_w
+        self.output_height, self.output_width = self.desc.OH, self.desc.OW
+        self.output_residual_gpu = None
+
+    def initialize(self, input, config):
+        dev = _dev()
+        d = self.desc
+        self.input_gpu = torch.empty((d.B, 3, d.H, d.W), dtype=torch.float32, device=dev)
+        self.set_input(input)
+        f = torch.from_numpy(config.read(d.R * d.S * 3 * d.O).reshape(d.R * d.S, 3, d.O)).to(dev)
+        self.filter_gpu = ops.pack_inconv_filter(f)
+        self.bn = config.read(d.O)
+        self.bn_gpu = torch.from_numpy(self.bn).to(dev)
+        Ow = (d.O + 31) // 32
+        self.output_gpu = torch.zeros((d.B, d.OH, d.OW, Ow), dtype=torch.int32, device=dev)
+        if self.save_residual:
+            self.output_residual_gpu = torch.zeros((d.B, d.pool * d.OH, d.pool * d.OW, d.O),
+                                                   dtype=torch.int32, device=dev)
+        return self
+
+    def set_input(self, input):
+        src = input if torch.is_tensor(input) else torch.from_numpy(np.ascontiguousarray(input, dtype=np.float32))
+        self.input_gpu.copy_(src.reshape(self.input_gpu.shape), non_blocking=True)
+
+    def forward(self):
+        d = self.desc
+        Ow = (d.O + 31) // 32
+        ops._l.call("tcbnn_inconv_layer", ops.C.byref(d), ops._ptr(self.input_gpu), ops._ptr(self.filter_gpu),
+                    ops._ptr(self.bn_gpu), ops._ptr(self.output_gpu), ops.C.c_longlong(d.OH * d.OW * Ow),
+                    ops._ptr(self.output_residual_gpu), ops.C.c_void_p(0), ops._stream())
+
+    def get_output_gpu(self):
+        return self.output_gpu
+
+    def get_output_residual_gpu(self):
+        return self.output_residual_gpu
+
+    def download_output(self):
+        return self.output_gpu.cpu().numpy().view(np.uint32)
+
+    def download_full_output(self):
+        d = self.desc
+        rows = d.B * d.OH * d.OW
+        return ops.unpack_rows(self.output_gpu.reshape(rows, -1), d.O).reshape(d.B, d.OH, d.OW, d.O).cpu().numpy()
+
+
+class Conv128LayerParam:
+    """param.h:872-1065.  Binary conv layer with threshold / OR-pool / residual fused."""
+
+    def __init__(self, name, input_height, input_width, filter_height, filter_width,
+                 input_channels, output_channels, batch, stride_height=1, stride_width=1,
+                 padding=True, pool_height=1, pool_width=1, ahead_fc=False, save_residual=False,
+                 inject_residual=False, residual_channels=0, residual_pool=False):
+        if pool_height != pool_width:
+            raise ValueError("only square pooling windows are supported")
+        self.name = name
+        self.input_height, self.input_width = input_height, input_width
+        self.filter_height, self.filter_width = filter_height, filter_width
+        self.input_channels, self.output_channels, self.batch = input_channels, output_channels, batch
+        self.stride_height, self.stride_width, self.padding = stride_height, stride_width, padding
+        self.pool_height, self.pool_width = pool_height, pool_width
+        self.ahead_fc, self.save_residual = ahead_fc, save_residual
+        self.inject_residual, self.residual_channels = inject_residual, residual_channels
+        self.residual_pool = residual_pool
+        self.desc = ops.conv_desc(batch, input_height, input_width, input_channels, output_channels,
+                                  filter_height, filter_width, stride_height, stride_width, padding,
+                                  pool_height)
+        self.pad_h, self.pad_w = self.desc.pad_h, self.desc.pad_w
+        self.output_height, self.output_width = self.desc.OH, self.desc.OW
+        self.output_residual_gpu = self.input_residual_gpu = None
+
+    def initialize(self, config, prev_layer_gpu, input_residual_gpu=None):
+        dev = _dev()
+        d = self.desc
+        f = torch.from_numpy(config.read(d.R * d.S * d.C * d.O).reshape(d.R * d.S, d.C, d.O)).to(dev)
+        self.filter_gpu = ops.pack_conv_filter(f)
+        self.prepared = ops.conv_prepare(d, self.filter_gpu)
+        self.bn = config.read(d.O)
+        self.bn_gpu = torch.from_numpy(self.bn).to(dev)
+        Ow = (d.O + 31) // 32
+        words = d.OH * d.OW * Ow
+        # a layer feeding an FC layer pads each image to a whole number of 128-bit rows
+        self.out_image_stride = ops.step128_words(words * 32) if self.ahead_fc else words
+        self.output_gpu = torch.zeros((d.B, self.out_image_stride), dtype=torch.int32, device=dev)
+        if self.save_residual:
+            self.output_residual_gpu = torch.zeros((d.B, d.pool * d.OH, d.pool * d.OW, d.O),
+                                                   dtype=torch.int32, device=dev)
+        self.set_input_gpu(prev_layer_gpu)
+        if self.inject_residual:
+            self.set_input_residual_gpu(input_residual_gpu)
+        return self
+
+    def set_input_gpu(self, t):
+        d = self.desc
+        self.input_gpu = t.reshape(d.B, d.H, d.W, (d.C + 31) // 32)
+
+    def set_input_residual_gpu(self, t):
+        if t is None:
+            raise ValueError("%s: inject_residual needs a residual tensor" % self.name)
+        self.input_residual_gpu = t
+
+    def forward(self):
+        ops.conv_layer(self.desc, self.input_gpu, self.prepared, self.bn_gpu,
+                       res_in=self.input_residual_gpu if self.inject_residual else None,
+                       residual_channels=self.residual_channels, residual_pool=self.residual_pool,
+                       out=self.output_gpu, out_image_stride=self.out_image_stride,
+                       res_out_buf=self.output_residual_gpu)
+
+    def get_output_gpu(self):
+        return self.output_gpu
+
+    def get_output_residual_gpu(self):
+        return self.output_residual_gpu
+
+    def download_output(self):
+        return self.output_gpu.cpu().numpy().view(np.uint32)
+
+    def download_full_output(self):
+        d = self.desc
+        Ow = (d.O + 31) // 32
+        bits = self.output_gpu[:, :d.OH * d.OW * Ow].reshape(d.B * d.OH * d.OW, Ow).contiguous()
+        return ops.unpack_rows(bits, d.O).reshape(d.B, d.OH, d.OW, d.O).cpu().numpy()

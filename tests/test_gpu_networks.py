@@ -1,0 +1,49 @@
+"""GPU parity of whole networks, layer by layer, against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import networks as onet
+from tcbnn_b200 import models
+
+pytestmark = pytest.mark.gpu
+
+
+def _compare(spec, seed, cuda):
+    w = models.synthetic_weights(spec, seed)
+    x = models.synthetic_input(spec, seed + 1)
+    acts, ress = onet.run(spec, w, x)
+    net = models.Network(spec, w, x)
+    logits = net.forward()
+    torch.cuda.synchronize()
+    for i, (layer, a, r) in enumerate(zip(net.layers, acts, ress)):
+        got = layer.get_output_gpu().cpu().numpy()
+        if got.dtype == np.int32:
+            got = got.view(np.uint32)
+            assert np.array_equal(got.reshape(a.shape), a), "layer %d %s bits" % (i, layer.name)
+        if r is not None:
+            gr = layer.get_output_residual_gpu().cpu().numpy()
+            assert np.array_equal(gr, r), "layer %d %s residual" % (i, layer.name)
+    ref = acts[-1]
+    got = logits.cpu().numpy()
+    np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-5)
+    # a second pass over the same objects gives the same logits (layers store, never OR)
+    again = net.forward().cpu().numpy()
+    assert np.array_equal(again, got)
+
+
+def test_mlp(cuda):
+    _compare(models.mlp_spec(256), 5, cuda)
+
+
+def test_vgg_cifar(cuda):
+    _compare(models.vgg_cifar_spec(8), 10, cuda)
+
+
+def test_resnet18_small_image(cuda):
+    # same topology, 64x64 input -> 16x16 ... 2x2 feature maps
+    _compare(models.resnet18_spec(8, image=64, classes=100), 20, cuda)
+
+
+def test_resnet18_224(cuda):
+    _compare(models.resnet18_spec(2), 30, cuda)
