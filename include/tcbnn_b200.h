@@ -101,6 +101,26 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
                        const float* thr, uint32_t* out, long long out_image_stride,
                        int32_t* res_out, float* acc_out, void* stream);
 
+/* No counterpart in the reference.  Same result as tcbnn_fc_layer, for callers that must not
+ * allocate device memory around the call: a process whose own arena already holds all of the
+ * GPU's memory (so a cudaMalloc for a workspace would fail or fragment it), or a serving loop
+ * that cannot afford the device-wide synchronisation an allocation implies.  The split-K
+ * partial sums go to a fixed array inside the library (tcbnn_noalloc_scratch_bytes() bytes,
+ * 8 MiB; resident on every GPU that loads the library until the process exits) instead of a
+ * caller workspace.  The call itself performs no cudaMalloc / cudaFree and uses no allocating
+ * library routine.
+ *   - Shapes whose split-K partials (splits * M * N * 4 bytes, the figure
+ *     tcbnn_gemm_workspace_bytes returns) exceed the array are rejected with an error.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents.  Nothing in
+ *     it needs to start at zero (every partial a call reads was stored by that same call),
+ *     but two calls that overlap on the GPU (different streams, or different host threads
+ *     without ordering) race on it: order them on one stream or with events. */
+size_t tcbnn_noalloc_scratch_bytes(void);
+int tcbnn_fc_layer_noalloc(const uint32_t* A, const uint32_t* W, const float* thr, int M, int K,
+                           int N, int lda, int ldw, uint32_t* out, int ldo, void* stream);
+
 /* Issue-rate probe of the warp-level MMA forms on all SMs: kind 0 = b1 and.popc m16n8k256,
  * 1 = b1 xor.popc m16n8k256, 2 = s8 m16n8k32.  Returns tera-ops/s (2*m*n*k per MMA) in *tops.
  * Synchronises the device.  The reference's counterpart is the WMMA latency probe

@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstdarg>
 #include <cstring>
+#include <mutex>
 
 using namespace tcbnn;
 
@@ -207,6 +208,36 @@ __global__ void k_mma_peak(int iters, unsigned seed, int* sink) {
     if (s == 0x7fffffff) sink[0] = s;
 }
 
+
+// ---- fixed scratch for callers that cannot allocate ---------------------------------------
+// Split-K partial sums for tcbnn_fc_layer_noalloc live in this array instead of a caller
+// workspace.  It is part of the loaded module: every GPU that loads the library keeps these
+// bytes resident until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, never a device address,
+// so the address each device uses is looked up once (with that device current) and cached.
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[64] = {nullptr};
+
+int static_scratch(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail("no CUDA device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail("fc_layer_noalloc: device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail("cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        g_scratch_ptr[dev] = p;
+    }
+    *out = g_scratch_ptr[dev];
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -405,6 +436,26 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
     const double ops = (kind == 2 ? 2.0 * 16 * 8 * 32 : 2.0 * 16 * 8 * 256);
     *tops = (double)ctas * (threads / 32) * iters * 8 * ops / (best * 1e-3) / 1e12;
     return 0;
+}
+
+size_t tcbnn_noalloc_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int tcbnn_fc_layer_noalloc(const uint32_t* A, const uint32_t* W, const float* thr, int M, int K,
+                           int N, int lda, int ldw, uint32_t* out, int ldo, void* stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return fail("fc_layer_noalloc: M, N, K must be positive");
+    if (ldo * 32 < N) return fail("fc_layer_noalloc: ldo too small");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    const int splits = gemm_splits(M, N, K, sms);
+    const size_t need = splits > 1 ? (size_t)splits * M * N * sizeof(int32_t) : 0;
+    if (need > kStaticScratchBytes)
+        return fail("fc_layer_noalloc: this shape needs %zu bytes of split-K scratch, the built-in "
+                    "scratch holds %zu; use tcbnn_fc_layer with a caller workspace",
+                    need, (size_t)kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (static_scratch(&scratch)) return 1;
+    GemmArgs g{A, W, M, N, K, lda, ldw, GEMM_FC_BITS, out, ldo, thr, nullptr, 1, nullptr};
+    return run_gemm(g, scratch, kStaticScratchBytes, (cudaStream_t)stream);
 }
 
 }  // extern "C"
