@@ -1,0 +1,77 @@
+"""Kernel microbenchmarks on the standalone configurations of the reference's side benchmarks.
+
+    python -m tcbnn_b200.microbench --case c1 [--iters 50]
+    python -m tcbnn_b200.microbench --case c2 [--batch 256] [--iters 20]
+
+c1: bit GEMM 1024 x 1024 x 4096 (bmm/benchmark-bmm.cu shape), int32 output.
+c2: one binary conv layer, NHWC batch x 56 x 56 x 128 -> 128 channels, 3x3, stride 1, pad 1,
+    threshold + repack (bconv/benchmark-bconv.cu shape), optionally saving an int32 residual.
+Prints one JSON line: tera bit-ops/s (2*M*N*K, all taps counted, the reference's formula at
+bmm/bmma_op_test/main_test.cu:368) and the fraction of the b1 MMA issue rate measured in the
+same process.  Seeded synthetic operands (Bernoulli 0.5 bits)."""
+import argparse
+import json
+
+import torch
+
+from . import ops
+
+
+def _words(shape, seed, dev):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    return torch.randint(-2**31, 2**31 - 1, shape, dtype=torch.int32, device=dev, generator=g)
+
+
+def _time(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="c2", choices=["c1", "c2"])
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--residual", action="store_true", help="c2: also save the int32 residual")
+    ap.add_argument("--no-peak", action="store_true")
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    if a.case == "c1":
+        M = N = 1024
+        K = 4096
+        A, B = _words((M, K // 32), 1, dev), _words((N, K // 32), 2, dev)
+        out = torch.empty((M, N), dtype=torch.int32, device=dev)
+        ws = ops.gemm_workspace(M, N, K, dev)
+        ms = _time(lambda: ops.bgemm(A, B, K, out=out, workspace=ws), a.iters)
+        work = 2.0 * M * N * K
+        desc = "bit GEMM %dx%dx%d" % (M, N, K)
+    else:
+        Bn, H, C, O = a.batch, 56, 128, 128
+        d = ops.conv_desc(Bn, H, H, C, O, 3, 3)
+        x, f = _words((Bn, H, H, C // 32), 2, dev), _words((O, 9, C // 32), 3, dev)
+        g = torch.Generator(device=dev)
+        g.manual_seed(4)
+        thr = torch.randn((O,), device=dev, generator=g) * 8.0
+        prep = ops.conv_prepare(d, f)
+        out = torch.zeros((Bn, H * H * (O // 32)), dtype=torch.int32, device=dev)
+        res = torch.empty((Bn, H, H, O), dtype=torch.int32, device=dev) if a.residual else None
+        ms = _time(lambda: ops.conv_layer(d, x, prep, thr, out=out, res_out_buf=res), a.iters)
+        work = 2.0 * Bn * H * H * O * 9 * C
+        desc = "bit conv %dx56x56x128 -> 128, 3x3%s" % (Bn, " + int32 residual" if a.residual else "")
+    tops = work / (ms * 1e-3) / 1e12
+    peak = None if a.no_peak else ops.mma_peak(0, 32, 4000)
+    print(json.dumps({"case": a.case, "workload": desc, "ms": ms, "tops": tops,
+                      "b1_mma_peak_tops": peak, "frac_of_b1_peak": tops / peak if peak else None}))
+
+
+if __name__ == "__main__":
+    main()
