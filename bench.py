@@ -145,22 +145,20 @@ def main():
 
     import numpy as np
     import torch
-    import torch.distributed as dist
+    from tcbnn_b200 import dist as tdist
     from tcbnn_b200 import models, ops
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU arm")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+    tdist.init("nccl", dev)
 
     B = args.batch
     spec = models.resnet18_spec(B)
     shapes = models.layer_shapes(spec)
     weights = models.synthetic_weights(spec, 1234)               # same weights on every rank
-    x_host = torch.from_numpy(models.synthetic_input(spec, 4321 + rank)).pin_memory()
+    x_host = torch.from_numpy(models.synthetic_input(spec, tdist.shard_seed(4321, rank))).pin_memory()
     net = models.Network(spec, weights, x_host)
     del weights
     logits_host = torch.empty((B, 1000), dtype=torch.float32).pin_memory()
@@ -178,12 +176,11 @@ def main():
                 events.append((l, e0, e1))
             out = net.layers[-1].get_output_gpu()
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            tdist.gather_logits(out, gathered)
         return out
 
     def sync():
-        if world > 1:
-            dist.barrier()
+        tdist.barrier()
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
@@ -221,10 +218,7 @@ def main():
     sync()
     ms_e2e = e0.elapsed_time(e1)
 
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = float(t[0]), float(t[1])
+    ms, ms_e2e = tdist.max_over_ranks([ms, ms_e2e], dev)
 
     if rank == 0:
         conv_ms, launches = 0.0, 0
@@ -266,8 +260,7 @@ def main():
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(args.cpu_images)
         print(json.dumps(out))
-    if world > 1:
-        dist.destroy_process_group()
+    tdist.finish()
 
 
 def cpu_baseline(images):
