@@ -94,6 +94,15 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
                      long long out_image_stride, int32_t* res_out, int32_t* acc_out,
                      void* stream);
 
+/* Which kernel tcbnn_conv_layer uses: 0 = automatic (tcgen05 int8 implicit GEMM where the layer
+ * is eligible, else the warp-level b1 MMA), 1 = always the b1 MMA, 2 = tcgen05 or an error.
+ * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
+ * kernel per layer type). */
+int tcbnn_set_conv_path(int path);
+/* Reads the layer's device-side status word (synchronises): 0 = fine, 1 = a bounded wait inside
+ * the tcgen05 kernel gave up and the layer's output is not valid. */
+int tcbnn_conv_status(const tcbnn_conv_desc* d, const void* prepared, int* status);
+
 /* First layer on fp32 NCHW input [B][3][H][W] (d->C must be 3).
  * InConv128LayerFMT, kernel.cuh:578-672.  filter_bits from tcbnn_pack_inconv_filter.
  * res_out: (int)acc, truncated toward zero; acc_out (optional): fp32 sums. */

@@ -2,6 +2,7 @@
 // include/tcbnn_b200.h for the contract of each entry point).
 #include "../../include/tcbnn_b200.h"
 #include "bnn_layers.cuh"
+#include "bconv_umma.cuh"
 #include <cstdio>
 #include <cstdarg>
 #include <cstring>
@@ -139,7 +140,10 @@ int run_gemm(GemmArgs g, void* workspace, size_t workspace_bytes, cudaStream_t s
 // ---- prepared conv filter blob ------------------------------------------------------------
 struct PreparedLayout {
     int KP;               // 64-bit pairs per filter row, multiple of 4
-    size_t off_wq, off_ktab, off_pwt, off_pwtot, bytes;
+    size_t off_wq, off_ktab, off_pwt, off_pwtot, off_err, off_wi8, bytes;
+    int umma_nt;          // n-tile of the tcgen05 path, 0 when the layer is not eligible
+    int umma_npos;        // raster positions of the shared-memory patch
+    size_t umma_smem;     // dynamic shared memory of the tcgen05 kernel
 };
 
 int conv_check(const tcbnn_conv_desc* d, bool binary) {
@@ -171,8 +175,57 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     L.off_ktab = o;  o += (size_t)L.KP * 4;             o = (o + 255) & ~(size_t)255;
     L.off_pwt = o;   o += (size_t)d->R * d->S * d->O * 4; o = (o + 255) & ~(size_t)255;
     L.off_pwtot = o; o += (size_t)d->O * 4;             o = (o + 255) & ~(size_t)255;
+    L.off_err = o;   o += 256;
+    // tcgen05 path: stride 1, "same" padding, no pooling, filter block resident in shared memory
+    L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o;
+    if (d->stride_h == 1 && d->stride_w == 1 && d->pool == 1 && d->padding &&
+        (d->C == 64 || d->C == 128) && d->O % 64 == 0 && d->R == d->S && (d->R & 1)) {
+        const int nt = (d->O % 128 == 0) ? 128 : 64;
+        const int PW = d->W + d->pad_w;
+        const int npos = (128 + (d->R - 1) * PW + (d->S - 1) + 7) & ~7;
+        const size_t smem = (size_t)(d->C / 16) * npos * 16 + (size_t)d->R * d->S * d->C * nt +
+                            nt * 4 + 64;
+        if (smem <= 227 * 1024 && npos * 16 < (1 << 18)) {
+            L.umma_nt = nt; L.umma_npos = npos; L.umma_smem = smem;
+            o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
+        }
+    }
     L.bytes = o;
     return L;
+}
+
+int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible)
+
+template <int C, int NT>
+__global__ void __launch_bounds__(128) k_conv_umma(umma::ConvUmmaArgs a) {
+    extern __shared__ __align__(128) unsigned char dyn_smem[];
+    umma::conv_umma_cta<C, NT>(a, dyn_smem);
+}
+__global__ void k_prepare_filter_i8(const uint32_t* fbits, int O, int RS, int C, int nt, uint4* out) {
+    umma::prepare_filter_i8(fbits, O, RS, C, nt, out);
+}
+
+template <int C, int NT>
+int launch_conv_umma(const umma::ConvUmmaArgs& a, size_t smem, int sms, cudaStream_t st) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_conv_umma<C, NT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured[dev] = true;
+    }
+    int per_sm = (int)((227 * 1024) / (smem + 1024));
+    const int tm_cols = NT < 32 ? 32 : NT;
+    if (per_sm > 512 / tm_cols) per_sm = 512 / tm_cols;
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    const long long tasks = ((a.NV + 127) / 128) * ((a.O + NT - 1) / NT);
+    long long grid = (long long)sms * per_sm;
+    if (grid > tasks) grid = tasks;
+    k_conv_umma<C, NT><<<(int)grid, 128, smem, st>>>(a);
+    return launch_check("conv_layer (tcgen05)");
 }
 
 // ---- MMA issue-rate probe ----------------------------------------------------------------
@@ -353,7 +406,15 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
     k_conv_prepare<<<elementwise_grid((long long)d->O * 2 * L.KP, sms), 256, 0, (cudaStream_t)stream>>>(
         filter_bits, d->O, d->R, d->S, (d->C + 31) / 32, d->W, L.KP, (uint32_t*)(p + L.off_wq),
         (uint32_t*)(p + L.off_ktab), (int*)(p + L.off_pwt), (int*)(p + L.off_pwtot));
-    return launch_check("conv_prepare");
+    if (launch_check("conv_prepare")) return 1;
+    CUDA_TRY(cudaMemsetAsync(p + L.off_err, 0, 256, (cudaStream_t)stream));
+    if (L.umma_nt) {
+        const long long units = (long long)d->O * d->R * d->S * (d->C / 16);
+        k_prepare_filter_i8<<<elementwise_grid(units, sms), 256, 0, (cudaStream_t)stream>>>(
+            filter_bits, d->O, d->R * d->S, d->C, L.umma_nt, (uint4*)(p + L.off_wi8));
+        if (launch_check("conv_prepare (int8 filter)")) return 1;
+    }
+    return 0;
 }
 
 int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
@@ -368,6 +429,27 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
     if ((uintptr_t)in & 7) return fail("conv_layer: input must be 8-byte aligned");
     const PreparedLayout L = prepared_layout(d);
     const char* p = (const char*)prepared;
+    if (g_conv_path == 2 && !L.umma_nt) return fail("conv_layer: layer is not eligible for the tcgen05 path");
+    if (L.umma_nt && g_conv_path != 1) {
+        umma::ConvUmmaArgs a;
+        a.in = in; a.wi8 = (const uint4*)(p + L.off_wi8); a.thr = thr;
+        a.B = d->B; a.H = d->H; a.W = d->W; a.C = d->C; a.O = d->O; a.R = d->R; a.S = d->S;
+        a.pad_h = d->pad_h; a.pad_w = d->pad_w;
+        a.PW = d->W + d->pad_w; a.VH = d->H + d->pad_h; a.NPOS = L.umma_npos;
+        a.NV = (long long)d->B * a.VH * a.PW;
+        a.res_in = res_in; a.res_in_ch = res_in_ch; a.residual_channels = residual_channels;
+        a.residual_pool = residual_pool;
+        a.out = out; a.out_image_stride = out_image_stride; a.res_out = res_out; a.acc_out = acc_out;
+        a.err_flag = (int*)(p + L.off_err);
+        int sms;
+        if (sm_count(&sms)) return 1;
+        cudaStream_t st = (cudaStream_t)stream;
+        if (d->C == 64 && L.umma_nt == 64) return launch_conv_umma<64, 64>(a, L.umma_smem, sms, st);
+        if (d->C == 64 && L.umma_nt == 128) return launch_conv_umma<64, 128>(a, L.umma_smem, sms, st);
+        if (d->C == 128 && L.umma_nt == 64) return launch_conv_umma<128, 64>(a, L.umma_smem, sms, st);
+        if (d->C == 128 && L.umma_nt == 128) return launch_conv_umma<128, 128>(a, L.umma_smem, sms, st);
+        return fail("conv_layer: no tcgen05 instance for C=%d n-tile=%d", d->C, L.umma_nt);
+    }
     ConvArgs c;
     c.in = in;
     c.wq = (const uint32_t*)(p + L.off_wq);
@@ -388,6 +470,20 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
     const long long tasks = ((rows + 31) / 32) * Ow;
     k_conv<<<warp_grid(tasks, sms), kThreads, 0, (cudaStream_t)stream>>>(c);
     return launch_check("conv_layer");
+}
+
+int tcbnn_set_conv_path(int path) {
+    if (path < 0 || path > 2) return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05");
+    g_conv_path = path;
+    return 0;
+}
+
+int tcbnn_conv_status(const tcbnn_conv_desc* d, const void* prepared, int* status) {
+    if (conv_check(d, true)) return 1;
+    if (!status) return fail("conv_status: null status");
+    const PreparedLayout L = prepared_layout(d);
+    CUDA_TRY(cudaMemcpy(status, (const char*)prepared + L.off_err, sizeof(int), cudaMemcpyDeviceToHost));
+    return 0;
 }
 
 int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t* filter_bits,

@@ -175,3 +175,14 @@ def mma_peak(kind, warps_per_sm=32, iters=4000):
     t = C.c_double(0)
     _l.call("tcbnn_mma_peak", kind, warps_per_sm, iters, C.byref(t))
     return t.value
+
+
+def set_conv_path(path):
+    """0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05 (error when a layer is not eligible)."""
+    _l.call("tcbnn_set_conv_path", int(path))
+
+
+def conv_status(d, prepared):
+    s = C.c_int(0)
+    _l.call("tcbnn_conv_status", C.byref(d), _ptr(prepared), C.byref(s))
+    return s.value

@@ -177,3 +177,68 @@ def test_bad_arguments_are_rejected(cuda):
     d = ops.conv_desc(1, 8, 8, 32, 64, 3, 3)                     # odd word count per pixel
     with pytest.raises(TcbnnError):
         ops.conv_prepare(d, torch.zeros((64, 9, 1), dtype=torch.int32, device=cuda))
+
+
+UMMA_CASES = [
+    # B, H, W, C, O, R, residual   (stride 1, "same" padding, no pooling: tcgen05-eligible)
+    (1, 4, 4, 64, 64, 3, None),
+    (2, 6, 6, 64, 64, 3, "plain"),
+    (2, 4, 4, 64, 128, 3, "pool"),
+    (3, 10, 12, 128, 128, 3, None),
+    (2, 9, 9, 64, 64, 5, None),
+    (5, 7, 7, 128, 64, 3, "plain"),
+    (4, 56, 56, 64, 64, 3, "plain"),
+    (8, 28, 28, 128, 128, 3, "pool"),
+    (130, 3, 5, 64, 64, 3, None),          # many tiny images per tile
+]
+
+
+@pytest.mark.parametrize("case", UMMA_CASES)
+def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
+    """Both conv kernels (tcgen05 int8 implicit GEMM, warp-level b1 MMA) against the oracle."""
+    B, H, W, C, O, R, resmode = case
+    g = util.rng(sum(case[:6]))
+    Cw = C // 32
+    x = util.rand_words(g, (B, H, W, Cw))
+    f = util.rand_words(g, (O, R * R, Cw))
+    thr = (g.standard_normal(O) * np.sqrt(C * R * R) * 0.5).astype(np.float32)
+    res_in, rc, rpool = None, 0, False
+    if resmode == "plain":
+        res_in = g.integers(-300, 300, size=(B, H, W, O)).astype(np.int32)
+        rc = O
+    elif resmode == "pool":
+        res_in = g.integers(-300, 300, size=(B, 2 * H, 2 * W, O // 2)).astype(np.int32)
+        rc, rpool = O // 2, True
+    eo, er, ea = orc.conv_layer(x, f, thr, C, R, R, 1, 1, True, 1, res_in=res_in,
+                                residual_channels=rc, residual_pool=rpool,
+                                save_residual=True, want_acc=True)
+    d = ops.conv_desc(B, H, W, C, O, R, R)
+    prep = ops.conv_prepare(d, dev(f, cuda))
+    try:
+        for path in (2, 1):
+            ops.set_conv_path(path)
+            go, gr, ga = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda),
+                                        res_in=dev(res_in, cuda) if res_in is not None else None,
+                                        residual_channels=rc, residual_pool=rpool,
+                                        save_residual=True, want_acc=True)
+            assert ops.conv_status(d, prep) == 0
+            assert np.array_equal(ga.cpu().numpy(), ea), path
+            assert np.array_equal(gr.cpu().numpy(), er), path
+            assert np.array_equal(host_u32(go), eo), path
+    finally:
+        ops.set_conv_path(0)
+
+
+def test_tcgen05_path_refuses_ineligible_layer(cuda):
+    from tcbnn_b200.lib import TcbnnError
+    d = ops.conv_desc(1, 8, 8, 256, 256, 3, 3)          # filter block does not fit shared memory
+    f = torch.zeros((256, 9, 8), dtype=torch.int32, device=cuda)
+    prep = ops.conv_prepare(d, f)
+    x = torch.zeros((1, 8, 8, 8), dtype=torch.int32, device=cuda)
+    thr = torch.zeros((256,), device=cuda)
+    try:
+        ops.set_conv_path(2)
+        with pytest.raises(TcbnnError):
+            ops.conv_layer(d, x, prep, thr)
+    finally:
+        ops.set_conv_path(0)
