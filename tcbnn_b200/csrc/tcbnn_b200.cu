@@ -3,6 +3,7 @@
 #include "../../include/tcbnn_b200.h"
 #include "bnn_layers.cuh"
 #include "bconv_umma.cuh"
+#include "inconv_tiled.cuh"
 #include <cstdio>
 #include <cstdarg>
 #include <cstring>
@@ -179,19 +180,48 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     // tcgen05 path: stride 1, "same" padding, no pooling, filter block resident in shared memory
     L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o;
     if (d->stride_h == 1 && d->stride_w == 1 && d->pool == 1 && d->padding &&
-        (d->C == 64 || d->C == 128) && d->O % 64 == 0 && d->R == d->S && (d->R & 1)) {
-        const int nt = (d->O % 128 == 0) ? 128 : 64;
+        (d->C == 64 || d->C == 128 || d->C == 256 || d->C == 512) && d->R == d->S && (d->R & 1)) {
+        // widest n-tile whose filter block (R*S*C*nt bytes) stays resident next to the patch
+        int nt = d->C <= 128 ? 128 : d->C == 256 ? 64 : 32;
+        while (nt > 32 && d->O % nt) nt >>= 1;
         const int PW = d->W + d->pad_w;
         const int npos = (128 + (d->R - 1) * PW + (d->S - 1) + 7) & ~7;
         const size_t smem = (size_t)(d->C / 16) * npos * 16 + (size_t)d->R * d->S * d->C * nt +
                             nt * 4 + 64;
-        if (smem <= 227 * 1024 && npos * 16 < (1 << 18)) {
+        if (d->O % nt == 0 && smem <= 227 * 1024 && npos * 16 < (1 << 18)) {
             L.umma_nt = nt; L.umma_npos = npos; L.umma_smem = smem;
             o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
         }
     }
     L.bytes = o;
     return L;
+}
+
+template <int PPT>
+__global__ void __launch_bounds__(kInconvThreads) k_inconv_tiled(InConvArgs c) {
+    extern __shared__ __align__(16) unsigned char dyn_smem_inconv[];
+    inconv_tiled_block<PPT>(c, dyn_smem_inconv);
+}
+
+template <int PPT>
+int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t st) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_inconv_tiled<PPT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured[dev] = true;
+    }
+    int per_sm = (int)((220 * 1024) / (smem + 1024));
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    const long long total = (long long)c.B * c.OH * c.OW * c.pool * c.pool;
+    long long grid = (total + kInconvPixels - 1) / kInconvPixels;
+    if (grid > (long long)sms * per_sm) grid = (long long)sms * per_sm;
+    k_inconv_tiled<PPT><<<(int)grid, kInconvThreads, smem, st>>>(c);
+    return launch_check("inconv_layer (tiled)");
 }
 
 int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible)
@@ -444,10 +474,13 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
         int sms;
         if (sm_count(&sms)) return 1;
         cudaStream_t st = (cudaStream_t)stream;
-        if (d->C == 64 && L.umma_nt == 64) return launch_conv_umma<64, 64>(a, L.umma_smem, sms, st);
-        if (d->C == 64 && L.umma_nt == 128) return launch_conv_umma<64, 128>(a, L.umma_smem, sms, st);
-        if (d->C == 128 && L.umma_nt == 64) return launch_conv_umma<128, 64>(a, L.umma_smem, sms, st);
-        if (d->C == 128 && L.umma_nt == 128) return launch_conv_umma<128, 128>(a, L.umma_smem, sms, st);
+#define TCBNN_UMMA_CASE(CC, NN) \
+        if (d->C == CC && L.umma_nt == NN) return launch_conv_umma<CC, NN>(a, L.umma_smem, sms, st);
+        TCBNN_UMMA_CASE(64, 32) TCBNN_UMMA_CASE(64, 64) TCBNN_UMMA_CASE(64, 128)
+        TCBNN_UMMA_CASE(128, 32) TCBNN_UMMA_CASE(128, 64) TCBNN_UMMA_CASE(128, 128)
+        TCBNN_UMMA_CASE(256, 32) TCBNN_UMMA_CASE(256, 64)
+        TCBNN_UMMA_CASE(512, 32)
+#undef TCBNN_UMMA_CASE
         return fail("conv_layer: no tcgen05 instance for C=%d n-tile=%d", d->C, L.umma_nt);
     }
     ConvArgs c;
@@ -500,6 +533,14 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
     c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out; c.acc_out = acc_out;
     int sms;
     if (sm_count(&sms)) return 1;
+    const int opad = ((d->O + 31) / 32) * 32;
+    const size_t smem = inconv_tiled_smem(d->R, d->S, d->O);
+    if (g_conv_path != 1 && smem <= 200 * 1024 && kInconvThreads % opad == 0) {
+        const int ppt = kInconvPixels / (kInconvThreads / opad);
+        if (ppt == 4) return launch_inconv_tiled<4>(c, smem, sms, (cudaStream_t)stream);
+        if (ppt == 8) return launch_inconv_tiled<8>(c, smem, sms, (cudaStream_t)stream);
+        if (ppt == 16) return launch_inconv_tiled<16>(c, smem, sms, (cudaStream_t)stream);
+    }
     k_inconv<<<warp_grid((long long)d->B * d->OH * d->OW, sms), kThreads, 0, (cudaStream_t)stream>>>(c);
     return launch_check("inconv_layer");
 }

@@ -190,6 +190,10 @@ UMMA_CASES = [
     (4, 56, 56, 64, 64, 3, "plain"),
     (8, 28, 28, 128, 128, 3, "pool"),
     (130, 3, 5, 64, 64, 3, None),          # many tiny images per tile
+    (6, 14, 14, 256, 256, 3, "plain"),
+    (5, 7, 7, 512, 512, 3, "pool"),
+    (3, 7, 7, 512, 64, 3, None),
+    (2, 8, 8, 256, 96, 3, None),
 ]
 
 
@@ -231,10 +235,10 @@ def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
 
 def test_tcgen05_path_refuses_ineligible_layer(cuda):
     from tcbnn_b200.lib import TcbnnError
-    d = ops.conv_desc(1, 8, 8, 256, 256, 3, 3)          # filter block does not fit shared memory
-    f = torch.zeros((256, 9, 8), dtype=torch.int32, device=cuda)
+    d = ops.conv_desc(1, 8, 8, 192, 256, 3, 3)          # channel count without a tcgen05 instance
+    f = torch.zeros((256, 9, 6), dtype=torch.int32, device=cuda)
     prep = ops.conv_prepare(d, f)
-    x = torch.zeros((1, 8, 8, 8), dtype=torch.int32, device=cuda)
+    x = torch.zeros((1, 8, 8, 6), dtype=torch.int32, device=cuda)
     thr = torch.zeros((256,), device=cuda)
     try:
         ops.set_conv_path(2)
