@@ -159,7 +159,7 @@ def main():
     shapes = models.layer_shapes(spec)
     weights = models.synthetic_weights(spec, 1234)               # same weights on every rank
     x_host = torch.from_numpy(models.synthetic_input(spec, tdist.shard_seed(4321, rank))).pin_memory()
-    net = models.Network(spec, weights, x_host)
+    net = models.Network(spec, weights, x_host, input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND)
     del weights
     logits_host = torch.empty((B, 1000), dtype=torch.float32).pin_memory()
     gathered = torch.empty((world * B, 1000), dtype=torch.float32, device=dev) if world > 1 else None

@@ -84,15 +84,19 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
  * Conv128LayerFMT, kernel.cuh:676-827.
  *   in   [B][H][W][Cw]; out: image b at out + b*out_image_stride words, [OH][OW][Ow]
  *        (out_image_stride > OH*OW*Ow lets the next FC layer see padded rows: ahead_fc)
- *   res_in  (optional) int32 [B][P or 2P][Q or 2Q][res_in_ch]; injected for
- *           o < residual_channels; residual_pool takes the max over the 2x2 window
- *   res_out (optional) int32 [B][P][Q][O]: value after injection (save_residual)
+ *   res_in  (optional) [B][P or 2P][Q or 2Q][res_in_ch], int32 or int16 elements
+ *           (res_in_bytes = 4 or 2); injected for o < residual_channels; residual_pool takes
+ *           the max over the 2x2 window
+ *   res_out (optional) [B][P][Q][O], int32 or int16 (res_out_bytes): value after injection
+ *           (save_residual).  int16 halves the dominant HBM traffic of the residual layers;
+ *           the caller picks it when the running sum is known to fit (|value| <= C*R*S +
+ *           bound of res_in); a value that does not fit sets status 2 (tcbnn_conv_status).
  *   acc_out (optional) int32 [B][P][Q][O]: value before injection (for checking)       */
 int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
-                     const float* thr, const int32_t* res_in, int res_in_ch,
+                     const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
                      int residual_channels, int residual_pool, uint32_t* out,
-                     long long out_image_stride, int32_t* res_out, int32_t* acc_out,
-                     void* stream);
+                     long long out_image_stride, void* res_out, int res_out_bytes,
+                     int32_t* acc_out, void* stream);
 
 /* Which kernel tcbnn_conv_layer uses: 0 = automatic (tcgen05 int8 implicit GEMM where the layer
  * is eligible, else the warp-level b1 MMA), 1 = always the b1 MMA, 2 = tcgen05 or an error.
@@ -100,15 +104,17 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);
 /* Reads the layer's device-side status word (synchronises): 0 = fine, 1 = a bounded wait inside
- * the tcgen05 kernel gave up and the layer's output is not valid. */
+ * the tcgen05 kernel gave up and the layer's output is not valid, 2 = a residual value did not
+ * fit the int16 element size the caller chose. */
 int tcbnn_conv_status(const tcbnn_conv_desc* d, const void* prepared, int* status);
 
 /* First layer on fp32 NCHW input [B][3][H][W] (d->C must be 3).
  * InConv128LayerFMT, kernel.cuh:578-672.  filter_bits from tcbnn_pack_inconv_filter.
- * res_out: (int)acc, truncated toward zero; acc_out (optional): fp32 sums. */
+ * res_out: (int)acc, truncated toward zero, stored as int32 or int16 (res_out_bytes = 4 or 2;
+ * int16 only when the caller knows R*S*3*max|x| < 32768); acc_out (optional): fp32 sums. */
 int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t* filter_bits,
                        const float* thr, uint32_t* out, long long out_image_stride,
-                       int32_t* res_out, float* acc_out, void* stream);
+                       void* res_out, int res_out_bytes, float* acc_out, void* stream);
 
 /* No counterpart in the reference.  Same result as tcbnn_fc_layer, for callers that must not
  * allocate device memory around the call: a process whose own arena already holds all of the

@@ -123,6 +123,19 @@ __device__ __forceinline__ uint4 expand16(uint32_t h) {
     return make_uint4(v[0], v[1], v[2], v[3]);
 }
 
+// Four consecutive residual channels (element index i, a multiple of 4) widened to int32.
+__device__ __forceinline__ int4 ld_res4(const void* p, int bytes, size_t i) {
+    if (bytes == 2) {
+        const uint2 q = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const short*>(p) + i));
+        return make_int4((int)(short)(q.x & 0xFFFFu), (int)(short)(q.x >> 16),
+                         (int)(short)(q.y & 0xFFFFu), (int)(short)(q.y >> 16));
+    }
+    return __ldg(reinterpret_cast<const int4*>(reinterpret_cast<const int*>(p) + i));
+}
+__device__ __forceinline__ int4 max4(int4 a, int4 b) {
+    return make_int4(max(a.x, b.x), max(a.y, b.y), max(a.z, b.z), max(a.w, b.w));
+}
+
 // ---- filter preparation -------------------------------------------------------------------
 // bits [O][R*S][Cw] -> int8 blocks [n-tile][tap][chunk][n in tile][16 bytes], the order the
 // kernel keeps them in shared memory.
@@ -155,10 +168,10 @@ struct ConvUmmaArgs {
     int PW, VH;              // raster pitch / rows per image
     int NPOS;                // patch positions held in shared memory (multiple of 8)
     long long NV;            // raster positions over the batch
-    const int32_t* res_in; int res_in_ch, residual_channels, residual_pool;
+    const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
     uint32_t* out; long long out_image_stride;
-    int32_t* res_out; int32_t* acc_out;
-    int* err_flag;           // set when a bounded wait gave up
+    void* res_out; int res_out_bytes; int32_t* acc_out;
+    int* err_flag;           // 1: a bounded wait gave up, 2: a residual did not fit int16
 };
 
 // One CTA of 128 threads; stride-1 conv, no pooling.  Phases per tile: expand the patch,
@@ -173,11 +186,17 @@ __device__ void conv_umma_cta(const ConvUmmaArgs& a, unsigned char* smem) {
     const int RS = a.R * a.S;
     const int ntiles_n = (a.O + NT - 1) / NT;
 
-    // shared memory carve-up: [A patch][B filter][thresholds][barrier][tmem ptr]
+    // shared memory carve-up: [A patch | residual staging tile][B filter][thresholds]
+    // [row -> output pixel][barrier][tmem ptr].  The staging tile (int32 [128][NT+4]) reuses
+    // the patch, which is dead once the tile's MMAs have completed.
+    constexpr int PITCH = NT + 4;
+    const size_t a_bytes = (size_t)CH * a.NPOS * 16, r_bytes = (size_t)128 * PITCH * 4;
     uint4* sA = reinterpret_cast<uint4*>(smem);
-    uint4* sB = sA + (size_t)CH * a.NPOS;
+    int* sR = reinterpret_cast<int*>(smem);
+    uint4* sB = reinterpret_cast<uint4*>(smem + (a_bytes > r_bytes ? a_bytes : r_bytes));
     float* sThr = reinterpret_cast<float*>(sB + (size_t)RS * CH * NT);
-    uint64_t* sBar = reinterpret_cast<uint64_t*>(sThr + NT);
+    int* sRow = reinterpret_cast<int*>(sThr + NT);
+    uint64_t* sBar = reinterpret_cast<uint64_t*>(sRow + 128);
     uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 1);
 
     if (warp == 0) tmem_alloc(smem_u32(sTmem), TM_COLS);
@@ -271,53 +290,107 @@ __device__ void conv_umma_cta(const ConvUmmaArgs& a, unsigned char* smem) {
         }
         const size_t opix = ((size_t)n * a.H + y) * a.W + x;
         const int Ow = (a.O + 31) >> 5;
+        const int obase = nt * NT;
+        sRow[tid] = live ? (int)opix : -1;
+        __syncthreads();                       // patch is dead (MMAs done), row table visible
+        constexpr int UPR = NT / 4;            // 4-channel units per staged row
+        constexpr int UNROLL = 8;
+        if (ok && a.res_in) {
+            // residual tile -> shared memory: consecutive threads take consecutive 4-channel
+            // units (whole rows are contiguous in memory), UNROLL independent loads in flight
+            const int lim = min(a.residual_channels, a.res_in_ch);
+            for (int u0 = tid; u0 < 128 * UPR; u0 += 128 * UNROLL) {
+                int4 val[UNROLL];
+#pragma unroll
+                for (int k = 0; k < UNROLL; k++) {
+                    const int u = u0 + k * 128;
+                    val[k] = make_int4(0, 0, 0, 0);
+                    if (u < 128 * UPR) {
+                        const int r = u / UPR, o = obase + (u % UPR) * 4;
+                        const int op = sRow[r];
+                        if (op >= 0 && o < lim) {
+                            if (a.residual_pool) {      // max over the 2x2 window (kernel.cuh:773-783)
+                                const int px = op % a.W, t2 = op / a.W, py = t2 % a.H, pn = t2 / a.H;
+                                const size_t b00 = (((size_t)pn * 2 * a.H + 2 * py) * 2 * a.W + 2 * px) *
+                                                   a.res_in_ch + o;
+                                const size_t rowp = (size_t)2 * a.W * a.res_in_ch;
+                                val[k] = max4(max4(ld_res4(a.res_in, a.res_in_bytes, b00),
+                                                   ld_res4(a.res_in, a.res_in_bytes, b00 + a.res_in_ch)),
+                                              max4(ld_res4(a.res_in, a.res_in_bytes, b00 + rowp),
+                                                   ld_res4(a.res_in, a.res_in_bytes, b00 + rowp + a.res_in_ch)));
+                            } else {
+                                val[k] = ld_res4(a.res_in, a.res_in_bytes, (size_t)op * a.res_in_ch + o);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < UNROLL; k++) {
+                    const int u = u0 + k * 128;
+                    if (u < 128 * UPR)
+                        *reinterpret_cast<int4*>(sR + (u / UPR) * PITCH + (u % UPR) * 4) = val[k];
+                }
+            }
+            __syncthreads();
+        }
         if (ok) {
-#pragma unroll 1
+            uint32_t words[NT / 32];
+#pragma unroll
             for (int nb = 0; nb < NT / 32; nb++) {
                 int v[32];
                 tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + nb * 32, v);
                 tmem_ld_wait();
-                const int o0 = nt * NT + nb * 32;
-                if (live && o0 < a.O) {
-                    if (a.acc_out) {
-                        int4* dst = reinterpret_cast<int4*>(a.acc_out + opix * a.O + o0);
+                const int o0 = obase + nb * 32;
+                int4* srow = reinterpret_cast<int4*>(sR + tid * PITCH + nb * 32);
+                if (live && a.acc_out) {
+                    int4* dst = reinterpret_cast<int4*>(a.acc_out + opix * a.O + o0);
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
-                            dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    }
-                    if (a.res_in) {
+                    for (int j = 0; j < 8; j++)
+                        dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+                if (a.res_in) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int o = o0 + j;
-                            if (o < a.residual_channels && o < a.res_in_ch) {
-                                int rv;
-                                if (a.residual_pool) {
-                                    rv = INT_MIN;
-                                    for (int u = 0; u < 2; u++)
-                                        for (int t = 0; t < 2; t++)
-                                            rv = max(rv, __ldg(a.res_in +
-                                                (((size_t)n * 2 * a.H + (2 * y + u)) * 2 * a.W +
-                                                 (2 * x + t)) * a.res_in_ch + o));
-                                } else {
-                                    rv = __ldg(a.res_in + opix * a.res_in_ch + o);
-                                }
-                                v[j] += rv;
-                            }
-                        }
-                    }
-                    uint32_t word = 0;
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (!((float)v[j] < sThr[nb * 32 + j])) word |= 0x80000000u >> j;
-                    a.out[(size_t)n * a.out_image_stride + ((size_t)y * a.W + x) * Ow +
-                          (o0 >> 5)] = word;
-                    if (a.res_out) {
-                        int4* dst = reinterpret_cast<int4*>(a.res_out + opix * a.O + o0);
-#pragma unroll
-                        for (int j = 0; j < 8; j++)
-                            dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    for (int j = 0; j < 8; j++) {
+                        const int4 rr = srow[j];
+                        v[4 * j] += rr.x; v[4 * j + 1] += rr.y; v[4 * j + 2] += rr.z; v[4 * j + 3] += rr.w;
                     }
                 }
+                uint32_t word = 0;
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (!((float)v[j] < sThr[nb * 32 + j])) word |= 0x80000000u >> j;
+                words[nb] = word;
+                if (a.res_out) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        srow[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+            if (live) {
+                uint32_t* dst = a.out + (size_t)n * a.out_image_stride +
+                                ((size_t)y * a.W + x) * Ow + (obase >> 5);
+#pragma unroll
+                for (int nb = 0; nb < NT / 32; nb++) dst[nb] = words[nb];
+            }
+            if (a.res_out) {
+                __syncthreads();
+                bool overflow = false;
+                for (int u = tid; u < 128 * UPR; u += 128) {
+                    const int r = u / UPR, c4 = (u % UPR) * 4;
+                    const int op = sRow[r];
+                    if (op < 0) continue;
+                    const int4 v4 = *reinterpret_cast<const int4*>(sR + r * PITCH + c4);
+                    const size_t idx = (size_t)op * a.O + obase + c4;
+                    if (a.res_out_bytes == 2) {
+                        overflow |= max(max(abs(v4.x), abs(v4.y)), max(abs(v4.z), abs(v4.w))) > 32767;
+                        *reinterpret_cast<uint2*>(reinterpret_cast<short*>(a.res_out) + idx) =
+                            make_uint2(((uint32_t)v4.x & 0xFFFFu) | ((uint32_t)v4.y << 16),
+                                       ((uint32_t)v4.z & 0xFFFFu) | ((uint32_t)v4.w << 16));
+                    } else {
+                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(a.res_out) + idx) = v4;
+                    }
+                }
+                if (overflow) atomicExch(a.err_flag, 2);
             }
         }
         tc_fence_before();

@@ -19,6 +19,17 @@
 
 namespace tcbnn {
 
+// Residual tensors are int32 or int16 (element size chosen by the caller, who knows the
+// bound of the running shortcut sum); the arithmetic is int32 either way.
+__device__ __forceinline__ int ld_res(const void* p, int bytes, size_t i) {
+    return bytes == 2 ? (int)__ldg(reinterpret_cast<const short*>(p) + i)
+                      : __ldg(reinterpret_cast<const int*>(p) + i);
+}
+__device__ __forceinline__ void st_res(void* p, int bytes, size_t i, int v) {
+    if (bytes == 2) reinterpret_cast<short*>(p)[i] = (short)v;
+    else reinterpret_cast<int*>(p)[i] = v;
+}
+
 // ----------------------------------------------------------------------------------------
 // Bit GEMM family: standalone int32 GEMM (bmm/tensorcore_kernel.cu:138-356), hidden FC
 // layer (Fc128LayerFMT, kernel.cuh:174-226) and output layer (Out128LayerFMT, :230-280).
@@ -187,11 +198,13 @@ struct ConvArgs {
     const int* pwtot;        // [O]       popc of filter o over all taps
     const float* thr;        // [O]
     int B, H, W, C, Cw, O, R, S, sh, sw, pad_h, pad_w, pool, OH, OW, KP;
-    const int32_t* res_in;   // [B][P or 2P][Q or 2Q][res_in_ch] or null
+    const void* res_in;      // [B][P or 2P][Q or 2Q][res_in_ch] or null
+    int res_in_bytes;        // 4 (int32) or 2 (int16)
     int res_in_ch, residual_channels, residual_pool;
     uint32_t* out;           // per image [OH][OW][Ow] words at stride out_image_stride
     long long out_image_stride;
-    int32_t* res_out;        // [B][P][Q][O] or null
+    void* res_out;           // [B][P][Q][O] or null
+    int res_out_bytes;
     int32_t* acc_out;        // [B][P][Q][O] or null (value before residual injection)
 };
 
@@ -295,18 +308,18 @@ __device__ __forceinline__ void conv_warp_tile(const ConvArgs& c, int tp, int tn
                             residual = INT_MIN;
                             for (int u = 0; u < 2; u++)
                                 for (int v = 0; v < 2; v++)
-                                    residual = max(residual, __ldg(c.res_in +
+                                    residual = max(residual, ld_res(c.res_in, c.res_in_bytes,
                                         (((size_t)pb[i] * 2 * P + (2 * py[i] + u)) * 2 * Q +
                                          (2 * px[i] + v)) * c.res_in_ch + o));
                         } else {
-                            residual = __ldg(c.res_in + opix * c.res_in_ch + o);
+                            residual = ld_res(c.res_in, c.res_in_bytes, opix * c.res_in_ch + o);
                         }
                     }
                     res += residual;
                 }
                 if (!((float)res < __ldg(c.thr + o)))            // kernel.cuh:795-796
                     words[c.pool == 2 ? 0 : i] |= 0x80000000u >> (j * 8 + 2 * t + e);
-                if (c.res_out) c.res_out[opix * c.O + o] = res;  // kernel.cuh:818-824
+                if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.O + o, res);  // kernel.cuh:818-824
             }
         }
     }
@@ -348,7 +361,8 @@ struct InConvArgs {
     int B, H, W, O, R, S, sh, sw, pad_h, pad_w, pool, OH, OW;
     uint32_t* out;
     long long out_image_stride;
-    int32_t* res_out;        // [B][P][Q][O] int32, (int)acc truncation (kernel.cuh:666-668)
+    void* res_out;           // [B][P][Q][O], (int)acc truncation (kernel.cuh:666-668)
+    int res_out_bytes;       // 4 or 2
     float* acc_out;          // optional fp32 accumulators
 };
 
@@ -400,7 +414,7 @@ __device__ __forceinline__ void inconv_warp_pixel(const InConvArgs& c, long long
                 const bool bit = o < c.O && !(acc[k] < __ldg(c.thr + min(o, c.O - 1)));
                 words[k] |= __brev(__ballot_sync(0xffffffffu, bit));
                 if (o < c.O) {
-                    if (c.res_out) c.res_out[opix * c.O + o] = (int)acc[k];
+                    if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.O + o, (int)acc[k]);
                     if (c.acc_out) c.acc_out[opix * c.O + o] = acc[k];
                 }
             }

@@ -186,8 +186,9 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
         while (nt > 32 && d->O % nt) nt >>= 1;
         const int PW = d->W + d->pad_w;
         const int npos = (128 + (d->R - 1) * PW + (d->S - 1) + 7) & ~7;
-        const size_t smem = (size_t)(d->C / 16) * npos * 16 + (size_t)d->R * d->S * d->C * nt +
-                            nt * 4 + 64;
+        const size_t a_bytes = (size_t)(d->C / 16) * npos * 16, r_bytes = (size_t)128 * (nt + 4) * 4;
+        const size_t smem = (a_bytes > r_bytes ? a_bytes : r_bytes) +
+                            (size_t)d->R * d->S * d->C * nt + nt * 4 + 128 * 4 + 64;
         if (d->O % nt == 0 && smem <= 227 * 1024 && npos * 16 < (1 << 18)) {
             L.umma_nt = nt; L.umma_npos = npos; L.umma_smem = smem;
             o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
@@ -448,28 +449,36 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
 }
 
 int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
-                     const float* thr, const int32_t* res_in, int res_in_ch,
+                     const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
                      int residual_channels, int residual_pool, uint32_t* out,
-                     long long out_image_stride, int32_t* res_out, int32_t* acc_out, void* stream) {
+                     long long out_image_stride, void* res_out, int res_out_bytes,
+                     int32_t* acc_out, void* stream) {
     if (conv_check(d, true)) return 1;
     const int Ow = (d->O + 31) / 32;
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("conv_layer: out_image_stride too small");
     if ((res_out || res_in) && d->pool != 1) return fail("conv_layer: residuals need pool == 1");
     if (res_in && (res_in_ch <= 0 || residual_channels <= 0)) return fail("conv_layer: residual channel counts must be positive");
+    if (res_in && res_in_bytes != 2 && res_in_bytes != 4) return fail("conv_layer: res_in_bytes must be 2 or 4");
+    if (res_out && res_out_bytes != 2 && res_out_bytes != 4) return fail("conv_layer: res_out_bytes must be 2 or 4");
     if ((uintptr_t)in & 7) return fail("conv_layer: input must be 8-byte aligned");
     const PreparedLayout L = prepared_layout(d);
     const char* p = (const char*)prepared;
     if (g_conv_path == 2 && !L.umma_nt) return fail("conv_layer: layer is not eligible for the tcgen05 path");
-    if (L.umma_nt && g_conv_path != 1) {
+    // the tcgen05 epilogue moves residuals in 4-channel vectors
+    const bool res_vec_ok = !res_in || (res_in_ch % 4 == 0 && residual_channels % 4 == 0 &&
+                                        ((uintptr_t)res_in & 15) == 0);
+    if (g_conv_path == 2 && !res_vec_ok) return fail("conv_layer: residual layout not eligible for the tcgen05 path");
+    if (L.umma_nt && g_conv_path != 1 && res_vec_ok && (!res_out || ((uintptr_t)res_out & 15) == 0)) {
         umma::ConvUmmaArgs a;
         a.in = in; a.wi8 = (const uint4*)(p + L.off_wi8); a.thr = thr;
         a.B = d->B; a.H = d->H; a.W = d->W; a.C = d->C; a.O = d->O; a.R = d->R; a.S = d->S;
         a.pad_h = d->pad_h; a.pad_w = d->pad_w;
         a.PW = d->W + d->pad_w; a.VH = d->H + d->pad_h; a.NPOS = L.umma_npos;
         a.NV = (long long)d->B * a.VH * a.PW;
-        a.res_in = res_in; a.res_in_ch = res_in_ch; a.residual_channels = residual_channels;
-        a.residual_pool = residual_pool;
-        a.out = out; a.out_image_stride = out_image_stride; a.res_out = res_out; a.acc_out = acc_out;
+        a.res_in = res_in; a.res_in_bytes = res_in_bytes; a.res_in_ch = res_in_ch;
+        a.residual_channels = residual_channels; a.residual_pool = residual_pool;
+        a.out = out; a.out_image_stride = out_image_stride; a.res_out = res_out;
+        a.res_out_bytes = res_out_bytes; a.acc_out = acc_out;
         a.err_flag = (int*)(p + L.off_err);
         int sms;
         if (sm_count(&sms)) return 1;
@@ -494,9 +503,10 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
     c.R = d->R; c.S = d->S; c.sh = d->stride_h; c.sw = d->stride_w;
     c.pad_h = d->pad_h; c.pad_w = d->pad_w; c.pool = d->pool; c.OH = d->OH; c.OW = d->OW;
     c.KP = L.KP;
-    c.res_in = res_in; c.res_in_ch = res_in_ch; c.residual_channels = residual_channels;
-    c.residual_pool = residual_pool;
-    c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out; c.acc_out = acc_out;
+    c.res_in = res_in; c.res_in_bytes = res_in_bytes; c.res_in_ch = res_in_ch;
+    c.residual_channels = residual_channels; c.residual_pool = residual_pool;
+    c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out;
+    c.res_out_bytes = res_out_bytes; c.acc_out = acc_out;
     int sms;
     if (sm_count(&sms)) return 1;
     const long long rows = (long long)d->B * d->OH * d->OW * d->pool * d->pool;
@@ -521,8 +531,9 @@ int tcbnn_conv_status(const tcbnn_conv_desc* d, const void* prepared, int* statu
 
 int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t* filter_bits,
                        const float* thr, uint32_t* out, long long out_image_stride,
-                       int32_t* res_out, float* acc_out, void* stream) {
+                       void* res_out, int res_out_bytes, float* acc_out, void* stream) {
     if (conv_check(d, false)) return 1;
+    if (res_out && res_out_bytes != 2 && res_out_bytes != 4) return fail("inconv_layer: res_out_bytes must be 2 or 4");
     const int Ow = (d->O + 31) / 32;
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("inconv_layer: out_image_stride too small");
     InConvArgs c;
@@ -530,7 +541,8 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
     c.B = d->B; c.H = d->H; c.W = d->W; c.O = d->O; c.R = d->R; c.S = d->S;
     c.sh = d->stride_h; c.sw = d->stride_w; c.pad_h = d->pad_h; c.pad_w = d->pad_w;
     c.pool = d->pool; c.OH = d->OH; c.OW = d->OW;
-    c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out; c.acc_out = acc_out;
+    c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out;
+    c.res_out_bytes = res_out_bytes; c.acc_out = acc_out;
     int sms;
     if (sm_count(&sms)) return 1;
     const int opad = ((d->O + 31) / 32) * 32;

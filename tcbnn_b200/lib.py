@@ -38,10 +38,10 @@ SIGNATURES = {
     "tcbnn_conv_shape": (_I, [C.POINTER(ConvDesc)]),
     "tcbnn_conv_prepared_bytes": (_SZ, [C.POINTER(ConvDesc)]),
     "tcbnn_conv_prepare": (_I, [C.POINTER(ConvDesc), _P, _P, _P]),
-    "tcbnn_conv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _I, _I, _I, _P, _LL, _P, _P, _P]),
+    "tcbnn_conv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_set_conv_path": (_I, [_I]),
     "tcbnn_conv_status": (_I, [C.POINTER(ConvDesc), _P, C.POINTER(C.c_int)]),
-    "tcbnn_inconv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _P, _P]),
+    "tcbnn_inconv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_noalloc_scratch_bytes": (_SZ, []),
     "tcbnn_fc_layer_noalloc": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
     "tcbnn_mma_peak": (_I, [_I, _I, _I, C.POINTER(C.c_double)]),

@@ -141,11 +141,17 @@ def synthetic_input(spec, seed, batch=None):
     return ((u8.astype(np.float32) / np.float32(255.0)) - mean) / std
 
 
+# max |value| synthetic_input() can produce for images: (1 - 0.406) / 0.225
+SYNTHETIC_IMAGE_ABS_BOUND = 2.65
+
+
 class Network:
     """Chain of layer objects built from a spec, the way the reference drivers build theirs
     (new XLayerParam(...) ; initialize(config, prev->get_output_gpu(), residual))."""
 
-    def __init__(self, spec, weights, input_host):
+    def __init__(self, spec, weights, input_host, input_abs_bound=None):
+        """input_abs_bound: max |pixel value| the caller guarantees; with it the residual chain
+        is provably small and is stored as int16 instead of int32."""
         self.spec = spec
         B = spec["batch"]
         cfg = weights if hasattr(weights, "read") else param.ArrayConfig(weights)
@@ -158,7 +164,8 @@ class Network:
             elif t == "inconv":
                 obj = param.InConv128LayerParam(l["name"], l["H"], l["W"], l["R"], l["S"], 3, l["O"], B,
                                                 l["stride"], l["stride"], True, l["pool"], l["pool"],
-                                                l.get("save_residual", False)).initialize(input_host, cfg)
+                                                l.get("save_residual", False),
+                                                input_abs_bound=input_abs_bound).initialize(input_host, cfg)
             elif t == "conv":
                 inj = l.get("inject")
                 obj = param.Conv128LayerParam(l["name"], l["H"], l["W"], l["R"], l["S"], l["C"], l["O"], B,
@@ -167,7 +174,8 @@ class Network:
                                               inj is not None, l.get("residual_channels", 0),
                                               l.get("residual_pool", False))
                 res = self.layers[inj].get_output_residual_gpu() if inj is not None else None
-                obj.initialize(cfg, prev.get_output_gpu(), res)
+                rb = self.layers[inj].residual_bound if inj is not None else None
+                obj.initialize(cfg, prev.get_output_gpu(), res, rb)
             elif t == "fc":
                 obj = param.Fc128LayerParam(l["name"], B, l["K"], l["N"]).initialize(cfg, prev.get_output_gpu())
             elif t == "out":

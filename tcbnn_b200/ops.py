@@ -136,8 +136,9 @@ def conv_prepare(d, filter_bits):
 
 def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_pool=False,
                out=None, out_image_stride=None, save_residual=False, want_acc=False,
-               res_out_buf=None):
-    """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out)."""
+               res_out_buf=None, residual_dtype=torch.int32):
+    """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out).
+    Residual tensors may be torch.int32 or torch.int16."""
     _need_cuda(x, prepared, thr, res_in)
     Ow = (d.O + 31) // 32
     stride = out_image_stride or d.OH * d.OW * Ow
@@ -146,17 +147,19 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
     P, Q = d.pool * d.OH, d.pool * d.OW
     res_out = res_out_buf
     if res_out is None and save_residual:
-        res_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device)
+        res_out = torch.empty((d.B, P, Q, d.O), dtype=residual_dtype, device=x.device)
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if want_acc else None
     res_in_ch = res_in.shape[-1] if res_in is not None else 0
     _l.call("tcbnn_conv_layer", C.byref(d), _ptr(x), _ptr(prepared), _ptr(thr), _ptr(res_in),
+            res_in.element_size() if res_in is not None else 4,
             res_in_ch, residual_channels, int(bool(residual_pool)), _ptr(out),
-            C.c_longlong(stride), _ptr(res_out), _ptr(acc_out), _stream())
+            C.c_longlong(stride), _ptr(res_out),
+            res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
     return out, res_out, acc_out
 
 
 def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_residual=False,
-                 want_acc=False):
+                 want_acc=False, res_out_buf=None, residual_dtype=torch.int32):
     """x: fp32 [B][3][H][W].  Returns (out_bits, res_out, acc_out)."""
     _need_cuda(x, filter_bits, thr)
     Ow = (d.O + 31) // 32
@@ -164,10 +167,13 @@ def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_r
     if out is None:
         out = torch.zeros((d.B, stride), dtype=torch.int32, device=x.device)
     P, Q = d.pool * d.OH, d.pool * d.OW
-    res_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if save_residual else None
+    res_out = res_out_buf
+    if res_out is None and save_residual:
+        res_out = torch.empty((d.B, P, Q, d.O), dtype=residual_dtype, device=x.device)
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.float32, device=x.device) if want_acc else None
     _l.call("tcbnn_inconv_layer", C.byref(d), _ptr(x), _ptr(filter_bits), _ptr(thr), _ptr(out),
-            C.c_longlong(stride), _ptr(res_out), _ptr(acc_out), _stream())
+            C.c_longlong(stride), _ptr(res_out),
+            res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
     return out, res_out, acc_out
 
 

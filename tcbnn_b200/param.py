@@ -51,6 +51,11 @@ class TextConfig(ArrayConfig):
         super().__init__(np.loadtxt(path, dtype=np.float32).ravel())
 
 
+def _residual_dtype(bound):
+    """int16 when the running shortcut sum provably fits, else int32."""
+    return torch.int16 if (bound is not None and bound <= 32767) else torch.int32
+
+
 def _dev():
     if not torch.cuda.is_available():
         raise RuntimeError("tcbnn_b200 needs a CUDA device; there is no CPU path")
@@ -175,7 +180,8 @@ class InConv128LayerParam:
 
     def __init__(self, name, input_height, input_width, filter_height, filter_width,
                  input_channels, output_channels, batch, stride_height=1, stride_width=1,
-                 padding=True, pool_height=1, pool_width=1, save_residual=False):
+                 padding=True, pool_height=1, pool_width=1, save_residual=False,
+                 input_abs_bound=None):
         if pool_height != pool_width:
             raise ValueError("only square pooling windows are supported")
         self.name = name
@@ -184,6 +190,12 @@ class InConv128LayerParam:
         self.input_channels, self.output_channels, self.batch = input_channels, output_channels, batch
         self.stride_height, self.stride_width, self.padding = stride_height, stride_width, padding
         self.pool_height, self.pool_width, self.save_residual = pool_height, pool_width, save_residual
+        # Bound of |saved residual| when the caller states max|input| (extension: lets the
+        # residual be stored as int16).  Unknown -> int32 like the reference (param.h:758).
+        self.residual_bound = None
+        if input_abs_bound is not None:
+            self.residual_bound = int(filter_height * filter_width * input_channels
+                                      * float(input_abs_bound) * 1.001) + 2
         self.desc = ops.conv_desc(batch, input_height, input_width, input_channels, output_channels,
                                   filter_height, filter_width, stride_height, stride_width, padding,
                                   pool_height)
@@ -204,7 +216,7 @@ class InConv128LayerParam:
         self.output_gpu = torch.zeros((d.B, d.OH, d.OW, Ow), dtype=torch.int32, device=dev)
         if self.save_residual:
             self.output_residual_gpu = torch.zeros((d.B, d.pool * d.OH, d.pool * d.OW, d.O),
-                                                   dtype=torch.int32, device=dev)
+                                                   dtype=_residual_dtype(self.residual_bound), device=dev)
         return self
 
     def set_input(self, input):
@@ -212,11 +224,8 @@ class InConv128LayerParam:
         self.input_gpu.copy_(src.reshape(self.input_gpu.shape), non_blocking=True)
 
     def forward(self):
-        d = self.desc
-        Ow = (d.O + 31) // 32
-        ops._l.call("tcbnn_inconv_layer", ops.C.byref(d), ops._ptr(self.input_gpu), ops._ptr(self.filter_gpu),
-                    ops._ptr(self.bn_gpu), ops._ptr(self.output_gpu), ops.C.c_longlong(d.OH * d.OW * Ow),
-                    ops._ptr(self.output_residual_gpu), ops.C.c_void_p(0), ops._stream())
+        ops.inconv_layer(self.desc, self.input_gpu, self.filter_gpu, self.bn_gpu, out=self.output_gpu,
+                         res_out_buf=self.output_residual_gpu)
 
     def get_output_gpu(self):
         return self.output_gpu
@@ -257,10 +266,18 @@ class Conv128LayerParam:
         self.pad_h, self.pad_w = self.desc.pad_h, self.desc.pad_w
         self.output_height, self.output_width = self.desc.OH, self.desc.OW
         self.output_residual_gpu = self.input_residual_gpu = None
+        self.residual_bound = None
 
-    def initialize(self, config, prev_layer_gpu, input_residual_gpu=None):
+    def initialize(self, config, prev_layer_gpu, input_residual_gpu=None, input_residual_bound=None):
+        """input_residual_bound (extension): bound of |injected residual| if known; it decides
+        whether this layer's saved residual can be int16."""
         dev = _dev()
         d = self.desc
+        fan = d.C * d.R * d.S
+        if not self.inject_residual:
+            self.residual_bound = fan
+        elif input_residual_bound is not None:
+            self.residual_bound = fan + int(input_residual_bound)
         f = torch.from_numpy(config.read(d.R * d.S * d.C * d.O).reshape(d.R * d.S, d.C, d.O)).to(dev)
         self.filter_gpu = ops.pack_conv_filter(f)
         self.prepared = ops.conv_prepare(d, self.filter_gpu)
@@ -273,7 +290,7 @@ class Conv128LayerParam:
         self.output_gpu = torch.zeros((d.B, self.out_image_stride), dtype=torch.int32, device=dev)
         if self.save_residual:
             self.output_residual_gpu = torch.zeros((d.B, d.pool * d.OH, d.pool * d.OW, d.O),
-                                                   dtype=torch.int32, device=dev)
+                                                   dtype=_residual_dtype(self.residual_bound), device=dev)
         self.set_input_gpu(prev_layer_gpu)
         if self.inject_residual:
             self.set_input_residual_gpu(input_residual_gpu)

@@ -167,6 +167,21 @@ def test_inconv_layer(cuda, case):
     assert np.array_equal(host_u32(go), eo)
 
 
+def test_int16_residual_overflow_is_flagged(cuda):
+    """A residual that does not fit the int16 element size the caller chose sets status 2."""
+    g = util.rng(77)
+    B, H, W, C, O = 1, 4, 4, 64, 64
+    x = util.rand_words(g, (B, H, W, 2))
+    f = util.rand_words(g, (O, 9, 2))
+    thr = np.zeros(O, np.float32)
+    res_in = np.full((B, H, W, O), 40000, np.int32)
+    d = ops.conv_desc(B, H, W, C, O, 3, 3)
+    prep = ops.conv_prepare(d, dev(f, cuda))
+    ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=dev(res_in, cuda),
+                   residual_channels=O, save_residual=True, residual_dtype=torch.int16)
+    assert ops.conv_status(d, prep) == 2
+
+
 def test_bad_arguments_are_rejected(cuda):
     from tcbnn_b200.lib import TcbnnError
     A = torch.zeros((8, 3), dtype=torch.int32, device=cuda)      # odd leading dimension
@@ -228,6 +243,14 @@ def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
             assert ops.conv_status(d, prep) == 0
             assert np.array_equal(ga.cpu().numpy(), ea), path
             assert np.array_equal(gr.cpu().numpy(), er), path
+            assert np.array_equal(host_u32(go), eo), path
+            # int16 residual tensors in and out: same values
+            r16 = dev(res_in.astype(np.int16), cuda) if res_in is not None else None
+            go, gr, _ = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16,
+                                       residual_channels=rc, residual_pool=rpool,
+                                       save_residual=True, residual_dtype=torch.int16)
+            assert gr.dtype == torch.int16 and ops.conv_status(d, prep) == 0
+            assert np.array_equal(gr.cpu().numpy().astype(np.int32), er), path
             assert np.array_equal(host_u32(go), eo), path
     finally:
         ops.set_conv_path(0)

@@ -9,11 +9,11 @@ from tcbnn_b200 import models
 pytestmark = pytest.mark.gpu
 
 
-def _compare(spec, seed, cuda):
+def _compare(spec, seed, cuda, input_abs_bound=None):
     w = models.synthetic_weights(spec, seed)
     x = models.synthetic_input(spec, seed + 1)
     acts, ress = onet.run(spec, w, x)
-    net = models.Network(spec, w, x)
+    net = models.Network(spec, w, x, input_abs_bound=input_abs_bound)
     logits = net.forward()
     torch.cuda.synchronize()
     for i, (layer, a, r) in enumerate(zip(net.layers, acts, ress)):
@@ -22,7 +22,10 @@ def _compare(spec, seed, cuda):
             got = got.view(np.uint32)
             assert np.array_equal(got.reshape(a.shape), a), "layer %d %s bits" % (i, layer.name)
         if r is not None:
-            gr = layer.get_output_residual_gpu().cpu().numpy()
+            gr = layer.get_output_residual_gpu()
+            if input_abs_bound is not None:
+                assert gr.dtype == torch.int16
+            gr = gr.cpu().numpy().astype(np.int32)
             assert np.array_equal(gr, r), "layer %d %s residual" % (i, layer.name)
     ref = acts[-1]
     got = logits.cpu().numpy()
@@ -47,3 +50,17 @@ def test_resnet18_small_image(cuda):
 
 def test_resnet18_224(cuda):
     _compare(models.resnet18_spec(2), 30, cuda)
+
+
+def test_resnet18_224_int16_residuals(cuda):
+    # same network with the stated input bound: residual chain stored as int16, values identical
+    _compare(models.resnet18_spec(3), 31, cuda, input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND)
+
+
+def test_resnet18_both_conv_kernels(cuda):
+    from tcbnn_b200 import ops
+    try:
+        ops.set_conv_path(1)                 # warp-level b1 MMA everywhere
+        _compare(models.resnet18_spec(2, image=64, classes=100), 21, cuda)
+    finally:
+        ops.set_conv_path(0)
