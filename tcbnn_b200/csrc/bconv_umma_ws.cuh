@@ -1,0 +1,387 @@
+// Warp-specialised, persistent tcgen05 binary convolution (stride 1 and stride 2).
+//
+// Same arithmetic and the same raster trick as bconv_umma.cuh (read that header first): packed
+// bits -> +-1 bytes in the no-swizzle K-major core-matrix layout, taps as start-address offsets,
+// int8 x int8 -> int32 in tensor memory.  What changes is the schedule.  One CTA per SM runs
+//
+//   warps 0-3  epilogue   : prefetch the residual rows, wait for an accumulator, tcgen05.ld,
+//                           add / threshold / pack, store bits and the new residual
+//   warps 4-7  expanders  : packed input bits (prefetched one stage ahead in registers) ->
+//                           +-1 bytes of one 64-channel block of the patch, ring of stages
+//   warp  8    MMA issuer : one lane issues 9 taps x 2 k-steps per stage, commits the stage
+//                           back to the expanders and the finished tile to the epilogue
+//
+// with mbarriers between them, two accumulators in tensor memory (epilogue of tile i overlaps
+// the MMAs of tile i+1) and the filter block of the CTA's n-tile resident in shared memory.
+//
+// Stride 2: the input is de-interleaved into its four (row parity, column parity) planes, each a
+// raster with the OUTPUT pitch; tap (r, s) then reads plane ((r-pad)&1, (s-pad)&1) at a fixed
+// raster offset, so it is again just a descriptor start address.
+//
+// Every wait is bounded: a wait that gives up raises the CTA's abort flag and the layer's
+// status word, all roles drain, tensor memory is released, the kernel returns.
+#pragma once
+#include "bconv_umma.cuh"
+
+namespace tcbnn {
+namespace umma {
+
+struct ConvWsArgs {
+    const uint32_t* in;       // [B][H][W][C/32]
+    const uint4* wi8;         // [n-tile][64-ch block][tap][4 chunks][NT][16 B]
+    const float* thr;         // [O]
+    int B, H, W, C, O, R, S, pad_h, pad_w, stride;
+    int OHg, OWg;             // outputs per image (pre-pool == post-pool here)
+    int PW, VH;               // raster pitch and rows per image (output grid + zero band)
+    int NPOS;                 // raster positions per plane patch (multiple of 8)
+    int back_y, back_x;       // patch origin = tile start - (back_y*PW + back_x)
+    long long NV;             // raster positions over the batch
+    int ntiles_n;
+    const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
+    uint32_t* out; long long out_image_stride;
+    void* res_out; int res_out_bytes; int32_t* acc_out;
+    int* err_flag;
+};
+
+constexpr int kWsThreads = 288;
+constexpr int kWsMaxEnt = 8;          // (positions per expander thread) x planes
+
+__host__ __device__ inline int ws_stages(int stride) { return stride == 2 ? 2 : 3; }
+__host__ __device__ inline size_t ws_stage_bytes(int stride, int npos) {
+    return (size_t)(stride == 2 ? 4 : 1) * 4 * npos * 16;
+}
+__host__ __device__ inline size_t ws_smem_bytes(int stride, int npos, int C, int RS, int nt) {
+    return ws_stages(stride) * ws_stage_bytes(stride, npos) + (size_t)RS * C * nt + nt * 4 +
+           RS * 4 + 16 * 8 + 64;
+}
+
+// filter bits [O][R*S][Cw] -> int8 blocks in the order the kernel keeps them in shared memory
+__device__ __forceinline__ void prepare_filter_ws(const uint32_t* fbits, int O, int RS, int C,
+                                                  int nt, uint4* out) {
+    const int Cw = C >> 5, ncb = C >> 6;
+    const long long total = (long long)O * RS * (C >> 4);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int n = (int)(i % nt);
+        long long r = i / nt;
+        const int c4 = (int)(r & 3); r >>= 2;
+        const int tap = (int)(r % RS); r /= RS;
+        const int cb = (int)(r % ncb);
+        const int tile = (int)(r / ncb);
+        const int o = tile * nt + n;
+        const uint32_t w = fbits[((size_t)o * RS + tap) * Cw + cb * 2 + (c4 >> 1)];
+        out[i] = expand16((c4 & 1) ? (w & 0xFFFFu) : (w >> 16));
+    }
+}
+
+struct WsWait {
+    volatile int* abort;
+    int* err;
+    __device__ __forceinline__ bool operator()(uint32_t bar, uint32_t parity) const {
+        for (int i = 0; i < (1 << 24); i++) {
+            if (mbar_try_wait(bar, parity)) return true;
+            if ((i & 1023) == 1023 && *abort) return false;
+        }
+        *abort = 1;
+        atomicExch(err, 1);
+        return false;
+    }
+};
+
+template <int NT, int STRIDE>
+__device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
+    constexpr int NSTAGE = STRIDE == 2 ? 2 : 3;
+    constexpr int NPLANE = STRIDE == 2 ? 4 : 1;
+    constexpr uint32_t TM_COLS = 2 * NT < 32 ? 32 : 2 * NT;
+    constexpr int NB = NT / 32;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int RS = a.R * a.S, NCB = a.C >> 6;
+    const uint32_t plane_bytes = 4u * a.NPOS * 16u, stage_bytes = NPLANE * plane_bytes;
+
+    unsigned char* sAraw = smem;
+    uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
+    float* sThr = reinterpret_cast<float*>(sB + (size_t)RS * (a.C >> 4) * NT);
+    int* sTap = reinterpret_cast<int*>(sThr + NT);
+    uint64_t* sBar = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(sTap + RS) + 7) & ~(uintptr_t)7);
+    // barriers: a_full[NSTAGE], a_empty[NSTAGE], acc_full[2], acc_empty[2]
+    uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 2 * NSTAGE + 4);
+    volatile int* sAbort = reinterpret_cast<volatile int*>(sTmem + 1);
+    const uint32_t bar0 = smem_u32(sBar);
+    auto BAR_AFULL = [&](int s) { return bar0 + 8u * s; };
+    auto BAR_AEMPTY = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
+    auto BAR_CFULL = [&](int b) { return bar0 + 8u * (2 * NSTAGE + b); };
+    auto BAR_CEMPTY = [&](int b) { return bar0 + 8u * (2 * NSTAGE + 2 + b); };
+
+    // this CTA's n-tile and m-tile sequence
+    const int nt = blockIdx.x % a.ntiles_n;
+    const int mfirst = blockIdx.x / a.ntiles_n, mstep = gridDim.x / a.ntiles_n;
+    const long long mtiles = (a.NV + 127) / 128;
+    const int obase = nt * NT;
+
+    // ---- one-time setup -------------------------------------------------------------------
+    if (tid == 0) {
+        for (int s = 0; s < NSTAGE; s++) { mbar_init(BAR_AFULL(s), 128); mbar_init(BAR_AEMPTY(s), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), 128); }
+        *sAbort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) tmem_alloc(smem_u32(sTmem), TM_COLS);
+    {
+        const uint4* src = a.wi8 + (size_t)nt * RS * (a.C >> 4) * NT;
+        const int nB = RS * (a.C >> 4) * NT;
+        for (int i = tid; i < nB; i += kWsThreads) sB[i] = __ldg(src + i);
+        for (int i = tid; i < NT; i += kWsThreads) sThr[i] = obase + i < a.O ? __ldg(a.thr + obase + i) : 0.0f;
+        for (int t = tid; t < RS; t += kWsThreads) {
+            const int r = t / a.S, s = t % a.S;
+            int plane = 0, off;
+            if (STRIDE == 2) {
+                const int ty = r - a.pad_h, tx = s - a.pad_w;
+                const int py = ty & 1, px = tx & 1;
+                const int dy = (ty - py) / 2, dx = (tx - px) / 2;
+                plane = py * 2 + px;
+                off = (dy + a.back_y) * a.PW + (dx + a.back_x);
+            } else {
+                off = r * a.PW + s;
+            }
+            sTap[t] = (plane << 24) | off;
+        }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *sTmem;
+    const WsWait wait{sAbort, a.err_flag};
+
+    if (warp >= 4 && warp < 8) {
+        // =============================== expanders ==========================================
+        const int et = tid - 128;
+        const int Cw = a.C >> 5;
+        const int nq = (a.NPOS + 127) >> 7;                 // positions per thread
+        const int nent = nq * NPLANE;
+        int ptr[kWsMaxEnt];                                 // word offset of the pixel, -1 = zeros
+        uint2 cur[kWsMaxEnt], nxt[kWsMaxEnt];
+        auto map_tile = [&](long long m) {
+            const long long q0 = m * 128 - ((long long)a.back_y * a.PW + a.back_x);
+#pragma unroll
+            for (int j = 0; j < kWsMaxEnt; j++) {
+                ptr[j] = -1;
+                if (j >= nent) continue;
+                const int qi = j / NPLANE, pl = j % NPLANE;
+                const int q = et + qi * 128;
+                const long long gq = q0 + q;
+                if (q < a.NPOS && gq >= 0 && gq < a.NV) {
+                    const long long vy = gq / a.PW;
+                    const int vx = (int)(gq - vy * a.PW);
+                    const int n = (int)(vy / a.VH);
+                    const int vr = (int)(vy - (long long)n * a.VH);
+                    const int iy = STRIDE == 2 ? 2 * vr + (pl >> 1) : vr;
+                    const int ix = STRIDE == 2 ? 2 * vx + (pl & 1) : vx;
+                    if (vr < a.OHg && vx < a.OWg && iy < a.H && ix < a.W)
+                        ptr[j] = (int)((((long long)n * a.H + iy) * a.W + ix) * Cw);
+                }
+            }
+        };
+        auto load = [&](uint2 (&dst)[kWsMaxEnt], int cb) {
+#pragma unroll
+            for (int j = 0; j < kWsMaxEnt; j++)
+                dst[j] = (j < nent && ptr[j] >= 0) ? ldg64(a.in + ptr[j] + cb * 2) : make_uint2(0u, 0u);
+        };
+        uint32_t it = 0;
+        long long m = mfirst;
+        if (m < mtiles) { map_tile(m); load(cur, 0); }
+        bool ok = true;
+        while (m < mtiles && ok) {
+            for (int cb = 0; cb < NCB && ok; cb++, it++) {
+                // prefetch the next stage's bits before touching shared memory
+                int pv[kWsMaxEnt];
+#pragma unroll
+                for (int j = 0; j < kWsMaxEnt; j++) pv[j] = ptr[j];
+                const bool last = cb + 1 == NCB;
+                const long long mn = m + mstep;
+                if (!last) load(nxt, cb + 1);
+                else if (mn < mtiles) { map_tile(mn); load(nxt, 0); }
+                const int s = it % NSTAGE;
+                ok = wait(BAR_AEMPTY(s), ((it / NSTAGE) & 1) ^ 1);
+                if (!ok) break;
+                uint4* stage = reinterpret_cast<uint4*>(sAraw + (size_t)s * stage_bytes);
+#pragma unroll
+                for (int j = 0; j < kWsMaxEnt; j++) {
+                    if (j >= nent) continue;
+                    const int qi = j / NPLANE, pl = j % NPLANE;
+                    const int q = et + qi * 128;
+                    if (q >= a.NPOS) continue;
+                    uint4* dst = stage + (size_t)pl * 4 * a.NPOS + q;
+                    if (pv[j] >= 0) {
+                        dst[0] = expand16(cur[j].x >> 16);
+                        dst[(size_t)a.NPOS] = expand16(cur[j].x & 0xFFFFu);
+                        dst[(size_t)2 * a.NPOS] = expand16(cur[j].y >> 16);
+                        dst[(size_t)3 * a.NPOS] = expand16(cur[j].y & 0xFFFFu);
+                    } else {
+                        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                        dst[0] = z; dst[(size_t)a.NPOS] = z;
+                        dst[(size_t)2 * a.NPOS] = z; dst[(size_t)3 * a.NPOS] = z;
+                    }
+                }
+                fence_proxy_async();
+                mbar_arrive(BAR_AFULL(s));
+#pragma unroll
+                for (int j = 0; j < kWsMaxEnt; j++) cur[j] = nxt[j];
+            }
+            m += mstep;
+        }
+    } else if (warp == 8) {
+        // =============================== MMA issuer =========================================
+        if (lane == 0) {
+            const uint32_t aBase = smem_u32(sAraw), bBase = smem_u32(sB);
+            const uint32_t lboA = (uint32_t)a.NPOS * 16u, lboB = NT * 16u;
+            uint32_t it = 0, tc = 0;
+            bool ok = true;
+            for (long long m = mfirst; m < mtiles && ok; m += mstep, tc++) {
+                const int b = tc & 1;
+                ok = wait(BAR_CEMPTY(b), ((tc >> 1) & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem + b * NT;
+                uint32_t acc = 0;
+                for (int cb = 0; cb < NCB && ok; cb++, it++) {
+                    const int s = it % NSTAGE;
+                    ok = wait(BAR_AFULL(s), (it / NSTAGE) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t stage = aBase + s * stage_bytes;
+                    for (int t = 0; t < RS; t++) {
+                        const int e = sTap[t];
+                        const uint32_t ta = stage + (uint32_t)(e >> 24) * plane_bytes + (uint32_t)(e & 0xFFFFFF) * 16u;
+                        const uint32_t tb = bBase + (uint32_t)((cb * RS + t) * 4) * lboB;
+#pragma unroll
+                        for (int ks = 0; ks < 2; ks++) {
+                            mma_i8(d, smem_desc(ta + 2 * ks * lboA, lboA, 128u),
+                                   smem_desc(tb + 2 * ks * lboB, lboB, 128u), idesc_i8(NT), acc);
+                            acc = 1;
+                        }
+                    }
+                    mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
+                }
+                if (ok) mma_commit(BAR_CFULL(b));       // accumulator complete
+            }
+        }
+        __syncwarp();
+    } else {
+        // =============================== epilogue ===========================================
+        const int Ow = (a.O + 31) >> 5;
+        const int lim = a.res_in ? min(a.residual_channels, a.res_in_ch) : 0;
+        uint32_t tc = 0;
+        bool ok = true;
+        for (long long m = mfirst; m < mtiles && ok; m += mstep, tc++) {
+            const int b = tc & 1;
+            const long long p = m * 128 + tid;
+            bool live = false;
+            int n = 0, y = 0, x = 0;
+            if (p < a.NV) {
+                const long long vy = p / a.PW;
+                x = (int)(p - vy * a.PW);
+                n = (int)(vy / a.VH);
+                y = (int)(vy - (long long)n * a.VH);
+                live = x < a.OWg && y < a.OHg;
+            }
+            const size_t opix = ((size_t)n * a.OHg + y) * a.OWg + x;
+            // residual of one 32-channel group, widened to int32 (zeros where not injected)
+            auto load_res = [&](int (&r)[32], int nb) {
+                const int o0 = obase + nb * 32;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    int4 v = make_int4(0, 0, 0, 0);
+                    const int o = o0 + 4 * j;
+                    if (live && o < lim) {
+                        if (a.residual_pool) {          // kernel.cuh:773-783
+                            const size_t b00 = (((size_t)n * 2 * a.OHg + 2 * y) * 2 * a.OWg + 2 * x) *
+                                               a.res_in_ch + o;
+                            const size_t rowp = (size_t)2 * a.OWg * a.res_in_ch;
+                            v = max4(max4(ld_res4(a.res_in, a.res_in_bytes, b00),
+                                          ld_res4(a.res_in, a.res_in_bytes, b00 + a.res_in_ch)),
+                                     max4(ld_res4(a.res_in, a.res_in_bytes, b00 + rowp),
+                                          ld_res4(a.res_in, a.res_in_bytes, b00 + rowp + a.res_in_ch)));
+                        } else {
+                            v = ld_res4(a.res_in, a.res_in_bytes, opix * a.res_in_ch + o);
+                        }
+                    }
+                    r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+                }
+            };
+            int rcur[32], rnext[32];
+            if (a.res_in) load_res(rcur, 0);              // in flight while the MMAs run
+            ok = wait(BAR_CFULL(b), (tc >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t words[NB];
+            bool overflow = false;
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++) {
+                if (a.res_in && nb + 1 < NB) load_res(rnext, nb + 1);
+                int v[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + b * NT + nb * 32, v);
+                tmem_ld_wait();
+                if (nb == NB - 1) {                       // accumulator drained: hand it back
+                    tc_fence_before();
+                    mbar_arrive(BAR_CEMPTY(b));
+                }
+                const int o0 = obase + nb * 32;
+                if (live && a.acc_out) {
+                    int4* dst = reinterpret_cast<int4*>(a.acc_out + opix * a.O + o0);
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+                if (a.res_in) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] += rcur[j];
+                }
+                uint32_t word = 0;
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (!((float)v[j] < sThr[nb * 32 + j])) word |= 0x80000000u >> j;
+                words[nb] = word;
+                if (a.res_out && live) {
+                    const size_t idx = opix * a.O + o0;
+                    if (a.res_out_bytes == 2) {
+                        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<short*>(a.res_out) + idx);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const int lo = v[8 * j + 2 * k], hi = v[8 * j + 2 * k + 1];
+                                overflow |= max(abs(lo), abs(hi)) > 32767;
+                                w[k] = ((uint32_t)lo & 0xFFFFu) | ((uint32_t)hi << 16);
+                            }
+                            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                        int4* dst = reinterpret_cast<int4*>(reinterpret_cast<int*>(a.res_out) + idx);
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
+                }
+                if (a.res_in && nb + 1 < NB) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) rcur[j] = rnext[j];
+                }
+            }
+            if (live) {
+                uint32_t* dst = a.out + (size_t)n * a.out_image_stride +
+                                ((size_t)y * a.OWg + x) * Ow + (obase >> 5);
+#pragma unroll
+                for (int nb = 0; nb < NB; nb++) dst[nb] = words[nb];
+            }
+            if (overflow) atomicExch(a.err_flag, 2);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) tmem_dealloc(tmem, TM_COLS);
+}
+
+}  // namespace umma
+}  // namespace tcbnn

@@ -3,6 +3,7 @@
 #include "../../include/tcbnn_b200.h"
 #include "bnn_layers.cuh"
 #include "bconv_umma.cuh"
+#include "bconv_umma_ws.cuh"
 #include "inconv_tiled.cuh"
 #include <cstdio>
 #include <cstdarg>
@@ -143,8 +144,9 @@ struct PreparedLayout {
     int KP;               // 64-bit pairs per filter row, multiple of 4
     size_t off_wq, off_ktab, off_pwt, off_pwtot, off_err, off_wi8, bytes;
     int umma_nt;          // n-tile of the tcgen05 path, 0 when the layer is not eligible
-    int umma_npos;        // raster positions of the shared-memory patch
+    int umma_npos;        // raster positions of the shared-memory patch (per plane)
     size_t umma_smem;     // dynamic shared memory of the tcgen05 kernel
+    int umma_pw, umma_vh, umma_back_y, umma_back_x;   // raster geometry
 };
 
 int conv_check(const tcbnn_conv_desc* d, bool binary) {
@@ -177,21 +179,34 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     L.off_pwt = o;   o += (size_t)d->R * d->S * d->O * 4; o = (o + 255) & ~(size_t)255;
     L.off_pwtot = o; o += (size_t)d->O * 4;             o = (o + 255) & ~(size_t)255;
     L.off_err = o;   o += 256;
-    // tcgen05 path: stride 1, "same" padding, no pooling, filter block resident in shared memory
+    // tcgen05 path: stride 1 or 2, "same" padding, no pooling, channels in blocks of 64,
+    // filter block of one n-tile resident in shared memory
     L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o;
-    if (d->stride_h == 1 && d->stride_w == 1 && d->pool == 1 && d->padding &&
-        (d->C == 64 || d->C == 128 || d->C == 256 || d->C == 512) && d->R == d->S && (d->R & 1)) {
-        // widest n-tile whose filter block (R*S*C*nt bytes) stays resident next to the patch
-        int nt = d->C <= 128 ? 128 : d->C == 256 ? 64 : 32;
-        while (nt > 32 && d->O % nt) nt >>= 1;
-        const int PW = d->W + d->pad_w;
-        const int npos = (128 + (d->R - 1) * PW + (d->S - 1) + 7) & ~7;
-        const size_t a_bytes = (size_t)(d->C / 16) * npos * 16, r_bytes = (size_t)128 * (nt + 4) * 4;
-        const size_t smem = (a_bytes > r_bytes ? a_bytes : r_bytes) +
-                            (size_t)d->R * d->S * d->C * nt + nt * 4 + 128 * 4 + 64;
-        if (d->O % nt == 0 && smem <= 227 * 1024 && npos * 16 < (1 << 18)) {
-            L.umma_nt = nt; L.umma_npos = npos; L.umma_smem = smem;
-            o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
+    L.umma_pw = L.umma_vh = L.umma_back_y = L.umma_back_x = 0;
+    if (d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) && d->pool == 1 &&
+        d->padding && d->C % 64 == 0 && d->O % 32 == 0) {
+        const int st = d->stride_h;
+        // tap (r,s) reads raster offset (dy,dx) of a plane; extremes over the taps
+        const int back_y = st == 2 ? (d->pad_h + 1) / 2 : d->pad_h;
+        const int back_x = st == 2 ? (d->pad_w + 1) / 2 : d->pad_w;
+        const int fwd_y = st == 2 ? (d->R - 1 - d->pad_h >= 0 ? (d->R - 1 - d->pad_h) / 2 : 0)
+                                  : d->R - 1 - d->pad_h;
+        const int fwd_x = st == 2 ? (d->S - 1 - d->pad_w >= 0 ? (d->S - 1 - d->pad_w) / 2 : 0)
+                                  : d->S - 1 - d->pad_w;
+        const int PW = d->OW + (back_x > fwd_x ? back_x : fwd_x);
+        const int VH = d->OH + (back_y > fwd_y ? back_y : fwd_y);
+        const int npos = (128 + (back_y + fwd_y) * PW + back_x + fwd_x + 7) & ~7;
+        const int max_npos = st == 2 ? 256 : 512;
+        if (fwd_y >= 0 && fwd_x >= 0 && npos <= max_npos && npos * 16 < (1 << 18)) {
+            for (int nt = 128; nt >= 32; nt >>= 1) {
+                if (d->O % nt) continue;
+                const size_t smem = umma::ws_smem_bytes(st, npos, d->C, d->R * d->S, nt);
+                if (smem > 227 * 1024) continue;
+                L.umma_nt = nt; L.umma_npos = npos; L.umma_smem = smem;
+                L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
+                o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
+                break;
+            }
         }
     }
     L.bytes = o;
@@ -227,35 +242,32 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
 
 int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible)
 
-template <int C, int NT>
-__global__ void __launch_bounds__(128) k_conv_umma(umma::ConvUmmaArgs a) {
+template <int NT, int STRIDE>
+__global__ void __launch_bounds__(umma::kWsThreads, 1) k_conv_umma_ws(umma::ConvWsArgs a) {
     extern __shared__ __align__(128) unsigned char dyn_smem[];
-    umma::conv_umma_cta<C, NT>(a, dyn_smem);
+    umma::conv_umma_ws_cta<NT, STRIDE>(a, dyn_smem);
 }
-__global__ void k_prepare_filter_i8(const uint32_t* fbits, int O, int RS, int C, int nt, uint4* out) {
-    umma::prepare_filter_i8(fbits, O, RS, C, nt, out);
+__global__ void k_prepare_filter_ws(const uint32_t* fbits, int O, int RS, int C, int nt, uint4* out) {
+    umma::prepare_filter_ws(fbits, O, RS, C, nt, out);
 }
 
-template <int C, int NT>
-int launch_conv_umma(const umma::ConvUmmaArgs& a, size_t smem, int sms, cudaStream_t st) {
+template <int NT, int STRIDE>
+int launch_conv_umma_ws(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_conv_umma<C, NT>,
+        cudaError_t e = cudaFuncSetAttribute(k_conv_umma_ws<NT, STRIDE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         configured[dev] = true;
     }
-    int per_sm = (int)((227 * 1024) / (smem + 1024));
-    const int tm_cols = NT < 32 ? 32 : NT;
-    if (per_sm > 512 / tm_cols) per_sm = 512 / tm_cols;
-    if (per_sm > 8) per_sm = 8;
-    if (per_sm < 1) per_sm = 1;
-    const long long tasks = ((a.NV + 127) / 128) * ((a.O + NT - 1) / NT);
-    long long grid = (long long)sms * per_sm;
-    if (grid > tasks) grid = tasks;
-    k_conv_umma<C, NT><<<(int)grid, 128, smem, st>>>(a);
+    a.ntiles_n = a.O / NT;
+    if (a.ntiles_n > sms) return fail("conv_layer: more n-tiles than SMs");
+    const long long mtiles = (a.NV + 127) / 128;
+    long long per = sms / a.ntiles_n;                 // CTAs per n-tile
+    if (per > mtiles) per = mtiles;
+    k_conv_umma_ws<NT, STRIDE><<<(int)(per * a.ntiles_n), umma::kWsThreads, smem, st>>>(a);
     return launch_check("conv_layer (tcgen05)");
 }
 
@@ -441,7 +453,7 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
     CUDA_TRY(cudaMemsetAsync(p + L.off_err, 0, 256, (cudaStream_t)stream));
     if (L.umma_nt) {
         const long long units = (long long)d->O * d->R * d->S * (d->C / 16);
-        k_prepare_filter_i8<<<elementwise_grid(units, sms), 256, 0, (cudaStream_t)stream>>>(
+        k_prepare_filter_ws<<<elementwise_grid(units, sms), 256, 0, (cudaStream_t)stream>>>(
             filter_bits, d->O, d->R * d->S, d->C, L.umma_nt, (uint4*)(p + L.off_wi8));
         if (launch_check("conv_prepare (int8 filter)")) return 1;
     }
@@ -469,11 +481,13 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
                                         ((uintptr_t)res_in & 15) == 0);
     if (g_conv_path == 2 && !res_vec_ok) return fail("conv_layer: residual layout not eligible for the tcgen05 path");
     if (L.umma_nt && g_conv_path != 1 && res_vec_ok && (!res_out || ((uintptr_t)res_out & 15) == 0)) {
-        umma::ConvUmmaArgs a;
+        umma::ConvWsArgs a;
         a.in = in; a.wi8 = (const uint4*)(p + L.off_wi8); a.thr = thr;
         a.B = d->B; a.H = d->H; a.W = d->W; a.C = d->C; a.O = d->O; a.R = d->R; a.S = d->S;
-        a.pad_h = d->pad_h; a.pad_w = d->pad_w;
-        a.PW = d->W + d->pad_w; a.VH = d->H + d->pad_h; a.NPOS = L.umma_npos;
+        a.pad_h = d->pad_h; a.pad_w = d->pad_w; a.stride = d->stride_h;
+        a.OHg = d->OH; a.OWg = d->OW;
+        a.PW = L.umma_pw; a.VH = L.umma_vh; a.NPOS = L.umma_npos;
+        a.back_y = L.umma_back_y; a.back_x = L.umma_back_x;
         a.NV = (long long)d->B * a.VH * a.PW;
         a.res_in = res_in; a.res_in_bytes = res_in_bytes; a.res_in_ch = res_in_ch;
         a.residual_channels = residual_channels; a.residual_pool = residual_pool;
@@ -483,14 +497,12 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
         int sms;
         if (sm_count(&sms)) return 1;
         cudaStream_t st = (cudaStream_t)stream;
-#define TCBNN_UMMA_CASE(CC, NN) \
-        if (d->C == CC && L.umma_nt == NN) return launch_conv_umma<CC, NN>(a, L.umma_smem, sms, st);
-        TCBNN_UMMA_CASE(64, 32) TCBNN_UMMA_CASE(64, 64) TCBNN_UMMA_CASE(64, 128)
-        TCBNN_UMMA_CASE(128, 32) TCBNN_UMMA_CASE(128, 64) TCBNN_UMMA_CASE(128, 128)
-        TCBNN_UMMA_CASE(256, 32) TCBNN_UMMA_CASE(256, 64)
-        TCBNN_UMMA_CASE(512, 32)
-#undef TCBNN_UMMA_CASE
-        return fail("conv_layer: no tcgen05 instance for C=%d n-tile=%d", d->C, L.umma_nt);
+#define TCBNN_WS_CASE(NN, SS) \
+        if (L.umma_nt == NN && d->stride_h == SS) return launch_conv_umma_ws<NN, SS>(a, L.umma_smem, sms, st);
+        TCBNN_WS_CASE(32, 1) TCBNN_WS_CASE(64, 1) TCBNN_WS_CASE(128, 1)
+        TCBNN_WS_CASE(32, 2) TCBNN_WS_CASE(64, 2) TCBNN_WS_CASE(128, 2)
+#undef TCBNN_WS_CASE
+        return fail("conv_layer: no tcgen05 instance for n-tile=%d stride=%d", L.umma_nt, d->stride_h);
     }
     ConvArgs c;
     c.in = in;

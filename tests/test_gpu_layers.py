@@ -195,7 +195,12 @@ def test_bad_arguments_are_rejected(cuda):
 
 
 UMMA_CASES = [
-    # B, H, W, C, O, R, residual   (stride 1, "same" padding, no pooling: tcgen05-eligible)
+    # B, H, W, C, O, R, residual[, stride]   ("same" padding, no pooling: tcgen05-eligible)
+    (2, 8, 8, 64, 128, 3, None, 2),
+    (3, 14, 14, 128, 256, 3, None, 2),
+    (2, 7, 9, 64, 64, 3, None, 2),           # odd sizes under stride 2
+    (9, 14, 14, 256, 512, 3, None, 2),
+    (300, 7, 7, 512, 64, 3, None),           # 8 channel blocks per tile, many tiles per CTA
     (1, 4, 4, 64, 64, 3, None),
     (2, 6, 6, 64, 64, 3, "plain"),
     (2, 4, 4, 64, 128, 3, "pool"),
@@ -215,7 +220,8 @@ UMMA_CASES = [
 @pytest.mark.parametrize("case", UMMA_CASES)
 def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
     """Both conv kernels (tcgen05 int8 implicit GEMM, warp-level b1 MMA) against the oracle."""
-    B, H, W, C, O, R, resmode = case
+    B, H, W, C, O, R, resmode = case[:7]
+    st = case[7] if len(case) > 7 else 1
     g = util.rng(sum(case[:6]))
     Cw = C // 32
     x = util.rand_words(g, (B, H, W, Cw))
@@ -228,10 +234,10 @@ def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
     elif resmode == "pool":
         res_in = g.integers(-300, 300, size=(B, 2 * H, 2 * W, O // 2)).astype(np.int32)
         rc, rpool = O // 2, True
-    eo, er, ea = orc.conv_layer(x, f, thr, C, R, R, 1, 1, True, 1, res_in=res_in,
+    eo, er, ea = orc.conv_layer(x, f, thr, C, R, R, st, st, True, 1, res_in=res_in,
                                 residual_channels=rc, residual_pool=rpool,
                                 save_residual=True, want_acc=True)
-    d = ops.conv_desc(B, H, W, C, O, R, R)
+    d = ops.conv_desc(B, H, W, C, O, R, R, st, st)
     prep = ops.conv_prepare(d, dev(f, cuda))
     try:
         for path in (2, 1):
@@ -258,11 +264,11 @@ def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
 
 def test_tcgen05_path_refuses_ineligible_layer(cuda):
     from tcbnn_b200.lib import TcbnnError
-    d = ops.conv_desc(1, 8, 8, 192, 256, 3, 3)          # channel count without a tcgen05 instance
-    f = torch.zeros((256, 9, 6), dtype=torch.int32, device=cuda)
+    d = ops.conv_desc(1, 8, 8, 64, 64, 3, 3, pool=2)    # pooled layers stay on the b1 MMA kernel
+    f = torch.zeros((64, 9, 2), dtype=torch.int32, device=cuda)
     prep = ops.conv_prepare(d, f)
-    x = torch.zeros((1, 8, 8, 6), dtype=torch.int32, device=cuda)
-    thr = torch.zeros((256,), device=cuda)
+    x = torch.zeros((1, 8, 8, 2), dtype=torch.int32, device=cuda)
+    thr = torch.zeros((64,), device=cuda)
     try:
         ops.set_conv_path(2)
         with pytest.raises(TcbnnError):
