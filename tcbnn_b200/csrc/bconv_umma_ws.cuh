@@ -4,12 +4,13 @@
 // bits -> +-1 bytes in the no-swizzle K-major core-matrix layout, taps as start-address offsets,
 // int8 x int8 -> int32 in tensor memory.  What changes is the schedule.  One CTA per SM runs
 //
-//   warps 0-3  epilogue   : prefetch the residual rows, wait for an accumulator, tcgen05.ld,
-//                           add / threshold / pack, store bits and the new residual
-//   warps 4-7  expanders  : packed input bits (prefetched one stage ahead in registers) ->
-//                           +-1 bytes of one 64-channel block of the patch, ring of stages
-//   warp  8    MMA issuer : one lane issues 9 taps x 2 k-steps per stage, commits the stage
-//                           back to the expanders and the finished tile to the epilogue
+//   warps 0-7   epilogue   : prefetch the residual rows, wait for an accumulator, tcgen05.ld,
+//                            add / threshold / pack, store bits and the new residual
+//                            (warp w reads TMEM lanes 32*(w%4).., column groups of parity w/4)
+//   warps 8-15  expanders  : packed input bits (prefetched two stages ahead in registers) ->
+//                            +-1 bytes of one 64-channel block of the patch, ring of stages
+//   warp  16    MMA issuer : one lane issues 9 taps x 2 k-steps per stage, commits the stage
+//                            back to the expanders and the finished tile to the epilogue
 //
 // with mbarriers between them, two accumulators in tensor memory (epilogue of tile i overlaps
 // the MMAs of tile i+1) and the filter block of the CTA's n-tile resident in shared memory.
@@ -43,8 +44,10 @@ struct ConvWsArgs {
     int* err_flag;
 };
 
-constexpr int kWsThreads = 288;
-constexpr int kWsMaxEnt = 8;          // (positions per expander thread) x planes
+constexpr int kWsEpiThreads = 256;
+constexpr int kWsExpThreads = 256;
+constexpr int kWsThreads = kWsEpiThreads + kWsExpThreads + 32;
+constexpr int kWsMaxEnt = 4;          // (positions per expander thread) x planes
 
 __host__ __device__ inline int ws_stages(int stride) { return stride == 2 ? 2 : 3; }
 __host__ __device__ inline size_t ws_stage_bytes(int stride, int npos) {
@@ -93,15 +96,18 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
     constexpr int NSTAGE = STRIDE == 2 ? 2 : 3;
     constexpr int NPLANE = STRIDE == 2 ? 4 : 1;
     constexpr uint32_t TM_COLS = 2 * NT < 32 ? 32 : 2 * NT;
-    constexpr int NB = NT / 32;
+    constexpr int NB = NT / 32;                       // 32-column groups per accumulator
+    constexpr int EPI_GROUPS = NB >= 2 ? 2 : 1;       // epilogue warp groups with work
+    constexpr int NB_PER = NB / EPI_GROUPS;
+    constexpr int MMA_WARP = (kWsEpiThreads + kWsExpThreads) / 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int RS = a.R * a.S, NCB = a.C >> 6;
     const uint32_t plane_bytes = 4u * a.NPOS * 16u, stage_bytes = NPLANE * plane_bytes;
 
     unsigned char* sAraw = smem;
     uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
-    float* sThr = reinterpret_cast<float*>(sB + (size_t)RS * (a.C >> 4) * NT);
-    int* sTap = reinterpret_cast<int*>(sThr + NT);
+    int* sThr = reinterpret_cast<int*>(sB + (size_t)RS * (a.C >> 4) * NT);
+    int* sTap = sThr + NT;
     uint64_t* sBar = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(sTap + RS) + 7) & ~(uintptr_t)7);
     // barriers: a_full[NSTAGE], a_empty[NSTAGE], acc_full[2], acc_empty[2]
     uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 2 * NSTAGE + 4);
@@ -112,25 +118,35 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
     auto BAR_CFULL = [&](int b) { return bar0 + 8u * (2 * NSTAGE + b); };
     auto BAR_CEMPTY = [&](int b) { return bar0 + 8u * (2 * NSTAGE + 2 + b); };
 
-    // this CTA's n-tile and m-tile sequence
+    // this CTA's n-tile and m-tile sequence (all raster arithmetic fits 32 bits: host checks)
     const int nt = blockIdx.x % a.ntiles_n;
     const int mfirst = blockIdx.x / a.ntiles_n, mstep = gridDim.x / a.ntiles_n;
-    const long long mtiles = (a.NV + 127) / 128;
+    const int NV = (int)a.NV;
+    const int mtiles = (NV + 127) / 128;
     const int obase = nt * NT;
 
     // ---- one-time setup -------------------------------------------------------------------
     if (tid == 0) {
-        for (int s = 0; s < NSTAGE; s++) { mbar_init(BAR_AFULL(s), 128); mbar_init(BAR_AEMPTY(s), 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), 128); }
+        for (int s = 0; s < NSTAGE; s++) { mbar_init(BAR_AFULL(s), kWsExpThreads); mbar_init(BAR_AEMPTY(s), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), 128 * EPI_GROUPS); }
         *sAbort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) tmem_alloc(smem_u32(sTmem), TM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(smem_u32(sTmem), TM_COLS);
     {
         const uint4* src = a.wi8 + (size_t)nt * RS * (a.C >> 4) * NT;
         const int nB = RS * (a.C >> 4) * NT;
         for (int i = tid; i < nB; i += kWsThreads) sB[i] = __ldg(src + i);
-        for (int i = tid; i < NT; i += kWsThreads) sThr[i] = obase + i < a.O ? __ldg(a.thr + obase + i) : 0.0f;
+        for (int i = tid; i < NT; i += kWsThreads) {
+            // integer form of  !((float)v < thr)  (kernel.cuh:795-796): v >= ceil(thr);
+            // NaN never compares less, so the bit is always set
+            int it = INT_MIN;
+            if (obase + i < a.O) {
+                const float t = __ldg(a.thr + obase + i);
+                if (t == t) it = t >= 2147483520.0f ? INT_MAX : t <= -2147483648.0f ? INT_MIN : (int)ceilf(t);
+            }
+            sThr[i] = it;
+        }
         for (int t = tid; t < RS; t += kWsThreads) {
             const int r = t / a.S, s = t % a.S;
             int plane = 0, off;
@@ -153,54 +169,67 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
     const uint32_t tmem = *sTmem;
     const WsWait wait{sAbort, a.err_flag};
 
-    if (warp >= 4 && warp < 8) {
+    if (tid >= kWsEpiThreads && tid < kWsEpiThreads + kWsExpThreads) {
         // =============================== expanders ==========================================
-        const int et = tid - 128;
+        const int et = tid - kWsEpiThreads;
         const int Cw = a.C >> 5;
-        const int nq = (a.NPOS + 127) >> 7;                 // positions per thread
+        const int nq = (a.NPOS + kWsExpThreads - 1) / kWsExpThreads;      // positions per thread
         const int nent = nq * NPLANE;
-        int ptr[kWsMaxEnt];                                 // word offset of the pixel, -1 = zeros
-        uint2 cur[kWsMaxEnt], nxt[kWsMaxEnt];
-        auto map_tile = [&](long long m) {
-            const long long q0 = m * 128 - ((long long)a.back_y * a.PW + a.back_x);
+        // The loader runs two stages ahead of the expander; a stage's bits travel through a
+        // three-deep register queue together with a per-entry "pixel exists" mask.
+        int ptr[kWsMaxEnt];                                 // loader: word offset of the pixel
+        uint32_t pmask = 0;
+        uint2 q0[kWsMaxEnt], q1[kWsMaxEnt], q2[kWsMaxEnt];
+        uint32_t m0 = 0, m1 = 0, m2 = 0;
+        auto map_tile = [&](int m) {
+            const int base = m * 128 - (a.back_y * a.PW + a.back_x);
+            pmask = 0;
 #pragma unroll
             for (int j = 0; j < kWsMaxEnt; j++) {
-                ptr[j] = -1;
+                ptr[j] = 0;
                 if (j >= nent) continue;
                 const int qi = j / NPLANE, pl = j % NPLANE;
-                const int q = et + qi * 128;
-                const long long gq = q0 + q;
-                if (q < a.NPOS && gq >= 0 && gq < a.NV) {
-                    const long long vy = gq / a.PW;
-                    const int vx = (int)(gq - vy * a.PW);
-                    const int n = (int)(vy / a.VH);
-                    const int vr = (int)(vy - (long long)n * a.VH);
+                const int q = et + qi * kWsExpThreads;
+                const int gq = base + q;
+                if (q < a.NPOS && gq >= 0 && gq < NV) {
+                    const int vy = gq / a.PW, vx = gq - vy * a.PW;
+                    const int n = vy / a.VH, vr = vy - n * a.VH;
                     const int iy = STRIDE == 2 ? 2 * vr + (pl >> 1) : vr;
                     const int ix = STRIDE == 2 ? 2 * vx + (pl & 1) : vx;
-                    if (vr < a.OHg && vx < a.OWg && iy < a.H && ix < a.W)
-                        ptr[j] = (int)((((long long)n * a.H + iy) * a.W + ix) * Cw);
+                    if (vr < a.OHg && vx < a.OWg && iy < a.H && ix < a.W) {
+                        ptr[j] = ((n * a.H + iy) * a.W + ix) * Cw;
+                        pmask |= 1u << j;
+                    }
                 }
             }
         };
-        auto load = [&](uint2 (&dst)[kWsMaxEnt], int cb) {
+        auto load = [&](uint2 (&dst)[kWsMaxEnt], uint32_t& dm, int cb) {
+            dm = pmask;
 #pragma unroll
             for (int j = 0; j < kWsMaxEnt; j++)
-                dst[j] = (j < nent && ptr[j] >= 0) ? ldg64(a.in + ptr[j] + cb * 2) : make_uint2(0u, 0u);
+                dst[j] = ((pmask >> j) & 1u) ? ldg64(a.in + ptr[j] + cb * 2) : make_uint2(0u, 0u);
         };
+        // loader position (lm, lcb) and its helper to advance by one stage
+        int lm = mfirst, lcb = 0;
+        bool lvalid = lm < mtiles;
+        if (lvalid) map_tile(lm);
+        auto load_next = [&](uint2 (&dst)[kWsMaxEnt], uint32_t& dm) {
+            if (!lvalid) { dm = 0; return; }
+            load(dst, dm, lcb);
+            if (++lcb == NCB) {
+                lcb = 0;
+                lm += mstep;
+                lvalid = lm < mtiles;
+                if (lvalid) map_tile(lm);
+            }
+        };
+        load_next(q0, m0);
+        load_next(q1, m1);
         uint32_t it = 0;
-        long long m = mfirst;
-        if (m < mtiles) { map_tile(m); load(cur, 0); }
         bool ok = true;
-        while (m < mtiles && ok) {
+        for (int m = mfirst; m < mtiles && ok; m += mstep) {
             for (int cb = 0; cb < NCB && ok; cb++, it++) {
-                // prefetch the next stage's bits before touching shared memory
-                int pv[kWsMaxEnt];
-#pragma unroll
-                for (int j = 0; j < kWsMaxEnt; j++) pv[j] = ptr[j];
-                const bool last = cb + 1 == NCB;
-                const long long mn = m + mstep;
-                if (!last) load(nxt, cb + 1);
-                else if (mn < mtiles) { map_tile(mn); load(nxt, 0); }
+                load_next(q2, m2);                          // two stages ahead
                 const int s = it % NSTAGE;
                 ok = wait(BAR_AEMPTY(s), ((it / NSTAGE) & 1) ^ 1);
                 if (!ok) break;
@@ -209,14 +238,14 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 for (int j = 0; j < kWsMaxEnt; j++) {
                     if (j >= nent) continue;
                     const int qi = j / NPLANE, pl = j % NPLANE;
-                    const int q = et + qi * 128;
+                    const int q = et + qi * kWsExpThreads;
                     if (q >= a.NPOS) continue;
                     uint4* dst = stage + (size_t)pl * 4 * a.NPOS + q;
-                    if (pv[j] >= 0) {
-                        dst[0] = expand16(cur[j].x >> 16);
-                        dst[(size_t)a.NPOS] = expand16(cur[j].x & 0xFFFFu);
-                        dst[(size_t)2 * a.NPOS] = expand16(cur[j].y >> 16);
-                        dst[(size_t)3 * a.NPOS] = expand16(cur[j].y & 0xFFFFu);
+                    if ((m0 >> j) & 1u) {
+                        dst[0] = expand16(q0[j].x >> 16);
+                        dst[(size_t)a.NPOS] = expand16(q0[j].x & 0xFFFFu);
+                        dst[(size_t)2 * a.NPOS] = expand16(q0[j].y >> 16);
+                        dst[(size_t)3 * a.NPOS] = expand16(q0[j].y & 0xFFFFu);
                     } else {
                         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
                         dst[0] = z; dst[(size_t)a.NPOS] = z;
@@ -226,18 +255,18 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 fence_proxy_async();
                 mbar_arrive(BAR_AFULL(s));
 #pragma unroll
-                for (int j = 0; j < kWsMaxEnt; j++) cur[j] = nxt[j];
+                for (int j = 0; j < kWsMaxEnt; j++) { q0[j] = q1[j]; q1[j] = q2[j]; }
+                m0 = m1; m1 = m2;
             }
-            m += mstep;
         }
-    } else if (warp == 8) {
+    } else if (warp == MMA_WARP) {
         // =============================== MMA issuer =========================================
         if (lane == 0) {
             const uint32_t aBase = smem_u32(sAraw), bBase = smem_u32(sB);
             const uint32_t lboA = (uint32_t)a.NPOS * 16u, lboB = NT * 16u;
             uint32_t it = 0, tc = 0;
             bool ok = true;
-            for (long long m = mfirst; m < mtiles && ok; m += mstep, tc++) {
+            for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
                 const int b = tc & 1;
                 ok = wait(BAR_CEMPTY(b), ((tc >> 1) & 1) ^ 1);
                 if (!ok) break;
@@ -267,22 +296,24 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
             }
         }
         __syncwarp();
-    } else {
+    } else if (tid < 128 * EPI_GROUPS) {
         // =============================== epilogue ===========================================
+        const int row = tid & 127, grp = tid >> 7, quad = warp & 3;
         const int Ow = (a.O + 31) >> 5;
         const int lim = a.res_in ? min(a.residual_channels, a.res_in_ch) : 0;
         uint32_t tc = 0;
         bool ok = true;
-        for (long long m = mfirst; m < mtiles && ok; m += mstep, tc++) {
+        bool overflow = false;
+        for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
             const int b = tc & 1;
-            const long long p = m * 128 + tid;
+            const int p = m * 128 + row;
             bool live = false;
             int n = 0, y = 0, x = 0;
-            if (p < a.NV) {
-                const long long vy = p / a.PW;
-                x = (int)(p - vy * a.PW);
-                n = (int)(vy / a.VH);
-                y = (int)(vy - (long long)n * a.VH);
+            if (p < NV) {
+                const int vy = p / a.PW;
+                x = p - vy * a.PW;
+                n = vy / a.VH;
+                y = vy - n * a.VH;
                 live = x < a.OWg && y < a.OHg;
             }
             const size_t opix = ((size_t)n * a.OHg + y) * a.OWg + x;
@@ -309,20 +340,19 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                     r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
                 }
             };
-            int rcur[32], rnext[32];
-            if (a.res_in) load_res(rcur, 0);              // in flight while the MMAs run
+            int rcur[32];
+            if (a.res_in) load_res(rcur, grp);            // in flight while the MMAs run
             ok = wait(BAR_CFULL(b), (tc >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
-            uint32_t words[NB];
-            bool overflow = false;
+            uint32_t words[NB_PER];
 #pragma unroll
-            for (int nb = 0; nb < NB; nb++) {
-                if (a.res_in && nb + 1 < NB) load_res(rnext, nb + 1);
+            for (int k = 0; k < NB_PER; k++) {
+                const int nb = grp + k * EPI_GROUPS;
                 int v[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + b * NT + nb * 32, v);
+                tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * NT + nb * 32, v);
                 tmem_ld_wait();
-                if (nb == NB - 1) {                       // accumulator drained: hand it back
+                if (k == NB_PER - 1) {                    // this thread is done with the accumulator
                     tc_fence_before();
                     mbar_arrive(BAR_CEMPTY(b));
                 }
@@ -336,12 +366,13 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 if (a.res_in) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] += rcur[j];
+                    if (k + 1 < NB_PER) load_res(rcur, nb + EPI_GROUPS);
                 }
                 uint32_t word = 0;
 #pragma unroll
                 for (int j = 0; j < 32; j++)
-                    if (!((float)v[j] < sThr[nb * 32 + j])) word |= 0x80000000u >> j;
-                words[nb] = word;
+                    if (v[j] >= sThr[nb * 32 + j]) word |= 0x80000000u >> j;
+                words[k] = word;
                 if (a.res_out && live) {
                     const size_t idx = opix * a.O + o0;
                     if (a.res_out_bytes == 2) {
@@ -350,10 +381,10 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                         for (int j = 0; j < 4; j++) {
                             uint32_t w[4];
 #pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                const int lo = v[8 * j + 2 * k], hi = v[8 * j + 2 * k + 1];
+                            for (int kk = 0; kk < 4; kk++) {
+                                const int lo = v[8 * j + 2 * kk], hi = v[8 * j + 2 * kk + 1];
                                 overflow |= max(abs(lo), abs(hi)) > 32767;
-                                w[k] = ((uint32_t)lo & 0xFFFFu) | ((uint32_t)hi << 16);
+                                w[kk] = ((uint32_t)lo & 0xFFFFu) | ((uint32_t)hi << 16);
                             }
                             dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
@@ -364,23 +395,19 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                             dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     }
                 }
-                if (a.res_in && nb + 1 < NB) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) rcur[j] = rnext[j];
-                }
             }
             if (live) {
                 uint32_t* dst = a.out + (size_t)n * a.out_image_stride +
                                 ((size_t)y * a.OWg + x) * Ow + (obase >> 5);
 #pragma unroll
-                for (int nb = 0; nb < NB; nb++) dst[nb] = words[nb];
+                for (int k = 0; k < NB_PER; k++) dst[grp + k * EPI_GROUPS] = words[k];
             }
-            if (overflow) atomicExch(a.err_flag, 2);
         }
+        if (overflow) atomicExch(a.err_flag, 2);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) tmem_dealloc(tmem, TM_COLS);
+    if (warp == MMA_WARP) tmem_dealloc(tmem, TM_COLS);
 }
 
 }  // namespace umma

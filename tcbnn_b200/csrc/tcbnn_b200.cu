@@ -196,8 +196,11 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
         const int PW = d->OW + (back_x > fwd_x ? back_x : fwd_x);
         const int VH = d->OH + (back_y > fwd_y ? back_y : fwd_y);
         const int npos = (128 + (back_y + fwd_y) * PW + back_x + fwd_x + 7) & ~7;
-        const int max_npos = st == 2 ? 256 : 512;
-        if (fwd_y >= 0 && fwd_x >= 0 && npos <= max_npos && npos * 16 < (1 << 18)) {
+        const int max_npos = st == 2 ? umma::kWsExpThreads : 2 * umma::kWsExpThreads;
+        const long long nv = (long long)d->B * VH * PW;
+        const long long in_words = (long long)d->B * d->H * d->W * (d->C / 32);
+        if (fwd_y >= 0 && fwd_x >= 0 && npos <= max_npos && npos * 16 < (1 << 18) &&
+            nv + 1024 < (1LL << 31) && in_words < (1LL << 31)) {
             for (int nt = 128; nt >= 32; nt >>= 1) {
                 if (d->O % nt) continue;
                 const size_t smem = umma::ws_smem_bytes(st, npos, d->C, d->R * d->S, nt);
