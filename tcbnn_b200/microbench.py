@@ -6,6 +6,9 @@
 c1: bit GEMM 1024 x 1024 x 4096 (bmm/benchmark-bmm.cu shape), int32 output.
 c2: one binary conv layer, NHWC batch x 56 x 56 x 128 -> 128 channels, 3x3, stride 1, pad 1,
     threshold + repack (bconv/benchmark-bconv.cu shape), optionally saving an int32 residual.
+conv: one binary 3x3 conv layer of any ResNet-18 shape: --hw, --cin, --cout, --stride,
+    --residual (int16 residual injected and saved, as in every second conv of a basic block).
+stem: the fp32 first layer, batch x 3 x 224 x 224 -> 56 x 56 x 64, 7x7 stride 4, int16 residual.
 Prints one JSON line: tera bit-ops/s (2*M*N*K, all taps counted, the reference's formula at
 bmm/bmma_op_test/main_test.cu:368) and the fraction of the b1 MMA issue rate measured in the
 same process.  Seeded synthetic operands (Bernoulli 0.5 bits)."""
@@ -38,7 +41,11 @@ def _time(fn, iters, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="c2", choices=["c1", "c2"])
+    ap.add_argument("--case", default="c2", choices=["c1", "c2", "conv", "stem"])
+    ap.add_argument("--hw", type=int, default=56)
+    ap.add_argument("--cin", type=int, default=64)
+    ap.add_argument("--cout", type=int, default=64)
+    ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--residual", action="store_true", help="c2: also save the int32 residual")
@@ -54,6 +61,36 @@ def main():
         ms = _time(lambda: ops.bgemm(A, B, K, out=out, workspace=ws), a.iters)
         work = 2.0 * M * N * K
         desc = "bit GEMM %dx%dx%d" % (M, N, K)
+    elif a.case == "stem":
+        Bn = a.batch
+        d = ops.conv_desc(Bn, 224, 224, 3, 64, 7, 7, 4, 4)
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        x = torch.randn((Bn, 3, 224, 224), device=dev, generator=g)
+        f = ops.pack_inconv_filter(torch.randn((49, 3, 64), device=dev, generator=g))
+        thr = torch.randn((64,), device=dev, generator=g) * 12.0
+        out = torch.zeros((Bn, d.OH * d.OW * 2), dtype=torch.int32, device=dev)
+        res = torch.empty((Bn, d.OH, d.OW, 64), dtype=torch.int16, device=dev)
+        ms = _time(lambda: ops.inconv_layer(d, x, f, thr, out=out, res_out_buf=res), a.iters)
+        work = 2.0 * Bn * d.OH * d.OW * 64 * 49 * 3
+        desc = "fp32 first layer %dx3x224x224 -> 56x56x64 (7x7/4), int16 residual; ops = fp32 add/sub" % Bn
+    elif a.case == "conv":
+        Bn, H, C, O, st = a.batch, a.hw, a.cin, a.cout, a.stride
+        d = ops.conv_desc(Bn, H, H, C, O, 3, 3, st, st)
+        x, f = _words((Bn, H, H, C // 32), 2, dev), _words((O, 9, C // 32), 3, dev)
+        g = torch.Generator(device=dev)
+        g.manual_seed(4)
+        thr = torch.randn((O,), device=dev, generator=g) * (9 * C) ** 0.5
+        prep = ops.conv_prepare(d, f)
+        out = torch.zeros((Bn, d.OH * d.OW * (O // 32)), dtype=torch.int32, device=dev)
+        rin = rout = None
+        if a.residual:
+            rin = torch.randint(-500, 500, (Bn, d.OH, d.OW, O), dtype=torch.int16, device=dev, generator=g)
+            rout = torch.empty((Bn, d.OH, d.OW, O), dtype=torch.int16, device=dev)
+        ms = _time(lambda: ops.conv_layer(d, x, prep, thr, res_in=rin, residual_channels=O if rin is not None else 0,
+                                          out=out, res_out_buf=rout), a.iters)
+        work = 2.0 * Bn * d.OH * d.OW * O * 9 * C
+        desc = "bit conv %dx%dx%dx%d -> %d, 3x3 stride %d%s" % (Bn, H, H, C, O, st, " + int16 residual in/out" if a.residual else "")
     else:
         Bn, H, C, O = a.batch, 56, 128, 128
         d = ops.conv_desc(Bn, H, H, C, O, 3, 3)
