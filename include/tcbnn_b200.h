@@ -103,6 +103,12 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
  * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);
+/* Tracing aid (the reference's counterpart is its in-kernel clock64 timer, utility.h:179-183):
+ * while `device_buffer` (at least 16 int64, device memory) is set, CTA 0 of every tcgen05 conv
+ * launch writes cycle counters: [0] expander total, [1] expander waiting for a free stage,
+ * [2] stages, [3] MMA issuer total, [4] waiting for a free accumulator, [5] waiting for a full
+ * stage, [6] epilogue total, [7] waiting for a full accumulator, [8] tiles.  NULL turns it off. */
+int tcbnn_conv_set_trace(void* device_buffer);
 /* Reads the layer's device-side status word (synchronises): 0 = fine, 1 = a bounded wait inside
  * the tcgen05 kernel gave up and the layer's output is not valid, 2 = a residual value did not
  * fit the int16 element size the caller chose. */

@@ -42,6 +42,7 @@ struct ConvWsArgs {
     uint32_t* out; long long out_image_stride;
     void* res_out; int res_out_bytes; int32_t* acc_out;
     int* err_flag;
+    long long* trace;         // optional: block 0 writes per-role cycle counters (see tcbnn_conv_set_trace)
 };
 
 constexpr int kWsEpiThreads = 256;
@@ -55,7 +56,7 @@ __host__ __device__ inline size_t ws_stage_bytes(int stride, int npos) {
 }
 __host__ __device__ inline size_t ws_smem_bytes(int stride, int npos, int C, int RS, int nt) {
     return ws_stages(stride) * ws_stage_bytes(stride, npos) + (size_t)RS * C * nt + nt * 4 +
-           RS * 4 + 16 * 8 + 64;
+           RS * 12 + 16 * 8 + 64;
 }
 
 // filter bits [O][R*S][Cw] -> int8 blocks in the order the kernel keeps them in shared memory
@@ -89,6 +90,13 @@ struct WsWait {
         atomicExch(err, 1);
         return false;
     }
+    // same, adding the cycles spent waiting to `acc` (tracing)
+    __device__ __forceinline__ bool timed(uint32_t bar, uint32_t parity, long long& acc) const {
+        const long long t0 = clock64();
+        const bool ok = (*this)(bar, parity);
+        acc += clock64() - t0;
+        return ok;
+    }
 };
 
 template <int NT, int STRIDE>
@@ -108,7 +116,8 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
     uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
     int* sThr = reinterpret_cast<int*>(sB + (size_t)RS * (a.C >> 4) * NT);
     int* sTap = sThr + NT;
-    uint64_t* sBar = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(sTap + RS) + 7) & ~(uintptr_t)7);
+    uint32_t* sTapK = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sTap + RS) + 7) & ~(uintptr_t)7);
+    uint64_t* sBar = reinterpret_cast<uint64_t*>(sTapK + 2 * RS);
     // barriers: a_full[NSTAGE], a_empty[NSTAGE], acc_full[2], acc_empty[2]
     uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 2 * NSTAGE + 4);
     volatile int* sAbort = reinterpret_cast<volatile int*>(sTmem + 1);
@@ -160,6 +169,10 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 off = r * a.PW + s;
             }
             sTap[t] = (plane << 24) | off;
+            // A-descriptor address increments (bytes >> 4) of this tap's two k-steps
+            const uint32_t byte_off = (uint32_t)plane * plane_bytes + (uint32_t)off * 16u;
+            sTapK[2 * t] = byte_off >> 4;
+            sTapK[2 * t + 1] = (byte_off + 2u * (uint32_t)a.NPOS * 16u) >> 4;
         }
     }
     fence_proxy_async();
@@ -175,12 +188,14 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
         const int Cw = a.C >> 5;
         const int nq = (a.NPOS + kWsExpThreads - 1) / kWsExpThreads;      // positions per thread
         const int nent = nq * NPLANE;
-        // The loader runs two stages ahead of the expander; a stage's bits travel through a
-        // three-deep register queue together with a per-entry "pixel exists" mask.
+        // The loader runs three stages ahead of the expander.  A stage's bits wait in one of four
+        // register buffers (with a per-entry "pixel exists" mask); the stage loop is unrolled
+        // by four so that buffers are addressed statically and no buffer is ever copied -- a
+        // copy would make the thread wait for the load it has just issued.
         int ptr[kWsMaxEnt];                                 // loader: word offset of the pixel
         uint32_t pmask = 0;
-        uint2 q0[kWsMaxEnt], q1[kWsMaxEnt], q2[kWsMaxEnt];
-        uint32_t m0 = 0, m1 = 0, m2 = 0;
+        uint2 qa[kWsMaxEnt], qb[kWsMaxEnt], qc[kWsMaxEnt], qd[kWsMaxEnt];
+        uint32_t ma = 0, mb = 0, mc = 0, md = 0;
         auto map_tile = [&](int m) {
             const int base = m * 128 - (a.back_y * a.PW + a.back_x);
             pmask = 0;
@@ -203,19 +218,17 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 }
             }
         };
-        auto load = [&](uint2 (&dst)[kWsMaxEnt], uint32_t& dm, int cb) {
-            dm = pmask;
-#pragma unroll
-            for (int j = 0; j < kWsMaxEnt; j++)
-                dst[j] = ((pmask >> j) & 1u) ? ldg64(a.in + ptr[j] + cb * 2) : make_uint2(0u, 0u);
-        };
-        // loader position (lm, lcb) and its helper to advance by one stage
+        // loader position (lm, lcb); load_next fetches that stage's bits and advances
         int lm = mfirst, lcb = 0;
         bool lvalid = lm < mtiles;
         if (lvalid) map_tile(lm);
         auto load_next = [&](uint2 (&dst)[kWsMaxEnt], uint32_t& dm) {
-            if (!lvalid) { dm = 0; return; }
-            load(dst, dm, lcb);
+            dm = 0;
+            if (!lvalid) return;
+            dm = pmask;
+#pragma unroll
+            for (int j = 0; j < kWsMaxEnt; j++)
+                dst[j] = ((pmask >> j) & 1u) ? ldg64(a.in + ptr[j] + lcb * 2) : make_uint2(0u, 0u);
             if (++lcb == NCB) {
                 lcb = 0;
                 lm += mstep;
@@ -223,77 +236,110 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 if (lvalid) map_tile(lm);
             }
         };
-        load_next(q0, m0);
-        load_next(q1, m1);
+        const int my_tiles = mfirst < mtiles ? (mtiles - mfirst + mstep - 1) / mstep : 0;
+        const uint32_t nstages = (uint32_t)my_tiles * NCB;
         uint32_t it = 0;
-        bool ok = true;
-        for (int m = mfirst; m < mtiles && ok; m += mstep) {
-            for (int cb = 0; cb < NCB && ok; cb++, it++) {
-                load_next(q2, m2);                          // two stages ahead
-                const int s = it % NSTAGE;
-                ok = wait(BAR_AEMPTY(s), ((it / NSTAGE) & 1) ^ 1);
-                if (!ok) break;
-                uint4* stage = reinterpret_cast<uint4*>(sAraw + (size_t)s * stage_bytes);
+        long long tr_wait = 0;
+        // one stage: refill `fill` (three stages ahead), expand `use` into ring slot it % NSTAGE
+        auto step = [&](uint2 (&use)[kWsMaxEnt], uint32_t um, uint2 (&fill)[kWsMaxEnt], uint32_t& fm) -> bool {
+            load_next(fill, fm);
+            const int s = it % NSTAGE;
+            if (!wait.timed(BAR_AEMPTY(s), ((it / NSTAGE) & 1) ^ 1, tr_wait)) return false;
+            uint4* stage = reinterpret_cast<uint4*>(sAraw + (size_t)s * stage_bytes);
 #pragma unroll
-                for (int j = 0; j < kWsMaxEnt; j++) {
-                    if (j >= nent) continue;
-                    const int qi = j / NPLANE, pl = j % NPLANE;
-                    const int q = et + qi * kWsExpThreads;
-                    if (q >= a.NPOS) continue;
-                    uint4* dst = stage + (size_t)pl * 4 * a.NPOS + q;
-                    if ((m0 >> j) & 1u) {
-                        dst[0] = expand16(q0[j].x >> 16);
-                        dst[(size_t)a.NPOS] = expand16(q0[j].x & 0xFFFFu);
-                        dst[(size_t)2 * a.NPOS] = expand16(q0[j].y >> 16);
-                        dst[(size_t)3 * a.NPOS] = expand16(q0[j].y & 0xFFFFu);
-                    } else {
-                        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                        dst[0] = z; dst[(size_t)a.NPOS] = z;
-                        dst[(size_t)2 * a.NPOS] = z; dst[(size_t)3 * a.NPOS] = z;
-                    }
+            for (int j = 0; j < kWsMaxEnt; j++) {
+                if (j >= nent) continue;
+                const int qi = j / NPLANE, pl = j % NPLANE;
+                const int q = et + qi * kWsExpThreads;
+                if (q >= a.NPOS) continue;
+                uint4* dst = stage + (size_t)pl * 4 * a.NPOS + q;
+                if ((um >> j) & 1u) {
+                    dst[0] = expand16(use[j].x >> 16);
+                    dst[(size_t)a.NPOS] = expand16(use[j].x & 0xFFFFu);
+                    dst[(size_t)2 * a.NPOS] = expand16(use[j].y >> 16);
+                    dst[(size_t)3 * a.NPOS] = expand16(use[j].y & 0xFFFFu);
+                } else {
+                    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                    dst[0] = z; dst[(size_t)a.NPOS] = z;
+                    dst[(size_t)2 * a.NPOS] = z; dst[(size_t)3 * a.NPOS] = z;
                 }
-                fence_proxy_async();
-                mbar_arrive(BAR_AFULL(s));
-#pragma unroll
-                for (int j = 0; j < kWsMaxEnt; j++) { q0[j] = q1[j]; q1[j] = q2[j]; }
-                m0 = m1; m1 = m2;
             }
+            fence_proxy_async();
+            mbar_arrive(BAR_AFULL(s));
+            it++;
+            return true;
+        };
+        const long long tr_t0 = clock64();
+        load_next(qa, ma);
+        load_next(qb, mb);
+        load_next(qc, mc);
+        while (it < nstages) {
+            if (!step(qa, ma, qd, md)) break;
+            if (it >= nstages) break;
+            if (!step(qb, mb, qa, ma)) break;
+            if (it >= nstages) break;
+            if (!step(qc, mc, qb, mb)) break;
+            if (it >= nstages) break;
+            if (!step(qd, md, qc, mc)) break;
         }
+        if (a.trace && blockIdx.x == 0 && et == 0) { a.trace[0] = clock64() - tr_t0; a.trace[1] = tr_wait; a.trace[2] = nstages; }
     } else if (warp == MMA_WARP) {
         // =============================== MMA issuer =========================================
         if (lane == 0) {
-            const uint32_t aBase = smem_u32(sAraw), bBase = smem_u32(sB);
+            // Descriptors differ only in their 14-bit address field (low word), so the issue
+            // loop adds precomputed (byte offset >> 4) values to two base descriptors: the A
+            // offset of (tap, k-step) comes from a table (held in registers for 3x3 filters),
+            // the B descriptor advances by one k-step (two 16-channel chunks) per MMA.
             const uint32_t lboA = (uint32_t)a.NPOS * 16u, lboB = NT * 16u;
+            const uint64_t descA0 = smem_desc(smem_u32(sAraw), lboA, 128u);
+            const uint64_t descB0 = smem_desc(smem_u32(sB), lboB, 128u);
+            const uint32_t aHi = (uint32_t)(descA0 >> 32), bHi = (uint32_t)(descB0 >> 32);
+            const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0;
+            const uint32_t stepB = (2u * lboB) >> 4, stepStage = stage_bytes >> 4;
+            constexpr uint32_t IDESC = idesc_i8(NT);
+            uint32_t ak[18];
+            const bool rs9 = RS == 9;
+#pragma unroll
+            for (int i = 0; i < 18; i++) ak[i] = rs9 ? sTapK[i] : 0u;
             uint32_t it = 0, tc = 0;
             bool ok = true;
+            long long tr_wc = 0, tr_wa = 0;
+            const long long tr_t0 = clock64();
             for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
                 const int b = tc & 1;
-                ok = wait(BAR_CEMPTY(b), ((tc >> 1) & 1) ^ 1);
+                ok = wait.timed(BAR_CEMPTY(b), ((tc >> 1) & 1) ^ 1, tr_wc);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + b * NT;
                 uint32_t acc = 0;
+                uint32_t bLo = bLo0;
                 for (int cb = 0; cb < NCB && ok; cb++, it++) {
                     const int s = it % NSTAGE;
-                    ok = wait(BAR_AFULL(s), (it / NSTAGE) & 1);
+                    ok = wait.timed(BAR_AFULL(s), (it / NSTAGE) & 1, tr_wa);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t stage = aBase + s * stage_bytes;
-                    for (int t = 0; t < RS; t++) {
-                        const int e = sTap[t];
-                        const uint32_t ta = stage + (uint32_t)(e >> 24) * plane_bytes + (uint32_t)(e & 0xFFFFFF) * 16u;
-                        const uint32_t tb = bBase + (uint32_t)((cb * RS + t) * 4) * lboB;
+                    const uint32_t aLo = aLo0 + s * stepStage;
+                    if (rs9) {
 #pragma unroll
-                        for (int ks = 0; ks < 2; ks++) {
-                            mma_i8(d, smem_desc(ta + 2 * ks * lboA, lboA, 128u),
-                                   smem_desc(tb + 2 * ks * lboB, lboB, 128u), idesc_i8(NT), acc);
+                        for (int i = 0; i < 18; i++) {
+                            mma_i8_split(d, aLo + ak[i], aHi, bLo + i * stepB, bHi, IDESC, i == 0 ? acc : 1u);
+                        }
+                        bLo += 18 * stepB;
+                    } else {
+                        for (int t = 0; t < RS; t++) {
+                            const uint2 ao = *reinterpret_cast<const uint2*>(sTapK + 2 * t);
+                            mma_i8_split(d, aLo + ao.x, aHi, bLo, bHi, IDESC, acc);
+                            mma_i8_split(d, aLo + ao.y, aHi, bLo + stepB, bHi, IDESC, 1u);
                             acc = 1;
+                            bLo += 2 * stepB;
                         }
                     }
+                    acc = 1;
                     mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
                 }
                 if (ok) mma_commit(BAR_CFULL(b));       // accumulator complete
             }
+            if (a.trace && blockIdx.x == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; }
         }
         __syncwarp();
     } else if (tid < 128 * EPI_GROUPS) {
@@ -304,6 +350,8 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
         uint32_t tc = 0;
         bool ok = true;
         bool overflow = false;
+        long long tr_w = 0;
+        const long long tr_t0 = clock64();
         for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
             const int b = tc & 1;
             const int p = m * 128 + row;
@@ -342,7 +390,7 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
             };
             int rcur[32];
             if (a.res_in) load_res(rcur, grp);            // in flight while the MMAs run
-            ok = wait(BAR_CFULL(b), (tc >> 1) & 1);
+            ok = wait.timed(BAR_CFULL(b), (tc >> 1) & 1, tr_w);
             if (!ok) break;
             tc_fence_after();
             uint32_t words[NB_PER];
@@ -404,6 +452,7 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
             }
         }
         if (overflow) atomicExch(a.err_flag, 2);
+        if (a.trace && blockIdx.x == 0 && tid == 0) { a.trace[6] = clock64() - tr_t0; a.trace[7] = tr_w; a.trace[8] = tc; }
     }
     tc_fence_before();
     __syncthreads();

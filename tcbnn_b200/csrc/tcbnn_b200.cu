@@ -201,7 +201,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
         const long long in_words = (long long)d->B * d->H * d->W * (d->C / 32);
         if (fwd_y >= 0 && fwd_x >= 0 && npos <= max_npos && npos * 16 < (1 << 18) &&
             nv + 1024 < (1LL << 31) && in_words < (1LL << 31)) {
-            for (int nt = 128; nt >= 32; nt >>= 1) {
+            for (int nt = 256; nt >= 32; nt >>= 1) {
                 if (d->O % nt) continue;
                 const size_t smem = umma::ws_smem_bytes(st, npos, d->C, d->R * d->S, nt);
                 if (smem > 227 * 1024) continue;
@@ -243,6 +243,7 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
     return launch_check("inconv_layer (tiled)");
 }
 
+long long* g_conv_trace = nullptr;   // device buffer for per-role cycle counters, or null
 int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible)
 
 template <int NT, int STRIDE>
@@ -497,13 +498,14 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
         a.out = out; a.out_image_stride = out_image_stride; a.res_out = res_out;
         a.res_out_bytes = res_out_bytes; a.acc_out = acc_out;
         a.err_flag = (int*)(p + L.off_err);
+        a.trace = g_conv_trace;
         int sms;
         if (sm_count(&sms)) return 1;
         cudaStream_t st = (cudaStream_t)stream;
 #define TCBNN_WS_CASE(NN, SS) \
         if (L.umma_nt == NN && d->stride_h == SS) return launch_conv_umma_ws<NN, SS>(a, L.umma_smem, sms, st);
-        TCBNN_WS_CASE(32, 1) TCBNN_WS_CASE(64, 1) TCBNN_WS_CASE(128, 1)
-        TCBNN_WS_CASE(32, 2) TCBNN_WS_CASE(64, 2) TCBNN_WS_CASE(128, 2)
+        TCBNN_WS_CASE(32, 1) TCBNN_WS_CASE(64, 1) TCBNN_WS_CASE(128, 1) TCBNN_WS_CASE(256, 1)
+        TCBNN_WS_CASE(32, 2) TCBNN_WS_CASE(64, 2) TCBNN_WS_CASE(128, 2) TCBNN_WS_CASE(256, 2)
 #undef TCBNN_WS_CASE
         return fail("conv_layer: no tcgen05 instance for n-tile=%d stride=%d", L.umma_nt, d->stride_h);
     }
@@ -533,6 +535,11 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
 int tcbnn_set_conv_path(int path) {
     if (path < 0 || path > 2) return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05");
     g_conv_path = path;
+    return 0;
+}
+
+int tcbnn_conv_set_trace(void* device_buffer) {
+    g_conv_trace = (long long*)device_buffer;
     return 0;
 }
 
