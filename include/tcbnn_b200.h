@@ -142,8 +142,9 @@ size_t tcbnn_noalloc_scratch_bytes(void);
 int tcbnn_fc_layer_noalloc(const uint32_t* A, const uint32_t* W, const float* thr, int M, int K,
                            int N, int lda, int ldw, uint32_t* out, int ldo, void* stream);
 
-/* Issue-rate probe of the warp-level MMA forms on all SMs: kind 0 = b1 and.popc m16n8k256,
- * 1 = b1 xor.popc m16n8k256, 2 = s8 m16n8k32.  Returns tera-ops/s (2*m*n*k per MMA) in *tops.
+/* Issue-rate probe of the MMA forms on all SMs: kind 0 = b1 and.popc m16n8k256 (mma.sync),
+ * 1 = b1 xor.popc m16n8k256, 2 = s8 m16n8k32, 3 = tcgen05.mma kind::i8 128x256x32 (warps_per_sm
+ * ignored).  Returns tera-ops/s (2*m*n*k per MMA) in *tops.
  * Synchronises the device.  The reference's counterpart is the WMMA latency probe
  * bmm/bmma_op_test/main_test.cu:35-220 and its TOPS formula at :368. */
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops);

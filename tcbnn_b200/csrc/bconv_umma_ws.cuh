@@ -417,9 +417,15 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                     if (k + 1 < NB_PER) load_res(rcur, nb + EPI_GROUPS);
                 }
                 uint32_t word = 0;
+                const int4* th4 = reinterpret_cast<const int4*>(sThr + nb * 32);
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    if (v[j] >= sThr[nb * 32 + j]) word |= 0x80000000u >> j;
+                for (int j = 0; j < 8; j++) {
+                    const int4 th = th4[j];                  // one broadcast load per 4 channels
+                    if (v[4 * j] >= th.x) word |= 0x80000000u >> (4 * j);
+                    if (v[4 * j + 1] >= th.y) word |= 0x80000000u >> (4 * j + 1);
+                    if (v[4 * j + 2] >= th.z) word |= 0x80000000u >> (4 * j + 2);
+                    if (v[4 * j + 3] >= th.w) word |= 0x80000000u >> (4 * j + 3);
+                }
                 words[k] = word;
                 if (a.res_out && live) {
                     const size_t idx = opix * a.O + o0;

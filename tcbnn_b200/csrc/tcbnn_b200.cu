@@ -309,6 +309,34 @@ __global__ void k_mma_peak(int iters, unsigned seed, int* sink) {
 }
 
 
+// tcgen05.mma kind::i8 M=128 N=256 K=32 issued back to back by one thread per SM on resident
+// shared-memory operands: the int8 tensor-core ceiling the conv kernel is measured against.
+__global__ void __launch_bounds__(128) k_umma_peak(int iters, long long* cycles, int* err) {
+    extern __shared__ __align__(1024) unsigned char peak_smem[];
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tm;
+    if (threadIdx.x < 32) umma::tmem_alloc(umma::smem_u32(&tm), 256);
+    if (threadIdx.x == 0) umma::mbar_init(umma::smem_u32(&bar), 1);
+    for (int i = threadIdx.x; i < 48 * 1024 / 4; i += blockDim.x) ((uint32_t*)peak_smem)[i] = 0x01FF01FFu;
+    umma::fence_proxy_async();
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    if (threadIdx.x == 0) {
+        const uint64_t da = umma::smem_desc(umma::smem_u32(peak_smem), 128 * 16, 128);
+        const uint64_t db = umma::smem_desc(umma::smem_u32(peak_smem + 16384), 256 * 16, 128);
+        const long long t0 = clock64();
+        for (int i = 0; i < iters; i++)
+            umma::mma_i8(tm, da + 2 * (i & 3), db + 2 * (i & 3), umma::idesc_i8(256), 1u);
+        umma::mma_commit(umma::smem_u32(&bar));
+        if (!umma::mbar_wait(umma::smem_u32(&bar), 0, err)) { /* status already recorded */ }
+        if (blockIdx.x == 0) cycles[0] = clock64() - t0;
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) umma::tmem_dealloc(tm, 256);
+}
+
 // ---- fixed scratch for callers that cannot allocate ---------------------------------------
 // Split-K partial sums for tcbnn_fc_layer_noalloc live in this array instead of a caller
 // workspace.  It is part of the loaded module: every GPU that loads the library keeps these
@@ -580,16 +608,39 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
 }
 
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
-    if (!tops || iters <= 0 || warps_per_sm <= 0 || kind < 0 || kind > 2) return fail("mma_peak: bad arguments");
+    if (!tops || iters <= 0 || warps_per_sm <= 0 || kind < 0 || kind > 3) return fail("mma_peak: bad arguments");
     int sms;
     if (sm_count(&sms)) return 1;
-    int* sink = nullptr;
-    CUDA_TRY(cudaMalloc(&sink, 4));
-    const int threads = 256, ctas = sms * warps_per_sm * 32 / threads;
     cudaEvent_t e0, e1;
     CUDA_TRY(cudaEventCreate(&e0));
     CUDA_TRY(cudaEventCreate(&e1));
     float best = 1e30f;
+    if (kind == 3) {
+        long long* buf = nullptr;
+        CUDA_TRY(cudaMalloc(&buf, 16));
+        CUDA_TRY(cudaMemset(buf, 0, 16));
+        CUDA_TRY(cudaFuncSetAttribute(k_umma_peak, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
+        for (int rep = 0; rep < 4; rep++) {
+            cudaEventRecord(e0);
+            k_umma_peak<<<sms, 128, 48 * 1024>>>(iters, buf, (int*)(buf + 1));
+            cudaEventRecord(e1);
+            CUDA_TRY(cudaEventSynchronize(e1));
+            float ms = 0;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (rep > 0 && ms < best) best = ms;
+        }
+        int status = 0;
+        CUDA_TRY(cudaMemcpy(&status, buf + 1, sizeof(int), cudaMemcpyDeviceToHost));
+        cudaFree(buf);
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        if (status) return fail("mma_peak: a bounded wait in the tcgen05 probe gave up");
+        *tops = (double)sms * iters * 2.0 * 128 * 256 * 32 / (best * 1e-3) / 1e12;
+        return 0;
+    }
+    int* sink = nullptr;
+    CUDA_TRY(cudaMalloc(&sink, 4));
+    const int threads = 256, ctas = sms * warps_per_sm * 32 / threads;
     for (int rep = 0; rep < 4; rep++) {
         cudaEventRecord(e0);
         if (kind == 0) k_mma_peak<0><<<ctas, threads>>>(iters, 1u, sink);

@@ -192,3 +192,51 @@ class Network:
         for l in self.layers:
             l.forward()
         return self.layers[-1].get_output_gpu()
+
+
+class HostFeeder:
+    """Feeds a Network from pinned host batches with the host->device copy of batch i+1 running
+    on its own stream while batch i is being computed (two device input buffers).  Every batch
+    still pays its own copy; only the waiting is overlapped."""
+
+    def __init__(self, net):
+        import torch
+        self.net = net
+        self.first = net.layers[0]
+        self.bufs = [self.first.input_gpu, torch.empty_like(self.first.input_gpu)]
+        self.copy_stream = torch.cuda.Stream()
+        self.copied = [torch.cuda.Event(), torch.cuda.Event()]
+        self.free = [torch.cuda.Event(), torch.cuda.Event()]
+        self.n = 0
+        self.pending = None
+
+    def _enqueue_copy(self, slot, x_host):
+        import torch
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.free[slot])
+            self.bufs[slot].copy_(x_host.reshape(self.bufs[slot].shape), non_blocking=True)
+            self.copied[slot].record(self.copy_stream)
+
+    def run(self, batches, on_result):
+        """batches: iterable of pinned host tensors; on_result(logits_device) is called after
+        each forward pass has been queued (it may queue the device->host read)."""
+        import torch
+        main = torch.cuda.current_stream()
+        for ev in self.free:
+            ev.record(main)
+        it = iter(batches)
+        nxt = next(it, None)
+        slot = 0
+        if nxt is not None:
+            self._enqueue_copy(slot, nxt)
+        while nxt is not None:
+            cur_slot = slot
+            nxt = next(it, None)
+            if nxt is not None:
+                slot ^= 1
+                self._enqueue_copy(slot, nxt)
+            main.wait_event(self.copied[cur_slot])
+            self.first.input_gpu = self.bufs[cur_slot]
+            out = self.net.forward()
+            self.free[cur_slot].record(main)
+            on_result(out)
