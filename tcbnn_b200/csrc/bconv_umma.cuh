@@ -132,7 +132,7 @@ __device__ __forceinline__ uint4 expand16(uint32_t h) {
     for (int g = 0; g < 4; g++) {
         const uint32_t nb = (h >> (4 * g)) & 0xFu;
         const uint32_t y = (nb * 0x00204081u) & 0x01010101u;      // one bit per byte
-        v[g] = y | ((y ^ 0x01010101u) * 0xFFu);                   // 1 -> 0x01, 0 -> 0xFF
+        v[g] = ~(y * 0xFEu);                                      // 1 -> 0x01, 0 -> 0xFF
     }
     return make_uint4(v[0], v[1], v[2], v[3]);
 }

@@ -7,9 +7,9 @@
 //   warps 0-7   epilogue   : prefetch the residual rows, wait for an accumulator, tcgen05.ld,
 //                            add / threshold / pack, store bits and the new residual
 //                            (warp w reads TMEM lanes 32*(w%4).., column groups of parity w/4)
-//   warps 8-15  expanders  : packed input bits (prefetched two stages ahead in registers) ->
+//   warps 8-14  expanders  : packed input bits (prefetched three stages ahead in registers) ->
 //                            +-1 bytes of one 64-channel block of the patch, ring of stages
-//   warp  16    MMA issuer : one lane issues 9 taps x 2 k-steps per stage, commits the stage
+//   warp  15    MMA issuer : one lane issues 9 taps x 2 k-steps per stage, commits the stage
 //                            back to the expanders and the finished tile to the epilogue
 //
 // with mbarriers between them, two accumulators in tensor memory (epilogue of tile i overlaps
@@ -34,6 +34,7 @@ struct ConvWsArgs {
     int B, H, W, C, O, R, S, pad_h, pad_w, stride;
     int OHg, OWg;             // outputs per image (pre-pool == post-pool here)
     int PW, VH;               // raster pitch and rows per image (output grid + zero band)
+    uint32_t pw_mul, pw_sh, vh_mul, vh_sh;   // x / PW and x / VH by multiply-shift (x < 2^31)
     int NPOS;                 // raster positions per plane patch (multiple of 8)
     int back_y, back_x;       // patch origin = tile start - (back_y*PW + back_x)
     long long NV;             // raster positions over the batch
@@ -46,7 +47,7 @@ struct ConvWsArgs {
 };
 
 constexpr int kWsEpiThreads = 256;
-constexpr int kWsExpThreads = 256;
+constexpr int kWsExpThreads = 224;       // 7 warps; with the issuer warp the CTA is 16 warps
 constexpr int kWsThreads = kWsEpiThreads + kWsExpThreads + 32;
 constexpr int kWsMaxEnt = 4;          // (positions per expander thread) x planes
 
@@ -76,6 +77,17 @@ __device__ __forceinline__ void prepare_filter_ws(const uint32_t* fbits, int O, 
         const uint32_t w = fbits[((size_t)o * RS + tap) * Cw + cb * 2 + (c4 >> 1)];
         out[i] = expand16((c4 & 1) ? (w & 0xFFFFu) : (w >> 16));
     }
+}
+
+// floor(x / d) for 0 <= x < 2^31 with mul = ceil(2^sh / d), sh = 31 + ceil(log2 d)
+__device__ __forceinline__ int fastdiv(int x, uint32_t mul, uint32_t sh) {
+    return (int)(((unsigned long long)(uint32_t)x * mul) >> sh);
+}
+__host__ inline void fastdiv_setup(int d, uint32_t* mul, uint32_t* sh) {
+    uint32_t s = 0;
+    while ((1u << s) < (uint32_t)d) s++;
+    *sh = 31 + s;
+    *mul = (uint32_t)((((unsigned long long)1 << (31 + s)) + d - 1) / d);
 }
 
 struct WsWait {
@@ -136,8 +148,8 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
 
     // ---- one-time setup -------------------------------------------------------------------
     if (tid == 0) {
-        for (int s = 0; s < NSTAGE; s++) { mbar_init(BAR_AFULL(s), kWsExpThreads); mbar_init(BAR_AEMPTY(s), 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), 128 * EPI_GROUPS); }
+        for (int s = 0; s < NSTAGE; s++) { mbar_init(BAR_AFULL(s), kWsExpThreads / 32); mbar_init(BAR_AEMPTY(s), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), 4 * EPI_GROUPS); }
         *sAbort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -207,8 +219,8 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 const int q = et + qi * kWsExpThreads;
                 const int gq = base + q;
                 if (q < a.NPOS && gq >= 0 && gq < NV) {
-                    const int vy = gq / a.PW, vx = gq - vy * a.PW;
-                    const int n = vy / a.VH, vr = vy - n * a.VH;
+                    const int vy = fastdiv(gq, a.pw_mul, a.pw_sh), vx = gq - vy * a.PW;
+                    const int n = fastdiv(vy, a.vh_mul, a.vh_sh), vr = vy - n * a.VH;
                     const int iy = STRIDE == 2 ? 2 * vr + (pl >> 1) : vr;
                     const int ix = STRIDE == 2 ? 2 * vx + (pl & 1) : vx;
                     if (vr < a.OHg && vx < a.OWg && iy < a.H && ix < a.W) {
@@ -239,12 +251,16 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
         const int my_tiles = mfirst < mtiles ? (mtiles - mfirst + mstep - 1) / mstep : 0;
         const uint32_t nstages = (uint32_t)my_tiles * NCB;
         uint32_t it = 0;
-        long long tr_wait = 0;
+        long long tr_wait = 0, tr_load = 0, tr_exp = 0, tr_fence = 0;
         // one stage: refill `fill` (three stages ahead), expand `use` into ring slot it % NSTAGE
         auto step = [&](uint2 (&use)[kWsMaxEnt], uint32_t um, uint2 (&fill)[kWsMaxEnt], uint32_t& fm) -> bool {
+            const long long c0 = clock64();
             load_next(fill, fm);
+            const long long c1 = clock64();
+            tr_load += c1 - c0;
             const int s = it % NSTAGE;
             if (!wait.timed(BAR_AEMPTY(s), ((it / NSTAGE) & 1) ^ 1, tr_wait)) return false;
+            const long long c2 = clock64();
             uint4* stage = reinterpret_cast<uint4*>(sAraw + (size_t)s * stage_bytes);
 #pragma unroll
             for (int j = 0; j < kWsMaxEnt; j++) {
@@ -264,8 +280,12 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                     dst[(size_t)2 * a.NPOS] = z; dst[(size_t)3 * a.NPOS] = z;
                 }
             }
-            fence_proxy_async();
-            mbar_arrive(BAR_AFULL(s));
+            const long long c3 = clock64();
+            tr_exp += c3 - c2;
+            fence_proxy_async();                        // each writer publishes its own stores,
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_AFULL(s));   // then one arrival per warp
+            tr_fence += clock64() - c3;
             it++;
             return true;
         };
@@ -282,7 +302,7 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
             if (it >= nstages) break;
             if (!step(qd, md, qc, mc)) break;
         }
-        if (a.trace && blockIdx.x == 0 && et == 0) { a.trace[0] = clock64() - tr_t0; a.trace[1] = tr_wait; a.trace[2] = nstages; }
+        if (a.trace && blockIdx.x == 0 && et == 0) { a.trace[0] = clock64() - tr_t0; a.trace[1] = tr_wait; a.trace[2] = nstages; a.trace[9] = tr_load; a.trace[10] = tr_exp; a.trace[11] = tr_fence; }
     } else if (warp == MMA_WARP) {
         // =============================== MMA issuer =========================================
         if (lane == 0) {
@@ -350,49 +370,102 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
         uint32_t tc = 0;
         bool ok = true;
         bool overflow = false;
-        long long tr_w = 0;
+        long long tr_w = 0, tr_tld = 0, tr_body = 0;
         const long long tr_t0 = clock64();
+        // 32 int16 residual channels [o0, o0+32) of one output pixel as 8 packed pairs-of-pairs
+        // (zeros where nothing is injected); 2x2 max for pooled residuals (kernel.cuh:773-783)
+        auto fetch_res16 = [&](uint2 (&r)[8], int n_, int y_, int x_, size_t opix_, bool live_, int o0) {
+            const short* base = reinterpret_cast<const short*>(a.res_in);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                uint2 v = make_uint2(0u, 0u);
+                const int o = o0 + 4 * j;
+                if (live_ && o < lim) {
+                    if (a.residual_pool) {
+                        const size_t b00 = (((size_t)n_ * 2 * a.OHg + 2 * y_) * 2 * a.OWg + 2 * x_) *
+                                           a.res_in_ch + o;
+                        const size_t rowp = (size_t)2 * a.OWg * a.res_in_ch;
+                        const uint2 p0 = __ldg(reinterpret_cast<const uint2*>(base + b00));
+                        const uint2 p1 = __ldg(reinterpret_cast<const uint2*>(base + b00 + a.res_in_ch));
+                        const uint2 p2 = __ldg(reinterpret_cast<const uint2*>(base + b00 + rowp));
+                        const uint2 p3 = __ldg(reinterpret_cast<const uint2*>(base + b00 + rowp + a.res_in_ch));
+                        v.x = __vmaxs2(__vmaxs2(p0.x, p1.x), __vmaxs2(p2.x, p3.x));
+                        v.y = __vmaxs2(__vmaxs2(p0.y, p1.y), __vmaxs2(p2.y, p3.y));
+                    } else {
+                        v = __ldg(reinterpret_cast<const uint2*>(base + opix_ * a.res_in_ch + o));
+                    }
+                }
+                r[j] = v;
+            }
+        };
+        // general path: add the residual of channels [o0, o0+32) straight from memory
+        auto add_res_inplace = [&](int (&v)[32], int n_, int y_, int x_, size_t opix_, bool live_, int o0) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                int4 r = make_int4(0, 0, 0, 0);
+                const int o = o0 + 4 * j;
+                if (live_ && o < lim) {
+                    if (a.residual_pool) {
+                        const size_t b00 = (((size_t)n_ * 2 * a.OHg + 2 * y_) * 2 * a.OWg + 2 * x_) *
+                                           a.res_in_ch + o;
+                        const size_t rowp = (size_t)2 * a.OWg * a.res_in_ch;
+                        r = max4(max4(ld_res4(a.res_in, a.res_in_bytes, b00),
+                                      ld_res4(a.res_in, a.res_in_bytes, b00 + a.res_in_ch)),
+                                 max4(ld_res4(a.res_in, a.res_in_bytes, b00 + rowp),
+                                      ld_res4(a.res_in, a.res_in_bytes, b00 + rowp + a.res_in_ch)));
+                    } else {
+                        r = ld_res4(a.res_in, a.res_in_bytes, opix_ * a.res_in_ch + o);
+                    }
+                }
+                v[4 * j] += r.x; v[4 * j + 1] += r.y; v[4 * j + 2] += r.z; v[4 * j + 3] += r.w;
+            }
+        };
+        uint2 rnext[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) rnext[j] = make_uint2(0u, 0u);
         for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
             const int b = tc & 1;
             const int p = m * 128 + row;
             bool live = false;
             int n = 0, y = 0, x = 0;
             if (p < NV) {
-                const int vy = p / a.PW;
+                const int vy = fastdiv(p, a.pw_mul, a.pw_sh);
                 x = p - vy * a.PW;
-                n = vy / a.VH;
+                n = fastdiv(vy, a.vh_mul, a.vh_sh);
                 y = vy - n * a.VH;
                 live = x < a.OWg && y < a.OHg;
             }
             const size_t opix = ((size_t)n * a.OHg + y) * a.OWg + x;
-            // residual of one 32-channel group, widened to int32 (zeros where not injected)
-            auto load_res = [&](int (&r)[32], int nb) {
-                const int o0 = obase + nb * 32;
+            // ---- residual prefetch --------------------------------------------------------
+            // The residual of this thread's row is fetched one tile ahead (packed int16 pairs
+            // stay packed in registers until they are added), so its memory latency overlaps
+            // the previous tile's epilogue instead of stalling this one.  int32 residuals and
+            // the rare case of several column groups per thread are loaded in place.
+            if (a.res_in && m == mfirst && NB_PER == 1 && a.res_in_bytes == 2)
+                fetch_res16(rnext, n, y, x, opix, live, obase + grp * 32);
+            uint2 rcur16[8];
+            if (a.res_in && NB_PER == 1 && a.res_in_bytes == 2) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    int4 v = make_int4(0, 0, 0, 0);
-                    const int o = o0 + 4 * j;
-                    if (live && o < lim) {
-                        if (a.residual_pool) {          // kernel.cuh:773-783
-                            const size_t b00 = (((size_t)n * 2 * a.OHg + 2 * y) * 2 * a.OWg + 2 * x) *
-                                               a.res_in_ch + o;
-                            const size_t rowp = (size_t)2 * a.OWg * a.res_in_ch;
-                            v = max4(max4(ld_res4(a.res_in, a.res_in_bytes, b00),
-                                          ld_res4(a.res_in, a.res_in_bytes, b00 + a.res_in_ch)),
-                                     max4(ld_res4(a.res_in, a.res_in_bytes, b00 + rowp),
-                                          ld_res4(a.res_in, a.res_in_bytes, b00 + rowp + a.res_in_ch)));
-                        } else {
-                            v = ld_res4(a.res_in, a.res_in_bytes, opix * a.res_in_ch + o);
-                        }
+                for (int j = 0; j < 8; j++) rcur16[j] = rnext[j];
+                const int mn = m + mstep;
+                if (mn < mtiles) {                         // next tile's row, same column group
+                    const int pn = mn * 128 + row;
+                    bool ln = false;
+                    int nn = 0, yn = 0, xn = 0;
+                    if (pn < NV) {
+                        const int vy = fastdiv(pn, a.pw_mul, a.pw_sh);
+                        xn = pn - vy * a.PW;
+                        nn = fastdiv(vy, a.vh_mul, a.vh_sh);
+                        yn = vy - nn * a.VH;
+                        ln = xn < a.OWg && yn < a.OHg;
                     }
-                    r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+                    fetch_res16(rnext, nn, yn, xn, ((size_t)nn * a.OHg + yn) * a.OWg + xn, ln, obase + grp * 32);
                 }
-            };
-            int rcur[32];
-            if (a.res_in) load_res(rcur, grp);            // in flight while the MMAs run
+            }
             ok = wait.timed(BAR_CFULL(b), (tc >> 1) & 1, tr_w);
             if (!ok) break;
             tc_fence_after();
+            const long long e0 = clock64();
             uint32_t words[NB_PER];
 #pragma unroll
             for (int k = 0; k < NB_PER; k++) {
@@ -400,9 +473,11 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 int v[32];
                 tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * NT + nb * 32, v);
                 tmem_ld_wait();
-                if (k == NB_PER - 1) {                    // this thread is done with the accumulator
+                if (k == 0) tr_tld += clock64() - e0;
+                if (k == NB_PER - 1) {                    // this warp is done with the accumulator
                     tc_fence_before();
-                    mbar_arrive(BAR_CEMPTY(b));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR_CEMPTY(b));
                 }
                 const int o0 = obase + nb * 32;
                 if (live && a.acc_out) {
@@ -412,9 +487,17 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                         dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
                 if (a.res_in) {
+                    if (NB_PER == 1 && a.res_in_bytes == 2) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) v[j] += rcur[j];
-                    if (k + 1 < NB_PER) load_res(rcur, nb + EPI_GROUPS);
+                        for (int j = 0; j < 8; j++) {
+                            v[4 * j] += (int)(short)(rcur16[j].x & 0xFFFFu);
+                            v[4 * j + 1] += (int)(short)(rcur16[j].x >> 16);
+                            v[4 * j + 2] += (int)(short)(rcur16[j].y & 0xFFFFu);
+                            v[4 * j + 3] += (int)(short)(rcur16[j].y >> 16);
+                        }
+                    } else {
+                        add_res_inplace(v, n, y, x, opix, live, o0);
+                    }
                 }
                 uint32_t word = 0;
                 const int4* th4 = reinterpret_cast<const int4*>(sThr + nb * 32);
@@ -456,9 +539,10 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
 #pragma unroll
                 for (int k = 0; k < NB_PER; k++) dst[grp + k * EPI_GROUPS] = words[k];
             }
+            tr_body += clock64() - e0;
         }
         if (overflow) atomicExch(a.err_flag, 2);
-        if (a.trace && blockIdx.x == 0 && tid == 0) { a.trace[6] = clock64() - tr_t0; a.trace[7] = tr_w; a.trace[8] = tc; }
+        if (a.trace && blockIdx.x == 0 && tid == 0) { a.trace[6] = clock64() - tr_t0; a.trace[7] = tr_w; a.trace[8] = tc; a.trace[12] = tr_tld; a.trace[13] = tr_body; }
     }
     tc_fence_before();
     __syncthreads();

@@ -521,6 +521,8 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
         a.PW = L.umma_pw; a.VH = L.umma_vh; a.NPOS = L.umma_npos;
         a.back_y = L.umma_back_y; a.back_x = L.umma_back_x;
         a.NV = (long long)d->B * a.VH * a.PW;
+        umma::fastdiv_setup(a.PW, &a.pw_mul, &a.pw_sh);
+        umma::fastdiv_setup(a.VH, &a.vh_mul, &a.vh_sh);
         a.res_in = res_in; a.res_in_bytes = res_in_bytes; a.res_in_ch = res_in_ch;
         a.residual_channels = residual_channels; a.residual_pool = residual_pool;
         a.out = out; a.out_image_stride = out_image_stride; a.res_out = res_out;
