@@ -203,8 +203,9 @@ struct ConvArgs {
     int res_in_ch, residual_channels, residual_pool;
     uint32_t* out;           // per image [OH][OW][Ow] words at stride out_image_stride
     long long out_image_stride;
-    void* res_out;           // [B][P][Q][O] or null
+    void* res_out;           // [B][P][Q][res_out_ld] or null
     int res_out_bytes;
+    int res_out_ld;          // channel stride of res_out (O, or a padded width)
     int32_t* acc_out;        // [B][P][Q][O] or null (value before residual injection)
 };
 
@@ -319,7 +320,7 @@ __device__ __forceinline__ void conv_warp_tile(const ConvArgs& c, int tp, int tn
                 }
                 if (!((float)res < __ldg(c.thr + o)))            // kernel.cuh:795-796
                     words[c.pool == 2 ? 0 : i] |= 0x80000000u >> (j * 8 + 2 * t + e);
-                if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.O + o, res);  // kernel.cuh:818-824
+                if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.res_out_ld + o, res);  // kernel.cuh:818-824
             }
         }
     }
@@ -361,8 +362,9 @@ struct InConvArgs {
     int B, H, W, O, R, S, sh, sw, pad_h, pad_w, pool, OH, OW;
     uint32_t* out;
     long long out_image_stride;
-    void* res_out;           // [B][P][Q][O], (int)acc truncation (kernel.cuh:666-668)
+    void* res_out;           // [B][P][Q][res_out_ld], (int)acc truncation (kernel.cuh:666-668)
     int res_out_bytes;       // 4 or 2
+    int res_out_ld;          // channel stride of res_out (O, or a padded width)
     float* acc_out;          // optional fp32 accumulators
 };
 
@@ -414,7 +416,7 @@ __device__ __forceinline__ void inconv_warp_pixel(const InConvArgs& c, long long
                 const bool bit = o < c.O && !(acc[k] < __ldg(c.thr + min(o, c.O - 1)));
                 words[k] |= __brev(__ballot_sync(0xffffffffu, bit));
                 if (o < c.O) {
-                    if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.O + o, (int)acc[k]);
+                    if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.res_out_ld + o, (int)acc[k]);
                     if (c.acc_out) c.acc_out[opix * c.O + o] = acc[k];
                 }
             }

@@ -153,7 +153,7 @@ __device__ void inconv_tiled_block(const InConvArgs& c, unsigned char* smem) {
             const uint32_t w = __brev(__ballot_sync(0xffffffffu, bit));
             if (live && o < c.O) {
                 const size_t opix = ((size_t)n * P + y) * Q + x;
-                if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.O + o, (int)acc[k]);  // kernel.cuh:666-668
+                if (c.res_out) st_res(c.res_out, c.res_out_bytes, opix * c.res_out_ld + o, (int)acc[k]);  // kernel.cuh:666-668
                 if (c.acc_out) c.acc_out[opix * c.O + o] = acc[k];
             }
             if (c.pool == 2) {

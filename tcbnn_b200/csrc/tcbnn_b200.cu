@@ -553,7 +553,7 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
     c.res_in = res_in; c.res_in_bytes = res_in_bytes; c.res_in_ch = res_in_ch;
     c.residual_channels = residual_channels; c.residual_pool = residual_pool;
     c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out;
-    c.res_out_bytes = res_out_bytes; c.acc_out = acc_out;
+    c.res_out_bytes = res_out_bytes; c.res_out_ld = d->O; c.acc_out = acc_out;
     int sms;
     if (sm_count(&sms)) return 1;
     const long long rows = (long long)d->B * d->OH * d->OW * d->pool * d->pool;
@@ -594,7 +594,7 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
     c.sh = d->stride_h; c.sw = d->stride_w; c.pad_h = d->pad_h; c.pad_w = d->pad_w;
     c.pool = d->pool; c.OH = d->OH; c.OW = d->OW;
     c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out;
-    c.res_out_bytes = res_out_bytes; c.acc_out = acc_out;
+    c.res_out_bytes = res_out_bytes; c.res_out_ld = d->O; c.acc_out = acc_out;
     int sms;
     if (sm_count(&sms)) return 1;
     const int opad = ((d->O + 31) / 32) * 32;

@@ -1,0 +1,87 @@
+"""Build the C++ side of the drop-in header API.
+
+    python -m tcbnn_b200.dropin.build [--ref-root /path/to/TCBNN]
+
+build/dropin/net_runner        : tcbnn_b200/dropin/net_runner.cu (generic cooperative-kernel driver)
+build/dropin/<driver>          : the reference's own, UNCHANGED driver sources (mnist_mlp.cu,
+    cifar10_vgg.cu, cifar10_resnet.cu, imagenet_resnet.cu) compiled against the drop-in
+    utility.h / param.h / kernel.cuh.  The sources are copied at build time into the git-ignored
+    build/ folder (a driver's `#include "param.h"` looks in its own folder first, so it must not
+    sit next to the reference headers), together with the reference's data.h; the dataset readers
+    are replaced by synthetic_data.cpp and libjpeg by empty stub headers.  Skipped when the
+    reference tree is absent.
+"""
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+OUT = os.path.join(ROOT, "build", "dropin")
+# -maxrregcount=64 as in the reference Makefile (Makefile:15): the drivers launch 1024-thread blocks
+NVCC = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-rdc=true",
+        "-maxrregcount=64", "-w"]
+DRIVERS = ["mnist_mlp", "cifar10_vgg", "cifar10_resnet", "imagenet_resnet"]
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        raise RuntimeError("build failed")
+
+
+def _stale(target, deps):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def _headers():
+    csrc = os.path.join(os.path.dirname(HERE), "csrc")
+    return [os.path.join(HERE, f) for f in ("utility.h", "param.h", "kernel.cuh")] + \
+           [os.path.join(csrc, f) for f in ("bnn_layers.cuh", "bnn_warp.cuh")]
+
+
+def build_runner():
+    os.makedirs(OUT, exist_ok=True)
+    src = os.path.join(HERE, "net_runner.cu")
+    out = os.path.join(OUT, "net_runner")
+    if _stale(out, [src] + _headers()):
+        _run(NVCC + ["-I", HERE, "-o", out, src])
+    return out
+
+
+def build_reference_drivers(ref_root="/root/reference"):
+    if not os.path.exists(os.path.join(ref_root, "data.h")):
+        return []
+    os.makedirs(OUT, exist_ok=True)
+    shutil.copyfile(os.path.join(ref_root, "data.h"), os.path.join(OUT, "data.h"))
+    data_src = os.path.join(HERE, "synthetic_data.cpp")
+    from concurrent.futures import ThreadPoolExecutor
+
+    def one(name):
+        src = os.path.join(ref_root, name + ".cu")
+        if not os.path.exists(src):
+            return None
+        staged = os.path.join(OUT, name + ".cu")
+        out = os.path.join(OUT, name)
+        if _stale(out, [src, data_src] + _headers()):
+            shutil.copyfile(src, staged)
+            _run(NVCC + ["-I", OUT, "-I", HERE, "-I", os.path.join(HERE, "stubs"), "-o", out, staged, data_src])
+        return out
+
+    with ThreadPoolExecutor(max_workers=len(DRIVERS)) as pool:      # the compiles are independent
+        return [b for b in pool.map(one, DRIVERS) if b]
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref-root", default="/root/reference")
+    a = ap.parse_args()
+    print(build_runner())
+    for b in build_reference_drivers(a.ref_root):
+        print(b)

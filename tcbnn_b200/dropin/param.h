@@ -1,0 +1,490 @@
+// Drop-in replacement for the reference's param.h (pnnl/TCBNN): the five layer-parameter
+// classes with the reference's constructor arguments, public fields and methods, on top of the
+// B200 layer code in ../csrc/bnn_layers.cuh.
+//
+// What is kept: class and method names, argument order and defaults (param.h:115-1065), the
+// weight-file order consumed through launch_array, "initialize() returns the device-side copy
+// that the driver's cooperative kernel receives", borrowed input / residual pointers, owned
+// outputs, exit-on-error.
+// What is different inside: activations are NHWC bit-packed words (no HWNC 8x128 tiling),
+// residuals are NHWC int32 with the reference's PAD128 channel stride, sizes are computed in size_t, and every object carries the
+// argument block the layer loops read on the device.
+#ifndef PARAM_H
+#define PARAM_H
+
+#include "utility.h"
+#include "../csrc/bnn_layers.cuh"
+
+const int dev = 0;
+
+namespace tcbnn_dropin {
+__global__ void k_pack_rows(const float* x, int rows, int cols, int ld, uin32* out) { tcbnn::pack_rows(x, rows, cols, ld, out); }
+__global__ void k_unpack_rows(const uin32* in, int rows, int cols, int ld, float* out) { tcbnn::unpack_rows(in, rows, cols, ld, out); }
+__global__ void k_pack_fc_weight(const float* W, int K, int N, int ld, uin32* out) { tcbnn::pack_fc_weight(W, K, N, ld, out); }
+__global__ void k_pack_conv_filter(const float* F, int RS, int C, int O, uin32* out) { tcbnn::pack_conv_filter(F, RS, C, O, out); }
+__global__ void k_pack_inconv_filter(const float* F, int RS, int O, uin32* out) { tcbnn::pack_inconv_filter(F, RS, O, out); }
+__global__ void k_conv_prepare(const uin32* fbits, int O, int R, int S, int Cw, int W_in, int KP, uin32* wq,
+                               uin32* ktab, int* pwt, int* pwtot) {
+    tcbnn::conv_prepare(fbits, O, R, S, Cw, W_in, KP, wq, ktab, pwt, pwtot);
+}
+inline int grid_for(size_t n) { size_t b = (n + 255) / 256; return (int)(b < 1 ? 1 : b > 4096 ? 4096 : b); }
+inline int fc_ld(int k) { return STEP128(k) * 4; }
+
+// reads `n` floats from the weight file and returns them in a fresh device buffer
+inline float* upload_from_file(FILE* cf, size_t n, float** host_keep) {
+    float* h = NULL;
+    SAFE_ALOC_HOST(h, n * sizeof(float));
+    launch_array(cf, h, (unsigned)n);
+    float* d = NULL;
+    SAFE_ALOC_GPU(d, n * sizeof(float));
+    CUDA_SAFE_CALL(cudaMemcpy(d, h, n * sizeof(float), cudaMemcpyHostToDevice));
+    if (host_keep) *host_keep = h; else { SAFE_FREE_HOST(h); }
+    return d;
+}
+// pad / output arithmetic of the reference constructors (param.h:719-728, 897-906)
+inline void conv_geometry(int H, int W, int R, int S, int sh, int sw, bool padding, int ph, int pw,
+                          int* pad_h, int* pad_w, int* OH, int* OW) {
+    *pad_h = padding ? ((((H + sh - (H % sh)) / sh - 1) * sh + R - H) / 2) : 0;
+    *pad_w = padding ? ((((W + sw - (W % sw)) / sw - 1) * sw + S - W) / 2) : 0;
+    const int bh = padding ? (H + sh - 1) / sh : ((H - R) / sh + 1);
+    const int bw = padding ? (W + sw - 1) / sw : ((W - S) / sw + 1);
+    *OH = (bh + ph - 1) / ph;
+    *OW = (bw + pw - 1) / pw;
+}
+inline float* unpack_to_host(const uin32* bits, size_t rows, int cols, int ld) {
+    float *d = NULL, *h = NULL;
+    SAFE_ALOC_GPU(d, rows * cols * sizeof(float));
+    SAFE_ALOC_HOST(h, rows * cols * sizeof(float));
+    k_unpack_rows<<<grid_for(rows * cols), 256>>>(bits, (int)rows, cols, ld, d);
+    CUDA_CHECK_KERNEL();
+    CUDA_SAFE_CALL(cudaMemcpy(h, d, rows * cols * sizeof(float), cudaMemcpyDeviceToHost));
+    SAFE_FREE_GPU(d);
+    return h;
+}
+}  // namespace tcbnn_dropin
+
+// fp32 [input_height][input_width] -> bit rows (param.h:115-222)
+class In128LayerParam {
+public:
+    In128LayerParam(const char* _name, int _input_height, int _input_width)
+        : input(NULL), input_gpu(NULL), output(NULL), output_gpu(NULL), input_width(_input_width),
+          input_height(_input_height), output_width(_input_width), output_height(_input_height), gpu(NULL) {
+        strncpy(name, _name, 8);
+    }
+    size_t input_size() { return (size_t)input_height * input_width; }
+    size_t input_bytes() { return input_size() * sizeof(float); }
+    size_t output_size() { return (size_t)output_height * output_width; }
+    size_t output_bytes() { return output_size() * sizeof(float); }
+    int ld() { return tcbnn_dropin::fc_ld(output_width); }
+    size_t output_bit_size() { return (size_t)output_height * ld() / 4; }
+    size_t output_bit_bytes() { return output_bit_size() * sizeof(uin128); }
+    In128LayerParam* initialize(float* input) {
+        CHECK_NULL_POINTER(input);
+        this->input = input;
+        SAFE_ALOC_GPU(input_gpu, input_bytes());
+        CUDA_SAFE_CALL(cudaMemcpy(input_gpu, input, input_bytes(), cudaMemcpyHostToDevice));
+        SAFE_ALOC_GPU(output_gpu, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemset(output_gpu, 0, output_bit_bytes()));
+        return ready();
+    }
+    In128LayerParam* ready() {
+        CHECK_NULL_POINTER(input_gpu);
+        CHECK_NULL_POINTER(output_gpu);
+        SAFE_ALOC_GPU(gpu, sizeof(In128LayerParam));
+        CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(In128LayerParam), cudaMemcpyHostToDevice));
+        return gpu;
+    }
+    void set_output_gpu(uin32* p) { output_gpu = p; }
+    uin32* get_output_gpu() { return output_gpu; }
+    uin32* download_output() {
+        if (output == NULL) SAFE_ALOC_HOST(output, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemcpy(output, output_gpu, output_bit_bytes(), cudaMemcpyDeviceToHost));
+        return output;
+    }
+    float* download_full_output() { return tcbnn_dropin::unpack_to_host(output_gpu, output_height, output_width, ld()); }
+    void release() {
+        SAFE_FREE_GPU(input_gpu); SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(gpu); SAFE_FREE_HOST(output);
+    }
+    ~In128LayerParam() { release(); }
+public:
+    float* input; float* input_gpu; uin32* output; uin32* output_gpu;
+    int input_width, input_height, output_width, output_height;
+    In128LayerParam* gpu;
+    char name[8];
+};
+
+// hidden FC layer (param.h:224-385)
+class Fc128LayerParam {
+public:
+    Fc128LayerParam(const char* _name, int _input_height, int _input_width, int _weight_width)
+        : weight(NULL), weight_gpu(NULL), bn(NULL), bn_gpu(NULL), input(NULL), input_gpu(NULL), output(NULL),
+          output_gpu(NULL), weight_height(_input_width), weight_width(_weight_width),
+          input_height(_input_height), input_width(_input_width), output_height(_input_height),
+          output_width(_weight_width), bn_width(_weight_width), input_ld(0), gpu(NULL) {
+        strncpy(name, _name, 8);
+    }
+    size_t weight_size() { return (size_t)weight_height * weight_width; }
+    size_t weight_bytes() { return weight_size() * sizeof(float); }
+    size_t weight_bit_bytes() { return (size_t)weight_width * tcbnn_dropin::fc_ld(weight_height) * 4; }
+    size_t output_size() { return (size_t)output_height * output_width; }
+    size_t output_bytes() { return output_size() * sizeof(float); }
+    int ld() { return tcbnn_dropin::fc_ld(output_width); }
+    size_t output_bit_size() { return (size_t)output_height * ld() / 4; }
+    size_t output_bit_bytes() { return output_bit_size() * sizeof(uin128); }
+    int bn_size() { return bn_width; }
+    size_t bn_bytes() { return bn_size() * sizeof(float); }
+    // rows of the producer: a conv layer that feeds an FC layer pads each image to 128 bits
+    void set_input_gpu(uin32* p) { input_gpu = p; input_ld = tcbnn_dropin::fc_ld(input_width); }
+    Fc128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu) {
+        float* w = tcbnn_dropin::upload_from_file(config_file, weight_size(), &weight);
+        SAFE_ALOC_GPU(weight_gpu, weight_bit_bytes());
+        tcbnn_dropin::k_pack_fc_weight<<<tcbnn_dropin::grid_for(weight_bit_bytes() / 4), 256>>>(
+            w, weight_height, weight_width, tcbnn_dropin::fc_ld(weight_height), weight_gpu);
+        CUDA_CHECK_KERNEL();
+        SAFE_FREE_GPU(w);
+        bn_gpu = tcbnn_dropin::upload_from_file(config_file, bn_size(), &bn);
+        SAFE_ALOC_GPU(output_gpu, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemset(output_gpu, 0, output_bit_bytes()));
+        set_input_gpu(prev_layer_gpu);
+        return ready();
+    }
+    Fc128LayerParam* ready() {
+        CHECK_NULL_POINTER(input_gpu);
+        CHECK_NULL_POINTER(output_gpu);
+        args.A = input_gpu; args.W = weight_gpu; args.M = input_height; args.N = weight_width;
+        args.K = input_width; args.lda = input_ld; args.ldw = tcbnn_dropin::fc_ld(weight_height);
+        args.mode = tcbnn::GEMM_FC_BITS; args.out = output_gpu; args.ldo = ld();
+        args.p0 = bn_gpu; args.p1 = NULL; args.splits = 1; args.partial = NULL;
+        SAFE_ALOC_GPU(gpu, sizeof(Fc128LayerParam));
+        CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Fc128LayerParam), cudaMemcpyHostToDevice));
+        return gpu;
+    }
+    uin32* get_output_gpu() { return output_gpu; }
+    uin32* download_output() {
+        if (output == NULL) SAFE_ALOC_HOST(output, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemcpy(output, output_gpu, output_bit_bytes(), cudaMemcpyDeviceToHost));
+        return output;
+    }
+    float* download_full_output() { return tcbnn_dropin::unpack_to_host(output_gpu, output_height, output_width, ld()); }
+    void release() {
+        SAFE_FREE_HOST(weight); SAFE_FREE_HOST(bn); SAFE_FREE_HOST(output);
+        SAFE_FREE_GPU(weight_gpu); SAFE_FREE_GPU(bn_gpu); SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(gpu);
+    }
+    ~Fc128LayerParam() { release(); }
+public:
+    float* weight; uin32* weight_gpu; float* bn; float* bn_gpu;
+    uin32* input; uin32* input_gpu; uin32* output; uin32* output_gpu;
+    int weight_height, weight_width, input_height, input_width, output_height, output_width, bn_width;
+    int input_ld;
+    tcbnn::GemmArgs args;
+    Fc128LayerParam* gpu;
+    char name[8];
+};
+
+// output layer (param.h:388-531)
+class Out128LayerParam {
+public:
+    Out128LayerParam(const char* _name, int _input_height, int _input_width, int _weight_width)
+        : weight(NULL), weight_gpu(NULL), bn_scale(NULL), bn_scale_gpu(NULL), bn_bias(NULL), bn_bias_gpu(NULL),
+          input(NULL), input_gpu(NULL), output(NULL), output_gpu(NULL), weight_height(_input_width),
+          weight_width(_weight_width), input_height(_input_height), input_width(_input_width),
+          output_height(_input_height), output_width(_weight_width), gpu(NULL) {
+        strncpy(name, _name, 8);
+    }
+    size_t weight_size() { return (size_t)weight_height * weight_width; }
+    size_t weight_bytes() { return weight_size() * sizeof(float); }
+    size_t weight_bit_bytes() { return (size_t)weight_width * tcbnn_dropin::fc_ld(weight_height) * 4; }
+    size_t output_size() { return (size_t)output_height * output_width; }
+    size_t output_bytes() { return output_size() * sizeof(float); }
+    int bn_size() { return weight_width; }
+    size_t bn_bytes() { return bn_size() * sizeof(float); }
+    void set_input_gpu(uin32* p) { input_gpu = p; }
+    Out128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu) {
+        float* w = tcbnn_dropin::upload_from_file(config_file, weight_size(), &weight);
+        SAFE_ALOC_GPU(weight_gpu, weight_bit_bytes());
+        tcbnn_dropin::k_pack_fc_weight<<<tcbnn_dropin::grid_for(weight_bit_bytes() / 4), 256>>>(
+            w, weight_height, weight_width, tcbnn_dropin::fc_ld(weight_height), weight_gpu);
+        CUDA_CHECK_KERNEL();
+        SAFE_FREE_GPU(w);
+        bn_scale_gpu = tcbnn_dropin::upload_from_file(config_file, bn_size(), &bn_scale);
+        bn_bias_gpu = tcbnn_dropin::upload_from_file(config_file, bn_size(), &bn_bias);
+        SAFE_ALOC_GPU(output_gpu, output_bytes());
+        CUDA_SAFE_CALL(cudaMemset(output_gpu, 0, output_bytes()));
+        set_input_gpu(prev_layer_gpu);
+        return ready();
+    }
+    Out128LayerParam* ready() {
+        CHECK_NULL_POINTER(input_gpu);
+        CHECK_NULL_POINTER(output_gpu);
+        args.A = input_gpu; args.W = weight_gpu; args.M = input_height; args.N = weight_width;
+        args.K = input_width; args.lda = tcbnn_dropin::fc_ld(input_width);
+        args.ldw = tcbnn_dropin::fc_ld(weight_height); args.mode = tcbnn::GEMM_OUT_AFFINE;
+        args.out = output_gpu; args.ldo = weight_width; args.p0 = bn_scale_gpu; args.p1 = bn_bias_gpu;
+        args.splits = 1; args.partial = NULL;
+        SAFE_ALOC_GPU(gpu, sizeof(Out128LayerParam));
+        CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Out128LayerParam), cudaMemcpyHostToDevice));
+        return gpu;
+    }
+    float* get_output_gpu() { return output_gpu; }
+    float* download_output() {
+        if (output == NULL) SAFE_ALOC_HOST(output, output_bytes());
+        CUDA_SAFE_CALL(cudaMemcpy(output, output_gpu, output_bytes(), cudaMemcpyDeviceToHost));
+        return output;
+    }
+    void release() {
+        SAFE_FREE_HOST(weight); SAFE_FREE_HOST(bn_scale); SAFE_FREE_HOST(bn_bias); SAFE_FREE_HOST(output);
+        SAFE_FREE_GPU(weight_gpu); SAFE_FREE_GPU(bn_scale_gpu); SAFE_FREE_GPU(bn_bias_gpu);
+        SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(gpu);
+    }
+    ~Out128LayerParam() { release(); }
+public:
+    float* weight; uin32* weight_gpu; float* bn_scale; float* bn_scale_gpu; float* bn_bias; float* bn_bias_gpu;
+    uin32* input; uin32* input_gpu; float* output; float* output_gpu;
+    int weight_height, weight_width, input_height, input_width, output_height, output_width;
+    tcbnn::GemmArgs args;
+    Out128LayerParam* gpu;
+    char name[8];
+};
+
+// first conv layer on fp32 NCHW images (param.h:701-870)
+class InConv128LayerParam {
+public:
+    InConv128LayerParam(const char* _name, int _input_height, int _input_width, int _filter_height,
+                        int _filter_width, int _input_channels, int _output_channels, int _batch,
+                        int _stride_height = 1, int _stride_width = 1, bool _padding = true,
+                        int _pool_height = 1, int _pool_width = 1, bool _save_residual = false)
+        : input(NULL), input_gpu(NULL), input_width(_input_width), input_height(_input_height),
+          input_channels(_input_channels), filter(NULL), filter_gpu(NULL), filter_width(_filter_width),
+          filter_height(_filter_height), output(NULL), output_gpu(NULL), output_channels(_output_channels),
+          padding(_padding), bn(NULL), bn_gpu(NULL), batch(_batch), stride_height(_stride_height),
+          stride_width(_stride_width), pool_width(_pool_width), pool_height(_pool_height),
+          save_residual(_save_residual), output_residual_gpu(NULL), gpu(NULL) {
+        strncpy(name, _name, 8);
+        tcbnn_dropin::conv_geometry(input_height, input_width, filter_height, filter_width, stride_height,
+                                    stride_width, padding, pool_height, pool_width, &pad_h, &pad_w,
+                                    &output_height, &output_width);
+        if (input_channels != 3 || output_channels > 128 || pool_height != pool_width || pool_height > 2) {
+            fprintf(stderr, "InConv128LayerParam %s: unsupported shape.\n", name);
+            exit(-1);
+        }
+    }
+    size_t input_size() { return (size_t)input_channels * input_height * input_width * batch; }
+    size_t input_bytes() { return input_size() * sizeof(float); }
+    size_t filter_size() { return (size_t)output_channels * input_channels * filter_height * filter_width; }
+    size_t filter_bytes() { return filter_size() * sizeof(float); }
+    size_t filter_bit_bytes() { return (size_t)filter_height * filter_width * 3 * STEP32(output_channels) * 4; }
+    size_t output_size() { return (size_t)output_channels * output_height * output_width * batch; }
+    size_t output_bytes() { return output_size() * sizeof(uin32); }
+    size_t output_bit_bytes() { return (size_t)batch * output_height * output_width * STEP32(output_channels) * 4; }
+    size_t output_bit_size() { return output_bit_bytes() / sizeof(uin128); }
+    int bn_size() { return output_channels; }
+    size_t bn_bytes() { return bn_size() * sizeof(float); }
+    // residual channel stride is PAD128(output_channels) and the buffer is zero-filled, as in the
+    // reference (param.h:756-758, 794-795): a consumer may ask for more channels than were written
+    size_t residual_size() { return (size_t)PAD128(output_channels) * batch * output_height * pool_height * output_width * pool_width; }
+    size_t residual_bytes() { return residual_size() * sizeof(int); }
+    InConv128LayerParam* initialize(float* input, FILE* config_file) {
+        CHECK_NULL_POINTER(input);
+        this->input = input;
+        SAFE_ALOC_GPU(input_gpu, input_bytes());
+        CUDA_SAFE_CALL(cudaMemcpy(input_gpu, input, input_bytes(), cudaMemcpyHostToDevice));
+        float* f = tcbnn_dropin::upload_from_file(config_file, filter_size(), &filter);
+        SAFE_ALOC_GPU(filter_gpu, filter_bit_bytes());
+        tcbnn_dropin::k_pack_inconv_filter<<<tcbnn_dropin::grid_for(filter_bit_bytes() / 4), 256>>>(
+            f, filter_height * filter_width, output_channels, filter_gpu);
+        CUDA_CHECK_KERNEL();
+        SAFE_FREE_GPU(f);
+        bn_gpu = tcbnn_dropin::upload_from_file(config_file, bn_size(), &bn);
+        SAFE_ALOC_GPU(output_gpu, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemset(output_gpu, 0, output_bit_bytes()));
+        if (save_residual) {
+            SAFE_ALOC_GPU(output_residual_gpu, residual_bytes());
+            CUDA_SAFE_CALL(cudaMemset(output_residual_gpu, 0, residual_bytes()));
+        }
+        return ready();
+    }
+    InConv128LayerParam* ready() {
+        CHECK_NULL_POINTER(input_gpu);
+        CHECK_NULL_POINTER(output_gpu);
+        if (save_residual) CHECK_NULL_POINTER(output_residual_gpu);
+        args.x = input_gpu; args.fbits = filter_gpu; args.thr = bn_gpu;
+        args.B = batch; args.H = input_height; args.W = input_width; args.O = output_channels;
+        args.R = filter_height; args.S = filter_width; args.sh = stride_height; args.sw = stride_width;
+        args.pad_h = pad_h; args.pad_w = pad_w; args.pool = pool_height; args.OH = output_height;
+        args.OW = output_width; args.out = output_gpu;
+        args.out_image_stride = (long long)output_height * output_width * STEP32(output_channels);
+        args.res_out = save_residual ? output_residual_gpu : NULL; args.res_out_bytes = 4;
+        args.res_out_ld = PAD128(output_channels); args.acc_out = NULL;
+        SAFE_ALOC_GPU(gpu, sizeof(InConv128LayerParam));
+        CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(InConv128LayerParam), cudaMemcpyHostToDevice));
+        return gpu;
+    }
+    uin32* get_output_gpu() { return output_gpu; }
+    int* get_output_residual_gpu() { return output_residual_gpu; }
+    unsigned* download_output() {
+        if (output == NULL) SAFE_ALOC_HOST(output, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemcpy(output, output_gpu, output_bit_bytes(), cudaMemcpyDeviceToHost));
+        return output;
+    }
+    // +-1 floats, NHWC [batch][output_height][output_width][output_channels] (param.h:809-827)
+    float* download_full_output() {
+        return tcbnn_dropin::unpack_to_host(output_gpu, (size_t)batch * output_height * output_width,
+                                            output_channels, STEP32(output_channels));
+    }
+    void release() {
+        SAFE_FREE_HOST(filter); SAFE_FREE_HOST(bn); SAFE_FREE_HOST(output);
+        SAFE_FREE_GPU(input_gpu); SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(filter_gpu); SAFE_FREE_GPU(bn_gpu);
+        SAFE_FREE_GPU(gpu); SAFE_FREE_GPU(output_residual_gpu);
+    }
+    ~InConv128LayerParam() { release(); }
+public:
+    float* input; float* input_gpu; int input_width, input_height, input_channels;
+    float* filter; uin32* filter_gpu; int filter_width, filter_height;
+    uin32* output; uin32* output_gpu; int output_width, output_height, output_channels;
+    bool padding; float* bn; float* bn_gpu; int batch, stride_height, stride_width, pad_h, pad_w;
+    int pool_width, pool_height; bool save_residual; int* output_residual_gpu;
+    tcbnn::InConvArgs args;
+    InConv128LayerParam* gpu;
+    char name[8];
+};
+
+// binary conv layer (param.h:872-1065)
+class Conv128LayerParam {
+public:
+    Conv128LayerParam(const char* _name, int _input_height, int _input_width, int _filter_height,
+                      int _filter_width, int _input_channels, int _output_channels, int _batch,
+                      int _stride_height = 1, int _stride_width = 1, bool _padding = true,
+                      int _pool_height = 1, int _pool_width = 1, bool _ahead_fc = false,
+                      bool _save_residual = false, bool _inject_residual = false,
+                      int _residual_channels = 0, bool _residual_pool = false)
+        : input(NULL), input_gpu(NULL), input_width(_input_width), input_height(_input_height),
+          input_channels(_input_channels), filter(NULL), filter_gpu(NULL), filter_width(_filter_width),
+          filter_height(_filter_height), output(NULL), output_gpu(NULL), output_channels(_output_channels),
+          bn(NULL), bn_gpu(NULL), batch(_batch), stride_height(_stride_height), stride_width(_stride_width),
+          padding(_padding), pool_width(_pool_width), pool_height(_pool_height), ahead_fc(_ahead_fc),
+          save_residual(_save_residual), output_residual_gpu(NULL), inject_residual(_inject_residual),
+          input_residual_gpu(NULL), residual_channels(_residual_channels), residual_pool(_residual_pool),
+          prepared_gpu(NULL), input_residual_channels(0), gpu(NULL) {
+        strncpy(name, _name, 8);
+        tcbnn_dropin::conv_geometry(input_height, input_width, filter_height, filter_width, stride_height,
+                                    stride_width, padding, pool_height, pool_width, &pad_h, &pad_w,
+                                    &output_height, &output_width);
+        if ((STEP32(input_channels) & 1) || filter_height > 15 || filter_width > 15 ||
+            pool_height != pool_width || pool_height > 2 ||
+            ((save_residual || inject_residual) && pool_height != 1)) {
+            fprintf(stderr, "Conv128LayerParam %s: unsupported shape.\n", name);
+            exit(-1);
+        }
+    }
+    int Cw() { return STEP32(input_channels); }
+    int Ow() { return STEP32(output_channels); }
+    int KP() { return ((filter_height * filter_width * Cw() + 7) / 8) * 4; }
+    size_t filter_size() { return (size_t)output_channels * input_channels * filter_height * filter_width; }
+    size_t filter_bytes() { return filter_size() * sizeof(float); }
+    size_t filter_bit_bytes() { return (size_t)output_channels * filter_height * filter_width * Cw() * 4; }
+    size_t output_size() { return (size_t)output_channels * output_height * output_width * batch; }
+    size_t output_bytes() { return output_size() * sizeof(uin32); }
+    // images that feed an FC layer are padded to whole 128-bit rows (they are the FC's input rows)
+    size_t image_words() {
+        const size_t w = (size_t)output_height * output_width * Ow();
+        return ahead_fc ? (size_t)tcbnn_dropin::fc_ld((int)(w * 32)) : w;
+    }
+    size_t output_bit_bytes() { return (size_t)batch * image_words() * 4; }
+    size_t output_bit_size() { return output_bit_bytes() / sizeof(uin128); }
+    int bn_size() { return output_channels; }
+    size_t bn_bytes() { return bn_size() * sizeof(float); }
+    // channel stride PAD128(output_channels), zero-filled (param.h:925-927, 979-980)
+    size_t residual_size() { return (size_t)PAD128(output_channels) * batch * output_height * output_width; }
+    size_t residual_bytes() { return residual_size() * sizeof(int); }
+    void set_input_gpu(uin32* p) { input_gpu = p; }
+    // the injected residual is indexed with channel stride PAD128(residual_channels), exactly as
+    // the reference indexes it (kernel.cuh:780-791)
+    void set_input_residual_gpu(int* p) {
+        input_residual_gpu = p;
+        input_residual_channels = PAD128(residual_channels);
+    }
+    Conv128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu, int* input_residual_gpu = NULL) {
+        float* f = tcbnn_dropin::upload_from_file(config_file, filter_size(), &filter);
+        SAFE_ALOC_GPU(filter_gpu, filter_bit_bytes());
+        tcbnn_dropin::k_pack_conv_filter<<<tcbnn_dropin::grid_for(filter_bit_bytes() / 4), 256>>>(
+            f, filter_height * filter_width, input_channels, output_channels, filter_gpu);
+        CUDA_CHECK_KERNEL();
+        SAFE_FREE_GPU(f);
+        // prepared filter: [O][2*KP] words, pair table [KP], per-tap popcounts [R*S][O], totals [O]
+        const size_t wq = (size_t)output_channels * 2 * KP(), kt = KP();
+        const size_t pw = (size_t)filter_height * filter_width * output_channels, pt = output_channels;
+        SAFE_ALOC_GPU(prepared_gpu, (wq + kt + pw + pt) * 4);
+        tcbnn_dropin::k_conv_prepare<<<tcbnn_dropin::grid_for(wq), 256>>>(
+            filter_gpu, output_channels, filter_height, filter_width, Cw(), input_width, KP(), prepared_gpu,
+            prepared_gpu + wq, (int*)(prepared_gpu + wq + kt), (int*)(prepared_gpu + wq + kt + pw));
+        CUDA_CHECK_KERNEL();
+        bn_gpu = tcbnn_dropin::upload_from_file(config_file, bn_size(), &bn);
+        SAFE_ALOC_GPU(output_gpu, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemset(output_gpu, 0, output_bit_bytes()));
+        set_input_gpu(prev_layer_gpu);
+        if (save_residual) {
+            SAFE_ALOC_GPU(output_residual_gpu, residual_bytes());
+            CUDA_SAFE_CALL(cudaMemset(output_residual_gpu, 0, residual_bytes()));
+        }
+        if (inject_residual) set_input_residual_gpu(input_residual_gpu);
+        return ready();
+    }
+    Conv128LayerParam* ready() {
+        CHECK_NULL_POINTER(input_gpu);
+        CHECK_NULL_POINTER(output_gpu);
+        if (save_residual) CHECK_NULL_POINTER(output_residual_gpu);
+        if (inject_residual) CHECK_NULL_POINTER(input_residual_gpu);
+        const size_t wq = (size_t)output_channels * 2 * KP(), kt = KP();
+        const size_t pw = (size_t)filter_height * filter_width * output_channels;
+        args.in = input_gpu; args.wq = prepared_gpu; args.ktab = prepared_gpu + wq;
+        args.pwt = (const int*)(prepared_gpu + wq + kt); args.pwtot = (const int*)(prepared_gpu + wq + kt + pw);
+        args.thr = bn_gpu; args.B = batch; args.H = input_height; args.W = input_width;
+        args.C = input_channels; args.Cw = Cw(); args.O = output_channels; args.R = filter_height;
+        args.S = filter_width; args.sh = stride_height; args.sw = stride_width; args.pad_h = pad_h;
+        args.pad_w = pad_w; args.pool = pool_height; args.OH = output_height; args.OW = output_width;
+        args.KP = KP();
+        args.res_in = inject_residual ? input_residual_gpu : NULL; args.res_in_bytes = 4;
+        args.res_in_ch = input_residual_channels; args.residual_channels = residual_channels;
+        args.residual_pool = residual_pool;
+        args.out = output_gpu; args.out_image_stride = (long long)image_words();
+        args.res_out = save_residual ? output_residual_gpu : NULL; args.res_out_bytes = 4;
+        args.res_out_ld = PAD128(output_channels); args.acc_out = NULL;
+        SAFE_ALOC_GPU(gpu, sizeof(Conv128LayerParam));
+        CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Conv128LayerParam), cudaMemcpyHostToDevice));
+        return gpu;
+    }
+    uin32* get_output_gpu() { return output_gpu; }
+    int* get_output_residual_gpu() { return output_residual_gpu; }
+    unsigned* download_output() {
+        if (output == NULL) SAFE_ALOC_HOST(output, output_bit_bytes());
+        CUDA_SAFE_CALL(cudaMemcpy(output, output_gpu, output_bit_bytes(), cudaMemcpyDeviceToHost));
+        return output;
+    }
+    // +-1 floats, NHWC (param.h:996-1014); also right for layers that feed an FC layer
+    float* download_full_output() {
+        if (ahead_fc) {
+            fprintf(stderr, "download_full_output: %s feeds an FC layer; unpack its rows with the FC width.\n", name);
+        }
+        return tcbnn_dropin::unpack_to_host(output_gpu, (size_t)batch * output_height * output_width,
+                                            output_channels, Ow());
+    }
+    void release() {
+        SAFE_FREE_HOST(filter); SAFE_FREE_HOST(bn); SAFE_FREE_HOST(output);
+        SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(filter_gpu); SAFE_FREE_GPU(prepared_gpu); SAFE_FREE_GPU(bn_gpu);
+        SAFE_FREE_GPU(gpu); SAFE_FREE_GPU(output_residual_gpu);
+    }
+    ~Conv128LayerParam() { release(); }
+public:
+    uin32* input; uin32* input_gpu; int input_width, input_height, input_channels;
+    float* filter; uin32* filter_gpu; int filter_width, filter_height;
+    uin32* output; uin32* output_gpu; int output_width, output_height, output_channels;
+    float* bn; float* bn_gpu; int batch, stride_height, stride_width; bool padding; int pad_h, pad_w;
+    int pool_width, pool_height; bool ahead_fc; bool save_residual; int* output_residual_gpu;
+    bool inject_residual; int* input_residual_gpu; int residual_channels; bool residual_pool;
+    uin32* prepared_gpu; int input_residual_channels;
+    tcbnn::ConvArgs args;
+    Conv128LayerParam* gpu;
+    char name[8];
+};
+
+#endif

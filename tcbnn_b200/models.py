@@ -9,6 +9,7 @@ Topologies follow the reference drivers, not the textbook networks:
                  saved), 16 binary 3x3 convs in 8 basic blocks (64/128/256/512; stride 2 at the
                  start of stages 2-4), every second conv adds the previous block's integer
                  residual (2x2 max-pooled when the stage changes), FC 25088->512, out 512->1000.
+  * resnet_cifar: cifar10_resnet.cu:189-259 -- three-stage variant on 32x32 images.
   * vgg_cifar  : cifar10_vgg.cu:162-199 -- conv 3->128, 128->128+pool, ->256, 256+pool, ->512,
                  512+pool (feeds FC), FC 8192->1024->1024, out ->10.
   * mlp        : mnist_mlp.cu:112-126 -- 784 -> 1024 -> 1024 -> 1024 -> 10.
@@ -48,6 +49,32 @@ def resnet18_spec(batch, image=224, classes=1000):
     L.append(dict(type="fc", name="Fc1", N=512))
     L.append(dict(type="out", name="Fout", N=classes))
     return dict(name="resnet18", batch=batch, layers=L)
+
+
+def resnet_cifar_spec(batch, image=32, classes=10):
+    """cifar10_resnet.cu:189-259 -- 3x3 first layer to 128 channels (residual saved), three stages
+    of two basic blocks (128/256/512, stride 2 at the start of stages 2 and 3), FC -> 512 -> out."""
+    L = [dict(type="inconv", name="Conv1", H=image, W=image, R=3, S=3, C=3, O=128, stride=1, pool=1,
+              save_residual=True)]
+
+    def conv(name, C, O, stride=1, **kw):
+        L.append(dict(type="conv", name=name, C=C, O=O, R=3, S=3, stride=stride, pool=1, **kw))
+
+    conv("L1B1C1", 128, 128)
+    conv("L1B1C2", 128, 128, save_residual=True, inject=0, residual_channels=128)
+    conv("L1B2C1", 128, 128)
+    conv("L1B2C2", 128, 128, save_residual=True, inject=2, residual_channels=128)
+    conv("L2B1C1", 128, 256, stride=2)
+    conv("L2B1C2", 256, 256, save_residual=True, inject=4, residual_channels=128, residual_pool=True)
+    conv("L2B2C1", 256, 256)
+    conv("L2B2C2", 256, 256, save_residual=True, inject=6, residual_channels=256)
+    conv("L3B1C1", 256, 512, stride=2)
+    conv("L3B1C2", 512, 512, save_residual=True, inject=8, residual_channels=256, residual_pool=True)
+    conv("L3B2C1", 512, 512)
+    conv("L3B2C2", 512, 512, ahead_fc=True, inject=10, residual_channels=512)
+    L.append(dict(type="fc", name="Fc1", N=512))
+    L.append(dict(type="out", name="Fout", N=classes))
+    return dict(name="resnet_cifar", batch=batch, layers=L)
 
 
 def vgg_cifar_spec(batch, image=32, classes=10):
