@@ -51,7 +51,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -203,25 +203,36 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end from host buffers ----------------------------------------------------
-    # Every step copies its fp32 images from pinned host memory and reads its logits back; the
-    # copy of step i+1 runs on a second stream while step i computes (models.HostFeeder).
-    feeder = models.HostFeeder(net)
+    # Every step copies its images from pinned host memory and reads its logits back; the copy
+    # of step i+1 runs on a second stream while step i computes (models.HostFeeder).
+    # `e2e` feeds the images as bytes (uint8 + per-channel value table, tcbnn_inconv_layer_u8:
+    # the reader's normalisation happens in the first layer, results identical);
+    # `e2e_fp32_images` feeds the reference's fp32 images.
+    def timed_feed(network, batch_host):
+        feeder = models.HostFeeder(network)
 
-    def on_result(out):
-        if world > 1:
-            tdist.gather_logits(out, gathered)
-        logits_host.copy_(out, non_blocking=True)
+        def on_result(out):
+            if world > 1:
+                tdist.gather_logits(out, gathered)
+            logits_host.copy_(out, non_blocking=True)
 
-    feeder.run([x_host] * 2, on_result)
-    sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    feeder.run([x_host] * args.steps, on_result)
-    e1.record()
-    sync()
-    ms_e2e = e0.elapsed_time(e1)
+        feeder.run([batch_host] * 2, on_result)
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        feeder.run([batch_host] * args.steps, on_result)
+        e1.record()
+        sync()
+        return e0.elapsed_time(e1)
 
-    ms, ms_e2e = tdist.max_over_ranks([ms, ms_e2e], dev)
+    ms_e2e_f32 = timed_feed(net, x_host)
+    u8_np, lut = models.synthetic_input_u8(spec, tdist.shard_seed(4321, rank))
+    x8_host = torch.from_numpy(u8_np).pin_memory()
+    net8 = models.Network(spec, models.synthetic_weights(spec, 1234), x8_host,
+                          input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND, input_lut=lut)
+    ms_e2e = timed_feed(net8, x8_host)
+
+    ms, ms_e2e, ms_e2e_f32 = tdist.max_over_ranks([ms, ms_e2e, ms_e2e_f32], dev)
 
     if rank == 0:
         conv_ms, launches = 0.0, 0
@@ -252,7 +263,12 @@ def main():
                        "parallelism": "batch-sharded x%d, NCCL all-gather of logits" % world,
                        "baseline_note": "vs_baseline divides by the 5.6 K images/s the reference README quotes for a Turing GPU"},
             "e2e": {"value": world * B * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": logits_host.numel() * 4},
+                    "h2d_bytes_per_step": x8_host.numel(), "d2h_bytes_per_step": logits_host.numel() * 4,
+                    "input": "uint8 NCHW images + [3][256] fp32 value table (normalisation fused into the first layer)"},
+            "e2e_fp32_images": {"value": world * B * args.steps / (ms_e2e_f32 * 1e-3), "unit": UNIT,
+                                "h2d_bytes_per_step": x_host.numel() * 4,
+                                "d2h_bytes_per_step": logits_host.numel() * 4,
+                                "input": "fp32 NCHW images, the reference's interface"},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s",

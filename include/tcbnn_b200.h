@@ -142,6 +142,18 @@ size_t tcbnn_noalloc_scratch_bytes(void);
 int tcbnn_fc_layer_noalloc(const uint32_t* A, const uint32_t* W, const float* thr, int M, int K,
                            int N, int lda, int ldw, uint32_t* out, int ldo, void* stream);
 
+/* The same first layer fed with the images as bytes: x is uint8 NCHW [B][3][H][W] and lut[c][v]
+ * (fp32 [3][256]) is the value the caller's reader would have produced for byte v of channel c
+ * -- e.g. (v/255.0f)*4.3668f-2.1179f for the reference's ImageNet reader (data.cpp:534-542).
+ * The kernel replaces every byte by its table entry and then runs exactly the arithmetic of
+ * tcbnn_inconv_layer, so results are identical to feeding the fp32 images; the host->device copy
+ * is a quarter of the size.  The reference normalises on the host (data.cpp) and has no such
+ * entry point. */
+int tcbnn_inconv_layer_u8(const tcbnn_conv_desc* d, const uint8_t* x, const float* lut,
+                          const uint32_t* filter_bits, const float* thr, uint32_t* out,
+                          long long out_image_stride, void* res_out, int res_out_bytes,
+                          float* acc_out, void* stream);
+
 /* Issue-rate probe of the MMA forms on all SMs: kind 0 = b1 and.popc m16n8k256 (mma.sync),
  * 1 = b1 xor.popc m16n8k256, 2 = s8 m16n8k32, 3 = tcgen05.mma kind::i8 128x256x32 (warps_per_sm
  * ignored).  Returns tera-ops/s (2*m*n*k per MMA) in *tops.

@@ -357,6 +357,8 @@ __device__ __forceinline__ void conv_layer(const ConvArgs& c) {
 // ----------------------------------------------------------------------------------------
 struct InConvArgs {
     const float* x;          // [B][3][H][W]
+    const unsigned char* x8; // alternative input: uint8 [B][3][H][W] (x is null) ...
+    const float* lut;        // ... with the fp32 value of every byte per channel, [3][256]
     const uint32_t* fbits;   // [R*S][3][Ow] words, out-channel o at bit 31-o%32 (param.h:613-632)
     const float* thr;        // [O]
     int B, H, W, O, R, S, sh, sw, pad_h, pad_w, pool, OH, OW;

@@ -23,7 +23,7 @@ constexpr int kInconvPitch = kInconvPixels + 4;   // floats per (tap, pattern) r
 
 __host__ __device__ inline size_t inconv_tiled_smem(int R, int S, int O) {
     const int opad = ((O + 31) / 32) * 32;
-    return (size_t)R * S * 8 * kInconvPitch * 4 + (size_t)R * S * opad + (size_t)opad * 4;
+    return (size_t)R * S * 8 * kInconvPitch * 4 + (size_t)R * S * opad + (size_t)opad * 4 + 3 * 256 * 4;
 }
 
 template <int PPT>   // pixels per thread = kInconvPixels / (kInconvThreads / opad)
@@ -33,6 +33,7 @@ __device__ void inconv_tiled_block(const InConvArgs& c, unsigned char* smem) {
     float* T = reinterpret_cast<float*>(smem);                                // [RS][8][pitch]
     unsigned char* codes = smem + (size_t)RS * 8 * kInconvPitch * 4;           // [RS][opad]
     float* sthr = reinterpret_cast<float*>(codes + (size_t)RS * opad);        // [opad]
+    float* slut = sthr + opad;                                                // [3][256], uint8 input only
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Ow = (c.O + 31) >> 5;
     const int P = c.pool * c.OH, Q = c.pool * c.OW;
@@ -50,6 +51,8 @@ __device__ void inconv_tiled_block(const InConvArgs& c, unsigned char* smem) {
         codes[i] = (unsigned char)code;
     }
     for (int i = tid; i < opad; i += kInconvThreads) sthr[i] = i < c.O ? __ldg(c.thr + i) : 0.0f;
+    if (c.x8)
+        for (int i = tid; i < 3 * 256; i += kInconvThreads) slut[i] = __ldg(c.lut + i);
 
     const int group = tid / opad;            // which PPT-pixel slab of the block this thread owns
     const int o = tid % opad;
@@ -97,14 +100,22 @@ __device__ void inconv_tiled_block(const InConvArgs& c, unsigned char* smem) {
             if (live) locate((unsigned)pix, n, y, x);
             const int y0 = y * c.sh - c.pad_h, x0 = x * c.sw - c.pad_w;
             const float* img = c.x + (size_t)n * 3 * plane;
+            const unsigned char* img8 = c.x8 + (size_t)n * 3 * plane;
             for (int tap = warp; tap < RS; tap += kInconvThreads / 32) {
                 const int ay = y0 + tap / c.S, ax = x0 + tap % c.S;
                 float v[8];
 #pragma unroll
                 for (int k = 0; k < 8; k++) v[k] = 0.0f;
                 if (live && (unsigned)ay < (unsigned)c.H && (unsigned)ax < (unsigned)c.W) {
-                    const float* px = img + (size_t)ay * c.W + ax;
-                    const float f0 = __ldg(px), f1 = __ldg(px + plane), f2 = __ldg(px + 2 * plane);
+                    const size_t po = (size_t)ay * c.W + ax;
+                    float f0, f1, f2;
+                    if (c.x8) {      // the byte's fp32 value as the caller's reader would have computed it
+                        f0 = slut[__ldg(img8 + po)];
+                        f1 = slut[256 + __ldg(img8 + po + plane)];
+                        f2 = slut[512 + __ldg(img8 + po + 2 * plane)];
+                    } else {
+                        f0 = __ldg(img + po); f1 = __ldg(img + po + plane); f2 = __ldg(img + po + 2 * plane);
+                    }
                     const float pp_ = __fadd_rn(f0, f1), pm = __fadd_rn(f0, -f1);
                     const float mp = __fadd_rn(-f0, f1), mm = __fadd_rn(-f0, -f1);
                     // index = b0<<2 | b1<<1 | b2, bit 1 = '+'

@@ -581,15 +581,16 @@ int tcbnn_conv_status(const tcbnn_conv_desc* d, const void* prepared, int* statu
     return 0;
 }
 
-int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t* filter_bits,
-                       const float* thr, uint32_t* out, long long out_image_stride,
-                       void* res_out, int res_out_bytes, float* acc_out, void* stream) {
+static int run_inconv(const tcbnn_conv_desc* d, const float* x, const unsigned char* x8, const float* lut,
+                      const uint32_t* filter_bits, const float* thr, uint32_t* out,
+                      long long out_image_stride, void* res_out, int res_out_bytes, float* acc_out,
+                      void* stream) {
     if (conv_check(d, false)) return 1;
     if (res_out && res_out_bytes != 2 && res_out_bytes != 4) return fail("inconv_layer: res_out_bytes must be 2 or 4");
     const int Ow = (d->O + 31) / 32;
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("inconv_layer: out_image_stride too small");
     InConvArgs c;
-    c.x = x; c.fbits = filter_bits; c.thr = thr;
+    c.x = x; c.x8 = x8; c.lut = lut; c.fbits = filter_bits; c.thr = thr;
     c.B = d->B; c.H = d->H; c.W = d->W; c.O = d->O; c.R = d->R; c.S = d->S;
     c.sh = d->stride_h; c.sw = d->stride_w; c.pad_h = d->pad_h; c.pad_w = d->pad_w;
     c.pool = d->pool; c.OH = d->OH; c.OW = d->OW;
@@ -599,14 +600,31 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
     if (sm_count(&sms)) return 1;
     const int opad = ((d->O + 31) / 32) * 32;
     const size_t smem = inconv_tiled_smem(d->R, d->S, d->O);
-    if (g_conv_path != 1 && smem <= 200 * 1024 && kInconvThreads % opad == 0) {
+    if ((g_conv_path != 1 || x8) && smem <= 200 * 1024 && kInconvThreads % opad == 0) {
         const int ppt = kInconvPixels / (kInconvThreads / opad);
         if (ppt == 4) return launch_inconv_tiled<4>(c, smem, sms, (cudaStream_t)stream);
         if (ppt == 8) return launch_inconv_tiled<8>(c, smem, sms, (cudaStream_t)stream);
         if (ppt == 16) return launch_inconv_tiled<16>(c, smem, sms, (cudaStream_t)stream);
     }
+    if (x8) return fail("inconv_layer_u8: this shape has no uint8-input kernel (filter too large or %d output channels)", d->O);
     k_inconv<<<warp_grid((long long)d->B * d->OH * d->OW, sms), kThreads, 0, (cudaStream_t)stream>>>(c);
     return launch_check("inconv_layer");
+}
+
+int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t* filter_bits,
+                       const float* thr, uint32_t* out, long long out_image_stride,
+                       void* res_out, int res_out_bytes, float* acc_out, void* stream) {
+    return run_inconv(d, x, nullptr, nullptr, filter_bits, thr, out, out_image_stride, res_out,
+                      res_out_bytes, acc_out, stream);
+}
+
+int tcbnn_inconv_layer_u8(const tcbnn_conv_desc* d, const uint8_t* x, const float* lut,
+                          const uint32_t* filter_bits, const float* thr, uint32_t* out,
+                          long long out_image_stride, void* res_out, int res_out_bytes,
+                          float* acc_out, void* stream) {
+    if (!x || !lut) return fail("inconv_layer_u8: null input or table");
+    return run_inconv(d, nullptr, x, lut, filter_bits, thr, out, out_image_stride, res_out,
+                      res_out_bytes, acc_out, stream);
 }
 
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {

@@ -307,7 +307,7 @@ public:
         CHECK_NULL_POINTER(input_gpu);
         CHECK_NULL_POINTER(output_gpu);
         if (save_residual) CHECK_NULL_POINTER(output_residual_gpu);
-        args.x = input_gpu; args.fbits = filter_gpu; args.thr = bn_gpu;
+        args.x = input_gpu; args.x8 = NULL; args.lut = NULL; args.fbits = filter_gpu; args.thr = bn_gpu;
         args.B = batch; args.H = input_height; args.W = input_width; args.O = output_channels;
         args.R = filter_height; args.S = filter_width; args.sh = stride_height; args.sw = stride_width;
         args.pad_h = pad_h; args.pad_w = pad_w; args.pool = pool_height; args.OH = output_height;

@@ -172,13 +172,31 @@ def synthetic_input(spec, seed, batch=None):
 SYNTHETIC_IMAGE_ABS_BOUND = 2.65
 
 
+def synthetic_input_u8(spec, seed, batch=None):
+    """The same synthetic images as synthetic_input(), as bytes plus the per-channel table of
+    their fp32 values: lut[c][v] is computed with the arithmetic synthetic_input() applies, so
+    lut[c][u8] reproduces its output bit for bit.  Returns (uint8 [B][3][H][W], fp32 [3][256])."""
+    g = np.random.Generator(np.random.PCG64(seed))
+    B = batch or spec["batch"]
+    first = spec["layers"][0]
+    if first["type"] == "in":
+        raise ValueError("byte input is for image networks")
+    u8 = g.integers(0, 256, size=(B, 3, first["H"], first["W"]), dtype=np.uint8)
+    mean = np.array([0.485, 0.456, 0.406], dtype=np.float32).reshape(3, 1)
+    std = np.array([0.229, 0.224, 0.225], dtype=np.float32).reshape(3, 1)
+    v = np.arange(256, dtype=np.float32).reshape(1, 256)
+    lut = ((v / np.float32(255.0)) - mean) / std
+    return u8, lut.astype(np.float32)
+
+
 class Network:
     """Chain of layer objects built from a spec, the way the reference drivers build theirs
     (new XLayerParam(...) ; initialize(config, prev->get_output_gpu(), residual))."""
 
-    def __init__(self, spec, weights, input_host, input_abs_bound=None):
+    def __init__(self, spec, weights, input_host, input_abs_bound=None, input_lut=None):
         """input_abs_bound: max |pixel value| the caller guarantees; with it the residual chain
-        is provably small and is stored as int16 instead of int32."""
+        is provably small and is stored as int16 instead of int32.
+        input_lut: images arrive as uint8 with this [3][256] table of their fp32 values."""
         self.spec = spec
         B = spec["batch"]
         cfg = weights if hasattr(weights, "read") else param.ArrayConfig(weights)
@@ -192,7 +210,8 @@ class Network:
                 obj = param.InConv128LayerParam(l["name"], l["H"], l["W"], l["R"], l["S"], 3, l["O"], B,
                                                 l["stride"], l["stride"], True, l["pool"], l["pool"],
                                                 l.get("save_residual", False),
-                                                input_abs_bound=input_abs_bound).initialize(input_host, cfg)
+                                                input_abs_bound=input_abs_bound).initialize(
+                                                    input_host, cfg, input_lut=input_lut)
             elif t == "conv":
                 inj = l.get("inject")
                 obj = param.Conv128LayerParam(l["name"], l["H"], l["W"], l["R"], l["S"], l["C"], l["O"], B,

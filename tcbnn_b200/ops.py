@@ -159,9 +159,12 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
 
 
 def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_residual=False,
-                 want_acc=False, res_out_buf=None, residual_dtype=torch.int32):
-    """x: fp32 [B][3][H][W].  Returns (out_bits, res_out, acc_out)."""
-    _need_cuda(x, filter_bits, thr)
+                 want_acc=False, res_out_buf=None, residual_dtype=torch.int32, lut=None):
+    """x: fp32 [B][3][H][W], or uint8 [B][3][H][W] together with lut (fp32 [3][256], the value
+    of every byte per channel).  Returns (out_bits, res_out, acc_out)."""
+    _need_cuda(x, filter_bits, thr, lut)
+    if (x.dtype == torch.uint8) != (lut is not None):
+        raise _l.TcbnnError("inconv_layer: uint8 images need a lut, fp32 images must not have one")
     Ow = (d.O + 31) // 32
     stride = out_image_stride or d.OH * d.OW * Ow
     if out is None:
@@ -171,9 +174,14 @@ def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_r
     if res_out is None and save_residual:
         res_out = torch.empty((d.B, P, Q, d.O), dtype=residual_dtype, device=x.device)
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.float32, device=x.device) if want_acc else None
-    _l.call("tcbnn_inconv_layer", C.byref(d), _ptr(x), _ptr(filter_bits), _ptr(thr), _ptr(out),
-            C.c_longlong(stride), _ptr(res_out),
-            res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
+    if lut is not None:
+        _l.call("tcbnn_inconv_layer_u8", C.byref(d), _ptr(x), _ptr(lut), _ptr(filter_bits), _ptr(thr),
+                _ptr(out), C.c_longlong(stride), _ptr(res_out),
+                res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
+    else:
+        _l.call("tcbnn_inconv_layer", C.byref(d), _ptr(x), _ptr(filter_bits), _ptr(thr), _ptr(out),
+                C.c_longlong(stride), _ptr(res_out),
+                res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
     return out, res_out, acc_out
 
 

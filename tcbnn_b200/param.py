@@ -203,10 +203,18 @@ class InConv128LayerParam:
         self.output_height, self.output_width = self.desc.OH, self.desc.OW
         self.output_residual_gpu = None
 
-    def initialize(self, input, config):
+    def initialize(self, input, config, input_lut=None):
+        """input: fp32 NCHW images as in the reference (param.h:760), or -- extension -- uint8 NCHW
+        images with input_lut, fp32 [3][256]: the value of every byte per channel, i.e. the
+        reader's normalisation tabulated (data.cpp:534-542).  Same results, a quarter of the
+        host->device traffic."""
         dev = _dev()
         d = self.desc
-        self.input_gpu = torch.empty((d.B, 3, d.H, d.W), dtype=torch.float32, device=dev)
+        u8 = input_lut is not None
+        self.input_lut_gpu = None
+        if u8:
+            self.input_lut_gpu = torch.from_numpy(np.ascontiguousarray(input_lut, dtype=np.float32).reshape(3, 256)).to(dev)
+        self.input_gpu = torch.empty((d.B, 3, d.H, d.W), dtype=torch.uint8 if u8 else torch.float32, device=dev)
         self.set_input(input)
         f = torch.from_numpy(config.read(d.R * d.S * 3 * d.O).reshape(d.R * d.S, 3, d.O)).to(dev)
         self.filter_gpu = ops.pack_inconv_filter(f)
@@ -220,12 +228,14 @@ class InConv128LayerParam:
         return self
 
     def set_input(self, input):
-        src = input if torch.is_tensor(input) else torch.from_numpy(np.ascontiguousarray(input, dtype=np.float32))
+        src = input if torch.is_tensor(input) else torch.from_numpy(np.ascontiguousarray(input))
+        if src.dtype != self.input_gpu.dtype:
+            raise ValueError("%s: input dtype %s, layer was initialised for %s" % (self.name, src.dtype, self.input_gpu.dtype))
         self.input_gpu.copy_(src.reshape(self.input_gpu.shape), non_blocking=True)
 
     def forward(self):
         ops.inconv_layer(self.desc, self.input_gpu, self.filter_gpu, self.bn_gpu, out=self.output_gpu,
-                         res_out_buf=self.output_residual_gpu)
+                         res_out_buf=self.output_residual_gpu, lut=self.input_lut_gpu)
 
     def get_output_gpu(self):
         return self.output_gpu

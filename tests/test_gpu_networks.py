@@ -64,3 +64,21 @@ def test_resnet18_both_conv_kernels(cuda):
         _compare(models.resnet18_spec(2, image=64, classes=100), 21, cuda)
     finally:
         ops.set_conv_path(0)
+
+
+def test_resnet18_uint8_images_give_identical_results(cuda):
+    """Byte images + per-channel value table through tcbnn_inconv_layer_u8: every tensor equal
+    to the fp32-image run of the same network."""
+    spec = models.resnet18_spec(3)
+    w = models.synthetic_weights(spec, 50)
+    x = models.synthetic_input(spec, 51)
+    u8, lut = models.synthetic_input_u8(spec, 51)
+    assert np.array_equal(lut[np.arange(3)[None, :, None, None], u8], x)       # same pixels
+    ref = models.Network(spec, w, x)
+    got = models.Network(spec, w, torch.from_numpy(u8), input_lut=lut)
+    a, b = ref.forward().cpu().numpy(), got.forward().cpu().numpy()
+    for la, lb in zip(ref.layers, got.layers):
+        assert torch.equal(la.get_output_gpu(), lb.get_output_gpu()), la.name
+    assert np.array_equal(a, b)
+    acts, _ = onet.run(spec, w, x)
+    np.testing.assert_allclose(b, acts[-1], rtol=1e-5, atol=1e-5)
