@@ -99,6 +99,7 @@ def run_reference(args, rank, world):
     import oracle as orc
     from tcbnn_b200 import models
     L = orc.lib(native=True)
+    orc.use_all_cores(L)
     threads = orc.num_threads(L)
     sample = max(1, min(args.batch, args.cpu_images))
     spec = models.resnet18_spec(sample)
@@ -291,6 +292,7 @@ def cpu_baseline(images):
     import oracle as orc
     from tcbnn_b200 import models
     L = orc.lib(native=True)
+    orc.use_all_cores(L)
     spec = models.resnet18_spec(images)
     w = models.synthetic_weights(spec, 1234)
     x = models.synthetic_input(spec, 4321)

@@ -172,6 +172,13 @@ def inconv_layer(x, F, thr, R, S, sh=1, sw=1, padding=True, pool=1, out_image_st
     return out, res_out, acc_out
 
 
+def use_all_cores(L=None):
+    """Make the oracle use every host core (a launcher may have exported OMP_NUM_THREADS=1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    (L or lib()).orc_set_num_threads(n)
+    return n
+
+
 def num_threads(L=None):
     return (L or lib()).orc_num_threads()
 

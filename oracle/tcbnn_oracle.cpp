@@ -41,6 +41,15 @@ int orc_num_threads() {
 #endif
 }
 
+// launchers such as torchrun export OMP_NUM_THREADS=1; the timed CPU baseline asks for all cores
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 static inline int popc32(uint32_t x) { return __builtin_popcount(x); }
 
 // ---------------------------------------------------------------------------------------
