@@ -39,6 +39,8 @@ struct ConvWsArgs {
     int back_y, back_x;       // patch origin = tile start - (back_y*PW + back_x)
     long long NV;             // raster positions over the batch
     int ntiles_n;
+    int as_split;             // activation-stationary kernel: parts the n-tiles of a task are split into
+    int as_slots;             // ... and units in its filter ring (9 or 18)
     const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
     uint32_t* out; long long out_image_stride;
     void* res_out; int res_out_bytes; int32_t* acc_out;

@@ -4,6 +4,7 @@
 #include "bnn_layers.cuh"
 #include "bconv_umma.cuh"
 #include "bconv_umma_ws.cuh"
+#include "bconv_umma_as.cuh"
 #include "inconv_tiled.cuh"
 #include <cstdio>
 #include <cstdarg>
@@ -147,6 +148,11 @@ struct PreparedLayout {
     int umma_npos;        // raster positions of the shared-memory patch (per plane)
     size_t umma_smem;     // dynamic shared memory of the tcgen05 kernel
     int umma_pw, umma_vh, umma_back_y, umma_back_x;   // raster geometry
+    // activation-stationary tcgen05 kernel (wide stride-1 layers): its own filter copy in
+    // 128-channel n-tiles (shared with the other kernel's when that one also uses 128)
+    int as_npos;          // 0 when the layer is not eligible
+    int as_slots;         // units in its filter ring
+    size_t as_smem, off_wi8_as;
 };
 
 int conv_check(const tcbnn_conv_desc* d, bool binary) {
@@ -183,6 +189,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     // filter block of one n-tile resident in shared memory
     L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o;
     L.umma_pw = L.umma_vh = L.umma_back_y = L.umma_back_x = 0;
+    L.as_npos = 0; L.as_smem = 0; L.as_slots = 0; L.off_wi8_as = o;
     if (d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) && d->pool == 1 &&
         d->padding && d->C % 64 == 0 && d->O % 32 == 0) {
         const int st = d->stride_h;
@@ -199,9 +206,8 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
         const int max_npos = st == 2 ? umma::kWsExpThreads : 2 * umma::kWsExpThreads;
         const long long nv = (long long)d->B * VH * PW;
         const long long in_words = (long long)d->B * d->H * d->W * (d->C / 32);
-        if (fwd_y >= 0 && fwd_x >= 0 && npos <= max_npos && npos * 16 < (1 << 18) &&
-            nv + 1024 < (1LL << 31) && in_words < (1LL << 31)) {
-            for (int nt = 256; nt >= 32; nt >>= 1) {
+        if (fwd_y >= 0 && fwd_x >= 0 && nv + 1024 < (1LL << 31) && in_words < (1LL << 31)) {
+            for (int nt = 256; nt >= 32 && npos <= max_npos; nt >>= 1) {
                 if (d->O % nt) continue;
                 const size_t smem = umma::ws_smem_bytes(st, npos, d->C, d->R * d->S, nt);
                 if (smem > 227 * 1024) continue;
@@ -209,6 +215,23 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
                 L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
                 o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
                 break;
+            }
+            // wide layers: keep 256 positions x all channels resident, stream the filter
+            const int npos_as = (256 + (back_y + fwd_y) * PW + back_x + fwd_x + 7) & ~7;
+            int slots_as = umma::kAsMaxSlots;
+            if (umma::as_smem_bytes(npos_as, d->C, d->O, d->R * d->S, slots_as) > 227 * 1024) slots_as = 9;
+            const size_t smem_as = umma::as_smem_bytes(npos_as, d->C, d->O, d->R * d->S, slots_as);
+            // (at 128 channels the filter-stationary kernel is as fast: measured)
+            if (st == 1 && d->C >= 256 && d->C <= 512 && d->O % umma::kAsNT == 0 &&
+                npos_as <= umma::kAsMaxPos * umma::kAsExpThreads && smem_as <= 227 * 1024) {
+                L.as_npos = npos_as; L.as_smem = smem_as; L.as_slots = slots_as;
+                L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
+                if (L.umma_nt == umma::kAsNT) {
+                    L.off_wi8_as = L.off_wi8;
+                } else {
+                    L.off_wi8_as = o;
+                    o += (size_t)d->R * d->S * d->C * d->O;  o = (o + 255) & ~(size_t)255;
+                }
             }
         }
     }
@@ -244,7 +267,7 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
 }
 
 long long* g_conv_trace = nullptr;   // device buffer for per-role cycle counters, or null
-int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible)
+int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible), 3 = 2 without the activation-stationary kernel
 
 template <int NT, int STRIDE>
 __global__ void __launch_bounds__(umma::kWsThreads, 1) k_conv_umma_ws(umma::ConvWsArgs a) {
@@ -273,6 +296,41 @@ int launch_conv_umma_ws(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t 
     if (per > mtiles) per = mtiles;
     k_conv_umma_ws<NT, STRIDE><<<(int)(per * a.ntiles_n), umma::kWsThreads, smem, st>>>(a);
     return launch_check("conv_layer (tcgen05)");
+}
+
+__global__ void __launch_bounds__(umma::kAsThreads, 1) k_conv_umma_as(umma::ConvWsArgs a) {
+    extern __shared__ __align__(128) unsigned char dyn_smem_as[];
+    umma::conv_umma_as_cta<0>(a, dyn_smem_as);
+}
+
+int launch_conv_umma_as(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_conv_umma_as,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured[dev] = true;
+    }
+    // Split the n-tiles of a task over several work items when that fills the last wave of
+    // CTAs better (the patch is then expanded once per part, which is cheap).
+    const long long ntasks = (a.NV + 255) / 256;
+    const int nnt = a.O / umma::kAsNT;
+    int best = 1;
+    double best_cost = 1e300;
+    for (int sp = 1; sp <= nnt; sp++) {
+        if (nnt % sp) continue;
+        const long long items = ntasks * sp;
+        const long long waves = (items + sms - 1) / sms;
+        const double cost = (double)waves * ((double)nnt / sp + 0.15);   // 0.15: expansion + fill
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = sp; }
+    }
+    a.as_split = best;
+    const long long items = ntasks * best;
+    const int grid = (int)(items < sms ? items : sms);
+    k_conv_umma_as<<<grid, umma::kAsThreads, smem, st>>>(a);
+    return launch_check("conv_layer (tcgen05, activation-stationary)");
 }
 
 // ---- MMA issue-rate probe ----------------------------------------------------------------
@@ -489,6 +547,12 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
             filter_bits, d->O, d->R * d->S, d->C, L.umma_nt, (uint4*)(p + L.off_wi8));
         if (launch_check("conv_prepare (int8 filter)")) return 1;
     }
+    if (L.as_npos && (!L.umma_nt || L.off_wi8_as != L.off_wi8)) {
+        const long long units = (long long)d->O * d->R * d->S * (d->C / 16);
+        k_prepare_filter_ws<<<elementwise_grid(units, sms), 256, 0, (cudaStream_t)stream>>>(
+            filter_bits, d->O, d->R * d->S, d->C, umma::kAsNT, (uint4*)(p + L.off_wi8_as));
+        if (launch_check("conv_prepare (int8 filter, 128-channel tiles)")) return 1;
+    }
     return 0;
 }
 
@@ -507,12 +571,13 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
     if ((uintptr_t)in & 7) return fail("conv_layer: input must be 8-byte aligned");
     const PreparedLayout L = prepared_layout(d);
     const char* p = (const char*)prepared;
-    if (g_conv_path == 2 && !L.umma_nt) return fail("conv_layer: layer is not eligible for the tcgen05 path");
+    const bool use_as = L.as_npos && g_conv_path != 3;
+    if (g_conv_path >= 2 && !L.umma_nt && !use_as) return fail("conv_layer: layer is not eligible for the tcgen05 path");
     // the tcgen05 epilogue moves residuals in 4-channel vectors
     const bool res_vec_ok = !res_in || (res_in_ch % 4 == 0 && residual_channels % 4 == 0 &&
                                         ((uintptr_t)res_in & 15) == 0);
-    if (g_conv_path == 2 && !res_vec_ok) return fail("conv_layer: residual layout not eligible for the tcgen05 path");
-    if (L.umma_nt && g_conv_path != 1 && res_vec_ok && (!res_out || ((uintptr_t)res_out & 15) == 0)) {
+    if (g_conv_path >= 2 && !res_vec_ok) return fail("conv_layer: residual layout not eligible for the tcgen05 path");
+    if ((L.umma_nt || use_as) && g_conv_path != 1 && res_vec_ok && (!res_out || ((uintptr_t)res_out & 15) == 0)) {
         umma::ConvWsArgs a;
         a.in = in; a.wi8 = (const uint4*)(p + L.off_wi8); a.thr = thr;
         a.B = d->B; a.H = d->H; a.W = d->W; a.C = d->C; a.O = d->O; a.R = d->R; a.S = d->S;
@@ -532,6 +597,11 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
         int sms;
         if (sm_count(&sms)) return 1;
         cudaStream_t st = (cudaStream_t)stream;
+        if (use_as) {
+            a.NPOS = L.as_npos; a.as_slots = L.as_slots;
+            a.wi8 = (const uint4*)(p + L.off_wi8_as);
+            return launch_conv_umma_as(a, L.as_smem, sms, st);
+        }
 #define TCBNN_WS_CASE(NN, SS) \
         if (L.umma_nt == NN && d->stride_h == SS) return launch_conv_umma_ws<NN, SS>(a, L.umma_smem, sms, st);
         TCBNN_WS_CASE(32, 1) TCBNN_WS_CASE(64, 1) TCBNN_WS_CASE(128, 1) TCBNN_WS_CASE(256, 1)
@@ -563,7 +633,8 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
 }
 
 int tcbnn_set_conv_path(int path) {
-    if (path < 0 || path > 2) return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05");
+    if (path < 0 || path > 3)
+        return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05, 3 = tcgen05 filter-stationary kernel only");
     g_conv_path = path;
     return 0;
 }

@@ -192,7 +192,8 @@ def mma_peak(kind, warps_per_sm=32, iters=4000):
 
 
 def set_conv_path(path):
-    """0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05 (error when a layer is not eligible)."""
+    """0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05 (error when a layer is not eligible),
+    3 = tcgen05 without the activation-stationary kernel."""
     _l.call("tcbnn_set_conv_path", int(path))
 
 
