@@ -156,6 +156,29 @@ int tcbnn_inconv_layer_u8(const tcbnn_conv_desc* d, const uint8_t* x, const floa
                           long long out_image_stride, void* res_out, int res_out_bytes,
                           float* acc_out, void* stream);
 
+/* First layer compiled for one filter.  No reference counterpart: InConv128LayerFMT
+ * (kernel.cuh:578-672) reads the filter bits at run time, as tcbnn_inconv_layer does.  A model's
+ * first-layer filter and thresholds never change, so tcbnn_inconv_specialize reads them back
+ * (filter_bits and thr are device pointers, laid out as for tcbnn_inconv_layer; synchronises the
+ * stream), generates a kernel whose instruction stream contains the filter -- one
+ * register-to-register fp32 add per (tap, output channel), same operands, order and roundings as
+ * the reference -- compiles it with NVRTC (libnvrtc.so.12 is looked up with dlopen; the
+ * environment variable TCBNN_NVRTC may name it) and loads it.  d->O <= 64.  The kernel does not
+ * depend on d->B, d->H or d->W.  tcbnn_inconv_specialized_layer then runs the layer on fp32 images
+ * (x, x8 = lut = NULL) or on uint8 images with their value table (x = NULL), with the outputs of
+ * tcbnn_inconv_layer; d must agree with the descriptor used to specialise in everything but
+ * B, H, W.  tcbnn_inconv_release unloads the kernel. */
+int tcbnn_inconv_specialize(const tcbnn_conv_desc* d, const uint32_t* filter_bits, const float* thr,
+                            void* stream, void** handle);
+int tcbnn_inconv_specialized_layer(void* handle, const tcbnn_conv_desc* d, const float* x,
+                                   const uint8_t* x8, const float* lut, uint32_t* out,
+                                   long long out_image_stride, void* res_out, int res_out_bytes,
+                                   float* acc_out, void* stream);
+int tcbnn_inconv_release(void* handle);
+/* Generates the kernel above for pseudo-random filter bits and compiles it, without loading it:
+ * needs NVRTC but no GPU.  *source_bytes (optional) receives the size of the generated source. */
+int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, long long* source_bytes);
+
 /* Issue-rate probe of the MMA forms on all SMs: kind 0 = b1 and.popc m16n8k256 (mma.sync),
  * 1 = b1 xor.popc m16n8k256, 2 = s8 m16n8k32, 3 = tcgen05.mma kind::i8 128x256x32 (warps_per_sm
  * ignored).  Returns tera-ops/s (2*m*n*k per MMA) in *tops.

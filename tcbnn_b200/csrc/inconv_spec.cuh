@@ -1,0 +1,227 @@
+// First layer specialised to one filter: run-time compiled kernel (host side).
+//
+// InConv128LayerFMT (kernel.cuh:578-672) adds, per in-frame tap and output channel, the term
+// ((+-f0) + (+-f1)) + (+-f2) to a running fp32 sum; the three signs are that channel's filter
+// bits.  With the filter read at run time the term has to be fetched by a data-dependent index
+// (inconv_tiled.cuh keeps an 8-entry table per tap in shared memory and is bound by the 128
+// bytes per clock an SM can move from shared memory to registers: one 4-byte operand per add).
+// A first-layer filter is fixed for the life of a model, so here the filter is compiled into
+// the instruction stream: one thread owns one pixel, computes the four distinct magnitudes of
+// the term in registers ((f0+f1)+-f2, (f0-f1)+-f2; the other four are their negations, which
+// an add takes for free) and runs one register-to-register add per (tap, channel) whose
+// operand is chosen by the generator.  No table, no shared-memory traffic: the bound becomes
+// the fp32 add rate.  Operands, order of the adds and roundings are those of the reference.
+//
+// The source is generated below, compiled with NVRTC for sm_100a (libnvrtc is opened with
+// dlopen, so the library itself does not depend on it) and loaded with cudaLibraryLoadData.
+#pragma once
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+#include <dlfcn.h>
+#include <cuda_runtime.h>
+
+namespace tcbnn {
+namespace spec {
+
+constexpr int kSpecThreads = 256;
+constexpr int kSpecMaxO = 64;
+
+// Kernel arguments; the same struct is declared in the generated source.
+struct SpecArgs {
+    const float* x;            // [B][3][H][W] fp32, or null
+    const unsigned char* x8;   // [B][3][H][W] uint8 with lut, when x is null
+    const float* lut;          // [3][256]
+    int B, H, W, OH, OW;       // OH, OW: outputs after pooling
+    uint32_t* out;
+    long long out_image_stride;
+    void* res_out;
+    int res_out_bytes, res_out_ld;
+    float* acc_out;
+    unsigned total;            // pre-pool pixels
+};
+
+struct SpecHandle {
+    int O, R, S, sh, sw, pad_h, pad_w, pool;
+    cudaLibrary_t lib;
+    cudaKernel_t k_f32, k_u8;
+};
+
+inline void emit(std::string& s, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    s += buf;
+}
+
+// codes[tap][o] = b0<<2 | b1<<1 | b2 (bit 1 = '+'), thr_bits[o] = the threshold's bit pattern
+inline std::string generate_source(const SpecHandle& h, const std::vector<unsigned char>& codes,
+                                   const std::vector<uint32_t>& thr_bits) {
+    const int O = h.O, RS = h.R * h.S, Ow = (O + 31) / 32;
+    std::string s;
+    s.reserve(400 * 1024);
+    s += "typedef unsigned int uint32_t;\n"
+         "struct SpecArgs { const float* x; const unsigned char* x8; const float* lut; int B, H, W, OH, OW;\n"
+         "  uint32_t* out; long long out_image_stride; void* res_out; int res_out_bytes, res_out_ld;\n"
+         "  float* acc_out; unsigned total; };\n";
+    emit(s, "template <bool U8> __device__ __forceinline__ void body(const SpecArgs& c, const float* slut) {\n");
+    s += " const unsigned pix = blockIdx.x * blockDim.x + threadIdx.x;\n"
+         " const bool live = pix < c.total;\n"
+         " int n, y, x;\n";
+    if (h.pool == 2) {
+        // four consecutive indices are the four positions of one pooling window
+        s += " { const unsigned pp = pix >> 2; const unsigned r = pp / (unsigned)c.OW; const int ox = (int)(pp - r * c.OW);\n"
+             "   n = (int)(r / (unsigned)c.OH); const int oy = (int)(r - (unsigned)n * c.OH);\n"
+             "   y = 2 * oy + ((int)(pix & 3) >> 1); x = 2 * ox + (int)(pix & 1); }\n";
+    } else {
+        s += " { const unsigned r = pix / (unsigned)c.OW; x = (int)(pix - r * c.OW);\n"
+             "   n = (int)(r / (unsigned)c.OH); y = (int)(r - (unsigned)n * c.OH); }\n";
+    }
+    emit(s, " const int P = %d * c.OH, Q = %d * c.OW;\n", h.pool, h.pool);
+    emit(s, " const int y0 = y * %d - %d, x0 = x * %d - %d;\n", h.sh, h.pad_h, h.sw, h.pad_w);
+    s += " const size_t plane = (size_t)c.H * c.W;\n"
+         " const float* img = c.x + (size_t)n * 3 * plane;\n"
+         " const unsigned char* img8 = c.x8 + (size_t)n * 3 * plane;\n";
+    s += " float ";
+    for (int o = 0; o < O; o++) emit(s, "a%d = 0.f%s", o, o + 1 < O ? ", " : ";\n");
+    for (int t = 0; t < RS; t++) {
+        emit(s, " { const int ay = y0 + %d, ax = x0 + %d; float f0 = 0.f, f1 = 0.f, f2 = 0.f;\n", t / h.S, t % h.S);
+        s += "  if (live && (unsigned)ay < (unsigned)c.H && (unsigned)ax < (unsigned)c.W) {\n"
+             "   const size_t po = (size_t)ay * c.W + ax;\n"
+             "   if (U8) { f0 = slut[__ldg(img8 + po)]; f1 = slut[256 + __ldg(img8 + po + plane)]; f2 = slut[512 + __ldg(img8 + po + 2 * plane)]; }\n"
+             "   else { f0 = __ldg(img + po); f1 = __ldg(img + po + plane); f2 = __ldg(img + po + 2 * plane); }\n"
+             "  }\n"
+             "  const float pp = __fadd_rn(f0, f1), pm = __fadd_rn(f0, -f1);\n"
+             "  const float v7 = __fadd_rn(pp, f2), v6 = __fadd_rn(pp, -f2), v5 = __fadd_rn(pm, f2), v4 = __fadd_rn(pm, -f2);\n";
+        for (int o = 0; o < O; o++) {
+            const int k = codes[(size_t)t * O + o];
+            if (k >= 4) emit(s, "  a%d = __fadd_rn(a%d, v%d);\n", o, o, k);
+            else emit(s, "  a%d = __fadd_rn(a%d, -v%d);\n", o, o, 7 - k);     // pattern k is minus pattern 7-k
+        }
+        s += " }\n";
+    }
+    // threshold (kernel.cuh:655), pack, pool
+    s += " uint32_t w0 = 0, w1 = 0;\n";
+    for (int o = 0; o < O; o++)
+        emit(s, " if (live && !(a%d < __uint_as_float(0x%08xu))) w%d |= 0x%08xu;\n", o, thr_bits[o], o >> 5,
+             0x80000000u >> (o & 31));
+    if (h.pool == 2)
+        s += " w0 |= __shfl_xor_sync(0xffffffffu, w0, 1); w0 |= __shfl_xor_sync(0xffffffffu, w0, 2);\n"
+             " w1 |= __shfl_xor_sync(0xffffffffu, w1, 1); w1 |= __shfl_xor_sync(0xffffffffu, w1, 2);\n";
+    s += " if (!live) return;\n";
+    emit(s, " { uint32_t* dst = c.out + (size_t)n * c.out_image_stride + ((size_t)(y / %d) * c.OW + (x / %d)) * %d;\n",
+         h.pool, h.pool, Ow);
+    if (h.pool == 2) s += "   if ((pix & 3) == 0)";
+    emit(s, "   { dst[0] = w0;%s } }\n", Ow == 2 ? " dst[1] = w1;" : "");
+    // residual = (int)acc (kernel.cuh:666-668), optional fp32 accumulators
+    s += " const size_t opix = ((size_t)n * P + y) * Q + x;\n"
+         " if (c.res_out) {\n"
+         "  if (c.res_out_bytes == 2) {\n"
+         "   short* r = reinterpret_cast<short*>(c.res_out) + opix * c.res_out_ld;\n";
+    if (O % 8 == 0) {
+        s += "   if ((c.res_out_ld & 7) == 0 && (reinterpret_cast<size_t>(c.res_out) & 15) == 0) {\n"
+             "    uint4* d4 = reinterpret_cast<uint4*>(r);\n";
+        for (int j = 0; j < O / 8; j++) {
+            emit(s, "    d4[%d] = make_uint4(", j);
+            for (int k = 0; k < 4; k++)
+                emit(s, "((uint32_t)(int)a%d & 0xFFFFu) | ((uint32_t)(int)a%d << 16)%s", 8 * j + 2 * k, 8 * j + 2 * k + 1,
+                     k < 3 ? ", " : ");\n");
+        }
+        s += "   } else\n";
+    }
+    s += "   {\n";
+    for (int o = 0; o < O; o++) emit(s, "    r[%d] = (short)(int)a%d;\n", o, o);
+    s += "   }\n  } else {\n   int* r = reinterpret_cast<int*>(c.res_out) + opix * c.res_out_ld;\n";
+    for (int o = 0; o < O; o++) emit(s, "   r[%d] = (int)a%d;\n", o, o);
+    s += "  }\n }\n if (c.acc_out) {\n";
+    emit(s, "  float* q = c.acc_out + opix * %d;\n", O);
+    for (int o = 0; o < O; o++) emit(s, "  q[%d] = a%d;\n", o, o);
+    s += " }\n}\n";
+    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d) tcbnn_spec_f32(SpecArgs c) { body<false>(c, nullptr); }\n",
+         kSpecThreads);
+    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d) tcbnn_spec_u8(SpecArgs c) {\n", kSpecThreads);
+    s += " __shared__ float slut[768];\n"
+         " for (int i = threadIdx.x; i < 768; i += blockDim.x) slut[i] = __ldg(c.lut + i);\n"
+         " __syncthreads();\n"
+         " body<true>(c, slut);\n}\n";
+    return s;
+}
+
+// ---- NVRTC through dlopen ------------------------------------------------------------------
+struct Nvrtc {
+    void* so = nullptr;
+    int (*createProgram)(void**, const char*, const char*, int, const char* const*, const char* const*) = nullptr;
+    int (*compileProgram)(void*, int, const char* const*) = nullptr;
+    int (*getCUBINSize)(void*, size_t*) = nullptr;
+    int (*getCUBIN)(void*, char*) = nullptr;
+    int (*getProgramLogSize)(void*, size_t*) = nullptr;
+    int (*getProgramLog)(void*, char*) = nullptr;
+    int (*destroyProgram)(void**) = nullptr;
+    const char* (*getErrorString)(int) = nullptr;
+    bool ok = false;
+};
+
+inline Nvrtc& nvrtc() {
+    static Nvrtc n;
+    static bool tried = false;
+    if (tried) return n;
+    tried = true;
+    const char* names[] = {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12",
+                           "/usr/local/cuda/lib64/libnvrtc.so"};
+    const char* env = getenv("TCBNN_NVRTC");
+    if (env) n.so = dlopen(env, RTLD_NOW | RTLD_LOCAL);
+    for (const char* nm : names) {
+        if (n.so) break;
+        n.so = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+    }
+    if (!n.so) return n;
+#define TCBNN_SYM(field, name) *(void**)(&n.field) = dlsym(n.so, name)
+    TCBNN_SYM(createProgram, "nvrtcCreateProgram");
+    TCBNN_SYM(compileProgram, "nvrtcCompileProgram");
+    TCBNN_SYM(getCUBINSize, "nvrtcGetCUBINSize");
+    TCBNN_SYM(getCUBIN, "nvrtcGetCUBIN");
+    TCBNN_SYM(getProgramLogSize, "nvrtcGetProgramLogSize");
+    TCBNN_SYM(getProgramLog, "nvrtcGetProgramLog");
+    TCBNN_SYM(destroyProgram, "nvrtcDestroyProgram");
+    TCBNN_SYM(getErrorString, "nvrtcGetErrorString");
+#undef TCBNN_SYM
+    n.ok = n.createProgram && n.compileProgram && n.getCUBINSize && n.getCUBIN && n.getProgramLogSize &&
+           n.getProgramLog && n.destroyProgram;
+    return n;
+}
+
+// Compiles `src` for sm_100a; on failure returns false with the reason in `err`.
+inline bool compile_cubin(const std::string& src, std::vector<char>& cubin, std::string& err) {
+    Nvrtc& n = nvrtc();
+    if (!n.ok) { err = "libnvrtc could not be opened (set TCBNN_NVRTC to its path)"; return false; }
+    void* prog = nullptr;
+    int r = n.createProgram(&prog, src.c_str(), "tcbnn_inconv_spec.cu", 0, nullptr, nullptr);
+    if (r) { err = "nvrtcCreateProgram failed"; return false; }
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo", "--fmad=false"};
+    r = n.compileProgram(prog, 4, opts);
+    if (r) {
+        size_t ls = 0;
+        n.getProgramLogSize(prog, &ls);
+        std::string log(ls, '\0');
+        if (ls) n.getProgramLog(prog, &log[0]);
+        err = "nvrtc: " + log.substr(0, 600);
+        n.destroyProgram(&prog);
+        return false;
+    }
+    size_t cs = 0;
+    n.getCUBINSize(prog, &cs);
+    cubin.resize(cs);
+    r = n.getCUBIN(prog, cubin.data());
+    n.destroyProgram(&prog);
+    if (r || !cs) { err = "nvrtcGetCUBIN failed"; return false; }
+    return true;
+}
+
+}  // namespace spec
+}  // namespace tcbnn

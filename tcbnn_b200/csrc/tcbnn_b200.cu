@@ -5,6 +5,7 @@
 #include "bconv_umma.cuh"
 #include "bconv_umma_ws.cuh"
 #include "bconv_umma_as.cuh"
+#include "inconv_spec.cuh"
 #include "inconv_tiled.cuh"
 #include <cstdio>
 #include <cstdarg>
@@ -696,6 +697,103 @@ int tcbnn_inconv_layer_u8(const tcbnn_conv_desc* d, const uint8_t* x, const floa
     if (!x || !lut) return fail("inconv_layer_u8: null input or table");
     return run_inconv(d, nullptr, x, lut, filter_bits, thr, out, out_image_stride, res_out,
                       res_out_bytes, acc_out, stream);
+}
+
+// ---- first layer specialised to one filter (run-time compiled) -----------------------------
+static int spec_build(spec::SpecHandle* h, const std::vector<unsigned char>& codes,
+                      const std::vector<uint32_t>& thr_bits, bool load) {
+    const std::string src = spec::generate_source(*h, codes, thr_bits);
+    std::vector<char> cubin;
+    std::string err;
+    if (!spec::compile_cubin(src, cubin, err)) return fail("inconv_specialize: %s", err.c_str());
+    if (!load) return 0;
+    CUDA_TRY(cudaLibraryLoadData(&h->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    CUDA_TRY(cudaLibraryGetKernel(&h->k_f32, h->lib, "tcbnn_spec_f32"));
+    CUDA_TRY(cudaLibraryGetKernel(&h->k_u8, h->lib, "tcbnn_spec_u8"));
+    return 0;
+}
+
+static int spec_check(const tcbnn_conv_desc* d) {
+    if (conv_check(d, false)) return 1;
+    if (d->O > spec::kSpecMaxO)
+        return fail("inconv_specialize: at most %d output channels (the sums of a pixel live in registers)", spec::kSpecMaxO);
+    return 0;
+}
+
+int tcbnn_inconv_specialize(const tcbnn_conv_desc* d, const uint32_t* filter_bits, const float* thr,
+                            void* stream, void** handle) {
+    if (!handle) return fail("inconv_specialize: null handle pointer");
+    *handle = nullptr;
+    if (spec_check(d)) return 1;
+    const int RS = d->R * d->S, Ow = (d->O + 31) / 32;
+    std::vector<uint32_t> fb((size_t)RS * 3 * Ow), thr_bits(d->O);
+    CUDA_TRY(cudaMemcpyAsync(fb.data(), filter_bits, fb.size() * 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    CUDA_TRY(cudaMemcpyAsync(thr_bits.data(), thr, (size_t)d->O * 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    std::vector<unsigned char> codes((size_t)RS * d->O);
+    for (int t = 0; t < RS; t++)
+        for (int o = 0; o < d->O; o++) {
+            const uint32_t* fw = fb.data() + (size_t)t * 3 * Ow + (o >> 5);      // param.h:613-632
+            const int sh = 31 - (o & 31);
+            codes[(size_t)t * d->O + o] = (unsigned char)((((fw[0] >> sh) & 1u) << 2) | (((fw[Ow] >> sh) & 1u) << 1) |
+                                                          ((fw[2 * Ow] >> sh) & 1u));
+        }
+    spec::SpecHandle* h = new spec::SpecHandle();
+    h->O = d->O; h->R = d->R; h->S = d->S; h->sh = d->stride_h; h->sw = d->stride_w;
+    h->pad_h = d->pad_h; h->pad_w = d->pad_w; h->pool = d->pool;
+    if (spec_build(h, codes, thr_bits, true)) { delete h; return 1; }
+    *handle = h;
+    return 0;
+}
+
+int tcbnn_inconv_specialized_layer(void* handle, const tcbnn_conv_desc* d, const float* x,
+                                   const uint8_t* x8, const float* lut, uint32_t* out,
+                                   long long out_image_stride, void* res_out, int res_out_bytes,
+                                   float* acc_out, void* stream) {
+    if (!handle) return fail("inconv_specialized_layer: null handle");
+    if (conv_check(d, false)) return 1;
+    const spec::SpecHandle* h = (const spec::SpecHandle*)handle;
+    if (d->O != h->O || d->R != h->R || d->S != h->S || d->stride_h != h->sh || d->stride_w != h->sw ||
+        d->pad_h != h->pad_h || d->pad_w != h->pad_w || d->pool != h->pool)
+        return fail("inconv_specialized_layer: descriptor does not match the one the kernel was built for");
+    if ((x != nullptr) == (x8 != nullptr)) return fail("inconv_specialized_layer: give fp32 images or uint8 images");
+    if (x8 && !lut) return fail("inconv_specialized_layer: uint8 images need the value table");
+    if (res_out && res_out_bytes != 2 && res_out_bytes != 4) return fail("inconv_specialized_layer: res_out_bytes must be 2 or 4");
+    const int Ow = (d->O + 31) / 32;
+    if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("inconv_specialized_layer: out_image_stride too small");
+    spec::SpecArgs c;
+    c.x = x; c.x8 = x8; c.lut = lut; c.B = d->B; c.H = d->H; c.W = d->W; c.OH = d->OH; c.OW = d->OW;
+    c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out;
+    c.res_out_bytes = res_out_bytes; c.res_out_ld = d->O; c.acc_out = acc_out;
+    c.total = (unsigned)((long long)d->B * d->OH * d->OW * d->pool * d->pool);
+    void* params[] = {&c};
+    const unsigned grid = (c.total + spec::kSpecThreads - 1) / spec::kSpecThreads;
+    CUDA_TRY(cudaLaunchKernel((const void*)(x ? h->k_f32 : h->k_u8), dim3(grid), dim3(spec::kSpecThreads), params, 0,
+                              (cudaStream_t)stream));
+    return launch_check("inconv_specialized_layer");
+}
+
+int tcbnn_inconv_release(void* handle) {
+    if (!handle) return 0;
+    spec::SpecHandle* h = (spec::SpecHandle*)handle;
+    cudaLibraryUnload(h->lib);
+    delete h;
+    return 0;
+}
+
+int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, long long* source_bytes) {
+    if (spec_check(d)) return 1;
+    const int RS = d->R * d->S;
+    std::vector<unsigned char> codes((size_t)RS * d->O);
+    std::vector<uint32_t> thr_bits(d->O);
+    unsigned s = seed * 2654435761u + 12345u;
+    for (auto& c : codes) { s = s * 1664525u + 1013904223u; c = (unsigned char)((s >> 24) & 7u); }
+    for (auto& t : thr_bits) { s = s * 1664525u + 1013904223u; t = 0x40000000u ^ (s & 0x807FFFFFu); }
+    spec::SpecHandle h{};
+    h.O = d->O; h.R = d->R; h.S = d->S; h.sh = d->stride_h; h.sw = d->stride_w;
+    h.pad_h = d->pad_h; h.pad_w = d->pad_w; h.pool = d->pool;
+    if (source_bytes) *source_bytes = (long long)spec::generate_source(h, codes, thr_bits).size();
+    return spec_build(&h, codes, thr_bits, false);
 }
 
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {

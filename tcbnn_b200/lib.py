@@ -45,6 +45,10 @@ SIGNATURES = {
     "tcbnn_inconv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_noalloc_scratch_bytes": (_SZ, []),
     "tcbnn_fc_layer_noalloc": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "tcbnn_inconv_specialize": (_I, [C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(C.c_void_p)]),
+    "tcbnn_inconv_specialized_layer": (_I, [_P, C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
+    "tcbnn_inconv_release": (_I, [_P]),
+    "tcbnn_inconv_specialize_selftest": (_I, [C.POINTER(ConvDesc), C.c_uint, C.POINTER(C.c_longlong)]),
     "tcbnn_inconv_layer_u8": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_mma_peak": (_I, [_I, _I, _I, C.POINTER(C.c_double)]),
 }

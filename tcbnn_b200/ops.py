@@ -158,10 +158,38 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
     return out, res_out, acc_out
 
 
+class InconvSpecialized:
+    """A first-layer kernel compiled for one filter and one set of thresholds
+    (tcbnn_inconv_specialize); pass it to inconv_layer(specialized=...)."""
+
+    def __init__(self, d, filter_bits, thr):
+        _need_cuda(filter_bits, thr)
+        h = C.c_void_p(None)
+        _l.call("tcbnn_inconv_specialize", C.byref(d), _ptr(filter_bits), _ptr(thr), _stream(), C.byref(h))
+        self.handle = h
+
+    def release(self):
+        if self.handle is not None and self.handle.value:
+            _l.call("tcbnn_inconv_release", self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+def inconv_specialize(d, filter_bits, thr):
+    return InconvSpecialized(d, filter_bits, thr)
+
+
 def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_residual=False,
-                 want_acc=False, res_out_buf=None, residual_dtype=torch.int32, lut=None):
+                 want_acc=False, res_out_buf=None, residual_dtype=torch.int32, lut=None,
+                 specialized=None):
     """x: fp32 [B][3][H][W], or uint8 [B][3][H][W] together with lut (fp32 [3][256], the value
-    of every byte per channel).  Returns (out_bits, res_out, acc_out)."""
+    of every byte per channel).  specialized: an InconvSpecialized built from the same filter
+    and thresholds (filter_bits and thr are then not read).  Returns (out_bits, res_out, acc_out)."""
     _need_cuda(x, filter_bits, thr, lut)
     if (x.dtype == torch.uint8) != (lut is not None):
         raise _l.TcbnnError("inconv_layer: uint8 images need a lut, fp32 images must not have one")
@@ -174,7 +202,13 @@ def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_r
     if res_out is None and save_residual:
         res_out = torch.empty((d.B, P, Q, d.O), dtype=residual_dtype, device=x.device)
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.float32, device=x.device) if want_acc else None
-    if lut is not None:
+    if specialized is not None:
+        u8 = lut is not None
+        _l.call("tcbnn_inconv_specialized_layer", specialized.handle, C.byref(d),
+                None if u8 else _ptr(x), _ptr(x) if u8 else None, _ptr(lut), _ptr(out),
+                C.c_longlong(stride), _ptr(res_out),
+                res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
+    elif lut is not None:
         _l.call("tcbnn_inconv_layer_u8", C.byref(d), _ptr(x), _ptr(lut), _ptr(filter_bits), _ptr(thr),
                 _ptr(out), C.c_longlong(stride), _ptr(res_out),
                 res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())

@@ -203,11 +203,14 @@ class InConv128LayerParam:
         self.output_height, self.output_width = self.desc.OH, self.desc.OW
         self.output_residual_gpu = None
 
-    def initialize(self, input, config, input_lut=None):
+    def initialize(self, input, config, input_lut=None, specialize=True):
         """input: fp32 NCHW images as in the reference (param.h:760), or -- extension -- uint8 NCHW
         images with input_lut, fp32 [3][256]: the value of every byte per channel, i.e. the
         reader's normalisation tabulated (data.cpp:534-542).  Same results, a quarter of the
-        host->device traffic."""
+        host->device traffic.
+        specialize: compile a kernel for this layer's filter and thresholds (layers of at most 64
+        output channels; same results, several times faster than the kernel that reads the
+        filter at run time, which is used otherwise)."""
         dev = _dev()
         d = self.desc
         u8 = input_lut is not None
@@ -220,6 +223,13 @@ class InConv128LayerParam:
         self.filter_gpu = ops.pack_inconv_filter(f)
         self.bn = config.read(d.O)
         self.bn_gpu = torch.from_numpy(self.bn).to(dev)
+        self.specialized = None
+        if specialize and d.O <= 64:
+            try:
+                self.specialized = ops.inconv_specialize(d, self.filter_gpu, self.bn_gpu)
+            except Exception as e:      # no NVRTC on this machine: the general CUDA kernel runs
+                import warnings
+                warnings.warn("%s: first-layer kernel not specialised (%s)" % (self.name, e))
         Ow = (d.O + 31) // 32
         self.output_gpu = torch.zeros((d.B, d.OH, d.OW, Ow), dtype=torch.int32, device=dev)
         if self.save_residual:
@@ -235,7 +245,8 @@ class InConv128LayerParam:
 
     def forward(self):
         ops.inconv_layer(self.desc, self.input_gpu, self.filter_gpu, self.bn_gpu, out=self.output_gpu,
-                         res_out_buf=self.output_residual_gpu, lut=self.input_lut_gpu)
+                         res_out_buf=self.output_residual_gpu, lut=self.input_lut_gpu,
+                         specialized=self.specialized)
 
     def get_output_gpu(self):
         return self.output_gpu

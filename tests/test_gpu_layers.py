@@ -167,6 +167,66 @@ def test_inconv_layer(cuda, case):
     assert np.array_equal(host_u32(go), eo)
 
 
+SPEC_CASES = [c for c in INCONV_CASES if c[3] <= 64] + [
+    (3, 20, 20, 16, 5, 5, 1, 1, 2),
+    (5, 30, 28, 64, 7, 7, 4, 4, 1),      # odd output sizes, several blocks of pixels
+]
+
+
+@pytest.mark.parametrize("case", SPEC_CASES)
+def test_inconv_layer_specialized_kernel(cuda, case):
+    """The first-layer kernel compiled for one filter against the oracle: fp32 images, uint8
+    images with their value table, int32 and int16 residuals, and a batch size other than the
+    one it was built with."""
+    B, H, W, O, R, S, sh, sw, pool = case
+    g = util.rng(sum(case) + 5)
+    F = g.standard_normal((R * S, 3, O)).astype(np.float32)
+    thr = (g.standard_normal(O) * 3).astype(np.float32)
+    thr[0] = np.nan                                                   # never "less than": bit always set
+    fb = ops.pack_inconv_filter(dev(F, cuda))
+    d = ops.conv_desc(B, H, W, 3, O, R, S, sh, sw, True, pool)
+    spec = ops.inconv_specialize(d, fb, dev(thr, cuda))
+    for batch in (B, B + 3):
+        x = g.standard_normal((batch, 3, H, W)).astype(np.float32)
+        eo, er, ea = orc.inconv_layer(x, F, thr, R, S, sh, sw, True, pool, save_residual=True, want_acc=True)
+        db = ops.conv_desc(batch, H, W, 3, O, R, S, sh, sw, True, pool)
+        go, gr, ga = ops.inconv_layer(db, dev(x, cuda), fb, dev(thr, cuda), save_residual=True, want_acc=True,
+                                      specialized=spec)
+        assert np.array_equal(ga.cpu().numpy(), ea)
+        assert np.array_equal(gr.cpu().numpy(), er)
+        assert np.array_equal(host_u32(go), eo)
+        go, gr, _ = ops.inconv_layer(db, dev(x, cuda), fb, dev(thr, cuda), save_residual=True,
+                                     residual_dtype=torch.int16, specialized=spec)
+        assert np.array_equal(gr.cpu().numpy().astype(np.int32), er)
+        assert np.array_equal(host_u32(go), eo)
+    # uint8 images: the table plays the reader's normalisation
+    x8 = g.integers(0, 256, size=(B, 3, H, W)).astype(np.uint8)
+    lut = ((np.arange(256, dtype=np.float32)[None, :] / 255.0 - np.array([[0.4], [0.5], [0.45]], np.float32))
+           / np.array([[0.2], [0.25], [0.22]], np.float32)).astype(np.float32)
+    xf = np.stack([lut[c][x8[:, c]] for c in range(3)], axis=1)
+    eo, er, ea = orc.inconv_layer(xf, F, thr, R, S, sh, sw, True, pool, save_residual=True, want_acc=True)
+    go, gr, ga = ops.inconv_layer(d, dev(x8, cuda), fb, dev(thr, cuda), save_residual=True, want_acc=True,
+                                  lut=dev(lut, cuda), specialized=spec)
+    assert np.array_equal(ga.cpu().numpy(), ea)
+    assert np.array_equal(gr.cpu().numpy(), er)
+    assert np.array_equal(host_u32(go), eo)
+    spec.release()
+
+
+def test_inconv_specialize_rejects_wide_layers_and_mismatched_descriptors(cuda):
+    from tcbnn_b200.lib import TcbnnError
+    d = ops.conv_desc(1, 8, 8, 3, 128, 3, 3)
+    fb = torch.zeros((9, 3, 4), dtype=torch.int32, device=cuda)
+    thr = torch.zeros((128,), device=cuda)
+    with pytest.raises(TcbnnError):
+        ops.inconv_specialize(d, fb, thr)
+    d = ops.conv_desc(1, 8, 8, 3, 32, 3, 3)
+    spec = ops.inconv_specialize(d, torch.zeros((9, 3, 1), dtype=torch.int32, device=cuda), thr[:32].contiguous())
+    other = ops.conv_desc(1, 8, 8, 3, 32, 5, 5)
+    with pytest.raises(TcbnnError):
+        ops.inconv_layer(other, torch.zeros((1, 3, 8, 8), device=cuda), None, None, specialized=spec)
+
+
 def test_int16_residual_overflow_is_flagged(cuda):
     """A residual that does not fit the int16 element size the caller chose sets status 2."""
     g = util.rng(77)
