@@ -98,10 +98,25 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
                      long long out_image_stride, void* res_out, int res_out_bytes,
                      int32_t* acc_out, void* stream);
 
+/* tcbnn_conv_layer with a scratch buffer.  Narrow stride-1 layers (at most 128 input channels)
+ * run fastest when their input is first written out as +-1 bytes in the tensor cores' operand
+ * layout by a streaming pass and the convolution kernel fetches it with bulk copies;
+ * tcbnn_conv_workspace_bytes says how much device memory (256-byte aligned) that takes for a
+ * descriptor, 0 when the layer has no use for it.  The buffer is only used during the call
+ * (stream order); one buffer of the largest size serves all layers of a network on one stream.
+ * With workspace == NULL this is tcbnn_conv_layer.  No reference counterpart. */
+size_t tcbnn_conv_workspace_bytes(const tcbnn_conv_desc* d);
+int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
+                       const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
+                       int residual_channels, int residual_pool, uint32_t* out,
+                       long long out_image_stride, void* res_out, int res_out_bytes,
+                       int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Which kernel tcbnn_conv_layer uses: 0 = automatic (tcgen05 int8 implicit GEMM where the layer
  * is eligible, else the warp-level b1 MMA), 1 = always the b1 MMA, 2 = tcgen05 or an error,
- * 3 = as 2 but only the filter-stationary tcgen05 kernel (wide stride-1 layers otherwise take the
- * activation-stationary one).
+ * 3 = as 2 but only the filter-stationary tcgen05 kernel with its in-kernel bit expansion (wide
+ * stride-1 layers otherwise take the activation-stationary kernel, narrow ones with a workspace the
+ * kernel fed from a pre-expanded input).
  * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);

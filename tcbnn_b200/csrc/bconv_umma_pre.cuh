@@ -1,0 +1,403 @@
+// tcgen05 binary convolution fed from a pre-expanded input (stride 1, C <= 128).
+//
+// In bconv_umma_ws.cuh seven warps of every CTA turn packed bits into +-1 bytes, stage by
+// stage, next to the epilogue warps; with 16 warps per SM that chain of dependent scalar
+// instructions is what the narrow layers (64 / 128 channels) wait for.  Here the expansion is a
+// separate streaming pass (expand_raster below: full occupancy, HBM-bound, 8 bytes in and 64 out
+// per pixel and 64-channel block) that writes the layer's input as +-1 bytes straight in the
+// layout the MMA wants: for every 16-channel chunk a plane [raster position][16 bytes] over the
+// zero-padded virtual raster of bconv_umma.cuh, zeros on the dead bands.  A tile's patch is
+// then four contiguous runs per 64-channel block, which one thread fetches with bulk
+// asynchronous copies (cp.async.bulk + mbarrier complete_tx).  The CTA becomes
+//
+//   warps 0-15  epilogue   : warp w reads TMEM lanes 32*(w%4).., columns (w/4) * NT/4 ..
+//   warp  16    loader     : one lane, bulk copies of the patch planes into the stage ring
+//   warp  17    MMA issuer : one lane, as in bconv_umma_ws.cuh
+//
+// i.e. twice the epilogue threads on every accumulator, each holding a quarter of its columns.
+// The scratch planes come from the caller (tcbnn_conv_workspace_bytes).
+#pragma once
+#include "bconv_umma_as.cuh"
+
+namespace tcbnn {
+namespace umma {
+
+constexpr int kPreEpiThreads = 512;
+constexpr int kPreThreads = kPreEpiThreads + 64;
+constexpr int kPreMaxStages = 8;           // patch ring depth is chosen by the host from the shared memory left
+
+// positions of zero padding in front of the planes (a tile's patch starts up to back_y*PW+back_x
+// positions before its first output position) and the rounded-up plane length
+__host__ __device__ inline long long pre_front(int back_y, int back_x, int PW) {
+    return ((long long)back_y * PW + back_x + 7) & ~7LL;
+}
+__host__ __device__ inline long long pre_plane_positions(long long NV, int npos, long long front) {
+    return ((front + ((NV + 127) / 128) * 128 + npos + 7) & ~7LL);
+}
+__host__ __device__ inline size_t pre_smem_bytes(int npos, int C, int RS, int nt, int stages) {
+    return (size_t)stages * 4 * npos * 16 + (size_t)RS * C * nt + nt * 4 + RS * 8 + 40 * 8 + 64;
+}
+
+// packed bits [B][H][W][C/32] -> planes [C/16][plane_positions][16 B] of +-1 bytes, zero where the
+// raster position is padding or outside the batch
+__device__ __forceinline__ void expand_raster(const ConvWsArgs& a, uint4* planes, long long plane_positions,
+                                              long long front) {
+    const int NCB = a.C >> 6, Cw = a.C >> 5;
+    const long long total = plane_positions * NCB;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int cb = (int)(i / plane_positions);
+        const long long slot = i - (long long)cb * plane_positions;
+        const long long gq = slot - front;
+        uint4 e0 = make_uint4(0u, 0u, 0u, 0u), e1 = e0, e2 = e0, e3 = e0;
+        if (gq >= 0 && gq < a.NV) {
+            const int vy = fastdiv((int)gq, a.pw_mul, a.pw_sh), vx = (int)gq - vy * a.PW;
+            const int n = fastdiv(vy, a.vh_mul, a.vh_sh), vr = vy - n * a.VH;
+            if (vr < a.H && vx < a.W) {
+                const uint2 b = ldg64(a.in + ((size_t)(n * a.H + vr) * a.W + vx) * Cw + cb * 2);
+                e0 = expand16(b.x >> 16); e1 = expand16(b.x & 0xFFFFu);
+                e2 = expand16(b.y >> 16); e3 = expand16(b.y & 0xFFFFu);
+            }
+        }
+        uint4* dst = planes + (size_t)(cb * 4) * plane_positions + slot;
+        dst[0] = e0;
+        dst[(size_t)plane_positions] = e1;
+        dst[(size_t)2 * plane_positions] = e2;
+        dst[(size_t)3 * plane_positions] = e3;
+    }
+}
+
+template <int NT>
+__device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
+    // All 512 columns of tensor memory serve as accumulators (8 at NT = 64) and the patch ring is
+    // as deep as shared memory allows, so that no role waits on another's latency.
+    constexpr uint32_t TM_COLS = 512;
+    constexpr int NACC = NT >= 128 ? 2 : ((512 / NT) > 8 ? 8 : (512 / NT));   // measured: deeper does not pay at NT = 128
+    const int NSTAGE = a.pre_stages;
+    constexpr int COLS = NT / 4;                      // accumulator columns per epilogue thread
+    static_assert(COLS == 8 || COLS == 16 || COLS == 32, "n-tile of 32, 64 or 128");
+    constexpr int LOAD_WARP = kPreEpiThreads / 32, MMA_WARP = LOAD_WARP + 1;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int RS = a.R * a.S, NCB = a.C >> 6;
+    const uint32_t stage_bytes = 4u * a.NPOS * 16u;
+
+    unsigned char* sAraw = smem;
+    uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
+    int* sThr = reinterpret_cast<int*>(sB + (size_t)RS * (a.C >> 4) * NT);
+    uint32_t* sTapK = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sThr + NT) + 7) & ~(uintptr_t)7);
+    uint64_t* sBar = reinterpret_cast<uint64_t*>(sTapK + 2 * RS);
+    // barriers: a_full[8], a_empty[8], acc_full[8], acc_empty[8]
+    uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 32);
+    volatile int* sAbort = reinterpret_cast<volatile int*>(sTmem + 1);
+    const uint32_t bar0 = smem_u32(sBar);
+    auto BAR_AFULL = [&](int s) { return bar0 + 8u * s; };
+    auto BAR_AEMPTY = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto BAR_CFULL = [&](int b) { return bar0 + 8u * (16 + b); };
+    auto BAR_CEMPTY = [&](int b) { return bar0 + 8u * (24 + b); };
+
+    const int nt = blockIdx.x % a.ntiles_n;
+    const int mfirst = blockIdx.x / a.ntiles_n, mstep = gridDim.x / a.ntiles_n;
+    const int NV = (int)a.NV;
+    const int mtiles = (NV + 127) / 128;
+    const int obase = nt * NT;
+
+    if (tid == 0) {
+        for (int s = 0; s < 8; s++) { mbar_init(BAR_AFULL(s), 1); mbar_init(BAR_AEMPTY(s), 1); }
+        for (int b = 0; b < 8; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), kPreEpiThreads / 32); }
+        *sAbort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) tmem_alloc(smem_u32(sTmem), TM_COLS);
+    {
+        const uint4* src = a.wi8 + (size_t)nt * RS * (a.C >> 4) * NT;
+        const int nB = RS * (a.C >> 4) * NT;
+        for (int i = tid; i < nB; i += kPreThreads) sB[i] = __ldg(src + i);
+        for (int i = tid; i < NT; i += kPreThreads) {
+            // integer form of  !((float)v < thr)  (kernel.cuh:795-796): v >= ceil(thr)
+            int it = INT_MIN;
+            if (obase + i < a.O) {
+                const float t = __ldg(a.thr + obase + i);
+                if (t == t) it = t >= 2147483520.0f ? INT_MAX : t <= -2147483648.0f ? INT_MIN : (int)ceilf(t);
+            }
+            sThr[i] = it;
+        }
+        for (int t = tid; t < RS; t += kPreThreads) {
+            const uint32_t byte_off = (uint32_t)((t / a.S) * a.PW + (t % a.S)) * 16u;
+            sTapK[2 * t] = byte_off >> 4;
+            sTapK[2 * t + 1] = (byte_off + 2u * (uint32_t)a.NPOS * 16u) >> 4;
+        }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *sTmem;
+    const WsWait wait{sAbort, a.err_flag};
+
+    if (warp == LOAD_WARP) {
+        // =============================== patch loader =======================================
+        if (lane == 0) {
+            const long long back = (long long)a.back_y * a.PW + a.back_x;
+            uint32_t it = 0, sph = 0;
+            int s = 0;
+            bool ok = true;
+            for (int m = mfirst; m < mtiles && ok; m += mstep) {
+                const long long slot0 = (long long)m * 128 - back + a.pre_front;
+                for (int cb = 0; cb < NCB; cb++, it++) {
+                    ok = wait(BAR_AEMPTY(s), sph ^ 1);
+                    if (!ok) break;
+                    mbar_expect_tx(BAR_AFULL(s), stage_bytes);
+                    const uint32_t dst = smem_u32(sAraw + (size_t)s * stage_bytes);
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+                        bulk_g2s(dst + c * (uint32_t)a.NPOS * 16u,
+                                 a.pre + (size_t)(cb * 4 + c) * a.pre_positions + slot0,
+                                 (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
+                    if (++s == NSTAGE) { s = 0; sph ^= 1; }
+                }
+            }
+            if (!ok) {
+                // giving up: wait (bounded) for the copies still in flight before the CTA exits;
+                // stages below `s` were last filled in this pass over the ring, the others in the one before
+                for (int s2 = 0; s2 < NSTAGE; s2++) {
+                    const bool this_pass = s2 < s;
+                    if (!this_pass && it < (uint32_t)NSTAGE) continue;
+                    for (int i = 0; i < (1 << 20); i++)
+                        if (mbar_try_wait(BAR_AFULL(s2), this_pass ? sph : sph ^ 1)) break;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == MMA_WARP) {
+        // =============================== MMA issuer =========================================
+        if (lane == 0) {
+            const uint32_t lboA = (uint32_t)a.NPOS * 16u, lboB = NT * 16u;
+            const uint64_t descA0 = smem_desc(smem_u32(sAraw), lboA, 128u);
+            const uint64_t descB0 = smem_desc(smem_u32(sB), lboB, 128u);
+            const uint32_t aHi = (uint32_t)(descA0 >> 32), bHi = (uint32_t)(descB0 >> 32);
+            const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0;
+            const uint32_t stepB = (2u * lboB) >> 4, stepStage = stage_bytes >> 4;
+            constexpr uint32_t IDESC = idesc_i8(NT);
+            uint32_t ak[18];
+            const bool rs9 = RS == 9;
+#pragma unroll
+            for (int i = 0; i < 18; i++) ak[i] = rs9 ? sTapK[i] : 0u;
+            uint32_t it = 0, tc = 0, sph = 0, bph = 0;
+            int s = 0, b = 0;
+            bool ok = true;
+            long long tr_wc = 0, tr_wa = 0;
+            const long long tr_t0 = clock64();
+            for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
+                ok = wait.timed(BAR_CEMPTY(b), bph ^ 1, tr_wc);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d = tmem + b * NT;
+                uint32_t acc = 0;
+                uint32_t bLo = bLo0;
+                for (int cb = 0; cb < NCB && ok; cb++, it++) {
+                    ok = wait.timed(BAR_AFULL(s), sph, tr_wa);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t aLo = aLo0 + s * stepStage;
+                    if (rs9) {
+#pragma unroll
+                        for (int i = 0; i < 18; i++)
+                            mma_i8_split(d, aLo + ak[i], aHi, bLo + i * stepB, bHi, IDESC, i == 0 ? acc : 1u);
+                        bLo += 18 * stepB;
+                    } else {
+                        for (int t = 0; t < RS; t++) {
+                            const uint2 ao = *reinterpret_cast<const uint2*>(sTapK + 2 * t);
+                            mma_i8_split(d, aLo + ao.x, aHi, bLo, bHi, IDESC, acc);
+                            mma_i8_split(d, aLo + ao.y, aHi, bLo + stepB, bHi, IDESC, 1u);
+                            acc = 1;
+                            bLo += 2 * stepB;
+                        }
+                    }
+                    acc = 1;
+                    mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
+                    if (++s == NSTAGE) { s = 0; sph ^= 1; }
+                }
+                if (ok) mma_commit(BAR_CFULL(b));       // accumulator complete
+                if (++b == NACC) { b = 0; bph ^= 1; }
+            }
+            if (a.trace && blockIdx.x == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[2] = it; }
+        }
+        __syncwarp();
+    } else if (tid < kPreEpiThreads) {
+        // =============================== epilogue ===========================================
+        constexpr int NQ = COLS / 8;                       // 8-channel groups (one uint4 of int16) per thread
+        const int row = tid & 127, quad = warp & 3, cg = warp >> 2;
+        const int Ow = (a.O + 31) >> 5;
+        const int lim = a.res_in ? min(a.residual_channels, a.res_in_ch) : 0;
+        const int o0 = obase + cg * COLS;                  // this thread's first output channel
+        const bool res16 = a.res_in && a.res_in_bytes == 2 && (a.res_in_ch & 7) == 0 && (lim & 7) == 0;
+        uint32_t tc = 0;
+        bool ok = true, overflow = false;
+        long long tr_w = 0;
+        const long long tr_t0 = clock64();
+        struct Pix { bool live; int n, y, x; size_t opix; };
+        auto locate = [&](int m) {
+            Pix q{false, 0, 0, 0, 0};
+            const int p = m * 128 + row;
+            if (p < NV) {
+                const int vy = fastdiv(p, a.pw_mul, a.pw_sh);
+                q.x = p - vy * a.PW;
+                q.n = fastdiv(vy, a.vh_mul, a.vh_sh);
+                q.y = vy - q.n * a.VH;
+                q.live = q.x < a.OWg && q.y < a.OHg;
+            }
+            q.opix = ((size_t)q.n * a.OHg + q.y) * a.OWg + q.x;
+            return q;
+        };
+        // int16 residual of channels [o0, o0+COLS) of one pixel, packed (zeros where nothing is
+        // injected); 2x2 max for pooled residuals (kernel.cuh:773-783)
+        auto fetch16 = [&](uint4 (&r)[NQ], const Pix& q) {
+            const short* base = reinterpret_cast<const short*>(a.res_in);
+            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            if (a.residual_pool) {
+                const size_t b00 = (((size_t)q.n * 2 * a.OHg + 2 * q.y) * 2 * a.OWg + 2 * q.x) * a.res_in_ch + o0;
+                const size_t rowp = (size_t)2 * a.OWg * a.res_in_ch;
+#pragma unroll
+                for (int h = 0; h < NQ; h += 2) {              // 8 loads in flight at a time
+                    uint4 w[4][2];
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const bool on = h + j < NQ && q.live && o0 + 8 * (h + j) < lim;
+                        const short* s = base + b00 + 8 * (h + j);
+                        w[0][j] = on ? __ldg(reinterpret_cast<const uint4*>(s)) : z;
+                        w[1][j] = on ? __ldg(reinterpret_cast<const uint4*>(s + a.res_in_ch)) : z;
+                        w[2][j] = on ? __ldg(reinterpret_cast<const uint4*>(s + rowp)) : z;
+                        w[3][j] = on ? __ldg(reinterpret_cast<const uint4*>(s + rowp + a.res_in_ch)) : z;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        if (h + j >= NQ) continue;
+                        r[h + j].x = __vmaxs2(__vmaxs2(w[0][j].x, w[1][j].x), __vmaxs2(w[2][j].x, w[3][j].x));
+                        r[h + j].y = __vmaxs2(__vmaxs2(w[0][j].y, w[1][j].y), __vmaxs2(w[2][j].y, w[3][j].y));
+                        r[h + j].z = __vmaxs2(__vmaxs2(w[0][j].z, w[1][j].z), __vmaxs2(w[2][j].z, w[3][j].z));
+                        r[h + j].w = __vmaxs2(__vmaxs2(w[0][j].w, w[1][j].w), __vmaxs2(w[2][j].w, w[3][j].w));
+                    }
+                }
+            } else {
+                const short* s = base + q.opix * a.res_in_ch + o0;
+#pragma unroll
+                for (int j = 0; j < NQ; j++)
+                    r[j] = (q.live && o0 + 8 * j < lim) ? __ldg(reinterpret_cast<const uint4*>(s + 8 * j)) : z;
+            }
+        };
+        uint4 rnext[NQ];
+#pragma unroll
+        for (int j = 0; j < NQ; j++) rnext[j] = make_uint4(0u, 0u, 0u, 0u);
+        Pix cur = locate(mfirst);
+        if (res16 && mfirst < mtiles) fetch16(rnext, cur);
+        int b = 0;
+        uint32_t bph = 0;
+        for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
+            const Pix q = cur;
+            uint4 rcur[NQ];
+#pragma unroll
+            for (int j = 0; j < NQ; j++) rcur[j] = rnext[j];
+            if (m + mstep < mtiles) {                      // next tile's row: its residual flies during this tile
+                cur = locate(m + mstep);
+                if (res16) fetch16(rnext, cur);
+            }
+            ok = wait.timed(BAR_CFULL(b), bph, tr_w);
+            if (!ok) break;
+            tc_fence_after();
+            int v[COLS];
+            tmem_ld_cols<COLS>(tmem + ((uint32_t)(quad * 32) << 16) + b * NT + cg * COLS, v);
+            tmem_ld_wait();
+            tc_fence_before();                             // this warp is done with the accumulator
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_CEMPTY(b));
+            if (++b == NACC) { b = 0; bph ^= 1; }
+            if (q.live && a.acc_out) {
+                int4* dst = reinterpret_cast<int4*>(a.acc_out + q.opix * a.O + o0);
+#pragma unroll
+                for (int j = 0; j < COLS / 4; j++)
+                    dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+            if (res16) {
+#pragma unroll
+                for (int j = 0; j < NQ; j++) {
+                    v[8 * j] += (int)(short)(rcur[j].x & 0xFFFFu);
+                    v[8 * j + 1] += (int)(short)(rcur[j].x >> 16);
+                    v[8 * j + 2] += (int)(short)(rcur[j].y & 0xFFFFu);
+                    v[8 * j + 3] += (int)(short)(rcur[j].y >> 16);
+                    v[8 * j + 4] += (int)(short)(rcur[j].z & 0xFFFFu);
+                    v[8 * j + 5] += (int)(short)(rcur[j].z >> 16);
+                    v[8 * j + 6] += (int)(short)(rcur[j].w & 0xFFFFu);
+                    v[8 * j + 7] += (int)(short)(rcur[j].w >> 16);
+                }
+            } else if (a.res_in && q.live && o0 < lim) {
+#pragma unroll
+                for (int j = 0; j < COLS / 4; j++) {
+                    const int o = o0 + 4 * j;
+                    if (o >= lim) continue;
+                    int4 r;
+                    if (a.residual_pool) {
+                        const size_t b00 = (((size_t)q.n * 2 * a.OHg + 2 * q.y) * 2 * a.OWg + 2 * q.x) * a.res_in_ch + o;
+                        const size_t rowp = (size_t)2 * a.OWg * a.res_in_ch;
+                        r = max4(max4(ld_res4(a.res_in, a.res_in_bytes, b00),
+                                      ld_res4(a.res_in, a.res_in_bytes, b00 + a.res_in_ch)),
+                                 max4(ld_res4(a.res_in, a.res_in_bytes, b00 + rowp),
+                                      ld_res4(a.res_in, a.res_in_bytes, b00 + rowp + a.res_in_ch)));
+                    } else {
+                        r = ld_res4(a.res_in, a.res_in_bytes, q.opix * a.res_in_ch + o);
+                    }
+                    v[4 * j] += r.x; v[4 * j + 1] += r.y; v[4 * j + 2] += r.z; v[4 * j + 3] += r.w;
+                }
+            }
+            uint32_t word = 0;                             // channel c of this thread at bit COLS-1-c
+            const int4* th4 = reinterpret_cast<const int4*>(sThr + cg * COLS);
+#pragma unroll
+            for (int j = 0; j < COLS / 4; j++) {
+                const int4 th = th4[j];
+                if (v[4 * j] >= th.x) word |= (1u << (COLS - 1)) >> (4 * j);
+                if (v[4 * j + 1] >= th.y) word |= (1u << (COLS - 1)) >> (4 * j + 1);
+                if (v[4 * j + 2] >= th.z) word |= (1u << (COLS - 1)) >> (4 * j + 2);
+                if (v[4 * j + 3] >= th.w) word |= (1u << (COLS - 1)) >> (4 * j + 3);
+            }
+            if (a.res_out && q.live) {
+                const size_t idx = q.opix * a.O + o0;
+                if (a.res_out_bytes == 2) {
+                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<short*>(a.res_out) + idx);
+                    uint32_t ovf = 0;                      // |v| of every value ORed together
+#pragma unroll
+                    for (int j = 0; j < NQ; j++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {
+                            const int lo = v[8 * j + 2 * kk], hi = v[8 * j + 2 * kk + 1];
+                            ovf |= (uint32_t)(lo ^ (lo >> 31)) | (uint32_t)(hi ^ (hi >> 31));
+                            w[kk] = ((uint32_t)lo & 0xFFFFu) | ((uint32_t)hi << 16);
+                        }
+                        dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                    overflow |= ovf > 32767u;              // some value outside [-32768, 32767]
+                } else {
+                    int4* dst = reinterpret_cast<int4*>(reinterpret_cast<int*>(a.res_out) + idx);
+#pragma unroll
+                    for (int j = 0; j < COLS / 4; j++)
+                        dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+            if (q.live) {
+                // bits of channel o live at bit 31 - o%32 of word o/32 (little-endian bytes)
+                unsigned char* wp = reinterpret_cast<unsigned char*>(
+                    a.out + (size_t)q.n * a.out_image_stride + ((size_t)q.y * a.OWg + q.x) * Ow + (o0 >> 5));
+                if (COLS == 32) *reinterpret_cast<uint32_t*>(wp) = word;
+                else if (COLS == 16) *reinterpret_cast<unsigned short*>(wp + ((o0 & 16) ? 0 : 2)) = (unsigned short)word;
+                else wp[3 - ((o0 & 31) >> 3)] = (unsigned char)word;
+            }
+        }
+        if (overflow) atomicExch(a.err_flag, 2);
+        if (a.trace && blockIdx.x == 0 && tid == 0) { a.trace[6] = clock64() - tr_t0; a.trace[7] = tr_w; a.trace[8] = tc; }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) tmem_dealloc(tmem, TM_COLS);
+}
+
+}  // namespace umma
+}  // namespace tcbnn

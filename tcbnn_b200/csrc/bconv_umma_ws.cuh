@@ -41,6 +41,9 @@ struct ConvWsArgs {
     int ntiles_n;
     int as_split;             // activation-stationary kernel: parts the n-tiles of a task are split into
     int as_slots;             // ... and units in its filter ring (9 or 18)
+    const uint4* pre;         // pre-expanded input planes (bconv_umma_pre.cuh), else null
+    long long pre_positions, pre_front;
+    int pre_stages;           // patch ring depth of that kernel
     const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
     uint32_t* out; long long out_image_stride;
     void* res_out; int res_out_bytes; int32_t* acc_out;
@@ -99,6 +102,18 @@ struct WsWait {
         for (int i = 0; i < (1 << 24); i++) {
             if (mbar_try_wait(bar, parity)) return true;
             if ((i & 1023) == 1023 && *abort) return false;
+        }
+        *abort = 1;
+        atomicExch(err, 1);
+        return false;
+    }
+    // the same for roles that can afford to look less often: sleeps between polls, so that many
+    // waiting warps do not keep the shared-memory pipe busy with barrier reads
+    __device__ __forceinline__ bool relaxed(uint32_t bar, uint32_t parity) const {
+        for (int i = 0; i < (1 << 22); i++) {
+            if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(64);
+            if ((i & 255) == 255 && *abort) return false;
         }
         *abort = 1;
         atomicExch(err, 1);

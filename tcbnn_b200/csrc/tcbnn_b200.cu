@@ -5,6 +5,7 @@
 #include "bconv_umma.cuh"
 #include "bconv_umma_ws.cuh"
 #include "bconv_umma_as.cuh"
+#include "bconv_umma_pre.cuh"
 #include "inconv_spec.cuh"
 #include "inconv_tiled.cuh"
 #include <cstdio>
@@ -151,6 +152,11 @@ struct PreparedLayout {
     int umma_pw, umma_vh, umma_back_y, umma_back_x;   // raster geometry
     // activation-stationary tcgen05 kernel (wide stride-1 layers): its own filter copy in
     // 128-channel n-tiles (shared with the other kernel's when that one also uses 128)
+    // kernel fed from a pre-expanded input (narrow stride-1 layers): needs a caller workspace
+    size_t pre_bytes;     // workspace size, 0 when the layer is not eligible
+    size_t pre_smem;
+    int pre_stages;
+    long long pre_positions, pre_front;
     int as_npos;          // 0 when the layer is not eligible
     int as_slots;         // units in its filter ring
     size_t as_smem, off_wi8_as;
@@ -191,6 +197,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o;
     L.umma_pw = L.umma_vh = L.umma_back_y = L.umma_back_x = 0;
     L.as_npos = 0; L.as_smem = 0; L.as_slots = 0; L.off_wi8_as = o;
+    L.pre_bytes = 0; L.pre_smem = 0; L.pre_stages = 0; L.pre_positions = 0; L.pre_front = 0;
     if (d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) && d->pool == 1 &&
         d->padding && d->C % 64 == 0 && d->O % 32 == 0) {
         const int st = d->stride_h;
@@ -216,6 +223,18 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
                 L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
                 o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
                 break;
+            }
+            if (L.umma_nt && st == 1 && d->C <= 128 && L.umma_nt <= 128) {
+                int stages = L.umma_nt >= 128 ? 3 : umma::kPreMaxStages;
+                while (stages > 2 && umma::pre_smem_bytes(npos, d->C, d->R * d->S, L.umma_nt, stages) > 227 * 1024) stages--;
+                const size_t smem_pre = umma::pre_smem_bytes(npos, d->C, d->R * d->S, L.umma_nt, stages);
+                L.pre_stages = stages;
+                if (smem_pre <= 227 * 1024) {
+                    L.pre_front = umma::pre_front(back_y, back_x, PW);
+                    L.pre_positions = umma::pre_plane_positions(nv, npos, L.pre_front);
+                    L.pre_bytes = (size_t)d->C * (size_t)L.pre_positions;     // C/16 planes x 16 bytes
+                    L.pre_smem = smem_pre;
+                }
             }
             // wide layers: keep 256 positions x all channels resident, stream the filter
             const int npos_as = (256 + (back_y + fwd_y) * PW + back_x + fwd_x + 7) & ~7;
@@ -297,6 +316,40 @@ int launch_conv_umma_ws(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t 
     if (per > mtiles) per = mtiles;
     k_conv_umma_ws<NT, STRIDE><<<(int)(per * a.ntiles_n), umma::kWsThreads, smem, st>>>(a);
     return launch_check("conv_layer (tcgen05)");
+}
+
+template <int NT>
+__global__ void __launch_bounds__(umma::kPreThreads, 1) k_conv_umma_pre(umma::ConvWsArgs a) {
+    extern __shared__ __align__(128) unsigned char dyn_smem_pre[];
+    umma::conv_umma_pre_cta<NT>(a, dyn_smem_pre);
+}
+__global__ void __launch_bounds__(256) k_expand_raster(umma::ConvWsArgs a, uint4* planes, long long positions,
+                                                       long long front) {
+    umma::expand_raster(a, planes, positions, front);
+}
+
+template <int NT>
+int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_conv_umma_pre<NT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured[dev] = true;
+    }
+    const long long units = a.pre_positions * (a.C >> 6);
+    k_expand_raster<<<elementwise_grid(units, sms), 256, 0, st>>>(a, const_cast<uint4*>(a.pre), a.pre_positions,
+                                                               a.pre_front);
+    if (launch_check("conv_layer (input expansion)")) return 1;
+    a.ntiles_n = a.O / NT;
+    if (a.ntiles_n > sms) return fail("conv_layer: more n-tiles than SMs");
+    const long long mtiles = (a.NV + 127) / 128;
+    long long per = sms / a.ntiles_n;
+    if (per > mtiles) per = mtiles;
+    k_conv_umma_pre<NT><<<(int)(per * a.ntiles_n), umma::kPreThreads, smem, st>>>(a);
+    return launch_check("conv_layer (tcgen05, pre-expanded input)");
 }
 
 __global__ void __launch_bounds__(umma::kAsThreads, 1) k_conv_umma_as(umma::ConvWsArgs a) {
@@ -557,11 +610,26 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
     return 0;
 }
 
+size_t tcbnn_conv_workspace_bytes(const tcbnn_conv_desc* d) {
+    if (conv_check(d, true)) return 0;
+    return prepared_layout(d).pre_bytes;
+}
+
 int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
                      const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
                      int residual_channels, int residual_pool, uint32_t* out,
                      long long out_image_stride, void* res_out, int res_out_bytes,
                      int32_t* acc_out, void* stream) {
+    return tcbnn_conv_layer_w(d, in, prepared, thr, res_in, res_in_bytes, res_in_ch, residual_channels,
+                              residual_pool, out, out_image_stride, res_out, res_out_bytes, acc_out,
+                              nullptr, 0, stream);
+}
+
+int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
+                       const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
+                       int residual_channels, int residual_pool, uint32_t* out,
+                       long long out_image_stride, void* res_out, int res_out_bytes,
+                       int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream) {
     if (conv_check(d, true)) return 1;
     const int Ow = (d->O + 31) / 32;
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("conv_layer: out_image_stride too small");
@@ -598,10 +666,23 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
         int sms;
         if (sm_count(&sms)) return 1;
         cudaStream_t st = (cudaStream_t)stream;
+        a.pre = nullptr; a.pre_positions = 0; a.pre_front = 0;
+        a.pre_stages = 0;
         if (use_as) {
             a.NPOS = L.as_npos; a.as_slots = L.as_slots;
             a.wi8 = (const uint4*)(p + L.off_wi8_as);
             return launch_conv_umma_as(a, L.as_smem, sms, st);
+        }
+        // worth its extra pass when the epilogue also moves residuals (measured); path 2 forces it
+        if (L.pre_bytes && workspace && g_conv_path != 3 && (res_in || res_out || g_conv_path == 2)) {
+            if (workspace_bytes < L.pre_bytes)
+                return fail("conv_layer: workspace of %zu bytes, the layer needs %zu", workspace_bytes, L.pre_bytes);
+            if ((uintptr_t)workspace & 255) return fail("conv_layer: workspace must be 256-byte aligned");
+            a.pre = (const uint4*)workspace; a.pre_positions = L.pre_positions; a.pre_front = L.pre_front;
+            a.pre_stages = L.pre_stages;
+            if (L.umma_nt == 32) return launch_conv_umma_pre<32>(a, L.pre_smem, sms, st);
+            if (L.umma_nt == 64) return launch_conv_umma_pre<64>(a, L.pre_smem, sms, st);
+            if (L.umma_nt == 128) return launch_conv_umma_pre<128>(a, L.pre_smem, sms, st);
         }
 #define TCBNN_WS_CASE(NN, SS) \
         if (L.umma_nt == NN && d->stride_h == SS) return launch_conv_umma_ws<NN, SS>(a, L.umma_smem, sms, st);

@@ -134,12 +134,38 @@ def conv_prepare(d, filter_bits):
     return blob
 
 
+_scratch = {}
+
+
+def conv_workspace(d, device):
+    """A scratch tensor large enough for tcbnn_conv_layer_w on this descriptor, or None when the
+    layer has no use for one.  One tensor per device, grown on demand and shared by every call
+    that does not bring its own: callers running layers on several streams at once must pass
+    separate workspaces."""
+    n = _l.load().tcbnn_conv_workspace_bytes(C.byref(d))
+    if n == 0:
+        return None
+    key = (device.type, device.index)
+    t = _scratch.get(key)
+    if t is None or t.numel() < n:
+        _scratch[key] = None
+        t = torch.empty((n,), dtype=torch.uint8, device=device)
+        _scratch[key] = t
+    return t
+
+
 def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_pool=False,
                out=None, out_image_stride=None, save_residual=False, want_acc=False,
-               res_out_buf=None, residual_dtype=torch.int32):
+               res_out_buf=None, residual_dtype=torch.int32, workspace=None):
     """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out).
-    Residual tensors may be torch.int32 or torch.int16."""
+    Residual tensors may be torch.int32 or torch.int16.
+    workspace: uint8 scratch tensor for tcbnn_conv_layer_w; None = the shared one of
+    conv_workspace(); False = none (tcbnn_conv_layer)."""
     _need_cuda(x, prepared, thr, res_in)
+    if workspace is None:
+        workspace = conv_workspace(d, x.device)
+    elif workspace is False:
+        workspace = None
     Ow = (d.O + 31) // 32
     stride = out_image_stride or d.OH * d.OW * Ow
     if out is None:
@@ -150,11 +176,15 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
         res_out = torch.empty((d.B, P, Q, d.O), dtype=residual_dtype, device=x.device)
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if want_acc else None
     res_in_ch = res_in.shape[-1] if res_in is not None else 0
-    _l.call("tcbnn_conv_layer", C.byref(d), _ptr(x), _ptr(prepared), _ptr(thr), _ptr(res_in),
+    args = (C.byref(d), _ptr(x), _ptr(prepared), _ptr(thr), _ptr(res_in),
             res_in.element_size() if res_in is not None else 4,
             res_in_ch, residual_channels, int(bool(residual_pool)), _ptr(out),
             C.c_longlong(stride), _ptr(res_out),
-            res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
+            res_out.element_size() if res_out is not None else 4, _ptr(acc_out))
+    if workspace is not None:
+        _l.call("tcbnn_conv_layer_w", *args, _ptr(workspace), C.c_size_t(workspace.numel()), _stream())
+    else:
+        _l.call("tcbnn_conv_layer", *args, _stream())
     return out, res_out, acc_out
 
 
