@@ -56,6 +56,9 @@ __device__ void conv_umma_as_cta(const ConvWsArgs& a, unsigned char* smem) {
     unsigned char* sA = smem;
     unsigned char* sB = smem + (size_t)NCB * cb_bytes;
     const int NS = a.as_slots;
+    const int GT = RS == 9 ? 3 : 1;                           // taps per filter group (a row of a 3x3 filter)
+    const int NG = NS / GT;                                   // groups in the ring
+    const uint32_t group_bytes = (uint32_t)GT * kAsUnitBytes;
     int* sThr = reinterpret_cast<int*>(sB + (size_t)NS * kAsUnitBytes);
     uint32_t* sTapK = reinterpret_cast<uint32_t*>(sThr + a.O);
     uint64_t* sBar = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(sTapK + 2 * RS) + 7) & ~(uintptr_t)7);
@@ -166,6 +169,8 @@ __device__ void conv_umma_as_cta(const ConvWsArgs& a, unsigned char* smem) {
         if (a.trace && blockIdx.x == 0 && et == 0) { a.trace[0] = clock64() - tr_t0; a.trace[1] = tr_wait; a.trace[2] = ic; }
     } else if (warp == 14) {
         // =============================== filter loader ======================================
+        // The filter moves in groups of GT taps (a filter row of a 3x3 filter: 24 KB, one copy,
+        // one barrier), so that the MMA warp waits and commits once per 12 MMAs.
         if (lane == 0) {
             int slot = 0;
             uint32_t ph = 0, issued = 0;                 // ph: parity of the current pass over the ring
@@ -175,23 +180,23 @@ __device__ void conv_umma_as_cta(const ConvWsArgs& a, unsigned char* smem) {
                 for (int nt = part * nts_per; nt < (part + 1) * nts_per && ok; nt++) {
                     const unsigned char* src = reinterpret_cast<const unsigned char*>(a.wi8) +
                                                (size_t)nt * NCB * RS * kAsUnitBytes;
-                    for (int k = 0; k < NCB * RS; k++) {
+                    for (int k = 0; k < NCB * RS; k += GT) {
                         ok = wait(BAR_BEMPTY(slot), ph ^ 1);
                         if (!ok) break;
-                        mbar_expect_tx(BAR_BFULL(slot), kAsUnitBytes);
-                        bulk_g2s(smem_u32(sB + (size_t)slot * kAsUnitBytes), src + (size_t)k * kAsUnitBytes,
-                                 kAsUnitBytes, BAR_BFULL(slot));
+                        mbar_expect_tx(BAR_BFULL(slot), group_bytes);
+                        bulk_g2s(smem_u32(sB + (size_t)slot * group_bytes), src + (size_t)k * kAsUnitBytes,
+                                 group_bytes, BAR_BFULL(slot));
                         issued++;
-                        if (++slot == NS) { slot = 0; ph ^= 1; }
+                        if (++slot == NG) { slot = 0; ph ^= 1; }
                     }
                 }
             }
             if (!ok) {
                 // giving up: wait (bounded) for the copies still in flight before the CTA exits;
                 // slots below `slot` were last filled in this pass, the others in the one before
-                for (int s2 = 0; s2 < NS; s2++) {
+                for (int s2 = 0; s2 < NG; s2++) {
                     const bool this_pass = s2 < slot;
-                    if (!this_pass && issued < (uint32_t)NS) continue;       // never filled
+                    if (!this_pass && issued < (uint32_t)NG) continue;       // never filled
                     const uint32_t par = this_pass ? ph : ph ^ 1;
                     for (int i = 0; i < (1 << 20); i++)
                         if (mbar_try_wait(BAR_BFULL(s2), par)) break;
@@ -201,27 +206,29 @@ __device__ void conv_umma_as_cta(const ConvWsArgs& a, unsigned char* smem) {
         __syncwarp();
     } else if (warp == 15) {
         // =============================== MMA issuer =========================================
-        // One thread issues everything, so its instruction count per MMA matters: a 128x128x32
-        // MMA occupies the tensor pipe for 64 clocks.  For 3x3 filters the ring holds whole
-        // 9-tap groups, every slot / barrier / tap offset of the unrolled loop is a constant or a
-        // register, and the waits on filter units are not timed.
-        if (lane == 0) {
+        // A 128x128x32 MMA occupies the tensor pipe for 64 clocks and the pipe does not run ahead
+        // of the issuing thread by much: whatever that thread executes between two MMAs is time
+        // the pipe idles.  So the whole warp runs the control flow converged (waits by all lanes
+        // with the non-blocking barrier test), one elected lane issues, and a wait / commit pair
+        // covers a group of taps (12 MMAs for a 3x3 filter).
+        {
+            const bool leader = elect_one();
             const uint32_t lboA = (uint32_t)a.NPOS * 16u, lboB = NT * 16u;
             const uint64_t descA0 = smem_desc(smem_u32(sA), lboA, 128u);
             const uint64_t descB0 = smem_desc(smem_u32(sB), lboB, 128u);
             const uint32_t aHi = (uint32_t)(descA0 >> 32), bHi = (uint32_t)(descB0 >> 32);
             const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0;
-            constexpr uint32_t stepKB = (2u * NT * 16u) >> 4;   // second k-step of a unit
-            constexpr uint32_t stepSlot = kAsUnitBytes >> 4;
+            constexpr uint32_t stepKB = (2u * NT * 16u) >> 4;   // second k-step of a tap
+            constexpr uint32_t stepTap = kAsUnitBytes >> 4;
             constexpr uint32_t stepSub = (128u * 16u) >> 4;     // second 128-row sub-tile
-            const uint32_t stepCb = cb_bytes >> 4;
+            const uint32_t stepCb = cb_bytes >> 4, stepGroup = group_bytes >> 4;
             constexpr uint32_t IDESC = idesc_i8(NT);
             const bool rs9 = RS == 9;
             uint32_t ak[18];
 #pragma unroll
             for (int i = 0; i < 18; i++) ak[i] = rs9 ? sTapK[i] : 0u;
             uint32_t cc = 0, ic = 0, units = 0;
-            int slot = 0;                    // first slot of the next unit (a multiple of 9 when rs9)
+            int slot = 0;
             uint32_t bph = 0;
             bool ok = true;
             long long tr_wc = 0, tr_wa = 0;
@@ -241,45 +248,53 @@ __device__ void conv_umma_as_cta(const ConvWsArgs& a, unsigned char* smem) {
                         }
                         const uint32_t aCb = aLo0 + cb * stepCb;
                         if (rs9) {
-                            const uint32_t bSet = bLo0 + slot * stepSlot;
-                            const uint32_t fullSet = BAR_BFULL(slot), emptySet = BAR_BEMPTY(slot);
 #pragma unroll
-                            for (int t = 0; t < 9; t++) {
-                                ok = ok && wait(fullSet + 8u * t, bph);
+                            for (int g = 0; g < 3; g++) {
+                                ok = ok && wait.spin(BAR_BFULL(slot), bph);
                                 if (!ok) break;
-                                const uint32_t acc = (t == 0 && cb == 0) ? 0u : 1u;
-                                const uint32_t bLo = bSet + t * stepSlot;
-                                mma_i8_split(d0, aCb + ak[2 * t], aHi, bLo, bHi, IDESC, acc);
-                                mma_i8_split(d1, aCb + ak[2 * t] + stepSub, aHi, bLo, bHi, IDESC, acc);
-                                mma_i8_split(d0, aCb + ak[2 * t + 1], aHi, bLo + stepKB, bHi, IDESC, 1u);
-                                mma_i8_split(d1, aCb + ak[2 * t + 1] + stepSub, aHi, bLo + stepKB, bHi, IDESC, 1u);
-                                mma_commit(emptySet + 8u * t);  // unit free once these MMAs have read it
-                            }
-                            units += 9;
-                            slot += 9;
-                            if (slot == NS) { slot = 0; bph ^= 1; }
-                        } else {
-                            for (int t = 0; t < RS; t++) {
-                                ok = wait(BAR_BFULL(slot), bph);
-                                if (!ok) break;
-                                const uint2 ao = *reinterpret_cast<const uint2*>(sTapK + 2 * t);
-                                const uint32_t bLo = bLo0 + slot * stepSlot;
-                                const uint32_t acc = (cb | t) ? 1u : 0u;
-                                mma_i8_split(d0, aCb + ao.x, aHi, bLo, bHi, IDESC, acc);
-                                mma_i8_split(d1, aCb + ao.x + stepSub, aHi, bLo, bHi, IDESC, acc);
-                                mma_i8_split(d0, aCb + ao.y, aHi, bLo + stepKB, bHi, IDESC, 1u);
-                                mma_i8_split(d1, aCb + ao.y + stepSub, aHi, bLo + stepKB, bHi, IDESC, 1u);
-                                mma_commit(BAR_BEMPTY(slot));
+                                tc_fence_after();
+                                if (leader) {
+                                    const uint32_t bG = bLo0 + slot * stepGroup;
+#pragma unroll
+                                    for (int j = 0; j < 3; j++) {
+                                        const int t = 3 * g + j;
+                                        const uint32_t acc = (t == 0 && cb == 0) ? 0u : 1u;
+                                        const uint32_t bLo = bG + j * stepTap;
+                                        mma_i8_split(d0, aCb + ak[2 * t], aHi, bLo, bHi, IDESC, acc);
+                                        mma_i8_split(d1, aCb + ak[2 * t] + stepSub, aHi, bLo, bHi, IDESC, acc);
+                                        mma_i8_split(d0, aCb + ak[2 * t + 1], aHi, bLo + stepKB, bHi, IDESC, 1u);
+                                        mma_i8_split(d1, aCb + ak[2 * t + 1] + stepSub, aHi, bLo + stepKB, bHi, IDESC, 1u);
+                                    }
+                                    mma_commit(BAR_BEMPTY(slot));   // group free once these MMAs have read it
+                                }
                                 units++;
-                                if (++slot == NS) { slot = 0; bph ^= 1; }
+                                if (++slot == NG) { slot = 0; bph ^= 1; }
+                            }
+                        } else {
+                            for (int t = 0; t < RS; t++) {          // GT == 1: one tap per group
+                                ok = wait.spin(BAR_BFULL(slot), bph);
+                                if (!ok) break;
+                                tc_fence_after();
+                                if (leader) {
+                                    const uint2 ao = *reinterpret_cast<const uint2*>(sTapK + 2 * t);
+                                    const uint32_t bLo = bLo0 + slot * stepGroup;
+                                    const uint32_t acc = (cb | t) ? 1u : 0u;
+                                    mma_i8_split(d0, aCb + ao.x, aHi, bLo, bHi, IDESC, acc);
+                                    mma_i8_split(d1, aCb + ao.x + stepSub, aHi, bLo, bHi, IDESC, acc);
+                                    mma_i8_split(d0, aCb + ao.y, aHi, bLo + stepKB, bHi, IDESC, 1u);
+                                    mma_i8_split(d1, aCb + ao.y + stepSub, aHi, bLo + stepKB, bHi, IDESC, 1u);
+                                    mma_commit(BAR_BEMPTY(slot));
+                                }
+                                units++;
+                                if (++slot == NG) { slot = 0; bph ^= 1; }
                             }
                         }
                     }
-                    if (ok) mma_commit(BAR_CFULL(buf));         // both sub-tile accumulators complete
+                    if (ok && leader) mma_commit(BAR_CFULL(buf));   // both sub-tile accumulators complete
                 }
-                if (ok) mma_commit(BAR_AEMPTY);                 // the patch may be overwritten
+                if (ok && leader) mma_commit(BAR_AEMPTY);           // the patch may be overwritten
             }
-            if (a.trace && blockIdx.x == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[10] = units; }
+            if (a.trace && blockIdx.x == 0 && leader) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[10] = units; }
         }
         __syncwarp();
     } else if (tid < kAsEpiThreads) {

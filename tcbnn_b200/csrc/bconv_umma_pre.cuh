@@ -170,7 +170,16 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         __syncwarp();
     } else if (warp == MMA_WARP) {
         // =============================== MMA issuer =========================================
-        if (lane == 0) {
+        // Where the MMAs are the critical path (n-tile of 128 or more, or several channel blocks per
+        // tile) the whole warp runs the control flow converged and polls the barriers, and one
+        // elected lane issues: what the issuing thread executes between two MMAs is time the
+        // tensor pipe idles, and a lone lane in a diverged warp pays far more per branch and per
+        // wait.  Narrow layers wait for their epilogue instead and measured faster with a single
+        // lane in the loop (the other 31 parked at the __syncwarp below).
+        const bool converged = NT >= 128 || NCB >= 2;
+        const bool elected = elect_one();
+        if (converged || lane == 0) {
+            const bool leader = converged ? elected : true;
             const uint32_t lboA = (uint32_t)a.NPOS * 16u, lboB = NT * 16u;
             const uint64_t descA0 = smem_desc(smem_u32(sAraw), lboA, 128u);
             const uint64_t descB0 = smem_desc(smem_u32(sB), lboB, 128u);
@@ -178,31 +187,33 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0;
             const uint32_t stepB = (2u * lboB) >> 4, stepStage = stage_bytes >> 4;
             constexpr uint32_t IDESC = idesc_i8(NT);
-            uint32_t ak[18];
             const bool rs9 = RS == 9;
-#pragma unroll
-            for (int i = 0; i < 18; i++) ak[i] = rs9 ? sTapK[i] : 0u;
             uint32_t it = 0, tc = 0, sph = 0, bph = 0;
             int s = 0, b = 0;
             bool ok = true;
             long long tr_wc = 0, tr_wa = 0;
             const long long tr_t0 = clock64();
             for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
-                ok = wait.timed(BAR_CEMPTY(b), bph ^ 1, tr_wc);
+                ok = a.trace ? wait.timed(BAR_CEMPTY(b), bph ^ 1, tr_wc) : wait.spin(BAR_CEMPTY(b), bph ^ 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + b * NT;
                 uint32_t acc = 0;
                 uint32_t bLo = bLo0;
                 for (int cb = 0; cb < NCB && ok; cb++, it++) {
-                    ok = wait.timed(BAR_AFULL(s), sph, tr_wa);
+                    ok = a.trace ? wait.timed(BAR_AFULL(s), sph, tr_wa) : wait.spin(BAR_AFULL(s), sph);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t aLo = aLo0 + s * stepStage;
+                    if (leader) {
                     if (rs9) {
 #pragma unroll
-                        for (int i = 0; i < 18; i++)
-                            mma_i8_split(d, aLo + ak[i], aHi, bLo + i * stepB, bHi, IDESC, i == 0 ? acc : 1u);
+                        for (int i = 0; i < 18; i++) {
+                            // tap (r, s), k-step ks: patch offset (r*PW + s) positions, + two chunk planes
+                            const int t = i >> 1, ks = i & 1;
+                            const uint32_t aoff = (uint32_t)((t / 3) * a.PW + (t % 3)) + ks * 2u * (uint32_t)a.NPOS;
+                            mma_i8_split(d, aLo + aoff, aHi, bLo + i * stepB, bHi, IDESC, i == 0 ? acc : 1u);
+                        }
                         bLo += 18 * stepB;
                     } else {
                         for (int t = 0; t < RS; t++) {
@@ -215,12 +226,13 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     }
                     acc = 1;
                     mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
+                    }
                     if (++s == NSTAGE) { s = 0; sph ^= 1; }
                 }
-                if (ok) mma_commit(BAR_CFULL(b));       // accumulator complete
+                if (ok && leader) mma_commit(BAR_CFULL(b));       // accumulator complete
                 if (++b == NACC) { b = 0; bph ^= 1; }
             }
-            if (a.trace && blockIdx.x == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[2] = it; }
+            if (a.trace && blockIdx.x == 0 && leader) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[2] = it; }
         }
         __syncwarp();
     } else if (tid < kPreEpiThreads) {

@@ -107,6 +107,13 @@ struct WsWait {
         atomicExch(err, 1);
         return false;
     }
+    // for the MMA warp, whose every instruction delays the next MMA: one non-blocking test first
+    // (measured cheaper than try_wait when the phase is already complete, the case that matters),
+    // then the suspending wait, which leaves the issue slots to the other warps
+    __device__ __forceinline__ bool spin(uint32_t bar, uint32_t parity) const {
+        if (mbar_test_wait(bar, parity)) return true;
+        return (*this)(bar, parity);
+    }
     // the same for roles that can afford to look less often: sleeps between polls, so that many
     // waiting warps do not keep the shared-memory pipe busy with barrier reads
     __device__ __forceinline__ bool relaxed(uint32_t bar, uint32_t parity) const {
@@ -322,7 +329,16 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
         if (a.trace && blockIdx.x == 0 && et == 0) { a.trace[0] = clock64() - tr_t0; a.trace[1] = tr_wait; a.trace[2] = nstages; a.trace[9] = tr_load; a.trace[10] = tr_exp; a.trace[11] = tr_fence; }
     } else if (warp == MMA_WARP) {
         // =============================== MMA issuer =========================================
-        if (lane == 0) {
+        // Where the MMAs are the critical path (n-tile of 128 or more, or several channel blocks per
+        // tile) the whole warp runs the control flow converged and polls the barriers, and one
+        // elected lane issues: what the issuing thread executes between two MMAs is time the
+        // tensor pipe idles, and a lone lane in a diverged warp pays far more per branch and per
+        // wait.  Narrow layers wait for their epilogue instead and measured faster with a single
+        // lane in the loop (the other 31 parked at the __syncwarp below).
+        const bool converged = NT >= 128 || NCB >= 2;
+        const bool elected = elect_one();
+        if (converged || lane == 0) {
+            const bool leader = converged ? elected : true;
             // Descriptors differ only in their 14-bit address field (low word), so the issue
             // loop adds precomputed (byte offset >> 4) values to two base descriptors: the A
             // offset of (tap, k-step) comes from a table (held in registers for 3x3 filters),
@@ -334,17 +350,17 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
             const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0;
             const uint32_t stepB = (2u * lboB) >> 4, stepStage = stage_bytes >> 4;
             constexpr uint32_t IDESC = idesc_i8(NT);
-            uint32_t ak[18];
             const bool rs9 = RS == 9;
+            uint32_t tapk[18];
 #pragma unroll
-            for (int i = 0; i < 18; i++) ak[i] = rs9 ? sTapK[i] : 0u;
+            for (int i = 0; i < 18; i++) tapk[i] = rs9 ? sTapK[i] : 0u;
             uint32_t it = 0, tc = 0;
             bool ok = true;
             long long tr_wc = 0, tr_wa = 0;
             const long long tr_t0 = clock64();
             for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
                 const int b = tc & 1;
-                ok = wait.timed(BAR_CEMPTY(b), ((tc >> 1) & 1) ^ 1, tr_wc);
+                ok = a.trace ? wait.timed(BAR_CEMPTY(b), ((tc >> 1) & 1) ^ 1, tr_wc) : wait.spin(BAR_CEMPTY(b), ((tc >> 1) & 1) ^ 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + b * NT;
@@ -352,15 +368,15 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                 uint32_t bLo = bLo0;
                 for (int cb = 0; cb < NCB && ok; cb++, it++) {
                     const int s = it % NSTAGE;
-                    ok = wait.timed(BAR_AFULL(s), (it / NSTAGE) & 1, tr_wa);
+                    ok = a.trace ? wait.timed(BAR_AFULL(s), (it / NSTAGE) & 1, tr_wa) : wait.spin(BAR_AFULL(s), (it / NSTAGE) & 1);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t aLo = aLo0 + s * stepStage;
+                    if (leader) {
                     if (rs9) {
 #pragma unroll
-                        for (int i = 0; i < 18; i++) {
-                            mma_i8_split(d, aLo + ak[i], aHi, bLo + i * stepB, bHi, IDESC, i == 0 ? acc : 1u);
-                        }
+                        for (int i = 0; i < 18; i++)
+                            mma_i8_split(d, aLo + tapk[i], aHi, bLo + i * stepB, bHi, IDESC, i == 0 ? acc : 1u);
                         bLo += 18 * stepB;
                     } else {
                         for (int t = 0; t < RS; t++) {
@@ -373,10 +389,11 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                     }
                     acc = 1;
                     mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
+                    }
                 }
-                if (ok) mma_commit(BAR_CFULL(b));       // accumulator complete
+                if (ok && leader) mma_commit(BAR_CFULL(b));       // accumulator complete
             }
-            if (a.trace && blockIdx.x == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; }
+            if (a.trace && blockIdx.x == 0 && leader) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; }
         }
         __syncwarp();
     } else if (tid < 128 * EPI_GROUPS) {
