@@ -243,7 +243,10 @@ def main():
             per_layer[l.name] = per_layer.get(l.name, 0.0) + d / args.steps
             if type(l).__name__ == "Conv128LayerParam":
                 conv_ms += d
-            launches += 2 if getattr(l, "workspace", None) is not None else 1
+            if hasattr(l, "kernel_launches"):
+                launches += l.kernel_launches()
+            else:
+                launches += 2 if getattr(l, "workspace", None) is not None else 1
         n_conv = sum(1 for l in shapes if l["type"] == "conv")
         ops_per_step = conv_ops(shapes) * B
         achieved = ops_per_step * args.steps / (conv_ms * 1e-3) / 1e12
@@ -274,7 +277,7 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s",
                          "frac": achieved / peak, "traffic": traffic,
-                         "kernel": "k_conv_umma_ws, tcgen05 int8 implicit-GEMM conv (%d launches per step)" % n_conv,
+                         "kernel": "tcgen05 int8 implicit-GEMM conv kernels k_conv_umma_ws / _pre / _as (%d layers per step)" % n_conv,
                          "peak_source": "tcgen05.mma kind::i8 128x256x32 issue rate measured in this run by tcbnn_mma_peak(3) (of measured)",
                          "b1_mma_peak": peak_b1, "frac_of_b1_mma_peak": achieved / peak_b1},
             "layer_ms": {k: round(v, 4) for k, v in per_layer.items()},

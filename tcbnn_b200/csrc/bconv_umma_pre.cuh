@@ -170,13 +170,10 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         __syncwarp();
     } else if (warp == MMA_WARP) {
         // =============================== MMA issuer =========================================
-        // Where the MMAs are the critical path (n-tile of 128 or more, or several channel blocks per
-        // tile) the whole warp runs the control flow converged and polls the barriers, and one
-        // elected lane issues: what the issuing thread executes between two MMAs is time the
-        // tensor pipe idles, and a lone lane in a diverged warp pays far more per branch and per
-        // wait.  Narrow layers wait for their epilogue instead and measured faster with a single
-        // lane in the loop (the other 31 parked at the __syncwarp below).
-        const bool converged = NT >= 128 || NCB >= 2;
+        // The whole warp runs the control flow converged and polls the barriers, and one elected
+        // lane issues: what the issuing thread executes between two MMAs is time the tensor pipe
+        // idles, and a lone lane in a diverged warp pays far more per branch and per wait.
+        constexpr bool converged = true;
         const bool elected = elect_one();
         if (converged || lane == 0) {
             const bool leader = converged ? elected : true;

@@ -143,9 +143,10 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
     emit(s, "  float* q = c.acc_out + opix * %d;\n", O);
     for (int o = 0; o < O; o++) emit(s, "  q[%d] = a%d;\n", o, o);
     s += " }\n}\n";
-    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d) tcbnn_spec_f32(SpecArgs c) { body<false>(c, nullptr); }\n",
+    // two blocks per SM: at most 128 registers per thread (the sums take O of them)
+    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d, 2) tcbnn_spec_f32(SpecArgs c) { body<false>(c, nullptr); }\n",
          kSpecThreads);
-    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d) tcbnn_spec_u8(SpecArgs c) {\n", kSpecThreads);
+    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d, 2) tcbnn_spec_u8(SpecArgs c) {\n", kSpecThreads);
     s += " __shared__ float slut[768];\n"
          " for (int i = threadIdx.x; i < 768; i += blockDim.x) slut[i] = __ldg(c.lut + i);\n"
          " __syncthreads();\n"

@@ -673,8 +673,7 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
             a.wi8 = (const uint4*)(p + L.off_wi8_as);
             return launch_conv_umma_as(a, L.as_smem, sms, st);
         }
-        // worth its extra pass when the epilogue also moves residuals (measured); path 2 forces it
-        if (L.pre_bytes && workspace && g_conv_path != 3 && (res_in || res_out || g_conv_path == 2)) {
+        if (L.pre_bytes && workspace && g_conv_path != 3) {
             if (workspace_bytes < L.pre_bytes)
                 return fail("conv_layer: workspace of %zu bytes, the layer needs %zu", workspace_bytes, L.pre_bytes);
             if ((uintptr_t)workspace & 255) return fail("conv_layer: workspace must be 256-byte aligned");

@@ -50,6 +50,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--residual", action="store_true", help="c2: also save the int32 residual")
     ap.add_argument("--no-peak", action="store_true")
+    ap.add_argument("--specialized", action="store_true", help="stem: the kernel compiled for the filter")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     if a.case == "c1":
@@ -71,7 +72,8 @@ def main():
         thr = torch.randn((64,), device=dev, generator=g) * 12.0
         out = torch.zeros((Bn, d.OH * d.OW * 2), dtype=torch.int32, device=dev)
         res = torch.empty((Bn, d.OH, d.OW, 64), dtype=torch.int16, device=dev)
-        ms = _time(lambda: ops.inconv_layer(d, x, f, thr, out=out, res_out_buf=res), a.iters)
+        spec = ops.inconv_specialize(d, f, thr) if a.specialized else None
+        ms = _time(lambda: ops.inconv_layer(d, x, f, thr, out=out, res_out_buf=res, specialized=spec), a.iters)
         work = 2.0 * Bn * d.OH * d.OW * 64 * 49 * 3
         desc = "fp32 first layer %dx3x224x224 -> 56x56x64 (7x7/4), int16 residual; ops = fp32 add/sub" % Bn
     elif a.case == "conv":

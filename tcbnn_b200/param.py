@@ -326,6 +326,11 @@ class Conv128LayerParam:
             raise ValueError("%s: inject_residual needs a residual tensor" % self.name)
         self.input_residual_gpu = t
 
+    def kernel_launches(self):
+        """Kernels one forward() launches: layers that run on a pre-expanded input (a workspace
+        exists for the descriptor) add the expansion pass."""
+        return 2 if ops.conv_workspace(self.desc, self.input_gpu.device) is not None else 1
+
     def forward(self):
         ops.conv_layer(self.desc, self.input_gpu, self.prepared, self.bn_gpu,
                        res_in=self.input_residual_gpu if self.inject_residual else None,
