@@ -196,7 +196,11 @@ int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, lo
 
 /* Issue-rate probe of the MMA forms on all SMs: kind 0 = b1 and.popc m16n8k256 (mma.sync),
  * 1 = b1 xor.popc m16n8k256, 2 = s8 m16n8k32, 3 = tcgen05.mma kind::i8 128x256x32 (warps_per_sm
- * ignored).  Returns tera-ops/s (2*m*n*k per MMA) in *tops.
+ * ignored).  Kinds 4-6 measure what the issuing thread's bookkeeping costs a tcgen05 stream of
+ * 128x128x32 MMAs issued in groups of warps_per_sm: 4 = nothing between the groups, 5 = a lone
+ * lane doing mbarrier.try_wait + tcgen05.commit per group, 6 = the converged warp doing
+ * mbarrier.test_wait and the elect.sync lane issuing and committing.  Returns tera-ops/s
+ * (2*m*n*k per MMA) in *tops.
  * Synchronises the device.  The reference's counterpart is the WMMA latency probe
  * bmm/bmma_op_test/main_test.cu:35-220 and its TOPS formula at :368. */
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops);

@@ -449,6 +449,56 @@ __global__ void __launch_bounds__(128) k_umma_peak(int iters, long long* cycles,
     if (threadIdx.x < 32) umma::tmem_dealloc(tm, 256);
 }
 
+// What the issuing thread's bookkeeping costs: 128x128x32 MMAs in groups of `group`, with per
+// group nothing (MODE 0), a try_wait on a completed barrier plus a commit by a lone lane inside
+// `if (threadIdx.x == 0)` (MODE 1), or a test_wait by the converged warp plus a commit by the lane
+// elect.sync picks (MODE 2) -- the three ways an MMA warp can be written.
+template <int MODE>
+__global__ void __launch_bounds__(128) k_umma_issue(int iters, int group, long long* cycles, int* err) {
+    extern __shared__ __align__(1024) unsigned char peak_smem[];
+    __shared__ uint64_t bar_done, bar_ready, bar_commit;
+    __shared__ uint32_t tm;
+    if (threadIdx.x < 32) umma::tmem_alloc(umma::smem_u32(&tm), 256);
+    if (threadIdx.x == 0) {
+        umma::mbar_init(umma::smem_u32(&bar_done), 1);
+        umma::mbar_init(umma::smem_u32(&bar_ready), 1);      // never arrived on: parity 1 reads as complete
+        umma::mbar_init(umma::smem_u32(&bar_commit), 1);
+    }
+    for (int i = threadIdx.x; i < 48 * 1024 / 4; i += blockDim.x) ((uint32_t*)peak_smem)[i] = 0x01FF01FFu;
+    umma::fence_proxy_async();
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    if (threadIdx.x < 32) {
+        const uint64_t da = umma::smem_desc(umma::smem_u32(peak_smem), 128 * 16, 128);
+        const uint64_t db = umma::smem_desc(umma::smem_u32(peak_smem + 16384), 128 * 16, 128);
+        const bool elected = umma::elect_one();
+        const bool in_loop = MODE == 2 ? true : threadIdx.x == 0;
+        const bool leader = MODE == 2 ? elected : threadIdx.x == 0;
+        if (in_loop) {
+            const long long t0 = clock64();
+            for (int i = 0; i < iters; i += group) {
+                if (MODE == 1) { for (int w = 0; w < 1000; w++) if (umma::mbar_try_wait(umma::smem_u32(&bar_ready), 1)) break; }
+                if (MODE == 2) { for (int w = 0; w < 1000; w++) if (umma::mbar_test_wait(umma::smem_u32(&bar_ready), 1)) break; }
+                if (leader) {
+                    for (int k = 0; k < group; k++)
+                        umma::mma_i8(tm + ((k & 1) ? 128 : 0), da + 2 * (k & 3), db + 2 * (k & 3), umma::idesc_i8(128), 1u);
+                    if (MODE != 0) umma::mma_commit(umma::smem_u32(&bar_commit));
+                }
+            }
+            if (leader) {
+                umma::mma_commit(umma::smem_u32(&bar_done));
+                if (!umma::mbar_wait(umma::smem_u32(&bar_done), 0, err)) { /* status already recorded */ }
+                if (blockIdx.x == 0) cycles[0] = clock64() - t0;
+            }
+        }
+        __syncwarp();
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) umma::tmem_dealloc(tm, 256);
+}
+
 // ---- fixed scratch for callers that cannot allocate ---------------------------------------
 // Split-K partial sums for tcbnn_fc_layer_noalloc live in this array instead of a caller
 // workspace.  It is part of the loaded module: every GPU that loads the library keeps these
@@ -877,21 +927,30 @@ int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, lo
 }
 
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
-    if (!tops || iters <= 0 || warps_per_sm <= 0 || kind < 0 || kind > 3) return fail("mma_peak: bad arguments");
+    if (!tops || iters <= 0 || warps_per_sm <= 0 || kind < 0 || kind > 6) return fail("mma_peak: bad arguments");
     int sms;
     if (sm_count(&sms)) return 1;
     cudaEvent_t e0, e1;
     CUDA_TRY(cudaEventCreate(&e0));
     CUDA_TRY(cudaEventCreate(&e1));
     float best = 1e30f;
-    if (kind == 3) {
+    if (kind >= 3) {
         long long* buf = nullptr;
         CUDA_TRY(cudaMalloc(&buf, 16));
         CUDA_TRY(cudaMemset(buf, 0, 16));
         CUDA_TRY(cudaFuncSetAttribute(k_umma_peak, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
+        CUDA_TRY(cudaFuncSetAttribute(k_umma_issue<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
+        CUDA_TRY(cudaFuncSetAttribute(k_umma_issue<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
+        CUDA_TRY(cudaFuncSetAttribute(k_umma_issue<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
+        const int group = warps_per_sm;            // kinds 4-6: MMAs per wait/commit group
+        if (kind > 3) iters = (iters / group) * group;
+        if (iters <= 0) return fail("mma_peak: fewer iterations than MMAs per group");
         for (int rep = 0; rep < 4; rep++) {
             cudaEventRecord(e0);
-            k_umma_peak<<<sms, 128, 48 * 1024>>>(iters, buf, (int*)(buf + 1));
+            if (kind == 3) k_umma_peak<<<sms, 128, 48 * 1024>>>(iters, buf, (int*)(buf + 1));
+            if (kind == 4) k_umma_issue<0><<<sms, 128, 48 * 1024>>>(iters, group, buf, (int*)(buf + 1));
+            if (kind == 5) k_umma_issue<1><<<sms, 128, 48 * 1024>>>(iters, group, buf, (int*)(buf + 1));
+            if (kind == 6) k_umma_issue<2><<<sms, 128, 48 * 1024>>>(iters, group, buf, (int*)(buf + 1));
             cudaEventRecord(e1);
             CUDA_TRY(cudaEventSynchronize(e1));
             float ms = 0;
@@ -904,7 +963,7 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);
         if (status) return fail("mma_peak: a bounded wait in the tcgen05 probe gave up");
-        *tops = (double)sms * iters * 2.0 * 128 * 256 * 32 / (best * 1e-3) / 1e12;
+        *tops = (double)sms * iters * 2.0 * 128 * (kind == 3 ? 256 : 128) * 32 / (best * 1e-3) / 1e12;
         return 0;
     }
     int* sink = nullptr;
