@@ -112,6 +112,27 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
                        long long out_image_stride, void* res_out, int res_out_bytes,
                        int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* tcbnn_conv_layer_w plus the two halves of a producer -> consumer hand-over of the pre-expanded
+ * input, which saves the consumer's expansion pass:
+ *  - next / next_planes / next_planes_bytes (all NULL / 0 for none): `next` is the descriptor of
+ *    the layer that consumes this layer's output (same batch, its H x W x C = this layer's
+ *    OH x OW x O, and tcbnn_conv_workspace_bytes(next) != 0); besides the packed bits the layer
+ *    then also writes its output as +-1 bytes into next_planes in that layer's operand layout.
+ *    The buffer (tcbnn_conv_workspace_bytes(next) bytes, 256-byte aligned) must have been zeroed
+ *    once and be used for this pair of layers only: the padding positions of the layout are never
+ *    written.  out_image_stride must be dense.  Kernels that cannot write the planes themselves
+ *    are followed by the expansion pass, so the result is the same for every layer.
+ *  - workspace_ready != 0: `workspace` already holds this layer's input planes (its producer was
+ *    called with next = this layer); the expansion pass is skipped.
+ * No reference counterpart. */
+int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
+                       const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
+                       int residual_channels, int residual_pool, uint32_t* out,
+                       long long out_image_stride, void* res_out, int res_out_bytes,
+                       int32_t* acc_out, void* workspace, size_t workspace_bytes, int workspace_ready,
+                       const tcbnn_conv_desc* next, void* next_planes, size_t next_planes_bytes,
+                       void* stream);
+
 /* Which kernel tcbnn_conv_layer uses: 0 = automatic (tcgen05 int8 implicit GEMM where the layer
  * is eligible, else the warp-level b1 MMA), 1 = always the b1 MMA, 2 = tcgen05 or an error,
  * 3 = as 2 but only the filter-stationary tcgen05 kernel with its in-kernel bit expansion (wide
@@ -189,6 +210,12 @@ int tcbnn_inconv_specialized_layer(void* handle, const tcbnn_conv_desc* d, const
                                    const uint8_t* x8, const float* lut, uint32_t* out,
                                    long long out_image_stride, void* res_out, int res_out_bytes,
                                    float* acc_out, void* stream);
+/* The same with the hand-over to the next layer of tcbnn_conv_layer_x. */
+int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, const float* x,
+                                     const uint8_t* x8, const float* lut, uint32_t* out,
+                                     long long out_image_stride, void* res_out, int res_out_bytes,
+                                     float* acc_out, const tcbnn_conv_desc* next, void* next_planes,
+                                     size_t next_planes_bytes, void* stream);
 int tcbnn_inconv_release(void* handle);
 /* Generates the kernel above for pseudo-random filter bits and compiles it, without loading it:
  * needs NVRTC but no GPU.  *source_bytes (optional) receives the size of the generated source. */

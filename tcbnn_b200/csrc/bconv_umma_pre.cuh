@@ -398,6 +398,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 if (COLS == 32) *reinterpret_cast<uint32_t*>(wp) = word;
                 else if (COLS == 16) *reinterpret_cast<unsigned short*>(wp + ((o0 & 16) ? 0 : 2)) = (unsigned short)word;
                 else wp[3 - ((o0 & 31) >> 3)] = (unsigned char)word;
+                if (a.nxt) store_next_planes(a, q.n, q.y, q.x, o0, word, COLS);
             }
         }
         if (overflow) atomicExch(a.err_flag, 2);

@@ -44,6 +44,9 @@ struct ConvWsArgs {
     const uint4* pre;         // pre-expanded input planes (bconv_umma_pre.cuh), else null
     long long pre_positions, pre_front;
     int pre_stages;           // patch ring depth of that kernel
+    // optional: also write the output as +-1 bytes into the next layer's input planes
+    // (bconv_umma_pre.cuh layout over THAT layer's raster; dead slots stay as the caller zeroed them)
+    uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
     const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
     uint32_t* out; long long out_image_stride;
     void* res_out; int res_out_bytes; int32_t* acc_out;
@@ -93,6 +96,26 @@ __host__ inline void fastdiv_setup(int d, uint32_t* mul, uint32_t* sh) {
     while ((1u << s) < (uint32_t)d) s++;
     *sh = 31 + s;
     *mul = (uint32_t)((((unsigned long long)1 << (31 + s)) + d - 1) / d);
+}
+
+// Writes the +-1 bytes of `nbits` output channels (8, 16 or 32; first channel o0, a multiple of
+// nbits; channel c at bit nbits-1-c of `word`) of output pixel (n, y, x) into the next layer's planes.
+__device__ __forceinline__ void store_next_planes(const ConvWsArgs& a, int n, int y, int x, int o0,
+                                                  uint32_t word, int nbits) {
+    uint4* base = a.nxt + (size_t)(o0 >> 4) * a.nxt_positions + a.nxt_front +
+                  ((long long)n * a.nxt_VH + y) * a.nxt_PW + x;
+    if (nbits == 32) {
+        base[0] = expand16(word >> 16);
+        base[(size_t)a.nxt_positions] = expand16(word & 0xFFFFu);
+    } else if (nbits == 16) {
+        base[0] = expand16(word & 0xFFFFu);
+    } else {                                    // 8 channels: half of a 16-channel chunk
+        const bool high = (o0 & 8) == 0;        // channels 0-7 of the chunk sit in bits 15..8
+        const uint4 e = expand16(high ? (word & 0xFFu) << 8 : (word & 0xFFu));
+        uint2* half = reinterpret_cast<uint2*>(base);
+        if (high) half[1] = make_uint2(e.z, e.w);
+        else half[0] = make_uint2(e.x, e.y);
+    }
 }
 
 struct WsWait {
@@ -572,6 +595,11 @@ __device__ void conv_umma_ws_cta(const ConvWsArgs& a, unsigned char* smem) {
                                 ((size_t)y * a.OWg + x) * Ow + (obase >> 5);
 #pragma unroll
                 for (int k = 0; k < NB_PER; k++) dst[grp + k * EPI_GROUPS] = words[k];
+                if (a.nxt) {
+#pragma unroll
+                    for (int k = 0; k < NB_PER; k++)
+                        store_next_planes(a, n, y, x, obase + (grp + k * EPI_GROUPS) * 32, words[k], 32);
+                }
             }
             tr_body += clock64() - e0;
         }

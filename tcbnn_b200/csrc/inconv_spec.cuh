@@ -43,6 +43,8 @@ struct SpecArgs {
     int res_out_bytes, res_out_ld;
     float* acc_out;
     unsigned total;            // pre-pool pixels
+    // optional: the output also as +-1 bytes in the next layer's input planes (bconv_umma_pre.cuh)
+    uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
 };
 
 struct SpecHandle {
@@ -69,7 +71,15 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
     s += "typedef unsigned int uint32_t;\n"
          "struct SpecArgs { const float* x; const unsigned char* x8; const float* lut; int B, H, W, OH, OW;\n"
          "  uint32_t* out; long long out_image_stride; void* res_out; int res_out_bytes, res_out_ld;\n"
-         "  float* acc_out; unsigned total; };\n";
+         "  float* acc_out; unsigned total;\n"
+         "  uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH; };\n"
+         // 16 packed bits -> 16 bytes of +1 / -1, the byte order the conv kernels' filters use
+         "__device__ __forceinline__ uint4 expand16(uint32_t h) {\n"
+         "  uint32_t v[4];\n"
+         "#pragma unroll\n"
+         "  for (int g = 0; g < 4; g++) { const uint32_t nb = (h >> (4 * g)) & 0xFu;\n"
+         "    const uint32_t y = (nb * 0x00204081u) & 0x01010101u; v[g] = ~(y * 0xFEu); }\n"
+         "  return make_uint4(v[0], v[1], v[2], v[3]); }\n";
     emit(s, "template <bool U8> __device__ __forceinline__ void body(const SpecArgs& c, const float* slut) {\n");
     s += " const unsigned pix = blockIdx.x * blockDim.x + threadIdx.x;\n"
          " const bool live = pix < c.total;\n"
@@ -118,7 +128,12 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
     emit(s, " { uint32_t* dst = c.out + (size_t)n * c.out_image_stride + ((size_t)(y / %d) * c.OW + (x / %d)) * %d;\n",
          h.pool, h.pool, Ow);
     if (h.pool == 2) s += "   if ((pix & 3) == 0)";
-    emit(s, "   { dst[0] = w0;%s } }\n", Ow == 2 ? " dst[1] = w1;" : "");
+    emit(s, "   { dst[0] = w0;%s\n", Ow == 2 ? " dst[1] = w1;" : "");
+    emit(s, "     if (c.nxt) { uint4* pl = c.nxt + c.nxt_front + ((long long)n * c.nxt_VH + (y / %d)) * c.nxt_PW + (x / %d);\n",
+         h.pool, h.pool);
+    for (int k = 0; k < (O + 15) / 16; k++)
+        emit(s, "       pl[(size_t)%d * c.nxt_positions] = expand16((w%d >> %d) & 0xFFFFu);\n", k, k / 2, (k & 1) ? 0 : 16);
+    s += "     }\n   } }\n";
     // residual = (int)acc (kernel.cuh:666-668), optional fp32 accumulators
     s += " const size_t opix = ((size_t)n * P + y) * Q + x;\n"
          " if (c.res_out) {\n"

@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(256) k_expand_raster(umma::ConvWsArgs a, uint4
 }
 
 template <int NT>
-int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
+int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st, bool expand) {
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -339,10 +339,12 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
         if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         configured[dev] = true;
     }
-    const long long units = a.pre_positions * (a.C >> 6);
-    k_expand_raster<<<elementwise_grid(units, sms), 256, 0, st>>>(a, const_cast<uint4*>(a.pre), a.pre_positions,
-                                                               a.pre_front);
-    if (launch_check("conv_layer (input expansion)")) return 1;
+    if (expand) {
+        const long long units = a.pre_positions * (a.C >> 6);
+        k_expand_raster<<<elementwise_grid(units, sms), 256, 0, st>>>(a, const_cast<uint4*>(a.pre), a.pre_positions,
+                                                                   a.pre_front);
+        if (launch_check("conv_layer (input expansion)")) return 1;
+    }
     a.ntiles_n = a.O / NT;
     if (a.ntiles_n > sms) return fail("conv_layer: more n-tiles than SMs");
     const long long mtiles = (a.NV + 127) / 128;
@@ -680,6 +682,51 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
                        int residual_channels, int residual_pool, uint32_t* out,
                        long long out_image_stride, void* res_out, int res_out_bytes,
                        int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream) {
+    return tcbnn_conv_layer_x(d, in, prepared, thr, res_in, res_in_bytes, res_in_ch, residual_channels,
+                              residual_pool, out, out_image_stride, res_out, res_out_bytes, acc_out,
+                              workspace, workspace_bytes, 0, nullptr, nullptr, 0, stream);
+}
+
+// the next layer's input planes, as its descriptor lays them out
+struct NextPlanes { uint4* planes; long long positions, front; int PW, VH; };
+
+// Checks that `next` can take `d`'s output as pre-expanded input and describes its planes.
+static int next_planes_of(const tcbnn_conv_desc* d, int out_h, int out_w, const tcbnn_conv_desc* next,
+                          void* planes, size_t planes_bytes, NextPlanes* nx) {
+    if (conv_check(next, true)) return 1;
+    const PreparedLayout N = prepared_layout(next);
+    if (!N.pre_bytes) return fail("next layer takes no pre-expanded input (tcbnn_conv_workspace_bytes is 0)");
+    if (next->B != d->B || next->H != out_h || next->W != out_w || next->C != d->O)
+        return fail("next layer's input %dx%dx%dx%d is not this layer's output %dx%dx%dx%d", next->B, next->H,
+                    next->W, next->C, d->B, out_h, out_w, d->O);
+    if (!planes || planes_bytes < N.pre_bytes) return fail("next layer's planes: %zu bytes given, %zu needed", planes_bytes, N.pre_bytes);
+    if ((uintptr_t)planes & 255) return fail("next layer's planes must be 256-byte aligned");
+    nx->planes = (uint4*)planes; nx->positions = N.pre_positions; nx->front = N.pre_front;
+    nx->PW = N.umma_pw; nx->VH = N.umma_vh;
+    return 0;
+}
+
+// Expansion pass of `next` run on bits that are already in memory (the producing kernel could not
+// write the planes itself).
+static int expand_for_next(const tcbnn_conv_desc* next, const uint32_t* bits, const NextPlanes& nx, cudaStream_t st) {
+    umma::ConvWsArgs a = {};
+    a.in = bits; a.B = next->B; a.H = next->H; a.W = next->W; a.C = next->C;
+    a.PW = nx.PW; a.VH = nx.VH; a.NV = (long long)next->B * nx.VH * nx.PW;
+    umma::fastdiv_setup(a.PW, &a.pw_mul, &a.pw_sh);
+    umma::fastdiv_setup(a.VH, &a.vh_mul, &a.vh_sh);
+    int sms;
+    if (sm_count(&sms)) return 1;
+    k_expand_raster<<<elementwise_grid(nx.positions * (next->C >> 6), sms), 256, 0, st>>>(a, nx.planes, nx.positions, nx.front);
+    return launch_check("expansion for the next layer");
+}
+
+static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
+                           const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
+                           int residual_channels, int residual_pool, uint32_t* out,
+                           long long out_image_stride, void* res_out, int res_out_bytes,
+                           int32_t* acc_out, void* workspace, size_t workspace_bytes, int workspace_ready,
+                           const NextPlanes* nx, bool* fed, void* stream) {
+    *fed = false;
     if (conv_check(d, true)) return 1;
     const int Ow = (d->O + 31) / 32;
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("conv_layer: out_image_stride too small");
@@ -718,6 +765,12 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
         cudaStream_t st = (cudaStream_t)stream;
         a.pre = nullptr; a.pre_positions = 0; a.pre_front = 0;
         a.pre_stages = 0;
+        a.nxt = nullptr; a.nxt_positions = 0; a.nxt_front = 0; a.nxt_PW = 0; a.nxt_VH = 0;
+        if (nx && !use_as) {
+            a.nxt = nx->planes; a.nxt_positions = nx->positions; a.nxt_front = nx->front;
+            a.nxt_PW = nx->PW; a.nxt_VH = nx->VH;
+            *fed = true;
+        }
         if (use_as) {
             a.NPOS = L.as_npos; a.as_slots = L.as_slots;
             a.wi8 = (const uint4*)(p + L.off_wi8_as);
@@ -729,9 +782,9 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
             if ((uintptr_t)workspace & 255) return fail("conv_layer: workspace must be 256-byte aligned");
             a.pre = (const uint4*)workspace; a.pre_positions = L.pre_positions; a.pre_front = L.pre_front;
             a.pre_stages = L.pre_stages;
-            if (L.umma_nt == 32) return launch_conv_umma_pre<32>(a, L.pre_smem, sms, st);
-            if (L.umma_nt == 64) return launch_conv_umma_pre<64>(a, L.pre_smem, sms, st);
-            if (L.umma_nt == 128) return launch_conv_umma_pre<128>(a, L.pre_smem, sms, st);
+            if (L.umma_nt == 32) return launch_conv_umma_pre<32>(a, L.pre_smem, sms, st, !workspace_ready);
+            if (L.umma_nt == 64) return launch_conv_umma_pre<64>(a, L.pre_smem, sms, st, !workspace_ready);
+            if (L.umma_nt == 128) return launch_conv_umma_pre<128>(a, L.pre_smem, sms, st, !workspace_ready);
         }
 #define TCBNN_WS_CASE(NN, SS) \
         if (L.umma_nt == NN && d->stride_h == SS) return launch_conv_umma_ws<NN, SS>(a, L.umma_smem, sms, st);
@@ -761,6 +814,30 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
     const long long tasks = ((rows + 31) / 32) * Ow;
     k_conv<<<warp_grid(tasks, sms), kThreads, 0, (cudaStream_t)stream>>>(c);
     return launch_check("conv_layer");
+}
+
+int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
+                       const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
+                       int residual_channels, int residual_pool, uint32_t* out,
+                       long long out_image_stride, void* res_out, int res_out_bytes,
+                       int32_t* acc_out, void* workspace, size_t workspace_bytes, int workspace_ready,
+                       const tcbnn_conv_desc* next, void* next_planes, size_t next_planes_bytes,
+                       void* stream) {
+    NextPlanes nx;
+    if (next) {
+        if (conv_check(d, true)) return 1;
+        if (next_planes_of(d, d->OH, d->OW, next, next_planes, next_planes_bytes, &nx)) return 1;
+        if (out_image_stride != (long long)d->OH * d->OW * ((d->O + 31) / 32))
+            return fail("conv_layer: feeding the next layer needs a dense output (out_image_stride == OH*OW*ceil(O/32))");
+    }
+    if (workspace_ready && !workspace) return fail("conv_layer: workspace_ready without a workspace");
+    bool fed = false;
+    if (conv_layer_impl(d, in, prepared, thr, res_in, res_in_bytes, res_in_ch, residual_channels, residual_pool,
+                        out, out_image_stride, res_out, res_out_bytes, acc_out, workspace, workspace_bytes,
+                        workspace_ready, next ? &nx : nullptr, &fed, stream))
+        return 1;
+    if (next && !fed) return expand_for_next(next, out, nx, (cudaStream_t)stream);
+    return 0;
 }
 
 int tcbnn_set_conv_path(int path) {
@@ -880,6 +957,15 @@ int tcbnn_inconv_specialized_layer(void* handle, const tcbnn_conv_desc* d, const
                                    const uint8_t* x8, const float* lut, uint32_t* out,
                                    long long out_image_stride, void* res_out, int res_out_bytes,
                                    float* acc_out, void* stream) {
+    return tcbnn_inconv_specialized_layer_x(handle, d, x, x8, lut, out, out_image_stride, res_out, res_out_bytes,
+                                            acc_out, nullptr, nullptr, 0, stream);
+}
+
+int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, const float* x,
+                                     const uint8_t* x8, const float* lut, uint32_t* out,
+                                     long long out_image_stride, void* res_out, int res_out_bytes,
+                                     float* acc_out, const tcbnn_conv_desc* next, void* next_planes,
+                                     size_t next_planes_bytes, void* stream) {
     if (!handle) return fail("inconv_specialized_layer: null handle");
     if (conv_check(d, false)) return 1;
     const spec::SpecHandle* h = (const spec::SpecHandle*)handle;
@@ -896,6 +982,12 @@ int tcbnn_inconv_specialized_layer(void* handle, const tcbnn_conv_desc* d, const
     c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out;
     c.res_out_bytes = res_out_bytes; c.res_out_ld = d->O; c.acc_out = acc_out;
     c.total = (unsigned)((long long)d->B * d->OH * d->OW * d->pool * d->pool);
+    c.nxt = nullptr; c.nxt_positions = 0; c.nxt_front = 0; c.nxt_PW = 0; c.nxt_VH = 0;
+    if (next) {
+        NextPlanes nx;
+        if (next_planes_of(d, d->OH, d->OW, next, next_planes, next_planes_bytes, &nx)) return 1;
+        c.nxt = nx.planes; c.nxt_positions = nx.positions; c.nxt_front = nx.front; c.nxt_PW = nx.PW; c.nxt_VH = nx.VH;
+    }
     void* params[] = {&c};
     const unsigned grid = (c.total + spec::kSpecThreads - 1) / spec::kSpecThreads;
     CUDA_TRY(cudaLaunchKernel((const void*)(x ? h->k_f32 : h->k_u8), dim3(grid), dim3(spec::kSpecThreads), params, 0,

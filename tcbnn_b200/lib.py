@@ -47,6 +47,10 @@ SIGNATURES = {
     "tcbnn_fc_layer_noalloc": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
     "tcbnn_conv_workspace_bytes": (_SZ, [C.POINTER(ConvDesc)]),
     "tcbnn_conv_layer_w": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _I, _P, _P, _SZ, _P]),
+    "tcbnn_conv_layer_x": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _I, _P, _P, _SZ, _I,
+                                C.POINTER(ConvDesc), _P, _SZ, _P]),
+    "tcbnn_inconv_specialized_layer_x": (_I, [_P, C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _I, _P,
+                                              C.POINTER(ConvDesc), _P, _SZ, _P]),
     "tcbnn_inconv_specialize": (_I, [C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(C.c_void_p)]),
     "tcbnn_inconv_specialized_layer": (_I, [_P, C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_inconv_release": (_I, [_P]),

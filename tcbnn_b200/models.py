@@ -16,7 +16,7 @@ Topologies follow the reference drivers, not the textbook networks:
 """
 import numpy as np
 
-from . import param
+from . import ops, param
 
 
 def resnet18_spec(batch, image=224, classes=1000):
@@ -193,10 +193,11 @@ class Network:
     """Chain of layer objects built from a spec, the way the reference drivers build theirs
     (new XLayerParam(...) ; initialize(config, prev->get_output_gpu(), residual))."""
 
-    def __init__(self, spec, weights, input_host, input_abs_bound=None, input_lut=None):
+    def __init__(self, spec, weights, input_host, input_abs_bound=None, input_lut=None, handover=True):
         """input_abs_bound: max |pixel value| the caller guarantees; with it the residual chain
         is provably small and is stored as int16 instead of int32.
-        input_lut: images arrive as uint8 with this [3][256] table of their fp32 values."""
+        input_lut: images arrive as uint8 with this [3][256] table of their fp32 values.
+        handover: producers write the pre-expanded input of the conv layers that follow them."""
         self.spec = spec
         B = spec["batch"]
         cfg = weights if hasattr(weights, "read") else param.ArrayConfig(weights)
@@ -230,6 +231,30 @@ class Network:
                 raise ValueError(t)
             self.layers.append(obj)
             prev = obj
+        if handover:
+            self._wire_handover()
+
+    def _wire_handover(self):
+        """Consecutive conv layers: where the consumer runs on a pre-expanded input, its producer
+        writes that input itself (tcbnn_conv_layer_x) and the consumer skips its expansion pass."""
+        for prod, cons in zip(self.layers, self.layers[1:]):
+            if type(cons).__name__ != "Conv128LayerParam":
+                continue
+            kind = type(prod).__name__
+            if kind == "Conv128LayerParam":
+                dense = prod.out_image_stride == prod.desc.OH * prod.desc.OW * ((prod.desc.O + 31) // 32)
+                if prod.desc.pool != 1 or not dense:
+                    continue
+            elif kind == "InConv128LayerParam":
+                if getattr(prod, "specialized", None) is None:
+                    continue
+            else:
+                continue
+            planes = ops.new_planes(cons.desc, cons.input_gpu.device)
+            if planes is None:
+                continue
+            prod.next_layer = (cons.desc, planes)
+            cons.input_planes = planes
 
     def set_input(self, x):
         self.layers[0].set_input(x)

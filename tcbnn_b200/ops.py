@@ -156,11 +156,15 @@ def conv_workspace(d, device):
 
 def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_pool=False,
                out=None, out_image_stride=None, save_residual=False, want_acc=False,
-               res_out_buf=None, residual_dtype=torch.int32, workspace=None):
+               res_out_buf=None, residual_dtype=torch.int32, workspace=None, workspace_ready=False,
+               next_layer=None):
     """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out).
     Residual tensors may be torch.int32 or torch.int16.
     workspace: uint8 scratch tensor for tcbnn_conv_layer_w; None = the shared one of
-    conv_workspace(); False = none (tcbnn_conv_layer)."""
+    conv_workspace(); False = none (tcbnn_conv_layer).
+    next_layer: (descriptor, planes tensor) of the layer consuming this output: the layer also
+    writes its output into that layer's input planes (new_planes()); the consumer is then called
+    with workspace=planes, workspace_ready=True (tcbnn_conv_layer_x)."""
     _need_cuda(x, prepared, thr, res_in)
     if workspace is None:
         workspace = conv_workspace(d, x.device)
@@ -181,11 +185,24 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
             res_in_ch, residual_channels, int(bool(residual_pool)), _ptr(out),
             C.c_longlong(stride), _ptr(res_out),
             res_out.element_size() if res_out is not None else 4, _ptr(acc_out))
-    if workspace is not None:
+    if next_layer is not None or workspace_ready:
+        nd, npl = next_layer if next_layer is not None else (None, None)
+        _l.call("tcbnn_conv_layer_x", *args, _ptr(workspace),
+                C.c_size_t(workspace.numel() if workspace is not None else 0), int(bool(workspace_ready)),
+                C.byref(nd) if nd is not None else None, _ptr(npl),
+                C.c_size_t(npl.numel() if npl is not None else 0), _stream())
+    elif workspace is not None:
         _l.call("tcbnn_conv_layer_w", *args, _ptr(workspace), C.c_size_t(workspace.numel()), _stream())
     else:
         _l.call("tcbnn_conv_layer", *args, _stream())
     return out, res_out, acc_out
+
+
+def new_planes(d, device):
+    """Zeroed input planes for the layer `d` when its producer writes them (next_layer=...), or
+    None when the layer takes no pre-expanded input."""
+    n = _l.load().tcbnn_conv_workspace_bytes(C.byref(d))
+    return torch.zeros((n,), dtype=torch.uint8, device=device) if n else None
 
 
 class InconvSpecialized:
@@ -216,7 +233,7 @@ def inconv_specialize(d, filter_bits, thr):
 
 def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_residual=False,
                  want_acc=False, res_out_buf=None, residual_dtype=torch.int32, lut=None,
-                 specialized=None):
+                 specialized=None, next_layer=None):
     """x: fp32 [B][3][H][W], or uint8 [B][3][H][W] together with lut (fp32 [3][256], the value
     of every byte per channel).  specialized: an InconvSpecialized built from the same filter
     and thresholds (filter_bits and thr are then not read).  Returns (out_bits, res_out, acc_out)."""
@@ -232,12 +249,17 @@ def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_r
     if res_out is None and save_residual:
         res_out = torch.empty((d.B, P, Q, d.O), dtype=residual_dtype, device=x.device)
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.float32, device=x.device) if want_acc else None
+    if next_layer is not None and specialized is None:
+        raise _l.TcbnnError("inconv_layer: next_layer needs the specialised kernel")
     if specialized is not None:
         u8 = lut is not None
-        _l.call("tcbnn_inconv_specialized_layer", specialized.handle, C.byref(d),
+        nd, npl = next_layer if next_layer is not None else (None, None)
+        _l.call("tcbnn_inconv_specialized_layer_x", specialized.handle, C.byref(d),
                 None if u8 else _ptr(x), _ptr(x) if u8 else None, _ptr(lut), _ptr(out),
                 C.c_longlong(stride), _ptr(res_out),
-                res_out.element_size() if res_out is not None else 4, _ptr(acc_out), _stream())
+                res_out.element_size() if res_out is not None else 4, _ptr(acc_out),
+                C.byref(nd) if nd is not None else None, _ptr(npl),
+                C.c_size_t(npl.numel() if npl is not None else 0), _stream())
     elif lut is not None:
         _l.call("tcbnn_inconv_layer_u8", C.byref(d), _ptr(x), _ptr(lut), _ptr(filter_bits), _ptr(thr),
                 _ptr(out), C.c_longlong(stride), _ptr(res_out),

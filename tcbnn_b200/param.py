@@ -237,6 +237,8 @@ class InConv128LayerParam:
                                                    dtype=_residual_dtype(self.residual_bound), device=dev)
         return self
 
+    next_layer = None      # (consumer's descriptor, its planes): see Conv128LayerParam
+
     def set_input(self, input):
         src = input if torch.is_tensor(input) else torch.from_numpy(np.ascontiguousarray(input))
         if src.dtype != self.input_gpu.dtype:
@@ -246,7 +248,8 @@ class InConv128LayerParam:
     def forward(self):
         ops.inconv_layer(self.desc, self.input_gpu, self.filter_gpu, self.bn_gpu, out=self.output_gpu,
                          res_out_buf=self.output_residual_gpu, lut=self.input_lut_gpu,
-                         specialized=self.specialized)
+                         specialized=self.specialized,
+                         next_layer=self.next_layer if self.specialized is not None else None)
 
     def get_output_gpu(self):
         return self.output_gpu
@@ -326,17 +329,26 @@ class Conv128LayerParam:
             raise ValueError("%s: inject_residual needs a residual tensor" % self.name)
         self.input_residual_gpu = t
 
+    # Hand-over of the pre-expanded input between consecutive layers (tcbnn_conv_layer_x), wired
+    # by models.Network: next_layer = (consumer's descriptor, its planes); input_planes = this
+    # layer's planes when its producer fills them.
+    next_layer = None
+    input_planes = None
+
     def kernel_launches(self):
-        """Kernels one forward() launches: layers that run on a pre-expanded input (a workspace
-        exists for the descriptor) add the expansion pass."""
-        return 2 if ops.conv_workspace(self.desc, self.input_gpu.device) is not None else 1
+        """Kernels one forward() launches: a layer that runs on a pre-expanded input launches the
+        expansion pass too unless its producer filled the planes."""
+        own_expand = self.input_planes is None and ops.conv_workspace(self.desc, self.input_gpu.device) is not None
+        return 2 if own_expand else 1
 
     def forward(self):
         ops.conv_layer(self.desc, self.input_gpu, self.prepared, self.bn_gpu,
                        res_in=self.input_residual_gpu if self.inject_residual else None,
                        residual_channels=self.residual_channels, residual_pool=self.residual_pool,
                        out=self.output_gpu, out_image_stride=self.out_image_stride,
-                       res_out_buf=self.output_residual_gpu)
+                       res_out_buf=self.output_residual_gpu,
+                       workspace=self.input_planes, workspace_ready=self.input_planes is not None,
+                       next_layer=self.next_layer)
 
     def get_output_gpu(self):
         return self.output_gpu

@@ -330,6 +330,70 @@ def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
         ops.set_conv_path(0)
 
 
+HANDOVER_CASES = [
+    # producer (C, O, stride), consumer O: the consumer has C = producer's O and at most 128 of them
+    (64, 64, 1, 64),        # loader-fed kernel writes the planes (16 columns per thread)
+    (128, 128, 1, 128),     # the same, 32 columns per thread
+    (64, 128, 2, 128),      # stride-2 filter-stationary kernel writes them
+    (256, 128, 1, 64),      # activation-stationary kernel cannot: followed by the expansion pass
+]
+
+
+@pytest.mark.parametrize("case", HANDOVER_CASES)
+def test_conv_layer_hands_its_output_to_the_next_layer(cuda, case):
+    """tcbnn_conv_layer_x: the producer writes the consumer's pre-expanded input, the consumer
+    skips its expansion pass; both layers against the oracle."""
+    C1, O1, st, O2 = case
+    B, H = 3, 12
+    g = util.rng(sum(case) + 11)
+    x = util.rand_words(g, (B, H, H, C1 // 32))
+    f1 = util.rand_words(g, (O1, 9, C1 // 32))
+    f2 = util.rand_words(g, (O2, 9, O1 // 32))
+    t1 = (g.standard_normal(O1) * np.sqrt(C1 * 9) * 0.5).astype(np.float32)
+    t2 = (g.standard_normal(O2) * np.sqrt(O1 * 9) * 0.5).astype(np.float32)
+    e1, _, _ = orc.conv_layer(x, f1, t1, C1, 3, 3, st, st, True, 1)
+    H2 = H // st
+    e2, _, _ = orc.conv_layer(e1.reshape(B, H2, H2, O1 // 32), f2, t2, O1, 3, 3, 1, 1, True, 1)
+    d1 = ops.conv_desc(B, H, H, C1, O1, 3, 3, st, st)
+    d2 = ops.conv_desc(B, H2, H2, O1, O2, 3, 3)
+    p1, p2 = ops.conv_prepare(d1, dev(f1, cuda)), ops.conv_prepare(d2, dev(f2, cuda))
+    planes = ops.new_planes(d2, cuda)
+    assert planes is not None
+    for _ in range(2):                      # a second pass over the same planes gives the same result
+        o1, _, _ = ops.conv_layer(d1, dev(x, cuda), p1, dev(t1, cuda), next_layer=(d2, planes))
+        o2, _, _ = ops.conv_layer(d2, o1.view(B, H2, H2, O1 // 32), p2, dev(t2, cuda),
+                                  workspace=planes, workspace_ready=True)
+        assert ops.conv_status(d1, p1) == 0 and ops.conv_status(d2, p2) == 0
+        assert np.array_equal(host_u32(o1), e1)
+        assert np.array_equal(host_u32(o2), e2)
+
+
+def test_specialized_first_layer_hands_its_output_to_the_next_layer(cuda):
+    g = util.rng(4711)
+    B, H, O1, O2 = 3, 32, 64, 64
+    x = g.standard_normal((B, 3, H, H)).astype(np.float32)
+    F = g.standard_normal((49, 3, O1)).astype(np.float32)
+    t1 = (g.standard_normal(O1) * 3).astype(np.float32)
+    f2 = util.rand_words(g, (O2, 9, O1 // 32))
+    t2 = (g.standard_normal(O2) * np.sqrt(O1 * 9) * 0.5).astype(np.float32)
+    e1, _, _ = orc.inconv_layer(x, F, t1, 7, 7, 4, 4, True, 1)
+    e2, _, _ = orc.conv_layer(e1.reshape(B, 8, 8, O1 // 32), f2, t2, O1, 3, 3, 1, 1, True, 1)
+    d1 = ops.conv_desc(B, H, H, 3, O1, 7, 7, 4, 4)
+    d2 = ops.conv_desc(B, 8, 8, O1, O2, 3, 3)
+    fb = ops.pack_inconv_filter(dev(F, cuda))
+    spec = ops.inconv_specialize(d1, fb, dev(t1, cuda))
+    p2 = ops.conv_prepare(d2, dev(f2, cuda))
+    planes = ops.new_planes(d2, cuda)
+    o1, _, _ = ops.inconv_layer(d1, dev(x, cuda), fb, dev(t1, cuda), specialized=spec, next_layer=(d2, planes))
+    o2, _, _ = ops.conv_layer(d2, o1.view(B, 8, 8, O1 // 32), p2, dev(t2, cuda), workspace=planes, workspace_ready=True)
+    assert np.array_equal(host_u32(o1), e1)
+    assert np.array_equal(host_u32(o2), e2)
+    from tcbnn_b200.lib import TcbnnError
+    with pytest.raises(TcbnnError):         # a consumer of another shape is refused
+        ops.inconv_layer(d1, dev(x, cuda), fb, dev(t1, cuda), specialized=spec,
+                         next_layer=(ops.conv_desc(B, 16, 16, O1, O2, 3, 3), planes))
+
+
 def test_tcgen05_path_refuses_ineligible_layer(cuda):
     from tcbnn_b200.lib import TcbnnError
     d = ops.conv_desc(1, 8, 8, 64, 64, 3, 3, pool=2)    # pooled layers stay on the b1 MMA kernel
