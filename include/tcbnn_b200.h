@@ -102,10 +102,14 @@ int tcbnn_conv_layer(const tcbnn_conv_desc* d, const uint32_t* in, const void* p
  * run fastest when their input is first written out as +-1 bytes in the tensor cores' operand
  * layout by a streaming pass and the convolution kernel fetches it with bulk copies;
  * tcbnn_conv_workspace_bytes says how much device memory (256-byte aligned) that takes for a
- * descriptor, 0 when the layer has no use for it.  The buffer is only used during the call
+ * descriptor, 0 when the layer has no use for it.  (Wide layers use the buffer for something
+ * else: a pooled int16 residual is first reduced into it by a streaming pass.
+ * tcbnn_conv_planes_bytes is the part that is the pre-expanded input: the size of the planes of
+ * tcbnn_conv_layer_x, 0 for layers that take none.)  The buffer is only used during the call
  * (stream order); one buffer of the largest size serves all layers of a network on one stream.
  * With workspace == NULL this is tcbnn_conv_layer.  No reference counterpart. */
 size_t tcbnn_conv_workspace_bytes(const tcbnn_conv_desc* d);
+size_t tcbnn_conv_planes_bytes(const tcbnn_conv_desc* d);
 int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void* prepared,
                        const float* thr, const void* res_in, int res_in_bytes, int res_in_ch,
                        int residual_channels, int residual_pool, uint32_t* out,
@@ -116,9 +120,9 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
  * input, which saves the consumer's expansion pass:
  *  - next / next_planes / next_planes_bytes (all NULL / 0 for none): `next` is the descriptor of
  *    the layer that consumes this layer's output (same batch, its H x W x C = this layer's
- *    OH x OW x O, and tcbnn_conv_workspace_bytes(next) != 0); besides the packed bits the layer
+ *    OH x OW x O, and tcbnn_conv_planes_bytes(next) != 0); besides the packed bits the layer
  *    then also writes its output as +-1 bytes into next_planes in that layer's operand layout.
- *    The buffer (tcbnn_conv_workspace_bytes(next) bytes, 256-byte aligned) must have been zeroed
+ *    The buffer (tcbnn_conv_planes_bytes(next) bytes, 256-byte aligned) must have been zeroed
  *    once and be used for this pair of layers only: the padding positions of the layout are never
  *    written.  out_image_stride must be dense.  Kernels that cannot write the planes themselves
  *    are followed by the expansion pass, so the result is the same for every layer.

@@ -158,6 +158,7 @@ struct PreparedLayout {
     int pre_stages;
     long long pre_positions, pre_front;
     int as_npos;          // 0 when the layer is not eligible
+    size_t pool_bytes;    // scratch the activation-stationary kernel can use to pre-pool a residual
     int as_slots;         // units in its filter ring
     size_t as_smem, off_wi8_as;
 };
@@ -197,7 +198,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o;
     L.umma_pw = L.umma_vh = L.umma_back_y = L.umma_back_x = 0;
     L.as_npos = 0; L.as_smem = 0; L.as_slots = 0; L.off_wi8_as = o;
-    L.pre_bytes = 0; L.pre_smem = 0; L.pre_stages = 0; L.pre_positions = 0; L.pre_front = 0;
+    L.pre_bytes = 0; L.pre_smem = 0; L.pre_stages = 0; L.pool_bytes = 0; L.pre_positions = 0; L.pre_front = 0;
     if (d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) && d->pool == 1 &&
         d->padding && d->C % 64 == 0 && d->O % 32 == 0) {
         const int st = d->stride_h;
@@ -245,6 +246,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
             if (st == 1 && d->C >= 256 && d->C <= 512 && d->O % umma::kAsNT == 0 &&
                 npos_as <= umma::kAsMaxPos * umma::kAsExpThreads && smem_as <= 227 * 1024) {
                 L.as_npos = npos_as; L.as_smem = smem_as; L.as_slots = slots_as;
+                L.pool_bytes = (size_t)d->B * d->OH * d->OW * d->O * 4;
                 L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
                 if (L.umma_nt == umma::kAsNT) {
                     L.off_wi8_as = L.off_wi8;
@@ -352,6 +354,29 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
     if (per > mtiles) per = mtiles;
     k_conv_umma_pre<NT><<<(int)(per * a.ntiles_n), umma::kPreThreads, smem, st>>>(a);
     return launch_check("conv_layer (tcgen05, pre-expanded input)");
+}
+
+// 2x2 max of an int16 residual [B][2P][2Q][ch] -> [B][P][Q][ch] (kernel.cuh:773-783), 8 channels
+// per thread: the activation-stationary kernel then reads one row per pixel instead of four.
+__global__ void __launch_bounds__(256) k_pool_residual16(const uint4* in, uint4* out, int B, int P, int Q, int ch8) {
+    const long long total = (long long)B * P * Q * ch8;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % ch8);
+        long long r = i / ch8;
+        const int x = (int)(r % Q); r /= Q;
+        const int y = (int)(r % P);
+        const long long n = r / P;
+        const uint4* s0 = in + ((n * 2 * P + 2 * y) * 2 * Q + 2 * x) * ch8 + c;
+        const uint4* s1 = s0 + (long long)2 * Q * ch8;
+        const uint4 a = __ldg(s0), b = __ldg(s0 + ch8), e = __ldg(s1), f = __ldg(s1 + ch8);
+        uint4 m;
+        m.x = __vmaxs2(__vmaxs2(a.x, b.x), __vmaxs2(e.x, f.x));
+        m.y = __vmaxs2(__vmaxs2(a.y, b.y), __vmaxs2(e.y, f.y));
+        m.z = __vmaxs2(__vmaxs2(a.z, b.z), __vmaxs2(e.z, f.z));
+        m.w = __vmaxs2(__vmaxs2(a.w, b.w), __vmaxs2(e.w, f.w));
+        out[i] = m;
+    }
 }
 
 __global__ void __launch_bounds__(umma::kAsThreads, 1) k_conv_umma_as(umma::ConvWsArgs a) {
@@ -664,6 +689,12 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
 
 size_t tcbnn_conv_workspace_bytes(const tcbnn_conv_desc* d) {
     if (conv_check(d, true)) return 0;
+    const PreparedLayout L = prepared_layout(d);
+    return L.pre_bytes > L.pool_bytes ? L.pre_bytes : L.pool_bytes;
+}
+
+size_t tcbnn_conv_planes_bytes(const tcbnn_conv_desc* d) {
+    if (conv_check(d, true)) return 0;
     return prepared_layout(d).pre_bytes;
 }
 
@@ -695,7 +726,7 @@ static int next_planes_of(const tcbnn_conv_desc* d, int out_h, int out_w, const 
                           void* planes, size_t planes_bytes, NextPlanes* nx) {
     if (conv_check(next, true)) return 1;
     const PreparedLayout N = prepared_layout(next);
-    if (!N.pre_bytes) return fail("next layer takes no pre-expanded input (tcbnn_conv_workspace_bytes is 0)");
+    if (!N.pre_bytes) return fail("next layer takes no pre-expanded input (tcbnn_conv_planes_bytes is 0)");
     if (next->B != d->B || next->H != out_h || next->W != out_w || next->C != d->O)
         return fail("next layer's input %dx%dx%dx%d is not this layer's output %dx%dx%dx%d", next->B, next->H,
                     next->W, next->C, d->B, out_h, out_w, d->O);
@@ -774,6 +805,17 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         if (use_as) {
             a.NPOS = L.as_npos; a.as_slots = L.as_slots;
             a.wi8 = (const uint4*)(p + L.off_wi8_as);
+            // a pooled int16 residual is reduced by a streaming pass first when there is scratch
+            // for it: four scattered 16-byte loads per value inside the epilogue cost more
+            const size_t pooled = (size_t)d->B * d->OH * d->OW * (size_t)res_in_ch * 2;
+            if (res_in && residual_pool && res_in_bytes == 2 && res_in_ch % 8 == 0 && workspace &&
+                workspace_bytes >= pooled && ((uintptr_t)workspace & 15) == 0) {
+                const long long units = (long long)d->B * d->OH * d->OW * (res_in_ch / 8);
+                k_pool_residual16<<<elementwise_grid(units, sms), 256, 0, st>>>((const uint4*)res_in, (uint4*)workspace,
+                                                                             d->B, d->OH, d->OW, res_in_ch / 8);
+                if (launch_check("conv_layer (residual pooling)")) return 1;
+                a.res_in = workspace; a.residual_pool = 0;
+            }
             return launch_conv_umma_as(a, L.as_smem, sms, st);
         }
         if (L.pre_bytes && workspace && g_conv_path != 3) {

@@ -46,6 +46,7 @@ SIGNATURES = {
     "tcbnn_noalloc_scratch_bytes": (_SZ, []),
     "tcbnn_fc_layer_noalloc": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
     "tcbnn_conv_workspace_bytes": (_SZ, [C.POINTER(ConvDesc)]),
+    "tcbnn_conv_planes_bytes": (_SZ, [C.POINTER(ConvDesc)]),
     "tcbnn_conv_layer_w": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _I, _P, _P, _SZ, _P]),
     "tcbnn_conv_layer_x": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _I, _P, _P, _SZ, _I,
                                 C.POINTER(ConvDesc), _P, _SZ, _P]),

@@ -198,10 +198,14 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
     return out, res_out, acc_out
 
 
+def new_planes_bytes(d):
+    return _l.load().tcbnn_conv_planes_bytes(C.byref(d))
+
+
 def new_planes(d, device):
     """Zeroed input planes for the layer `d` when its producer writes them (next_layer=...), or
     None when the layer takes no pre-expanded input."""
-    n = _l.load().tcbnn_conv_workspace_bytes(C.byref(d))
+    n = _l.load().tcbnn_conv_planes_bytes(C.byref(d))
     return torch.zeros((n,), dtype=torch.uint8, device=device) if n else None
 
 

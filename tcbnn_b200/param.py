@@ -338,8 +338,10 @@ class Conv128LayerParam:
     def kernel_launches(self):
         """Kernels one forward() launches: a layer that runs on a pre-expanded input launches the
         expansion pass too unless its producer filled the planes."""
-        own_expand = self.input_planes is None and ops.conv_workspace(self.desc, self.input_gpu.device) is not None
-        return 2 if own_expand else 1
+        own_expand = self.input_planes is None and ops.new_planes_bytes(self.desc) > 0
+        pools_first = (ops.new_planes_bytes(self.desc) == 0 and self.inject_residual and self.residual_pool and
+                       ops.conv_workspace(self.desc, self.input_gpu.device) is not None)
+        return 2 if (own_expand or pools_first) else 1
 
     def forward(self):
         ops.conv_layer(self.desc, self.input_gpu, self.prepared, self.bn_gpu,
