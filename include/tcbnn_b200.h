@@ -200,10 +200,13 @@ int tcbnn_inconv_layer_u8(const tcbnn_conv_desc* d, const uint8_t* x, const floa
  * (kernel.cuh:578-672) reads the filter bits at run time, as tcbnn_inconv_layer does.  A model's
  * first-layer filter and thresholds never change, so tcbnn_inconv_specialize reads them back
  * (filter_bits and thr are device pointers, laid out as for tcbnn_inconv_layer; synchronises the
- * stream), generates a kernel whose instruction stream contains the filter -- one
- * register-to-register fp32 add per (tap, output channel), same operands, order and roundings as
- * the reference -- compiles it with NVRTC (libnvrtc.so.12 is looked up with dlopen; the
- * environment variable TCBNN_NVRTC may name it) and loads it.  d->O <= 64.  The kernel does not
+ * stream) and keeps them; the layer calls then run a generated kernel whose instruction stream
+ * contains the filter -- one register-to-register fp32 add per (tap, output channel), same
+ * operands, order and roundings as the reference -- compiled with NVRTC (libnvrtc.so.12 is looked
+ * up with dlopen; the environment variable TCBNN_NVRTC may name it).  There are four variants
+ * (fp32 or uint8 images; aligned row loads for stride 4 and rows of a multiple of 4 pixels, or one
+ * load per tap); each is compiled and loaded by the first call that needs it (1-4 s), so run one
+ * call before timing or capturing a graph.  d->O <= 64.  The kernel does not
  * depend on d->B, d->H or d->W.  tcbnn_inconv_specialized_layer then runs the layer on fp32 images
  * (x, x8 = lut = NULL) or on uint8 images with their value table (x = NULL), with the outputs of
  * tcbnn_inconv_layer; d must agree with the descriptor used to specialise in everything but

@@ -20,6 +20,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 #include <dlfcn.h>
@@ -47,10 +48,15 @@ struct SpecArgs {
     uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
 };
 
+// One kernel per (input type, load style), compiled when first used: a 7x7x64 kernel takes
+// 1.5 - 4 s to compile and most callers only ever use one of the four.
 struct SpecHandle {
     int O, R, S, sh, sw, pad_h, pad_w, pool;
-    cudaLibrary_t lib;
-    cudaKernel_t k_f32, k_u8;
+    std::vector<unsigned char> codes;
+    std::vector<uint32_t> thr_bits;
+    std::mutex mu;
+    cudaLibrary_t lib[4] = {nullptr, nullptr, nullptr, nullptr};       // index = u8 * 2 + vec
+    cudaKernel_t kernel[4] = {nullptr, nullptr, nullptr, nullptr};
 };
 
 inline void emit(std::string& s, const char* fmt, ...) {
@@ -63,8 +69,10 @@ inline void emit(std::string& s, const char* fmt, ...) {
 }
 
 // codes[tap][o] = b0<<2 | b1<<1 | b2 (bit 1 = '+'), thr_bits[o] = the threshold's bit pattern
+// variant = u8 * 2 + vec: which of the four kernels the source defines (entry point tcbnn_spec)
 inline std::string generate_source(const SpecHandle& h, const std::vector<unsigned char>& codes,
-                                   const std::vector<uint32_t>& thr_bits) {
+                                   const std::vector<uint32_t>& thr_bits, int variant) {
+    const bool want_u8 = (variant & 2) != 0, want_vec = (variant & 1) != 0;
     const int O = h.O, RS = h.R * h.S, Ow = (O + 31) / 32;
     std::string s;
     s.reserve(400 * 1024);
@@ -80,7 +88,13 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
          "  for (int g = 0; g < 4; g++) { const uint32_t nb = (h >> (4 * g)) & 0xFu;\n"
          "    const uint32_t y = (nb * 0x00204081u) & 0x01010101u; v[g] = ~(y * 0xFEu); }\n"
          "  return make_uint4(v[0], v[1], v[2], v[3]); }\n";
-    emit(s, "template <bool U8> __device__ __forceinline__ void body(const SpecArgs& c, const float* slut) {\n");
+    // VEC (stride 4 only, image rows a multiple of 4 pixels, aligned base): a thread's taps of one
+    // image row are fetched with aligned 16-byte (fp32) / 4-byte (uint8) loads instead of one
+    // load per tap; consecutive lanes then read consecutive 16 bytes.
+    const bool vec_ok = h.sw == 4 && want_vec;
+    const int OFF = (4 - h.pad_w % 4) % 4;          // x0 - OFF is a multiple of 4
+    const int NQ4 = (OFF + h.S + 3) / 4;            // 4-column groups per row
+    emit(s, "template <bool U8, bool VEC> __device__ __forceinline__ void body(const SpecArgs& c, const float* slut) {\n");
     s += " const unsigned pix = blockIdx.x * blockDim.x + threadIdx.x;\n"
          " const bool live = pix < c.total;\n"
          " int n, y, x;\n";
@@ -100,19 +114,49 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
          " const unsigned char* img8 = c.x8 + (size_t)n * 3 * plane;\n";
     s += " float ";
     for (int o = 0; o < O; o++) emit(s, "a%d = 0.f%s", o, o + 1 < O ? ", " : ";\n");
-    for (int t = 0; t < RS; t++) {
-        emit(s, " { const int ay = y0 + %d, ax = x0 + %d; float f0 = 0.f, f1 = 0.f, f2 = 0.f;\n", t / h.S, t % h.S);
-        s += "  if (live && (unsigned)ay < (unsigned)c.H && (unsigned)ax < (unsigned)c.W) {\n"
-             "   const size_t po = (size_t)ay * c.W + ax;\n"
-             "   if (U8) { f0 = slut[__ldg(img8 + po)]; f1 = slut[256 + __ldg(img8 + po + plane)]; f2 = slut[512 + __ldg(img8 + po + 2 * plane)]; }\n"
-             "   else { f0 = __ldg(img + po); f1 = __ldg(img + po + plane); f2 = __ldg(img + po + 2 * plane); }\n"
-             "  }\n"
-             "  const float pp = __fadd_rn(f0, f1), pm = __fadd_rn(f0, -f1);\n"
-             "  const float v7 = __fadd_rn(pp, f2), v6 = __fadd_rn(pp, -f2), v5 = __fadd_rn(pm, f2), v4 = __fadd_rn(pm, -f2);\n";
-        for (int o = 0; o < O; o++) {
-            const int k = codes[(size_t)t * O + o];
-            if (k >= 4) emit(s, "  a%d = __fadd_rn(a%d, v%d);\n", o, o, k);
-            else emit(s, "  a%d = __fadd_rn(a%d, -v%d);\n", o, o, 7 - k);     // pattern k is minus pattern 7-k
+    for (int r = 0; r < h.R; r++) {
+        s += " {\n";
+        emit(s, "  float g0[%d], g1[%d], g2[%d];\n", 4 * NQ4, 4 * NQ4, 4 * NQ4);
+        if (vec_ok) {
+            emit(s, "  if (VEC) { const int ay = y0 + %d; const bool rok = live && (unsigned)ay < (unsigned)c.H; const int cx = x0 - %d;\n", r, OFF);
+            for (int q = 0; q < NQ4; q++) {
+                emit(s, "   { const bool ok = rok && cx + %d >= 0 && cx + %d < c.W; const size_t po = (size_t)ay * c.W + (cx + %d);\n",
+                     4 * q, 4 * q + 3, 4 * q);
+                s += "     if (U8) { unsigned b0 = 0, b1 = 0, b2 = 0;\n"
+                     "       if (ok) { b0 = __ldg(reinterpret_cast<const unsigned*>(img8 + po)); b1 = __ldg(reinterpret_cast<const unsigned*>(img8 + po + plane)); b2 = __ldg(reinterpret_cast<const unsigned*>(img8 + po + 2 * plane)); }\n";
+                for (int k = 0; k < 4; k++) {
+                    const int gi = 4 * q + k;
+                    if (gi < OFF || gi >= OFF + h.S) continue;          // column no tap uses
+                    emit(s, "       g0[%d] = ok ? slut[(b0 >> %d) & 255u] : 0.f; g1[%d] = ok ? slut[256 + ((b1 >> %d) & 255u)] : 0.f; g2[%d] = ok ? slut[512 + ((b2 >> %d) & 255u)] : 0.f;\n",
+                         gi, 8 * k, gi, 8 * k, gi, 8 * k);
+                }
+                s += "     } else { float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0;\n"
+                     "       if (ok) { t0 = __ldg(reinterpret_cast<const float4*>(img + po)); t1 = __ldg(reinterpret_cast<const float4*>(img + po + plane)); t2 = __ldg(reinterpret_cast<const float4*>(img + po + 2 * plane)); }\n";
+                emit(s, "       g0[%d] = t0.x; g0[%d] = t0.y; g0[%d] = t0.z; g0[%d] = t0.w;\n", 4 * q, 4 * q + 1, 4 * q + 2, 4 * q + 3);
+                emit(s, "       g1[%d] = t1.x; g1[%d] = t1.y; g1[%d] = t1.z; g1[%d] = t1.w;\n", 4 * q, 4 * q + 1, 4 * q + 2, 4 * q + 3);
+                emit(s, "       g2[%d] = t2.x; g2[%d] = t2.y; g2[%d] = t2.z; g2[%d] = t2.w;\n", 4 * q, 4 * q + 1, 4 * q + 2, 4 * q + 3);
+                s += "     } }\n";
+            }
+            s += "  }\n";
+        }
+        for (int sx = 0; sx < h.S; sx++) {
+            const int t = r * h.S + sx;
+            s += "  { float f0 = 0.f, f1 = 0.f, f2 = 0.f;\n";
+            if (vec_ok) emit(s, "   if (VEC) { f0 = g0[%d]; f1 = g1[%d]; f2 = g2[%d]; } else\n", OFF + sx, OFF + sx, OFF + sx);
+            emit(s, "   { const int ay = y0 + %d, ax = x0 + %d;\n", r, sx);
+            s += "    if (live && (unsigned)ay < (unsigned)c.H && (unsigned)ax < (unsigned)c.W) {\n"
+                 "     const size_t po = (size_t)ay * c.W + ax;\n"
+                 "     if (U8) { f0 = slut[__ldg(img8 + po)]; f1 = slut[256 + __ldg(img8 + po + plane)]; f2 = slut[512 + __ldg(img8 + po + 2 * plane)]; }\n"
+                 "     else { f0 = __ldg(img + po); f1 = __ldg(img + po + plane); f2 = __ldg(img + po + 2 * plane); }\n"
+                 "    } }\n"
+                 "   const float pp = __fadd_rn(f0, f1), pm = __fadd_rn(f0, -f1);\n"
+                 "   const float v7 = __fadd_rn(pp, f2), v6 = __fadd_rn(pp, -f2), v5 = __fadd_rn(pm, f2), v4 = __fadd_rn(pm, -f2);\n";
+            for (int o = 0; o < O; o++) {
+                const int k = codes[(size_t)t * O + o];
+                if (k >= 4) emit(s, "   a%d = __fadd_rn(a%d, v%d);\n", o, o, k);
+                else emit(s, "   a%d = __fadd_rn(a%d, -v%d);\n", o, o, 7 - k);     // pattern k is minus pattern 7-k
+            }
+            s += "  }\n";
         }
         s += " }\n";
     }
@@ -159,13 +203,14 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
     for (int o = 0; o < O; o++) emit(s, "  q[%d] = a%d;\n", o, o);
     s += " }\n}\n";
     // two blocks per SM: at most 128 registers per thread (the sums take O of them)
-    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d, 2) tcbnn_spec_f32(SpecArgs c) { body<false>(c, nullptr); }\n",
-         kSpecThreads);
-    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d, 2) tcbnn_spec_u8(SpecArgs c) {\n", kSpecThreads);
-    s += " __shared__ float slut[768];\n"
-         " for (int i = threadIdx.x; i < 768; i += blockDim.x) slut[i] = __ldg(c.lut + i);\n"
-         " __syncthreads();\n"
-         " body<true>(c, slut);\n}\n";
+    emit(s, "extern \"C\" __global__ void __launch_bounds__(%d, 2) tcbnn_spec(SpecArgs c) {\n", kSpecThreads);
+    if (want_u8)
+        s += " __shared__ float slut[768];\n"
+             " for (int i = threadIdx.x; i < 768; i += blockDim.x) slut[i] = __ldg(c.lut + i);\n"
+             " __syncthreads();\n";
+    else
+        s += " const float* slut = nullptr;\n";
+    emit(s, " body<%s, %s>(c, slut);\n}\n", want_u8 ? "true" : "false", vec_ok ? "true" : "false");
     return s;
 }
 

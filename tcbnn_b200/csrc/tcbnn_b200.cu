@@ -949,16 +949,17 @@ int tcbnn_inconv_layer_u8(const tcbnn_conv_desc* d, const uint8_t* x, const floa
 }
 
 // ---- first layer specialised to one filter (run-time compiled) -----------------------------
-static int spec_build(spec::SpecHandle* h, const std::vector<unsigned char>& codes,
-                      const std::vector<uint32_t>& thr_bits, bool load) {
-    const std::string src = spec::generate_source(*h, codes, thr_bits);
+// Compiles (and loads, unless only_compile) one variant of the handle's kernel; variant = u8 * 2 + vec.
+static int spec_build(spec::SpecHandle* h, int variant, bool only_compile) {
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->kernel[variant]) return 0;
+    const std::string src = spec::generate_source(*h, h->codes, h->thr_bits, variant);
     std::vector<char> cubin;
     std::string err;
     if (!spec::compile_cubin(src, cubin, err)) return fail("inconv_specialize: %s", err.c_str());
-    if (!load) return 0;
-    CUDA_TRY(cudaLibraryLoadData(&h->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
-    CUDA_TRY(cudaLibraryGetKernel(&h->k_f32, h->lib, "tcbnn_spec_f32"));
-    CUDA_TRY(cudaLibraryGetKernel(&h->k_u8, h->lib, "tcbnn_spec_u8"));
+    if (only_compile) return 0;
+    CUDA_TRY(cudaLibraryLoadData(&h->lib[variant], cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    CUDA_TRY(cudaLibraryGetKernel(&h->kernel[variant], h->lib[variant], "tcbnn_spec"));
     return 0;
 }
 
@@ -979,18 +980,19 @@ int tcbnn_inconv_specialize(const tcbnn_conv_desc* d, const uint32_t* filter_bit
     CUDA_TRY(cudaMemcpyAsync(fb.data(), filter_bits, fb.size() * 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     CUDA_TRY(cudaMemcpyAsync(thr_bits.data(), thr, (size_t)d->O * 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
-    std::vector<unsigned char> codes((size_t)RS * d->O);
+    if (!spec::nvrtc().ok) return fail("inconv_specialize: libnvrtc could not be opened (set TCBNN_NVRTC to its path)");
+    spec::SpecHandle* h = new spec::SpecHandle();
+    h->O = d->O; h->R = d->R; h->S = d->S; h->sh = d->stride_h; h->sw = d->stride_w;
+    h->pad_h = d->pad_h; h->pad_w = d->pad_w; h->pool = d->pool;
+    h->thr_bits = thr_bits;
+    h->codes.resize((size_t)RS * d->O);
     for (int t = 0; t < RS; t++)
         for (int o = 0; o < d->O; o++) {
             const uint32_t* fw = fb.data() + (size_t)t * 3 * Ow + (o >> 5);      // param.h:613-632
             const int sh = 31 - (o & 31);
-            codes[(size_t)t * d->O + o] = (unsigned char)((((fw[0] >> sh) & 1u) << 2) | (((fw[Ow] >> sh) & 1u) << 1) |
-                                                          ((fw[2 * Ow] >> sh) & 1u));
+            h->codes[(size_t)t * d->O + o] = (unsigned char)((((fw[0] >> sh) & 1u) << 2) | (((fw[Ow] >> sh) & 1u) << 1) |
+                                                             ((fw[2 * Ow] >> sh) & 1u));
         }
-    spec::SpecHandle* h = new spec::SpecHandle();
-    h->O = d->O; h->R = d->R; h->S = d->S; h->sh = d->stride_h; h->sw = d->stride_w;
-    h->pad_h = d->pad_h; h->pad_w = d->pad_w; h->pool = d->pool;
-    if (spec_build(h, codes, thr_bits, true)) { delete h; return 1; }
     *handle = h;
     return 0;
 }
@@ -1010,7 +1012,7 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
                                      size_t next_planes_bytes, void* stream) {
     if (!handle) return fail("inconv_specialized_layer: null handle");
     if (conv_check(d, false)) return 1;
-    const spec::SpecHandle* h = (const spec::SpecHandle*)handle;
+    spec::SpecHandle* h = (spec::SpecHandle*)handle;
     if (d->O != h->O || d->R != h->R || d->S != h->S || d->stride_h != h->sh || d->stride_w != h->sw ||
         d->pad_h != h->pad_h || d->pad_w != h->pad_w || d->pool != h->pool)
         return fail("inconv_specialized_layer: descriptor does not match the one the kernel was built for");
@@ -1032,7 +1034,11 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
     }
     void* params[] = {&c};
     const unsigned grid = (c.total + spec::kSpecThreads - 1) / spec::kSpecThreads;
-    CUDA_TRY(cudaLaunchKernel((const void*)(x ? h->k_f32 : h->k_u8), dim3(grid), dim3(spec::kSpecThreads), params, 0,
+    // aligned row loads when the geometry allows (stride 4, rows a multiple of 4 pixels, aligned base)
+    const bool vec = h->sw == 4 && d->W % 4 == 0 && (x ? ((uintptr_t)x & 15) == 0 : ((uintptr_t)x8 & 3) == 0);
+    const int variant = (x ? 0 : 2) + (vec ? 1 : 0);
+    if (!h->kernel[variant] && spec_build(h, variant, false)) return 1;       // first use: compile it
+    CUDA_TRY(cudaLaunchKernel((const void*)h->kernel[variant], dim3(grid), dim3(spec::kSpecThreads), params, 0,
                               (cudaStream_t)stream));
     return launch_check("inconv_specialized_layer");
 }
@@ -1040,7 +1046,8 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
 int tcbnn_inconv_release(void* handle) {
     if (!handle) return 0;
     spec::SpecHandle* h = (spec::SpecHandle*)handle;
-    cudaLibraryUnload(h->lib);
+    for (int v = 0; v < 4; v++)
+        if (h->lib[v]) cudaLibraryUnload(h->lib[v]);
     delete h;
     return 0;
 }
@@ -1048,16 +1055,18 @@ int tcbnn_inconv_release(void* handle) {
 int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, long long* source_bytes) {
     if (spec_check(d)) return 1;
     const int RS = d->R * d->S;
-    std::vector<unsigned char> codes((size_t)RS * d->O);
-    std::vector<uint32_t> thr_bits(d->O);
-    unsigned s = seed * 2654435761u + 12345u;
-    for (auto& c : codes) { s = s * 1664525u + 1013904223u; c = (unsigned char)((s >> 24) & 7u); }
-    for (auto& t : thr_bits) { s = s * 1664525u + 1013904223u; t = 0x40000000u ^ (s & 0x807FFFFFu); }
-    spec::SpecHandle h{};
+    spec::SpecHandle h;
     h.O = d->O; h.R = d->R; h.S = d->S; h.sh = d->stride_h; h.sw = d->stride_w;
     h.pad_h = d->pad_h; h.pad_w = d->pad_w; h.pool = d->pool;
-    if (source_bytes) *source_bytes = (long long)spec::generate_source(h, codes, thr_bits).size();
-    return spec_build(&h, codes, thr_bits, false);
+    h.codes.resize((size_t)RS * d->O);
+    h.thr_bits.resize(d->O);
+    unsigned s = seed * 2654435761u + 12345u;
+    for (auto& c : h.codes) { s = s * 1664525u + 1013904223u; c = (unsigned char)((s >> 24) & 7u); }
+    for (auto& t : h.thr_bits) { s = s * 1664525u + 1013904223u; t = 0x40000000u ^ (s & 0x807FFFFFu); }
+    // the uint8 variant with row loads where the stride allows them, the plain fp32 one otherwise
+    const int variant = d->stride_w == 4 ? 3 : 0;
+    if (source_bytes) *source_bytes = (long long)spec::generate_source(h, h.codes, h.thr_bits, variant).size();
+    return spec_build(&h, variant, true);
 }
 
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
