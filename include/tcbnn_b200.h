@@ -40,9 +40,21 @@ int tcbnn_pack_conv_filter(const float* F, int RS, int C, int O, uint32_t* out, 
 /* fp32 F[R*S][3][O] -> [R*S][3][Ow] words over O.  PackFiltersByOutChannels32, param.h:613-632. */
 int tcbnn_pack_inconv_filter(const float* F, int RS, int O, uint32_t* out, void* stream);
 
-/* Scratch a GEMM-family call can use to split K when M x N alone leaves SMs idle.
- * Passing NULL / 0 is always allowed (no split). */
+/* Scratch a GEMM-family call can use: partial sums to split K when M x N alone leaves SMs idle
+ * and, for large problems (M >= 128, N >= 64, K >= 1024, M*N*K >= 2^31), both operands written
+ * out as +-1 bytes for the tcgen05 int8 kernel (csrc/bgemm_umma.cuh), which is then used.
+ * Passing NULL / 0 is always allowed (warp-level b1 MMA kernel, no split); the buffer must be
+ * 256-byte aligned for the tcgen05 kernel to be taken. */
 size_t tcbnn_gemm_workspace_bytes(int M, int N, int K);
+/* Which kernel the GEMM family uses: 0 = automatic, 1 = always the warp-level b1 MMA kernel.
+ * Process-wide; for tests and measurements.  tcbnn_gemm_status reads the tcgen05 GEMM kernel's
+ * device-side status word (synchronises): 0 = fine, 1 = a bounded wait inside it gave up and the
+ * last results are not valid.  No reference counterparts. */
+int tcbnn_set_gemm_path(int path);
+int tcbnn_gemm_status(int* status);
+/* How many kernels a GEMM-family call of this shape launches when given a workspace of that size
+ * (1, 2 with split K, 4 on the tcgen05 path); for callers that account for their launches. */
+int tcbnn_gemm_launches(int M, int N, int K, size_t workspace_bytes);
 
 /* C[m][n] = K - 2*popc(A[m] xor B[n]), int32 [M][ldc].
  * BMMA / BMMAS_new, bmm/tensorcore_kernel.cu:138-356 (C = K - 2*acc at :331). */
@@ -172,8 +184,8 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
  * 8 MiB; resident on every GPU that loads the library until the process exits) instead of a
  * caller workspace.  The call itself performs no cudaMalloc / cudaFree and uses no allocating
  * library routine.
- *   - Shapes whose split-K partials (splits * M * N * 4 bytes, the figure
- *     tcbnn_gemm_workspace_bytes returns) exceed the array are rejected with an error.
+ *   - Shapes whose split-K partials (splits * M * N * 4 bytes) exceed the array are rejected
+ *     with an error.
  *   - The first call on each device looks up the array's device address (with that device
  *     current); make that first call before starting any stream capture.
  *   - All calls share the one array and it keeps the previous call's contents.  Nothing in

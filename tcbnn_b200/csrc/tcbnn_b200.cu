@@ -6,6 +6,7 @@
 #include "bconv_umma_ws.cuh"
 #include "bconv_umma_as.cuh"
 #include "bconv_umma_pre.cuh"
+#include "bgemm_umma.cuh"
 #include "inconv_spec.cuh"
 #include "inconv_tiled.cuh"
 #include <cstdio>
@@ -111,6 +112,85 @@ int gemm_splits(int M, int N, int K, int sms) {
     return s < 1 ? 1 : (int)s;
 }
 
+// ---- tcgen05 bit GEMM (bgemm_umma.cuh) -----------------------------------------------------
+__device__ int g_gemm_status;        // 1 after a bounded wait inside k_gemm_umma gave up
+
+__global__ void __launch_bounds__(256) k_expand_rows(const uint32_t* bits, int rows, int ld, int K, int RT, int KB,
+                                                     uint4* out) {
+    umma::expand_rows(bits, rows, ld, K, RT, KB, out);
+}
+__global__ void __launch_bounds__(umma::kGemmThreads, 1) k_gemm_umma(umma::GemmUmmaArgs g) {
+    extern __shared__ __align__(128) unsigned char dyn_smem_gemm[];
+    umma::gemm_umma_cta(g, dyn_smem_gemm);
+}
+
+struct GemmUmmaPlan {
+    bool use;
+    int MT, NT, KB, splits, per;
+    size_t off_ea, off_ew, off_partial, bytes;
+};
+
+// The tcgen05 path pays two expansion passes and a finishing pass: worth it for large problems.
+GemmUmmaPlan gemm_umma_plan(int M, int N, int K, int sms) {
+    GemmUmmaPlan p = {};
+    p.use = M >= 128 && N >= 64 && K >= 1024 && (long long)M * N * K >= (1LL << 31);
+    if (!p.use) return p;
+    p.MT = (M + 127) / 128; p.NT = (N + 127) / 128; p.KB = (K + 63) / 64;
+    const int tiles = ((p.MT + 1) / 2) * p.NT;
+    int splits = sms / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > p.KB / 4) splits = p.KB / 4;           // at least 4 k-blocks per split
+    if (splits < 1) splits = 1;
+    p.per = (p.KB + splits - 1) / splits;
+    p.splits = (p.KB + p.per - 1) / p.per;              // no empty split
+    size_t o = 0;
+    p.off_ea = o;      o += (size_t)p.MT * p.KB * umma::kGemmUnit;  o = (o + 255) & ~(size_t)255;
+    p.off_ew = o;      o += (size_t)p.NT * p.KB * umma::kGemmUnit;  o = (o + 255) & ~(size_t)255;
+    p.off_partial = o; o += (size_t)p.splits * M * N * sizeof(int32_t);
+    p.bytes = o;
+    return p;
+}
+
+int run_gemm_umma(const GemmArgs& g, const GemmUmmaPlan& p, void* workspace, int sms, cudaStream_t st) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)umma::kGemmSmem);
+        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        configured[dev] = true;
+    }
+    char* w = (char*)workspace;
+    k_expand_rows<<<elementwise_grid((long long)p.MT * p.KB * 512, sms), 256, 0, st>>>(g.A, g.M, g.lda, g.K, p.MT, p.KB,
+                                                                                     (uint4*)(w + p.off_ea));
+    k_expand_rows<<<elementwise_grid((long long)p.NT * p.KB * 512, sms), 256, 0, st>>>(g.W, g.N, g.ldw, g.K, p.NT, p.KB,
+                                                                                     (uint4*)(w + p.off_ew));
+    if (launch_check("gemm (operand expansion)")) return 1;
+    umma::GemmUmmaArgs a;
+    a.ea = (const unsigned char*)(w + p.off_ea); a.ew = (const unsigned char*)(w + p.off_ew);
+    a.M = g.M; a.N = g.N; a.KB = p.KB; a.MT = p.MT; a.NT = p.NT; a.splits = p.splits; a.per = p.per;
+    a.partial = (int32_t*)(w + p.off_partial);
+    static int* status_addr[64] = {nullptr};
+    if (dev >= 64 || !status_addr[dev]) {
+        int* q = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress((void**)&q, g_gemm_status));
+        if (dev < 64) status_addr[dev] = q;
+        a.status = q;
+    } else {
+        a.status = status_addr[dev];
+    }
+    k_gemm_umma<<<((p.MT + 1) / 2) * p.NT * p.splits, umma::kGemmThreads, umma::kGemmSmem, st>>>(a);
+    if (launch_check("gemm (tcgen05)")) return 1;
+    GemmArgs f = g;
+    f.K = 0;                                             // the partial sums are already K - 2*popc
+    f.splits = p.splits;
+    f.partial = a.partial;
+    k_gemm_finish<<<warp_grid((long long)g.M * ((g.N + 31) / 32), sms), kThreads, 0, st>>>(f);
+    return launch_check("gemm (tcgen05) finish");
+}
+
+int g_gemm_path = 0;     // 0 automatic, 1 warp-level b1 MMA only
+
 int run_gemm(GemmArgs g, void* workspace, size_t workspace_bytes, cudaStream_t st) {
     if (g.M <= 0 || g.N <= 0 || g.K <= 0) return fail("gemm: M, N, K must be positive");
     if ((g.lda & 1) || (g.ldw & 1)) return fail("gemm: lda and ldw must be even (64-bit loads)");
@@ -120,6 +200,9 @@ int run_gemm(GemmArgs g, void* workspace, size_t workspace_bytes, cudaStream_t s
     if (((uintptr_t)g.A & 7) || ((uintptr_t)g.W & 7)) return fail("gemm: operands must be 8-byte aligned");
     int sms;
     if (sm_count(&sms)) return 1;
+    const GemmUmmaPlan plan = gemm_umma_plan(g.M, g.N, g.K, sms);
+    if (plan.use && g_gemm_path != 1 && workspace && workspace_bytes >= plan.bytes && ((uintptr_t)workspace & 255) == 0)
+        return run_gemm_umma(g, plan, workspace, sms, st);
     int splits = gemm_splits(g.M, g.N, g.K, sms);
     const size_t need = (size_t)splits * g.M * g.N * sizeof(int32_t);
     if (splits > 1 && (workspace == nullptr || workspace_bytes < need)) splits = 1;
@@ -613,7 +696,31 @@ size_t tcbnn_gemm_workspace_bytes(int M, int N, int K) {
     int sms;
     if (M <= 0 || N <= 0 || K <= 0 || sm_count(&sms)) return 0;
     const int s = gemm_splits(M, N, K, sms);
-    return s > 1 ? (size_t)s * M * N * sizeof(int32_t) : 0;
+    const size_t split_k = s > 1 ? (size_t)s * M * N * sizeof(int32_t) : 0;
+    const GemmUmmaPlan plan = gemm_umma_plan(M, N, K, sms);
+    return plan.use && plan.bytes > split_k ? plan.bytes : split_k;
+}
+
+int tcbnn_gemm_launches(int M, int N, int K, size_t workspace_bytes) {
+    int sms;
+    if (M <= 0 || N <= 0 || K <= 0 || sm_count(&sms)) return 0;
+    const GemmUmmaPlan plan = gemm_umma_plan(M, N, K, sms);
+    if (plan.use && g_gemm_path != 1 && workspace_bytes >= plan.bytes) return 4;   // 2 expansions, GEMM, finish
+    const int s = gemm_splits(M, N, K, sms);
+    return (s > 1 && workspace_bytes >= (size_t)s * M * N * sizeof(int32_t)) ? 2 : 1;
+}
+
+int tcbnn_set_gemm_path(int path) {
+    if (path < 0 || path > 1) return fail("set_gemm_path: 0 = automatic, 1 = warp-level b1 MMA only");
+    g_gemm_path = path;
+    return 0;
+}
+
+int tcbnn_gemm_status(int* status) {
+    if (!status) return fail("gemm_status: null pointer");
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemcpyFromSymbol(status, g_gemm_status, sizeof(int)));
+    return 0;
 }
 
 int tcbnn_bgemm(const uint32_t* A, const uint32_t* B, int M, int N, int K, int lda, int ldb,

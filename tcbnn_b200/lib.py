@@ -32,6 +32,9 @@ SIGNATURES = {
     "tcbnn_pack_conv_filter": (_I, [_P, _I, _I, _I, _P, _P]),
     "tcbnn_pack_inconv_filter": (_I, [_P, _I, _I, _P, _P]),
     "tcbnn_gemm_workspace_bytes": (_SZ, [_I, _I, _I]),
+    "tcbnn_gemm_launches": (_I, [_I, _I, _I, _SZ]),
+    "tcbnn_set_gemm_path": (_I, [_I]),
+    "tcbnn_gemm_status": (_I, [C.POINTER(C.c_int)]),
     "tcbnn_bgemm": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _SZ, _P]),
     "tcbnn_fc_layer": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _SZ, _P]),
     "tcbnn_out_layer": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P, _SZ, _P]),

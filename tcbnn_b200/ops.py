@@ -80,6 +80,12 @@ def gemm_workspace(M, N, K, device):
     return torch.empty((max(n, 4) // 4,), dtype=torch.int32, device=device) if n else None
 
 
+def gemm_launches(M, N, K, workspace):
+    """Kernels a GEMM-family call of this shape launches with this workspace tensor."""
+    nbytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    return _l.load().tcbnn_gemm_launches(M, N, K, C.c_size_t(nbytes))
+
+
 def _ws(ws):
     return (_ptr(ws), C.c_size_t(ws.numel() * 4 if ws is not None else 0))
 
@@ -279,6 +285,17 @@ def mma_peak(kind, warps_per_sm=32, iters=4000):
     t = C.c_double(0)
     _l.call("tcbnn_mma_peak", kind, warps_per_sm, iters, C.byref(t))
     return t.value
+
+
+def set_gemm_path(path):
+    """0 = automatic, 1 = warp-level b1 MMA kernel only."""
+    _l.call("tcbnn_set_gemm_path", int(path))
+
+
+def gemm_status():
+    s = C.c_int(0)
+    _l.call("tcbnn_gemm_status", C.byref(s))
+    return s.value
 
 
 def set_conv_path(path):

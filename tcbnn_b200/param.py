@@ -116,6 +116,7 @@ class Fc128LayerParam:
         self.bn_gpu = torch.from_numpy(self.bn).to(dev)
         self.output_gpu = torch.zeros((self.input_height, ops.step128_words(N)), dtype=torch.int32, device=dev)
         self.workspace = ops.gemm_workspace(self.input_height, N, K, dev)
+        self.launches = ops.gemm_launches(self.input_height, N, K, self.workspace)
         self.set_input_gpu(prev_layer_gpu)
         return self
 
@@ -125,6 +126,9 @@ class Fc128LayerParam:
         if t.shape[1] * 32 < K or t.shape[1] % 2:
             raise ValueError("%s: input rows of %d words do not cover K=%d" % (self.name, t.shape[1], K))
         self.input_gpu = t
+
+    def kernel_launches(self):
+        return self.launches
 
     def forward(self):
         ops.fc_layer(self.input_gpu, self.weight_gpu, self.bn_gpu, self.input_width,
@@ -161,8 +165,12 @@ class Out128LayerParam:
         self.bn_bias_gpu = torch.from_numpy(self.bn_bias).to(dev)
         self.output_gpu = torch.zeros((self.input_height, N), dtype=torch.float32, device=dev)
         self.workspace = ops.gemm_workspace(self.input_height, N, K, dev)
+        self.launches = ops.gemm_launches(self.input_height, N, K, self.workspace)
         self.input_gpu = prev_layer_gpu.reshape(self.input_height, -1)
         return self
+
+    def kernel_launches(self):
+        return self.launches
 
     def forward(self):
         ops.out_layer(self.input_gpu, self.weight_gpu, self.bn_scale_gpu, self.bn_bias_gpu,

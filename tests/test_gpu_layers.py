@@ -69,6 +69,42 @@ def test_bgemm_fc_out(cuda, M, N, K, split):
     np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-5)
 
 
+UMMA_GEMM_CASES = [
+    # M, N, K: large enough for the tcgen05 int8 GEMM (M*N*K >= 2^31), ragged on purpose
+    (300, 200, 40010),       # partial row tiles, K not a multiple of 16
+    (1024, 512, 25088),      # the ResNet-18 FC layer
+    (129, 64, 300000),       # one full + one almost empty row tile, very long K
+    (512, 1000, 4200),       # N not a multiple of 128
+    (256, 130, 65536),       # N not a multiple of 4: scalar stores of the partial sums
+]
+
+
+@pytest.mark.parametrize("M,N,K", UMMA_GEMM_CASES)
+def test_gemm_family_on_tcgen05_matches_oracle_and_b1_kernel(cuda, M, N, K):
+    g = util.rng(M + 3 * N + 7 * K)
+    ld = orc.step128_words(K)
+    A = util.mask_row_pad(util.rand_words(g, (M, ld)), K)
+    W = util.mask_row_pad(util.rand_words(g, (N, ld)), K)
+    thr = (g.standard_normal(N) * np.sqrt(K)).astype(np.float32)
+    scale = g.standard_normal(N).astype(np.float32)
+    bias = g.standard_normal(N).astype(np.float32)
+    dA, dW = dev(A, cuda), dev(W, cuda)
+    ws = ops.gemm_workspace(M, N, K, cuda)
+    assert ws is not None and ws.numel() * 4 >= (M + N) * K          # room for both operands as bytes
+    ref = orc.bgemm(A, W, K)
+    try:
+        for path in (0, 1):
+            ops.set_gemm_path(path)
+            assert np.array_equal(ops.bgemm(dA, dW, K, workspace=ws).cpu().numpy(), ref), path
+            bits = ops.fc_layer(dA, dW, dev(thr, cuda), K, workspace=ws)
+            assert np.array_equal(host_u32(bits), orc.fc_layer(A, W, thr, K)), path
+            out = ops.out_layer(dA, dW, dev(scale, cuda), dev(bias, cuda), K, workspace=ws).cpu().numpy()
+            np.testing.assert_allclose(out, orc.out_layer(A, W, scale, bias, K), rtol=1e-5, atol=1e-5)
+            assert ops.gemm_status() == 0
+    finally:
+        ops.set_gemm_path(0)
+
+
 def test_gemm_kat_srand4(cuda):
     """The reference's seeded known-answer recipe, through the GPU path."""
     import os
