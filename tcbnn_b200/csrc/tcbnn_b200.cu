@@ -242,6 +242,7 @@ struct PreparedLayout {
     long long pre_positions, pre_front;
     int as_npos;          // 0 when the layer is not eligible
     size_t pool_bytes;    // scratch the activation-stationary kernel can use to pre-pool a residual
+    size_t prepool_bytes; // pooled layers: their pre-pool output bits (the OR-pooling pass reads them)
     int as_slots;         // units in its filter ring
     size_t as_smem, off_wi8_as;
 };
@@ -282,7 +283,9 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     L.umma_pw = L.umma_vh = L.umma_back_y = L.umma_back_x = 0;
     L.as_npos = 0; L.as_smem = 0; L.as_slots = 0; L.off_wi8_as = o;
     L.pre_bytes = 0; L.pre_smem = 0; L.pre_stages = 0; L.pool_bytes = 0; L.pre_positions = 0; L.pre_front = 0;
-    if (d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) && d->pool == 1 &&
+    // (a pooled layer runs the tcgen05 kernels on its pre-pool grid, followed by an OR-pooling pass)
+    const int OHu = d->OH * d->pool, OWu = d->OW * d->pool;
+    if (d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) &&
         d->padding && d->C % 64 == 0 && d->O % 32 == 0) {
         const int st = d->stride_h;
         // tap (r,s) reads raster offset (dy,dx) of a plane; extremes over the taps
@@ -292,8 +295,8 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
                                   : d->R - 1 - d->pad_h;
         const int fwd_x = st == 2 ? (d->S - 1 - d->pad_w >= 0 ? (d->S - 1 - d->pad_w) / 2 : 0)
                                   : d->S - 1 - d->pad_w;
-        const int PW = d->OW + (back_x > fwd_x ? back_x : fwd_x);
-        const int VH = d->OH + (back_y > fwd_y ? back_y : fwd_y);
+        const int PW = OWu + (back_x > fwd_x ? back_x : fwd_x);
+        const int VH = OHu + (back_y > fwd_y ? back_y : fwd_y);
         const int npos = (128 + (back_y + fwd_y) * PW + back_x + fwd_x + 7) & ~7;
         const int max_npos = st == 2 ? umma::kWsExpThreads : 2 * umma::kWsExpThreads;
         const long long nv = (long long)d->B * VH * PW;
@@ -329,7 +332,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
             if (st == 1 && d->C >= 256 && d->C <= 512 && d->O % umma::kAsNT == 0 &&
                 npos_as <= umma::kAsMaxPos * umma::kAsExpThreads && smem_as <= 227 * 1024) {
                 L.as_npos = npos_as; L.as_smem = smem_as; L.as_slots = slots_as;
-                L.pool_bytes = (size_t)d->B * d->OH * d->OW * d->O * 4;
+                L.pool_bytes = d->pool == 1 ? (size_t)d->B * d->OH * d->OW * d->O * 4 : 0;
                 L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
                 if (L.umma_nt == umma::kAsNT) {
                     L.off_wi8_as = L.off_wi8;
@@ -340,6 +343,9 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
             }
         }
     }
+    L.prepool_bytes = 0;
+    if (d->pool != 1 && (L.umma_nt || L.as_npos))
+        L.prepool_bytes = ((size_t)d->B * OHu * OWu * ((d->O + 31) / 32) * 4 + 255) & ~(size_t)255;
     L.bytes = o;
     return L;
 }
@@ -459,6 +465,25 @@ __global__ void __launch_bounds__(256) k_pool_residual16(const uint4* in, uint4*
         m.z = __vmaxs2(__vmaxs2(a.z, b.z), __vmaxs2(e.z, f.z));
         m.w = __vmaxs2(__vmaxs2(a.w, b.w), __vmaxs2(e.w, f.w));
         out[i] = m;
+    }
+}
+
+// OR over 2x2 windows of packed output bits [B][2P][2Q][Ow] -> [B][P][Q][Ow] (kernel.cuh:756-770
+// pools by OR-ing the window's bits): the tcgen05 kernels compute a pooled layer on its pre-pool
+// grid, this pass reduces it.
+__global__ void __launch_bounds__(256) k_pool_bits(const uint32_t* in, uint32_t* out, int B, int P, int Q, int Ow,
+                                                  long long out_image_stride) {
+    const long long total = (long long)B * P * Q * Ow;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int w = (int)(i % Ow);
+        long long r = i / Ow;
+        const int x = (int)(r % Q); r /= Q;
+        const int y = (int)(r % P);
+        const long long n = r / P;
+        const uint32_t* s0 = in + ((n * 2 * P + 2 * y) * 2 * Q + 2 * x) * Ow + w;
+        const uint32_t* s1 = s0 + (long long)2 * Q * Ow;
+        out[n * out_image_stride + ((long long)y * Q + x) * Ow + w] = __ldg(s0) | __ldg(s0 + Ow) | __ldg(s1) | __ldg(s1 + Ow);
     }
 }
 
@@ -797,7 +822,7 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
 size_t tcbnn_conv_workspace_bytes(const tcbnn_conv_desc* d) {
     if (conv_check(d, true)) return 0;
     const PreparedLayout L = prepared_layout(d);
-    return L.pre_bytes > L.pool_bytes ? L.pre_bytes : L.pool_bytes;
+    return (L.pre_bytes > L.pool_bytes ? L.pre_bytes : L.pool_bytes) + L.prepool_bytes;
 }
 
 size_t tcbnn_conv_planes_bytes(const tcbnn_conv_desc* d) {
@@ -881,12 +906,25 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
     const bool res_vec_ok = !res_in || (res_in_ch % 4 == 0 && residual_channels % 4 == 0 &&
                                         ((uintptr_t)res_in & 15) == 0);
     if (g_conv_path >= 2 && !res_vec_ok) return fail("conv_layer: residual layout not eligible for the tcgen05 path");
-    if ((L.umma_nt || use_as) && g_conv_path != 1 && res_vec_ok && (!res_out || ((uintptr_t)res_out & 15) == 0)) {
+    // a pooled layer needs room behind the kernel's own scratch for its pre-pool bits
+    const size_t main_ws = L.pre_bytes > L.pool_bytes ? L.pre_bytes : L.pool_bytes;
+    const bool pooled = d->pool != 1;
+    const bool pooled_ok = !pooled || (workspace && workspace_bytes >= main_ws + L.prepool_bytes &&
+                                       ((uintptr_t)workspace & 255) == 0);
+    if (g_conv_path >= 2 && !pooled_ok) return fail("conv_layer: a pooled layer needs its workspace for the tcgen05 path");
+    if ((L.umma_nt || use_as) && g_conv_path != 1 && res_vec_ok && pooled_ok &&
+        (!res_out || ((uintptr_t)res_out & 15) == 0)) {
+      const int P = d->OH * d->pool, Q = d->OW * d->pool;
+      uint32_t* prepool = pooled ? (uint32_t*)((char*)workspace + main_ws) : nullptr;
+      int sms;
+      if (sm_count(&sms)) return 1;
+      cudaStream_t st = (cudaStream_t)stream;
+      auto launch_tc = [&]() -> int {
         umma::ConvWsArgs a;
         a.in = in; a.wi8 = (const uint4*)(p + L.off_wi8); a.thr = thr;
         a.B = d->B; a.H = d->H; a.W = d->W; a.C = d->C; a.O = d->O; a.R = d->R; a.S = d->S;
         a.pad_h = d->pad_h; a.pad_w = d->pad_w; a.stride = d->stride_h;
-        a.OHg = d->OH; a.OWg = d->OW;
+        a.OHg = P; a.OWg = Q;
         a.PW = L.umma_pw; a.VH = L.umma_vh; a.NPOS = L.umma_npos;
         a.back_y = L.umma_back_y; a.back_x = L.umma_back_x;
         a.NV = (long long)d->B * a.VH * a.PW;
@@ -894,17 +932,16 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         umma::fastdiv_setup(a.VH, &a.vh_mul, &a.vh_sh);
         a.res_in = res_in; a.res_in_bytes = res_in_bytes; a.res_in_ch = res_in_ch;
         a.residual_channels = residual_channels; a.residual_pool = residual_pool;
-        a.out = out; a.out_image_stride = out_image_stride; a.res_out = res_out;
+        a.out = pooled ? prepool : out;
+        a.out_image_stride = pooled ? (long long)P * Q * Ow : out_image_stride;
+        a.res_out = res_out;
         a.res_out_bytes = res_out_bytes; a.acc_out = acc_out;
         a.err_flag = (int*)(p + L.off_err);
         a.trace = g_conv_trace;
-        int sms;
-        if (sm_count(&sms)) return 1;
-        cudaStream_t st = (cudaStream_t)stream;
         a.pre = nullptr; a.pre_positions = 0; a.pre_front = 0;
         a.pre_stages = 0;
         a.nxt = nullptr; a.nxt_positions = 0; a.nxt_front = 0; a.nxt_PW = 0; a.nxt_VH = 0;
-        if (nx && !use_as) {
+        if (nx && !use_as && !pooled) {
             a.nxt = nx->planes; a.nxt_positions = nx->positions; a.nxt_front = nx->front;
             a.nxt_PW = nx->PW; a.nxt_VH = nx->VH;
             *fed = true;
@@ -914,9 +951,9 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
             a.wi8 = (const uint4*)(p + L.off_wi8_as);
             // a pooled int16 residual is reduced by a streaming pass first when there is scratch
             // for it: four scattered 16-byte loads per value inside the epilogue cost more
-            const size_t pooled = (size_t)d->B * d->OH * d->OW * (size_t)res_in_ch * 2;
+            const size_t pooled_res_bytes = (size_t)d->B * d->OH * d->OW * (size_t)res_in_ch * 2;
             if (res_in && residual_pool && res_in_bytes == 2 && res_in_ch % 8 == 0 && workspace &&
-                workspace_bytes >= pooled && ((uintptr_t)workspace & 15) == 0) {
+                workspace_bytes >= pooled_res_bytes && ((uintptr_t)workspace & 15) == 0) {
                 const long long units = (long long)d->B * d->OH * d->OW * (res_in_ch / 8);
                 k_pool_residual16<<<elementwise_grid(units, sms), 256, 0, st>>>((const uint4*)res_in, (uint4*)workspace,
                                                                              d->B, d->OH, d->OW, res_in_ch / 8);
@@ -941,6 +978,14 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         TCBNN_WS_CASE(32, 2) TCBNN_WS_CASE(64, 2) TCBNN_WS_CASE(128, 2) TCBNN_WS_CASE(256, 2)
 #undef TCBNN_WS_CASE
         return fail("conv_layer: no tcgen05 instance for n-tile=%d stride=%d", L.umma_nt, d->stride_h);
+      };
+      if (launch_tc()) return 1;
+      if (pooled) {
+          k_pool_bits<<<elementwise_grid((long long)d->B * d->OH * d->OW * Ow, sms), 256, 0, st>>>(
+              prepool, out, d->B, d->OH, d->OW, Ow, out_image_stride);
+          return launch_check("conv_layer (OR pooling)");
+      }
+      return 0;
     }
     ConvArgs c;
     c.in = in;

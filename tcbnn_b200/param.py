@@ -346,10 +346,12 @@ class Conv128LayerParam:
     def kernel_launches(self):
         """Kernels one forward() launches: a layer that runs on a pre-expanded input launches the
         expansion pass too unless its producer filled the planes."""
+        has_ws = ops.conv_workspace(self.desc, self.input_gpu.device) is not None
         own_expand = self.input_planes is None and ops.new_planes_bytes(self.desc) > 0
-        pools_first = (ops.new_planes_bytes(self.desc) == 0 and self.inject_residual and self.residual_pool and
-                       ops.conv_workspace(self.desc, self.input_gpu.device) is not None)
-        return 2 if (own_expand or pools_first) else 1
+        pools_residual = (ops.new_planes_bytes(self.desc) == 0 and self.inject_residual and self.residual_pool and
+                          has_ws)
+        pools_output = self.desc.pool != 1 and has_ws          # tcgen05 on the pre-pool grid + OR-pooling pass
+        return 1 + int(own_expand) + int(pools_residual) + int(pools_output)
 
     def forward(self):
         ops.conv_layer(self.desc, self.input_gpu, self.prepared, self.bn_gpu,

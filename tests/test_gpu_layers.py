@@ -430,9 +430,43 @@ def test_specialized_first_layer_hands_its_output_to_the_next_layer(cuda):
                          next_layer=(ops.conv_desc(B, 16, 16, O1, O2, 3, 3), planes))
 
 
+POOLED_UMMA_CASES = [
+    # B, H, W, C, O, stride: 2x2 OR-pooled layers on the tcgen05 kernels (pre-pool grid + pooling pass)
+    (4, 16, 16, 128, 128, 1),      # loader-fed kernel
+    (3, 8, 8, 256, 256, 1),        # activation-stationary kernel
+    (2, 16, 12, 64, 128, 2),       # stride-2 filter-stationary kernel
+    (5, 6, 10, 64, 64, 1),
+]
+
+
+@pytest.mark.parametrize("case", POOLED_UMMA_CASES)
+def test_pooled_conv_layer_on_tcgen05_matches_oracle(cuda, case):
+    B, H, W, C, O, st = case
+    g = util.rng(sum(case) + 3)
+    x = util.rand_words(g, (B, H, W, C // 32))
+    f = util.rand_words(g, (O, 9, C // 32))
+    thr = (g.standard_normal(O) * np.sqrt(C * 9) * 0.5).astype(np.float32)
+    eo, _, ea = orc.conv_layer(x, f, thr, C, 3, 3, st, st, True, 2, want_acc=True)
+    d = ops.conv_desc(B, H, W, C, O, 3, 3, st, st, True, 2)
+    prep = ops.conv_prepare(d, dev(f, cuda))
+    try:
+        for path in (2, 3, 1, 0):
+            ops.set_conv_path(path)
+            go, _, ga = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), want_acc=True)
+            assert ops.conv_status(d, prep) == 0
+            assert np.array_equal(ga.cpu().numpy(), ea), path
+            assert np.array_equal(host_u32(go), eo), path
+        ops.set_conv_path(2)
+        from tcbnn_b200.lib import TcbnnError
+        with pytest.raises(TcbnnError):          # no room for the pre-pool bits: not on this path
+            ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), workspace=False)
+    finally:
+        ops.set_conv_path(0)
+
+
 def test_tcgen05_path_refuses_ineligible_layer(cuda):
     from tcbnn_b200.lib import TcbnnError
-    d = ops.conv_desc(1, 8, 8, 64, 64, 3, 3, pool=2)    # pooled layers stay on the b1 MMA kernel
+    d = ops.conv_desc(1, 8, 8, 64, 64, 3, 3, padding=False)    # "valid" padding stays on the b1 MMA kernel
     f = torch.zeros((64, 9, 2), dtype=torch.int32, device=cuda)
     prep = ops.conv_prepare(d, f)
     x = torch.zeros((1, 8, 8, 2), dtype=torch.int32, device=cuda)
