@@ -218,7 +218,8 @@ int tcbnn_inconv_layer_u8(const tcbnn_conv_desc* d, const uint8_t* x, const floa
  * up with dlopen; the environment variable TCBNN_NVRTC may name it).  There are four variants
  * (fp32 or uint8 images; aligned row loads for stride 4 and rows of a multiple of 4 pixels, or one
  * load per tap); each is compiled and loaded by the first call that needs it (1-4 s), so run one
- * call before timing or capturing a graph.  d->O <= 64.  The kernel does not
+ * call before timing or capturing a graph.  d->O <= 128 (64 channels per thread; a second
+ * group of threads takes channels 64 and up).  The kernel does not
  * depend on d->B, d->H or d->W.  tcbnn_inconv_specialized_layer then runs the layer on fp32 images
  * (x, x8 = lut = NULL) or on uint8 images with their value table (x = NULL), with the outputs of
  * tcbnn_inconv_layer; d must agree with the descriptor used to specialise in everything but

@@ -30,7 +30,7 @@ namespace tcbnn {
 namespace spec {
 
 constexpr int kSpecThreads = 256;
-constexpr int kSpecMaxO = 64;
+constexpr int kSpecMaxO = 128;
 
 // Kernel arguments; the same struct is declared in the generated source.
 struct SpecArgs {
@@ -73,7 +73,8 @@ inline void emit(std::string& s, const char* fmt, ...) {
 inline std::string generate_source(const SpecHandle& h, const std::vector<unsigned char>& codes,
                                    const std::vector<uint32_t>& thr_bits, int variant) {
     const bool want_u8 = (variant & 2) != 0, want_vec = (variant & 1) != 0;
-    const int O = h.O, RS = h.R * h.S, Ow = (O + 31) / 32;
+    // Output channels are handled 64 at a time: blockIdx.y picks the group (its own code path).
+    const int Oall = h.O, RS = h.R * h.S, OwAll = (Oall + 31) / 32, nhalf = (Oall + 63) / 64;
     std::string s;
     s.reserve(400 * 1024);
     s += "typedef unsigned int uint32_t;\n"
@@ -88,13 +89,16 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
          "  for (int g = 0; g < 4; g++) { const uint32_t nb = (h >> (4 * g)) & 0xFu;\n"
          "    const uint32_t y = (nb * 0x00204081u) & 0x01010101u; v[g] = ~(y * 0xFEu); }\n"
          "  return make_uint4(v[0], v[1], v[2], v[3]); }\n";
+    for (int half = 0; half < nhalf; half++) {
+    const int OB = 64 * half, O = Oall - OB < 64 ? Oall - OB : 64;
     // VEC (stride 4 only, image rows a multiple of 4 pixels, aligned base): a thread's taps of one
     // image row are fetched with aligned 16-byte (fp32) / 4-byte (uint8) loads instead of one
     // load per tap; consecutive lanes then read consecutive 16 bytes.
     const bool vec_ok = h.sw == 4 && want_vec;
     const int OFF = (4 - h.pad_w % 4) % 4;          // x0 - OFF is a multiple of 4
     const int NQ4 = (OFF + h.S + 3) / 4;            // 4-column groups per row
-    emit(s, "template <bool U8, bool VEC> __device__ __forceinline__ void body(const SpecArgs& c, const float* slut) {\n");
+    emit(s, "template <bool U8, bool VEC> __device__ __forceinline__ void body%d(const SpecArgs& c, const float* slut) {\n", half);
+    emit(s, " constexpr int OBASE = %d;\n", OB);
     s += " const unsigned pix = blockIdx.x * blockDim.x + threadIdx.x;\n"
          " const bool live = pix < c.total;\n"
          " int n, y, x;\n";
@@ -152,7 +156,7 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
                  "   const float pp = __fadd_rn(f0, f1), pm = __fadd_rn(f0, -f1);\n"
                  "   const float v7 = __fadd_rn(pp, f2), v6 = __fadd_rn(pp, -f2), v5 = __fadd_rn(pm, f2), v4 = __fadd_rn(pm, -f2);\n";
             for (int o = 0; o < O; o++) {
-                const int k = codes[(size_t)t * O + o];
+                const int k = codes[(size_t)t * Oall + OB + o];
                 if (k >= 4) emit(s, "   a%d = __fadd_rn(a%d, v%d);\n", o, o, k);
                 else emit(s, "   a%d = __fadd_rn(a%d, -v%d);\n", o, o, 7 - k);     // pattern k is minus pattern 7-k
             }
@@ -163,26 +167,28 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
     // threshold (kernel.cuh:655), pack, pool
     s += " uint32_t w0 = 0, w1 = 0;\n";
     for (int o = 0; o < O; o++)
-        emit(s, " if (live && !(a%d < __uint_as_float(0x%08xu))) w%d |= 0x%08xu;\n", o, thr_bits[o], o >> 5,
+        emit(s, " if (live && !(a%d < __uint_as_float(0x%08xu))) w%d |= 0x%08xu;\n", o, thr_bits[OB + o], o >> 5,
              0x80000000u >> (o & 31));
     if (h.pool == 2)
         s += " w0 |= __shfl_xor_sync(0xffffffffu, w0, 1); w0 |= __shfl_xor_sync(0xffffffffu, w0, 2);\n"
              " w1 |= __shfl_xor_sync(0xffffffffu, w1, 1); w1 |= __shfl_xor_sync(0xffffffffu, w1, 2);\n";
     s += " if (!live) return;\n";
     emit(s, " { uint32_t* dst = c.out + (size_t)n * c.out_image_stride + ((size_t)(y / %d) * c.OW + (x / %d)) * %d;\n",
-         h.pool, h.pool, Ow);
+         h.pool, h.pool, OwAll);
     if (h.pool == 2) s += "   if ((pix & 3) == 0)";
-    emit(s, "   { dst[0] = w0;%s\n", Ow == 2 ? " dst[1] = w1;" : "");
+    emit(s, "   { dst[%d] = w0;", OB / 32);
+    if (O > 32) emit(s, " dst[%d] = w1;", OB / 32 + 1);
+    s += "\n";
     emit(s, "     if (c.nxt) { uint4* pl = c.nxt + c.nxt_front + ((long long)n * c.nxt_VH + (y / %d)) * c.nxt_PW + (x / %d);\n",
          h.pool, h.pool);
     for (int k = 0; k < (O + 15) / 16; k++)
-        emit(s, "       pl[(size_t)%d * c.nxt_positions] = expand16((w%d >> %d) & 0xFFFFu);\n", k, k / 2, (k & 1) ? 0 : 16);
+        emit(s, "       pl[(size_t)%d * c.nxt_positions] = expand16((w%d >> %d) & 0xFFFFu);\n", OB / 16 + k, k / 2, (k & 1) ? 0 : 16);
     s += "     }\n   } }\n";
     // residual = (int)acc (kernel.cuh:666-668), optional fp32 accumulators
     s += " const size_t opix = ((size_t)n * P + y) * Q + x;\n"
          " if (c.res_out) {\n"
          "  if (c.res_out_bytes == 2) {\n"
-         "   short* r = reinterpret_cast<short*>(c.res_out) + opix * c.res_out_ld;\n";
+         "   short* r = reinterpret_cast<short*>(c.res_out) + opix * c.res_out_ld + OBASE;\n";
     if (O % 8 == 0) {
         s += "   if ((c.res_out_ld & 7) == 0 && (reinterpret_cast<size_t>(c.res_out) & 15) == 0) {\n"
              "    uint4* d4 = reinterpret_cast<uint4*>(r);\n";
@@ -196,12 +202,22 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
     }
     s += "   {\n";
     for (int o = 0; o < O; o++) emit(s, "    r[%d] = (short)(int)a%d;\n", o, o);
-    s += "   }\n  } else {\n   int* r = reinterpret_cast<int*>(c.res_out) + opix * c.res_out_ld;\n";
-    for (int o = 0; o < O; o++) emit(s, "   r[%d] = (int)a%d;\n", o, o);
+    s += "   }\n  } else {\n   int* r = reinterpret_cast<int*>(c.res_out) + opix * c.res_out_ld + OBASE;\n";
+    if (O % 4 == 0) {
+        s += "   if ((c.res_out_ld & 3) == 0 && (reinterpret_cast<size_t>(c.res_out) & 15) == 0) {\n"
+             "    int4* d4 = reinterpret_cast<int4*>(r);\n";
+        for (int j = 0; j < O / 4; j++)
+            emit(s, "    d4[%d] = make_int4((int)a%d, (int)a%d, (int)a%d, (int)a%d);\n", j, 4 * j, 4 * j + 1, 4 * j + 2, 4 * j + 3);
+        s += "   } else\n";
+    }
+    s += "   {\n";
+    for (int o = 0; o < O; o++) emit(s, "    r[%d] = (int)a%d;\n", o, o);
+    s += "   }\n";
     s += "  }\n }\n if (c.acc_out) {\n";
-    emit(s, "  float* q = c.acc_out + opix * %d;\n", O);
+    emit(s, "  float* q = c.acc_out + opix * %d + OBASE;\n", Oall);
     for (int o = 0; o < O; o++) emit(s, "  q[%d] = a%d;\n", o, o);
     s += " }\n}\n";
+    }   // channel groups
     // two blocks per SM: at most 128 registers per thread (the sums take O of them)
     emit(s, "extern \"C\" __global__ void __launch_bounds__(%d, 2) tcbnn_spec(SpecArgs c) {\n", kSpecThreads);
     if (want_u8)
@@ -210,7 +226,11 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
              " __syncthreads();\n";
     else
         s += " const float* slut = nullptr;\n";
-    emit(s, " body<%s, %s>(c, slut);\n}\n", want_u8 ? "true" : "false", vec_ok ? "true" : "false");
+    const bool vec_kernel = h.sw == 4 && want_vec;
+    for (int half = 0; half < nhalf; half++)
+        emit(s, " %sbody%d<%s, %s>(c, slut);\n", nhalf == 1 ? "" : (half == 0 ? "if (blockIdx.y == 0) " : "else "), half,
+             want_u8 ? "true" : "false", vec_kernel ? "true" : "false");
+    s += "}\n";
     return s;
 }
 

@@ -1118,7 +1118,7 @@ static int spec_build(spec::SpecHandle* h, int variant, bool only_compile) {
 static int spec_check(const tcbnn_conv_desc* d) {
     if (conv_check(d, false)) return 1;
     if (d->O > spec::kSpecMaxO)
-        return fail("inconv_specialize: at most %d output channels (the sums of a pixel live in registers)", spec::kSpecMaxO);
+        return fail("inconv_specialize: at most %d output channels", spec::kSpecMaxO);
     return 0;
 }
 
@@ -1190,8 +1190,8 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
     const bool vec = h->sw == 4 && d->W % 4 == 0 && (x ? ((uintptr_t)x & 15) == 0 : ((uintptr_t)x8 & 3) == 0);
     const int variant = (x ? 0 : 2) + (vec ? 1 : 0);
     if (!h->kernel[variant] && spec_build(h, variant, false)) return 1;       // first use: compile it
-    CUDA_TRY(cudaLaunchKernel((const void*)h->kernel[variant], dim3(grid), dim3(spec::kSpecThreads), params, 0,
-                              (cudaStream_t)stream));
+    CUDA_TRY(cudaLaunchKernel((const void*)h->kernel[variant], dim3(grid, (h->O + 63) / 64), dim3(spec::kSpecThreads),
+                              params, 0, (cudaStream_t)stream));
     return launch_check("inconv_specialized_layer");
 }
 

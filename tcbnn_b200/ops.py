@@ -212,7 +212,10 @@ def new_planes(d, device):
     """Zeroed input planes for the layer `d` when its producer writes them (next_layer=...), or
     None when the layer takes no pre-expanded input."""
     n = _l.load().tcbnn_conv_planes_bytes(C.byref(d))
-    return torch.zeros((n,), dtype=torch.uint8, device=device) if n else None
+    if not n:
+        return None
+    # the planes come first in the layer's workspace; a pooled layer keeps its pre-pool bits behind them
+    return torch.zeros((max(n, _l.load().tcbnn_conv_workspace_bytes(C.byref(d))),), dtype=torch.uint8, device=device)
 
 
 class InconvSpecialized:

@@ -216,7 +216,7 @@ class InConv128LayerParam:
         images with input_lut, fp32 [3][256]: the value of every byte per channel, i.e. the
         reader's normalisation tabulated (data.cpp:534-542).  Same results, a quarter of the
         host->device traffic.
-        specialize: compile a kernel for this layer's filter and thresholds (layers of at most 64
+        specialize: compile a kernel for this layer's filter and thresholds (layers of at most 128
         output channels; same results, several times faster than the kernel that reads the
         filter at run time, which is used otherwise)."""
         dev = _dev()
@@ -232,7 +232,7 @@ class InConv128LayerParam:
         self.bn = config.read(d.O)
         self.bn_gpu = torch.from_numpy(self.bn).to(dev)
         self.specialized = None
-        if specialize and d.O <= 64:
+        if specialize and d.O <= 128:
             try:
                 self.specialized = ops.inconv_specialize(d, self.filter_gpu, self.bn_gpu)
             except Exception as e:      # no NVRTC on this machine: the general CUDA kernel runs

@@ -40,13 +40,13 @@ def test_specialised_first_layer_source_compiles_without_a_gpu():
         C.CDLL("libnvrtc.so.12")
     except OSError:
         pytest.skip("no libnvrtc on this machine")
-    for (O, R, stride, pool) in [(64, 7, 4, 1), (24, 3, 1, 2)]:
+    for (O, R, stride, pool) in [(64, 7, 4, 1), (24, 3, 1, 2), (128, 3, 1, 1)]:
         d = lib.ConvDesc(B=2, H=32, W=32, C=3, O=O, R=R, S=R, stride_h=stride, stride_w=stride, padding=1, pool=pool)
         lib.call("tcbnn_conv_shape", C.byref(d))
         n = C.c_longlong(0)
         lib.call("tcbnn_inconv_specialize_selftest", C.byref(d), 3, C.byref(n))
         assert n.value > 20 * R * R * O
-    d = lib.ConvDesc(B=2, H=32, W=32, C=3, O=128, R=3, S=3, stride_h=1, stride_w=1, padding=1, pool=1)
+    d = lib.ConvDesc(B=2, H=32, W=32, C=3, O=160, R=3, S=3, stride_h=1, stride_w=1, padding=1, pool=1)
     lib.call("tcbnn_conv_shape", C.byref(d))
     with pytest.raises(lib.TcbnnError):
         lib.call("tcbnn_inconv_specialize_selftest", C.byref(d), 3, None)

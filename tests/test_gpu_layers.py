@@ -203,8 +203,9 @@ def test_inconv_layer(cuda, case):
     assert np.array_equal(host_u32(go), eo)
 
 
-SPEC_CASES = [c for c in INCONV_CASES if c[3] <= 64] + [
+SPEC_CASES = INCONV_CASES + [
     (3, 20, 20, 16, 5, 5, 1, 1, 2),
+    (2, 16, 16, 96, 3, 3, 1, 1, 2),      # two channel groups, the second one half full; pooled
     (5, 30, 28, 64, 7, 7, 4, 4, 1),      # odd output sizes, several blocks of pixels
 ]
 
@@ -251,9 +252,9 @@ def test_inconv_layer_specialized_kernel(cuda, case):
 
 def test_inconv_specialize_rejects_wide_layers_and_mismatched_descriptors(cuda):
     from tcbnn_b200.lib import TcbnnError
-    d = ops.conv_desc(1, 8, 8, 3, 128, 3, 3)
-    fb = torch.zeros((9, 3, 4), dtype=torch.int32, device=cuda)
-    thr = torch.zeros((128,), device=cuda)
+    d = ops.conv_desc(1, 8, 8, 3, 160, 3, 3)
+    fb = torch.zeros((9, 3, 5), dtype=torch.int32, device=cuda)
+    thr = torch.zeros((160,), device=cuda)
     with pytest.raises(TcbnnError):
         ops.inconv_specialize(d, fb, thr)
     d = ops.conv_desc(1, 8, 8, 3, 32, 3, 3)
