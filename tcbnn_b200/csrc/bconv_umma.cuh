@@ -17,6 +17,10 @@
 // filter tap (r, s) is nothing but a start-address offset of ((r*PW + s) * 16) bytes, so the
 // nine taps reuse one expanded patch.  Positions that fall on the zero bands produce junk
 // rows that are simply not stored.
+//
+// This header holds the PTX wrappers, descriptors and bit -> byte expansion shared by the kernels:
+// bconv_umma_ws.cuh (filter-stationary), bconv_umma_as.cuh (activation-stationary),
+// bconv_umma_pre.cuh (fed from a pre-expanded input), bgemm_umma.cuh (bit GEMM).
 #pragma once
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -189,270 +193,6 @@ __device__ __forceinline__ int4 ld_res4(const void* p, int bytes, size_t i) {
 }
 __device__ __forceinline__ int4 max4(int4 a, int4 b) {
     return make_int4(max(a.x, b.x), max(a.y, b.y), max(a.z, b.z), max(a.w, b.w));
-}
-
-// ---- filter preparation -------------------------------------------------------------------
-// bits [O][R*S][Cw] -> int8 blocks [n-tile][tap][chunk][n in tile][16 bytes], the order the
-// kernel keeps them in shared memory.
-__device__ __forceinline__ void prepare_filter_i8(const uint32_t* fbits, int O, int RS, int C,
-                                                  int n_tile, uint4* out) {
-    const int Cw = (C + 31) >> 5, chunks = C >> 4;
-    const long long total = (long long)O * RS * chunks;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
-        const int n = (int)(i % n_tile);
-        long long r = i / n_tile;
-        const int chunk = (int)(r % chunks); r /= chunks;
-        const int tap = (int)(r % RS);
-        const int nt = (int)(r / RS);
-        const int o = nt * n_tile + n;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (o < O) {
-            const uint32_t w = fbits[((size_t)o * RS + tap) * Cw + (chunk >> 1)];
-            v = expand16((chunk & 1) ? (w & 0xFFFFu) : (w >> 16));
-        }
-        out[i] = v;
-    }
-}
-
-struct ConvUmmaArgs {
-    const uint32_t* in;      // [B][H][W][Cw]
-    const uint4* wi8;        // prepared int8 filter blocks
-    const float* thr;        // [O]
-    int B, H, W, C, O, R, S, pad_h, pad_w;
-    int PW, VH;              // raster pitch / rows per image
-    int NPOS;                // patch positions held in shared memory (multiple of 8)
-    long long NV;            // raster positions over the batch
-    const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
-    uint32_t* out; long long out_image_stride;
-    void* res_out; int res_out_bytes; int32_t* acc_out;
-    int* err_flag;           // 1: a bounded wait gave up, 2: a residual did not fit int16
-};
-
-// One CTA of 128 threads; stride-1 conv, no pooling.  Phases per tile: expand the patch,
-// issue the MMAs (one thread), read the accumulators back and run the epilogue.  Overlap
-// between phases comes from co-resident CTAs.
-template <int C, int NT>
-__device__ void conv_umma_cta(const ConvUmmaArgs& a, unsigned char* smem) {
-    constexpr int CH = C / 16;                 // 16-channel chunks
-    constexpr int KS = C / 32;                 // MMA k-steps per tap
-    constexpr uint32_t TM_COLS = NT < 32 ? 32 : NT;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int RS = a.R * a.S;
-    const int ntiles_n = (a.O + NT - 1) / NT;
-
-    // shared memory carve-up: [A patch | residual staging tile][B filter][thresholds]
-    // [row -> output pixel][barrier][tmem ptr].  The staging tile (int32 [128][NT+4]) reuses
-    // the patch, which is dead once the tile's MMAs have completed.
-    constexpr int PITCH = NT + 4;
-    const size_t a_bytes = (size_t)CH * a.NPOS * 16, r_bytes = (size_t)128 * PITCH * 4;
-    uint4* sA = reinterpret_cast<uint4*>(smem);
-    int* sR = reinterpret_cast<int*>(smem);
-    uint4* sB = reinterpret_cast<uint4*>(smem + (a_bytes > r_bytes ? a_bytes : r_bytes));
-    float* sThr = reinterpret_cast<float*>(sB + (size_t)RS * CH * NT);
-    int* sRow = reinterpret_cast<int*>(sThr + NT);
-    uint64_t* sBar = reinterpret_cast<uint64_t*>(sRow + 128);
-    uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 1);
-
-    if (warp == 0) tmem_alloc(smem_u32(sTmem), TM_COLS);
-    if (tid == 0) mbar_init(smem_u32(sBar), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *sTmem;
-    uint32_t phase = 0;
-    bool ok = true;
-
-    const long long mtiles = (a.NV + 127) / 128;
-    const long long total = mtiles * ntiles_n;
-    int cur_nt = -1;
-    for (long long task = blockIdx.x; task < total && ok; task += gridDim.x) {
-        // n-tile major order so a CTA keeps its filter block as long as possible
-        const int nt = (int)(task / mtiles);
-        const long long mt = task - (long long)nt * mtiles;
-        if (nt != cur_nt) {
-            const uint4* src = a.wi8 + (size_t)nt * RS * CH * NT;
-            for (int i = tid; i < RS * CH * NT; i += 128) sB[i] = __ldg(src + i);
-            for (int i = tid; i < NT; i += 128) {
-                const int o = nt * NT + i;
-                sThr[i] = o < a.O ? __ldg(a.thr + o) : 0.0f;
-            }
-            cur_nt = nt;
-        }
-        // ---- expand the patch -----------------------------------------------------------
-        const long long p0 = mt * 128;
-        const long long q0 = p0 - (long long)a.pad_h * a.PW - a.pad_w;
-        for (int q = tid; q < a.NPOS; q += 128) {
-            const long long gq = q0 + q;
-            const uint32_t* px = nullptr;
-            if (gq >= 0 && gq < a.NV) {
-                const long long vy = gq / a.PW;
-                const int vx = (int)(gq - vy * a.PW);
-                const int n = (int)(vy / a.VH);
-                const int y = (int)(vy - (long long)n * a.VH);
-                if (vx < a.W && y < a.H)
-                    px = a.in + (((size_t)n * a.H + y) * a.W + vx) * (C / 32);
-            }
-#pragma unroll
-            for (int w = 0; w < C / 32; w++) {
-                if (px) {
-                    const uint32_t bits = __ldg(px + w);
-                    sA[(size_t)(2 * w) * a.NPOS + q] = expand16(bits >> 16);
-                    sA[(size_t)(2 * w + 1) * a.NPOS + q] = expand16(bits & 0xFFFFu);
-                } else {
-                    sA[(size_t)(2 * w) * a.NPOS + q] = make_uint4(0u, 0u, 0u, 0u);
-                    sA[(size_t)(2 * w + 1) * a.NPOS + q] = make_uint4(0u, 0u, 0u, 0u);
-                }
-            }
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();
-        // ---- MMAs: one thread ----------------------------------------------------------------
-        if (tid == 0) {
-            tc_fence_after();
-            const uint32_t aBase = smem_u32(sA), bBase = smem_u32(sB);
-            const uint32_t lboA = (uint32_t)a.NPOS * 16u, lboB = NT * 16u;
-            uint32_t acc = 0;
-            for (int r = 0; r < a.R; r++)
-                for (int s = 0; s < a.S; s++) {
-                    const uint32_t tapA = aBase + (uint32_t)(r * a.PW + s) * 16u;
-                    const uint32_t tapB = bBase + (uint32_t)((r * a.S + s) * CH) * NT * 16u;
-#pragma unroll
-                    for (int ks = 0; ks < KS; ks++) {
-                        mma_i8(tmem, smem_desc(tapA + 2 * ks * lboA, lboA, 128u),
-                               smem_desc(tapB + 2 * ks * lboB, lboB, 128u), idesc_i8(NT), acc);
-                        acc = 1;
-                    }
-                }
-            mma_commit(smem_u32(sBar));
-        }
-        ok = mbar_wait(smem_u32(sBar), phase, a.err_flag);
-        ok = __syncthreads_and(ok ? 1 : 0) != 0;      // all threads agree before going on
-        phase ^= 1;
-        tc_fence_after();
-        // ---- epilogue: thread <-> raster position p0 + tid ---------------------------------------
-        const long long p = p0 + tid;
-        bool live = false;
-        int n = 0, y = 0, x = 0;
-        if (p < a.NV) {
-            const long long vy = p / a.PW;
-            x = (int)(p - vy * a.PW);
-            n = (int)(vy / a.VH);
-            y = (int)(vy - (long long)n * a.VH);
-            live = x < a.W && y < a.H;
-        }
-        const size_t opix = ((size_t)n * a.H + y) * a.W + x;
-        const int Ow = (a.O + 31) >> 5;
-        const int obase = nt * NT;
-        sRow[tid] = live ? (int)opix : -1;
-        __syncthreads();                       // patch is dead (MMAs done), row table visible
-        constexpr int UPR = NT / 4;            // 4-channel units per staged row
-        constexpr int UNROLL = 8;
-        if (ok && a.res_in) {
-            // residual tile -> shared memory: consecutive threads take consecutive 4-channel
-            // units (whole rows are contiguous in memory), UNROLL independent loads in flight
-            const int lim = min(a.residual_channels, a.res_in_ch);
-            for (int u0 = tid; u0 < 128 * UPR; u0 += 128 * UNROLL) {
-                int4 val[UNROLL];
-#pragma unroll
-                for (int k = 0; k < UNROLL; k++) {
-                    const int u = u0 + k * 128;
-                    val[k] = make_int4(0, 0, 0, 0);
-                    if (u < 128 * UPR) {
-                        const int r = u / UPR, o = obase + (u % UPR) * 4;
-                        const int op = sRow[r];
-                        if (op >= 0 && o < lim) {
-                            if (a.residual_pool) {      // max over the 2x2 window (kernel.cuh:773-783)
-                                const int px = op % a.W, t2 = op / a.W, py = t2 % a.H, pn = t2 / a.H;
-                                const size_t b00 = (((size_t)pn * 2 * a.H + 2 * py) * 2 * a.W + 2 * px) *
-                                                   a.res_in_ch + o;
-                                const size_t rowp = (size_t)2 * a.W * a.res_in_ch;
-                                val[k] = max4(max4(ld_res4(a.res_in, a.res_in_bytes, b00),
-                                                   ld_res4(a.res_in, a.res_in_bytes, b00 + a.res_in_ch)),
-                                              max4(ld_res4(a.res_in, a.res_in_bytes, b00 + rowp),
-                                                   ld_res4(a.res_in, a.res_in_bytes, b00 + rowp + a.res_in_ch)));
-                            } else {
-                                val[k] = ld_res4(a.res_in, a.res_in_bytes, (size_t)op * a.res_in_ch + o);
-                            }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < UNROLL; k++) {
-                    const int u = u0 + k * 128;
-                    if (u < 128 * UPR)
-                        *reinterpret_cast<int4*>(sR + (u / UPR) * PITCH + (u % UPR) * 4) = val[k];
-                }
-            }
-            __syncthreads();
-        }
-        if (ok) {
-            uint32_t words[NT / 32];
-#pragma unroll
-            for (int nb = 0; nb < NT / 32; nb++) {
-                int v[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + nb * 32, v);
-                tmem_ld_wait();
-                const int o0 = obase + nb * 32;
-                int4* srow = reinterpret_cast<int4*>(sR + tid * PITCH + nb * 32);
-                if (live && a.acc_out) {
-                    int4* dst = reinterpret_cast<int4*>(a.acc_out + opix * a.O + o0);
-#pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                }
-                if (a.res_in) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int4 rr = srow[j];
-                        v[4 * j] += rr.x; v[4 * j + 1] += rr.y; v[4 * j + 2] += rr.z; v[4 * j + 3] += rr.w;
-                    }
-                }
-                uint32_t word = 0;
-#pragma unroll
-                for (int j = 0; j < 32; j++)
-                    if (!((float)v[j] < sThr[nb * 32 + j])) word |= 0x80000000u >> j;
-                words[nb] = word;
-                if (a.res_out) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        srow[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                }
-            }
-            if (live) {
-                uint32_t* dst = a.out + (size_t)n * a.out_image_stride +
-                                ((size_t)y * a.W + x) * Ow + (obase >> 5);
-#pragma unroll
-                for (int nb = 0; nb < NT / 32; nb++) dst[nb] = words[nb];
-            }
-            if (a.res_out) {
-                __syncthreads();
-                bool overflow = false;
-                for (int u = tid; u < 128 * UPR; u += 128) {
-                    const int r = u / UPR, c4 = (u % UPR) * 4;
-                    const int op = sRow[r];
-                    if (op < 0) continue;
-                    const int4 v4 = *reinterpret_cast<const int4*>(sR + r * PITCH + c4);
-                    const size_t idx = (size_t)op * a.O + obase + c4;
-                    if (a.res_out_bytes == 2) {
-                        overflow |= max(max(abs(v4.x), abs(v4.y)), max(abs(v4.z), abs(v4.w))) > 32767;
-                        *reinterpret_cast<uint2*>(reinterpret_cast<short*>(a.res_out) + idx) =
-                            make_uint2(((uint32_t)v4.x & 0xFFFFu) | ((uint32_t)v4.y << 16),
-                                       ((uint32_t)v4.z & 0xFFFFu) | ((uint32_t)v4.w << 16));
-                    } else {
-                        *reinterpret_cast<int4*>(reinterpret_cast<int*>(a.res_out) + idx) = v4;
-                    }
-                }
-                if (overflow) atomicExch(a.err_flag, 2);
-            }
-        }
-        tc_fence_before();
-        __syncthreads();       // accumulators and patch are free again
-    }
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, TM_COLS);
 }
 
 }  // namespace umma

@@ -1,8 +1,8 @@
 // Warp-specialised, persistent tcgen05 binary convolution (stride 1 and stride 2).
 //
-// Same arithmetic and the same raster trick as bconv_umma.cuh (read that header first): packed
-// bits -> +-1 bytes in the no-swizzle K-major core-matrix layout, taps as start-address offsets,
-// int8 x int8 -> int32 in tensor memory.  What changes is the schedule.  One CTA per SM runs
+// Arithmetic and raster trick: see bconv_umma.cuh (read that header first).  Packed bits become
+// +-1 bytes in the no-swizzle K-major core-matrix layout, taps are start-address offsets,
+// int8 x int8 -> int32 accumulates in tensor memory.  One CTA per SM runs
 //
 //   warps 0-7   epilogue   : prefetch the residual rows, wait for an accumulator, tcgen05.ld,
 //                            add / threshold / pack, store bits and the new residual
