@@ -41,7 +41,7 @@ int tcbnn_pack_conv_filter(const float* F, int RS, int C, int O, uint32_t* out, 
 int tcbnn_pack_inconv_filter(const float* F, int RS, int O, uint32_t* out, void* stream);
 
 /* Scratch a GEMM-family call can use: partial sums to split K when M x N alone leaves SMs idle
- * and, for large problems (M >= 128, N >= 64, K >= 1024, M*N*K >= 2^31), both operands written
+ * and, for large problems (M >= 128, N >= 64, K >= 2048, M*N*K >= 2^31), both operands written
  * out as +-1 bytes for the tcgen05 int8 kernel (csrc/bgemm_umma.cuh), which is then used.
  * Passing NULL / 0 is always allowed (warp-level b1 MMA kernel, no split); the buffer must be
  * 256-byte aligned for the tcgen05 kernel to be taken. */
