@@ -231,6 +231,7 @@ struct PreparedLayout {
     int KP;               // 64-bit pairs per filter row, multiple of 4
     size_t off_wq, off_ktab, off_pwt, off_pwtot, off_err, off_wi8, bytes;
     int umma_nt;          // n-tile of the tcgen05 path, 0 when the layer is not eligible
+    bool ws_ok;           // the filter-stationary kernel with in-CTA expansion can take the layer
     int umma_npos;        // raster positions of the shared-memory patch (per plane)
     size_t umma_smem;     // dynamic shared memory of the tcgen05 kernel
     int umma_pw, umma_vh, umma_back_y, umma_back_x;   // raster geometry
@@ -280,7 +281,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     L.off_err = o;   o += 256;
     // tcgen05 path: stride 1 or 2, "same" padding, no pooling, channels in blocks of 64,
     // filter block of one n-tile resident in shared memory
-    L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o;
+    L.umma_nt = 0; L.umma_npos = 0; L.umma_smem = 0; L.off_wi8 = o; L.ws_ok = false;
     L.umma_pw = L.umma_vh = L.umma_back_y = L.umma_back_x = 0;
     L.as_npos = 0; L.as_smem = 0; L.as_slots = 0; L.off_wi8_as = o;
     L.pre_bytes = 0; L.pre_smem = 0; L.pre_stages = 0; L.pool_bytes = 0; L.pre_positions = 0; L.pre_front = 0;
@@ -311,6 +312,19 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
                 L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
                 o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
                 break;
+            }
+            L.ws_ok = L.umma_nt != 0;
+            if (!L.umma_nt && st == 1 && d->C <= 128 && (npos * 16) < (1 << 18)) {
+                // images too wide for the in-CTA expansion (its patch is limited by the expander
+                // threads): the loader-fed kernel alone can still take the layer
+                for (int nt = 128; nt >= 32; nt >>= 1) {
+                    if (d->O % nt) continue;
+                    if (umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, 2) > 227 * 1024) continue;
+                    L.umma_nt = nt; L.umma_npos = npos;
+                    L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
+                    o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
+                    break;
+                }
             }
             if (L.umma_nt && st == 1 && d->C <= 128 && L.umma_nt <= 128) {
                 int stages = L.umma_nt >= 128 ? 3 : umma::kPreMaxStages;
@@ -902,7 +916,9 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
     const PreparedLayout L = prepared_layout(d);
     const char* p = (const char*)prepared;
     const bool use_as = L.as_npos && g_conv_path != 3;
-    if (g_conv_path >= 2 && !L.umma_nt && !use_as) return fail("conv_layer: layer is not eligible for the tcgen05 path");
+    const bool use_pre = L.pre_bytes && workspace && g_conv_path != 3;
+    const bool have_tc = use_as || use_pre || L.ws_ok;
+    if (g_conv_path >= 2 && !have_tc) return fail("conv_layer: layer is not eligible for the tcgen05 path (or needs its workspace)");
     // the tcgen05 epilogue moves residuals in 4-channel vectors
     const bool res_vec_ok = !res_in || (res_in_ch % 4 == 0 && residual_channels % 4 == 0 &&
                                         ((uintptr_t)res_in & 15) == 0);
@@ -913,7 +929,7 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
     const bool pooled_ok = !pooled || (workspace && workspace_bytes >= main_ws + L.prepool_bytes &&
                                        ((uintptr_t)workspace & 255) == 0);
     if (g_conv_path >= 2 && !pooled_ok) return fail("conv_layer: a pooled layer needs its workspace for the tcgen05 path");
-    if ((L.umma_nt || use_as) && g_conv_path != 1 && res_vec_ok && pooled_ok &&
+    if (have_tc && g_conv_path != 1 && res_vec_ok && pooled_ok &&
         (!res_out || ((uintptr_t)res_out & 15) == 0)) {
       const int P = d->OH * d->pool, Q = d->OW * d->pool;
       uint32_t* prepool = pooled ? (uint32_t*)((char*)workspace + main_ws) : nullptr;
@@ -963,7 +979,7 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
             }
             return launch_conv_umma_as(a, L.as_smem, sms, st);
         }
-        if (L.pre_bytes && workspace && g_conv_path != 3) {
+        if (use_pre) {
             if (workspace_bytes < L.pre_bytes)
                 return fail("conv_layer: workspace of %zu bytes, the layer needs %zu", workspace_bytes, L.pre_bytes);
             if ((uintptr_t)workspace & 255) return fail("conv_layer: workspace must be 256-byte aligned");

@@ -41,7 +41,10 @@ def _time(fn, iters, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="c2", choices=["c1", "c2", "conv", "stem"])
+    ap.add_argument("--case", default="c2", choices=["c1", "c2", "conv", "stem", "net"])
+    ap.add_argument("--net", default="vgg_cifar",
+                    choices=["mlp", "vgg_cifar", "resnet_cifar", "alexnet", "vgg16_imagenet", "resnet18"],
+                    help="net: which reference driver's topology (C3 = mlp at batch 8192, C4 = vgg_cifar at 1024)")
     ap.add_argument("--hw", type=int, default=56)
     ap.add_argument("--cin", type=int, default=64)
     ap.add_argument("--cout", type=int, default=64)
@@ -53,6 +56,32 @@ def main():
     ap.add_argument("--specialized", action="store_true", help="stem: the kernel compiled for the filter")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
+    if a.case == "net":
+        import numpy as np
+        from . import models
+        spec = getattr(models, a.net + "_spec")(a.batch)
+        net = models.Network(spec, models.synthetic_weights(spec, 1),
+                             torch.from_numpy(np.ascontiguousarray(models.synthetic_input(spec, 2))),
+                             input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND if "resnet" in a.net else None)
+        for _ in range(3):
+            net.forward()
+        torch.cuda.synchronize()
+        ev = []
+        for _ in range(a.iters):
+            for l in net.layers:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                l.forward()
+                e1.record()
+                ev.append((l.name, e0, e1))
+        torch.cuda.synchronize()
+        per = {}
+        for n, e0, e1 in ev:
+            per[n] = per.get(n, 0.0) + e0.elapsed_time(e1) / a.iters
+        ms = sum(per.values())
+        print(json.dumps({"case": "net", "net": a.net, "batch": a.batch, "ms": ms,
+                          "images_per_s": a.batch / (ms * 1e-3), "layer_ms": {k: round(v, 4) for k, v in per.items()}}))
+        return
     if a.case == "c1":
         M = N = 1024
         K = 4096

@@ -13,6 +13,8 @@ Topologies follow the reference drivers, not the textbook networks:
   * vgg_cifar  : cifar10_vgg.cu:162-199 -- conv 3->128, 128->128+pool, ->256, 256+pool, ->512,
                  512+pool (feeds FC), FC 8192->1024->1024, out ->10.
   * mlp        : mnist_mlp.cu:112-126 -- 784 -> 1024 -> 1024 -> 1024 -> 10.
+  * alexnet, vgg16_imagenet : alexnet.cu:141-178, imagenet_vgg.cu:217-280 (11x11 / 5x5 filters,
+                 192 / 384 channels, pooled layers at 224 x 224).
 """
 import numpy as np
 
@@ -86,6 +88,33 @@ def vgg_cifar_spec(batch, image=32, classes=10):
     L += [dict(type="fc", name="Fc1", N=1024), dict(type="fc", name="Fc2", N=1024),
           dict(type="out", name="Fout", N=classes)]
     return dict(name="vgg_cifar", batch=batch, layers=L)
+
+
+def alexnet_spec(batch, image=224, hidden=4096, classes=1000):
+    """alexnet.cu:141-178 -- 11x11/4 first layer with 2x2 pool (64 channels), 5x5 64->192 with
+    pool, 3x3 192->384, 384->256, 256->256 with pool (feeds FC), FC -> hidden -> hidden -> out."""
+    L = [dict(type="inconv", name="Conv1", H=image, W=image, R=11, S=11, C=3, O=64, stride=4, pool=2),
+         dict(type="conv", name="Conv2", C=64, O=192, R=5, S=5, stride=1, pool=2),
+         dict(type="conv", name="Conv3", C=192, O=384, R=3, S=3, stride=1, pool=1),
+         dict(type="conv", name="Conv4", C=384, O=256, R=3, S=3, stride=1, pool=1),
+         dict(type="conv", name="Conv5", C=256, O=256, R=3, S=3, stride=1, pool=2, ahead_fc=True),
+         dict(type="fc", name="Fc1", N=hidden), dict(type="fc", name="Fc2", N=hidden),
+         dict(type="out", name="Fout", N=classes)]
+    return dict(name="alexnet", batch=batch, layers=L)
+
+
+def vgg16_imagenet_spec(batch, image=224, hidden=4096, classes=1000):
+    """imagenet_vgg.cu:217-280 -- thirteen 3x3 layers (64, 64+pool, 128, 128+pool, 256, 256,
+    256+pool, 512, 512, 512+pool, 512, 512, 512+pool feeding FC), FC -> hidden -> hidden -> out."""
+    L = [dict(type="inconv", name="Conv1", H=image, W=image, R=3, S=3, C=3, O=64, stride=1, pool=1)]
+    cfg = [(64, 64, 2), (64, 128, 1), (128, 128, 2), (128, 256, 1), (256, 256, 1), (256, 256, 2),
+           (256, 512, 1), (512, 512, 1), (512, 512, 2), (512, 512, 1), (512, 512, 1), (512, 512, 2)]
+    for i, (C, O, pool) in enumerate(cfg):
+        L.append(dict(type="conv", name="Conv%d" % (i + 2), C=C, O=O, R=3, S=3, stride=1, pool=pool,
+                      ahead_fc=(i == len(cfg) - 1)))
+    L += [dict(type="fc", name="Fc1", N=hidden), dict(type="fc", name="Fc2", N=hidden),
+          dict(type="out", name="Fout", N=classes)]
+    return dict(name="vgg16_imagenet", batch=batch, layers=L)
 
 
 def mlp_spec(batch, features=784, hidden=1024, classes=10):

@@ -318,6 +318,7 @@ UMMA_CASES = [
     (3, 9, 9, 256, 128, 5, None),           # 5x5 filter, one n-tile
     (2, 14, 14, 384, 256, 3, "pool"),       # 6 channel blocks
     (1, 3, 3, 256, 128, 3, None),           # a single partial task
+    (1, 40, 200, 64, 64, 3, "plain"),       # rows too wide for the in-CTA expansion: loader-fed kernel only
 ]
 
 
@@ -345,7 +346,8 @@ def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
     prep = ops.conv_prepare(d, dev(f, cuda))
     try:
         # 5x5 filters over 256 channels do not fit the filter-stationary kernel's shared memory
-        for path in ((2, 1) if (R == 5 and C >= 256) else (2, 3, 1)):
+        # ... and 200-pixel rows do not fit its patch
+        for path in ((2, 1) if ((R == 5 and C >= 256) or W >= 160) else (2, 3, 1)):
             ops.set_conv_path(path)
             go, gr, ga = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda),
                                         res_in=dev(res_in, cuda) if res_in is not None else None,
@@ -437,6 +439,7 @@ POOLED_UMMA_CASES = [
     (3, 8, 8, 256, 256, 1),        # activation-stationary kernel
     (2, 16, 12, 64, 128, 2),       # stride-2 filter-stationary kernel
     (5, 6, 10, 64, 64, 1),
+    (1, 24, 224, 64, 64, 1),       # VGG-16's second layer: 224-pixel rows, loader-fed kernel only
 ]
 
 
@@ -451,7 +454,7 @@ def test_pooled_conv_layer_on_tcgen05_matches_oracle(cuda, case):
     d = ops.conv_desc(B, H, W, C, O, 3, 3, st, st, True, 2)
     prep = ops.conv_prepare(d, dev(f, cuda))
     try:
-        for path in (2, 3, 1, 0):
+        for path in ((2, 1, 0) if W >= 160 else (2, 3, 1, 0)):
             ops.set_conv_path(path)
             go, _, ga = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), want_acc=True)
             assert ops.conv_status(d, prep) == 0

@@ -43,6 +43,16 @@ def test_vgg_cifar(cuda):
     _compare(models.vgg_cifar_spec(8), 10, cuda)
 
 
+def test_alexnet_small_image(cuda):
+    # alexnet.cu topology (11x11/4 + pool, 5x5 + pool, 192 / 384 channels) on 96x96 images
+    _compare(models.alexnet_spec(4, image=96, hidden=256, classes=100), 40, cuda)
+
+
+def test_vgg16_imagenet_small_image(cuda):
+    # imagenet_vgg.cu topology (13 conv layers, five of them pooled) on 32x32 images
+    _compare(models.vgg16_imagenet_spec(3, image=32, hidden=256, classes=100), 50, cuda)
+
+
 def test_resnet18_small_image(cuda):
     # same topology, 64x64 input -> 16x16 ... 2x2 feature maps
     _compare(models.resnet18_spec(8, image=64, classes=100), 20, cuda)
