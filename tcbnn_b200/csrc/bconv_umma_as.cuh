@@ -24,7 +24,7 @@ namespace tcbnn {
 namespace umma {
 
 constexpr int kAsNT = 128;                 // output channels per filter unit / accumulator
-constexpr int kAsMaxSlots = 18;            // filter ring: 9 or 18 units (whole 3x3 tap groups)
+constexpr int kAsMaxSlots = 18;            // filter ring: 6, 9 or 18 units (whole rows of a 3x3 filter)
 constexpr int kAsUnitBytes = kAsNT * 64;   // 128 out x 64 in x 1 tap, int8
 constexpr int kAsEpiThreads = 256;
 constexpr int kAsExpThreads = 192;

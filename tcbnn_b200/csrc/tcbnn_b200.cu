@@ -342,6 +342,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
             const int npos_as = (256 + (back_y + fwd_y) * PW + back_x + fwd_x + 7) & ~7;
             int slots_as = umma::kAsMaxSlots;
             if (umma::as_smem_bytes(npos_as, d->C, d->O, d->R * d->S, slots_as) > 227 * 1024) slots_as = 9;
+            if (umma::as_smem_bytes(npos_as, d->C, d->O, d->R * d->S, slots_as) > 227 * 1024) slots_as = 6;
             const size_t smem_as = umma::as_smem_bytes(npos_as, d->C, d->O, d->R * d->S, slots_as);
             // (at 128 channels the filter-stationary kernel is as fast: measured)
             if (st == 1 && d->C >= 256 && d->C <= 512 && d->O % umma::kAsNT == 0 &&

@@ -318,6 +318,7 @@ UMMA_CASES = [
     (3, 9, 9, 256, 128, 5, None),           # 5x5 filter, one n-tile
     (2, 14, 14, 384, 256, 3, "pool"),       # 6 channel blocks
     (1, 3, 3, 256, 128, 3, None),           # a single partial task
+    (2, 28, 28, 512, 128, 3, None),         # 512 channels at 28 x 28: patch leaves room for a 2-group filter ring only
     (1, 40, 200, 64, 64, 3, "plain"),       # rows too wide for the in-CTA expansion: loader-fed kernel only
 ]
 
