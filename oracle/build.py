@@ -60,6 +60,39 @@ def build_ref(ref_root="/root/reference"):
     return out
 
 
+REF_DRIVERS = ["mnist_mlp", "cifar10_vgg", "cifar10_resnet", "imagenet_resnet"]
+
+
+def build_ref_drivers(ref_root="/root/reference"):
+    """The reference's unchanged drivers with the reference's own headers (WMMA b1 kernels) for
+    sm_100a: _ref/ref_<driver>.  Compiled from the sources where they lie (nothing is copied);
+    only the dataset readers are replaced (seeded synthetic images, the drop-in's
+    synthetic_data.cpp, libjpeg stubbed) and ref_driver_shim.h is force-included so that the
+    drivers print the time they measure.  Flags as the reference Makefile (:15)."""
+    if not os.path.exists(os.path.join(ref_root, "kernel.cuh")):
+        return []
+    outdir = os.path.join(HERE, "_ref")
+    os.makedirs(outdir, exist_ok=True)
+    dropin = os.path.join(os.path.dirname(HERE), "tcbnn_b200", "dropin")
+    data_src = os.path.join(dropin, "synthetic_data.cpp")
+    shim = os.path.join(HERE, "ref_driver_shim.h")
+    from concurrent.futures import ThreadPoolExecutor
+
+    def one(name):
+        src = os.path.join(ref_root, name + ".cu")
+        if not os.path.exists(src):
+            return None
+        out = os.path.join(outdir, "ref_" + name)
+        if _stale(out, [src, data_src, shim, os.path.join(ref_root, "kernel.cuh"), os.path.join(ref_root, "param.h")]):
+            _run(["nvcc", "-std=c++14", "-O3", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
+                  "-maxrregcount=64", "-rdc=true", "-include", shim, "-I", ref_root,
+                  "-I", os.path.join(dropin, "stubs"), "-o", out, src, data_src])
+        return out
+
+    with ThreadPoolExecutor(max_workers=len(REF_DRIVERS)) as pool:
+        return [b for b in pool.map(one, REF_DRIVERS) if b]
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--native", action="store_true")
@@ -69,3 +102,5 @@ if __name__ == "__main__":
     if a.native:
         print(build_oracle(True))
     print(build_ref(a.ref_root))
+    for b in build_ref_drivers(a.ref_root):
+        print(b)
