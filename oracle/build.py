@@ -93,6 +93,29 @@ def build_ref_drivers(ref_root="/root/reference"):
         return [b for b in pool.map(one, REF_DRIVERS) if b]
 
 
+def build_ref_runner(ref_root="/root/reference"):
+    """tcbnn_b200/dropin/net_runner.cu (this repository's generic driver on the reference's public
+    API: network from a text description, one cooperative kernel, logits and every layer's
+    download_full_output() to files) compiled against the REFERENCE's own utility.h / param.h /
+    kernel.cuh: _ref/ref_net_runner, the layer-by-layer pin of the oracle.  The runner source is
+    staged next to the binary so that its quote-includes resolve to the reference's headers."""
+    if not os.path.exists(os.path.join(ref_root, "kernel.cuh")):
+        return None
+    import shutil
+    outdir = os.path.join(HERE, "_ref")
+    os.makedirs(outdir, exist_ok=True)
+    src = os.path.join(os.path.dirname(HERE), "tcbnn_b200", "dropin", "net_runner.cu")
+    staged = os.path.join(outdir, "ref_net_runner.cu")
+    out = os.path.join(outdir, "ref_net_runner")
+    if _stale(out, [src, os.path.join(ref_root, "kernel.cuh"), os.path.join(ref_root, "param.h"),
+                    os.path.join(HERE, "ref_driver_shim.h")]):
+        shutil.copyfile(src, staged)
+        _run(["nvcc", "-std=c++14", "-O3", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
+              "-maxrregcount=64", "-rdc=true", "-include", os.path.join(HERE, "ref_driver_shim.h"),
+              "-I", ref_root, "-o", out, staged])
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--native", action="store_true")
@@ -104,3 +127,4 @@ if __name__ == "__main__":
     print(build_ref(a.ref_root))
     for b in build_ref_drivers(a.ref_root):
         print(b)
+    print(build_ref_runner(a.ref_root))

@@ -13,6 +13,7 @@
 //   out N
 // weights.txt : whitespace-separated floats in launch_array order (utility.h).
 // input.bin   : fp32, [B][K] for "in" networks, NCHW [B][3][H][W] otherwise.
+#include <cooperative_groups.h>
 #include <vector>
 #include <string>
 #include "utility.h"

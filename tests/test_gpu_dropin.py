@@ -31,8 +31,10 @@ def _unpacked(act, layer):
     return orc.unpack_rows(np.ascontiguousarray(bits), O)
 
 
-def _run(spec, seed, tmp_path, cuda):
-    runner = dbuild.build_runner()
+def _run(spec, seed, tmp_path, cuda, runner=None):
+    """runner: the binary to run; default the generic driver built on the drop-in headers (the
+    reference-header build of the same driver is tests/test_gpu_reference_kernels.py's)."""
+    runner = runner or dbuild.build_runner()
     w = models.synthetic_weights(spec, seed)
     x = models.synthetic_input(spec, seed + 1)
     d = str(tmp_path)

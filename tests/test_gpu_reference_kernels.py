@@ -55,34 +55,53 @@ def test_reference_bitgemm_kernels_match_and_time(cuda):
 def test_reference_network_drivers_same_box(cuda, tmp_path):
     """The reference's unchanged drivers built with the reference's OWN headers (its WMMA b1
     kernels in one cooperative launch) for sm_100a into oracle/_ref/ref_<driver>, run once each on
-    synthetic weight files and images.  They must finish without a CUDA error; the time each
-    driver measures around its forward launch (one cold launch, utility.h:161-173) is printed next
-    to this repository's time for the same topology and batch (run with -s)."""
+    synthetic weight files and the stand-in readers' images.
+
+    Parity: the logits the reference computes (its output layer's download_output(), captured by
+    oracle/ref_driver_shim.h) against this library's on the same weights and the same images --
+    the network-level pin of every layer epilogue on the way (threshold, OR-pool, residual add /
+    2x2 max, first-layer sums, FC, scale + bias).  A subset of images also goes through the CPU
+    oracle.  Timing: what each driver measures around its forward launch (one cold launch,
+    utility.h:161-173) next to this library's time (run with -s)."""
     import os
     import re
     import subprocess
+    import networks as onet
     from tcbnn_b200 import dropin, models
     ref = os.path.join(os.path.dirname(os.path.abspath(orc.__file__)), "_ref")
-    cases = [("mnist_mlp", "mlp_mnist.csv", models.mlp_spec(32768)),
-             ("cifar10_vgg", "vgg_cifar10.csv", models.vgg_cifar_spec(512)),
-             ("cifar10_resnet", "resnet_cifar10.csv", models.resnet_cifar_spec(512)),
-             ("imagenet_resnet", "resnet_imagenet.csv", models.resnet18_spec(512))]
+    cases = [("mnist_mlp", "mlp_mnist.csv", models.mlp_spec(32768), "mnist"),
+             ("cifar10_vgg", "vgg_cifar10.csv", models.vgg_cifar_spec(512), "cifar"),
+             ("cifar10_resnet", "resnet_cifar10.csv", models.resnet_cifar_spec(512), "cifar"),
+             ("imagenet_resnet", "resnet_imagenet.csv", models.resnet18_spec(512), "imagenet")]
     res = {}
-    for exe, csv, spec in cases:
+    for exe, csv, spec, kind in cases:
         path = os.path.join(ref, "ref_" + exe)
         if not os.path.exists(path):
             continue
         w = models.synthetic_weights(spec, 5)
         dropin.write_weights(w, os.path.join(str(tmp_path), csv))
-        r = subprocess.run([path], cwd=str(tmp_path), capture_output=True, text=True, timeout=600)
+        dump = os.path.join(str(tmp_path), exe + "_logits.bin")
+        r = subprocess.run([path], cwd=str(tmp_path), capture_output=True, text=True, timeout=600,
+                           env=dict(os.environ, TCBNN_REF_DUMP=dump))
         assert r.returncode == 0, exe + ": " + r.stdout[-1500:] + r.stderr[-1500:]
         m = re.search(r"TCBNN_REF_INFERENCE_MS ([0-9.]+) (.*)", r.stdout)
         assert m, exe + ": no timing line\n" + r.stdout[-1500:]
         assert m.group(2).strip() == "no error", exe + ": " + m.group(2)
         ref_ms = float(m.group(1))
-        x = models.synthetic_input(spec, 6)
-        net = models.Network(spec, w, torch.from_numpy(np.ascontiguousarray(x)),
-                             input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND if "resnet" in exe else None)
+        B = spec["batch"]
+        classes = spec["layers"][-1]["N"]
+        ref_logits = np.fromfile(dump, dtype=np.float32)
+        assert ref_logits.size >= B * classes, (exe, ref_logits.size)
+        ref_logits = ref_logits[:B * classes].reshape(B, classes)
+        x = util.reader_images(kind, B)
+        bound = float(np.abs(x).max()) if "resnet" in exe else None   # int16 residual rows when it fits
+        net = models.Network(spec, w, torch.from_numpy(np.ascontiguousarray(x)).to(cuda), input_abs_bound=bound)
+        ours = net.forward().cpu().numpy()[:, :classes]
+        np.testing.assert_allclose(ours, ref_logits, rtol=1e-5, atol=1e-4, err_msg=exe)
+        sub = 16                                        # the CPU oracle on the first images
+        sspec = dict(spec, batch=sub)
+        acts, _ = onet.run(sspec, w, x[:sub])
+        np.testing.assert_allclose(acts[-1][:, :classes], ref_logits[:sub], rtol=1e-5, atol=1e-4, err_msg=exe + " (oracle)")
         for _ in range(3):
             net.forward()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -91,11 +110,33 @@ def test_reference_network_drivers_same_box(cuda, tmp_path):
             net.forward()
         e1.record()
         torch.cuda.synchronize()
-        ours = e0.elapsed_time(e1) / 5
-        B = spec["batch"]
+        t = e0.elapsed_time(e1) / 5
         res[exe] = {"batch": B, "reference_ms": ref_ms, "reference_images_per_s": B / (ref_ms * 1e-3),
-                    "tcbnn_b200_ms": ours, "tcbnn_b200_images_per_s": B / (ours * 1e-3), "ratio": ref_ms / ours}
+                    "tcbnn_b200_ms": t, "tcbnn_b200_images_per_s": B / (t * 1e-3), "ratio": ref_ms / t,
+                    "max_abs_logit_diff": float(np.max(np.abs(ours - ref_logits)))}
         del net
     if not res:
         pytest.skip("oracle/_ref/ref_<driver> not built (reference tree absent at build time)")
     print("\nSAME_BOX_NETWORKS " + json.dumps(res))
+
+
+def _ref_runner():
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(orc.__file__)), "_ref", "ref_net_runner")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/ref_net_runner not built (reference tree absent at build time)")
+    return path
+
+
+@pytest.mark.parametrize("which", ["mlp", "vgg_cifar", "resnet18_small", "resnet_cifar"])
+def test_oracle_matches_reference_implementation_layer_by_layer(cuda, tmp_path, which):
+    """The layer-level pin: the generic driver (tcbnn_b200/dropin/net_runner.cu) compiled against
+    the REFERENCE's own headers runs the reference's In128 / Fc128 / Out128 / InConv128 / Conv128
+    kernels on the GPU; every layer's unpacked +-1 activations (download_full_output()) and the
+    logits must equal the CPU oracle's on the same weights and inputs."""
+    from tcbnn_b200 import models
+    from test_gpu_dropin import _run
+    spec = {"mlp": models.mlp_spec(256), "vgg_cifar": models.vgg_cifar_spec(8),
+            "resnet18_small": models.resnet18_spec(8, image=64, classes=100),
+            "resnet_cifar": models.resnet_cifar_spec(8)}[which]
+    _run(spec, 60, tmp_path, cuda, runner=_ref_runner())

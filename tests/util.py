@@ -87,3 +87,28 @@ def conv_pm1_reference(x_pm1, f_pm1, thr, sh, sw, padding, pool, res_in=None,
     bit = ~(res.astype(np.float32) < thr.astype(np.float32)[None, None, None, :])
     pooled = bit.reshape(B, OH, pool, OW, pool, O).any(axis=(2, 4))
     return pooled.astype(np.uint8), res.astype(np.int32), acc.astype(np.int32)
+
+
+def _mix(i):
+    """The counter hash of tcbnn_b200/dropin/synthetic_data.cpp (the stand-in dataset readers the
+    reference's drivers are linked with), vectorised: uint64 index array -> uint32."""
+    z = i.astype(np.uint64) + np.uint64(0x9E3779B97F4A7C15)
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return ((z ^ (z >> np.uint64(31))) >> np.uint64(32)).astype(np.uint32)
+
+
+def reader_images(kind, batch):
+    """The fp32 images those readers hand to the drivers: 'mnist' [B][784], 'cifar' [B][3][32][32],
+    'imagenet' [B][3][224][224], same float32 arithmetic as the C++ code."""
+    if kind == "mnist":
+        n = batch * 784
+        v = (_mix(np.arange(n, dtype=np.uint64)) & 0xFF).astype(np.float32)
+        return ((v / np.float32(255.0) - np.float32(0.1307)) / np.float32(0.3081)).reshape(batch, 784)
+    hw, mean, sd = {"cifar": (32, (0.4914, 0.4822, 0.4465), (0.2470, 0.2435, 0.2616)),
+                    "imagenet": (224, (0.485, 0.456, 0.406), (0.229, 0.224, 0.225))}[kind]
+    n = batch * 3 * hw * hw
+    v = (_mix(np.arange(n, dtype=np.uint64)) & 0xFF).astype(np.float32).reshape(batch, 3, hw, hw)
+    m = np.array(mean, np.float32).reshape(1, 3, 1, 1)
+    s_ = np.array(sd, np.float32).reshape(1, 3, 1, 1)
+    return (v / np.float32(255.0) - m) / s_
