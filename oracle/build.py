@@ -42,15 +42,16 @@ def build_oracle(native=False):
 def build_ref(ref_root="/root/reference"):
     tc = os.path.join(ref_root, "bmm", "tensorcore_kernel.cu")
     mt = os.path.join(ref_root, "bmm", "bmma_op_test", "main_test.cu")
-    if not (os.path.exists(tc) and os.path.exists(mt)):
+    bc = os.path.join(ref_root, "bconv", "bmma_kernel.cu")
+    if not (os.path.exists(tc) and os.path.exists(mt) and os.path.exists(bc)):
         return None
     outdir = os.path.join(HERE, "_ref")
     os.makedirs(outdir, exist_ok=True)
     out = os.path.join(outdir, "libref_bmm.so")
     wrap = os.path.join(HERE, "ref_wrap.cu")
-    if _stale(out, [wrap, tc, mt]):
+    if _stale(out, [wrap, tc, mt, bc]):
         objs = []
-        for which, src in ((1, tc), (2, mt)):
+        for which, src in ((1, tc), (2, mt), (3, bc)):
             obj = os.path.join(outdir, "ref_wrap_%d.o" % which)
             _run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-w",
                   "-Xcompiler", "-fPIC", "-DWHICH=%d" % which, '-DREF_SRC="%s"' % src,

@@ -47,6 +47,16 @@ def gather_logits(local, out=None):
     return out
 
 
+def ensemble_max(local, root=0):
+    """The reference harness's own exchange (benn_scaleup.cu:400, benn_scaleout.cu): every rank
+    holds a member network's [B][classes] logits for the SAME images and rank `root` ends with
+    their element-wise maximum -- one reduce(max), in place.  Other ranks' tensors keep their
+    own values.  Returns `local`."""
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.reduce(local, dst=root, op=dist.ReduceOp.MAX)
+    return local
+
+
 def max_over_ranks(values, device=None):
     """Element-wise max of a list of floats over all ranks (timings are reported as the max)."""
     t = torch.tensor(list(values), dtype=torch.float64, device=device)

@@ -25,8 +25,10 @@ def _worker(rank, world, port, q):
     local = torch.arange(b, e, dtype=torch.float32).reshape(-1, 1).repeat(1, 3) + 0.5
     full = d.gather_logits(local)
     times = d.max_over_ranks([1.0 + rank, 5.0 - rank])
+    member = torch.tensor([[1.0, -2.0 + 5 * rank, 3.0 - rank], [0.5 * rank, 0.0, -1.0]])
+    voted = d.ensemble_max(member.clone())
     d.barrier()
-    q.put((rank, full.tolist(), times, d.shard_seed(100, rank)))
+    q.put((rank, full.tolist(), times, d.shard_seed(100, rank), voted.tolist()))
     d.finish()
 
 
@@ -43,10 +45,12 @@ def test_two_rank_gather_and_timing():
         p.join(timeout=60)
         assert p.exitcode == 0
     expect = [[i + 0.5] * 3 for i in range(8)]
-    for rank, full, times, seed in res:
+    for rank, full, times, seed, voted in res:
         assert full == expect                    # rank-major order, every rank sees all logits
         assert times == [2.0, 5.0]               # max over ranks
         assert seed == 100 + rank
+        if rank == 0:                            # ensemble mode: element-wise max lands on the root
+            assert voted == [[1.0, 3.0, 3.0], [0.5, 0.0, -1.0]]
 
 
 def test_single_process_needs_no_group():
@@ -57,3 +61,4 @@ def test_single_process_needs_no_group():
     x = torch.ones(2, 3)
     assert d.gather_logits(x) is x
     assert d.max_over_ranks([3.0]) == [3.0]
+    assert d.ensemble_max(x) is x

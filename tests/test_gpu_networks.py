@@ -92,3 +92,22 @@ def test_resnet18_uint8_images_give_identical_results(cuda):
     assert np.array_equal(a, b)
     acts, _ = onet.run(spec, w, x)
     np.testing.assert_allclose(b, acts[-1], rtol=1e-5, atol=1e-5)
+
+
+def test_forward_graph_replay_equals_eager_forward(cuda):
+    """Network.forward_graph: the same launches captured into a CUDA graph; replays follow the
+    contents of the input buffer and give the eager results bit for bit."""
+    spec = models.resnet18_spec(4, image=64, classes=100)
+    w = models.synthetic_weights(spec, 60)
+    x0 = models.synthetic_input(spec, 61)
+    x1 = models.synthetic_input(spec, 62)
+    net = models.Network(spec, w, x0, input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND)
+    eager0 = net.forward().clone()
+    g0 = net.forward_graph().clone()            # captures
+    assert torch.equal(g0, eager0)
+    net.layers[0].input_gpu.copy_(torch.from_numpy(x1).to(cuda).reshape(net.layers[0].input_gpu.shape))
+    g1 = net.forward_graph().clone()            # replays on the new images
+    eager1 = net.forward().clone()
+    assert torch.equal(g1, eager1) and not torch.equal(g1, g0)
+    acts, _ = onet.run(spec, w, x1)
+    np.testing.assert_allclose(g1.cpu().numpy(), acts[-1], rtol=1e-5, atol=1e-5)

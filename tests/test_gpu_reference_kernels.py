@@ -52,6 +52,53 @@ def test_reference_bitgemm_kernels_match_and_time(cuda):
     print("\nSAME_BOX_BITGEMM " + json.dumps(res))
 
 
+def test_reference_bitconv_kernel_matches_and_times(cuda):
+    """The reference's standalone bit convolution (bconv/bmma_kernel.cu BTC_bin_*_128 +
+    BTC_Conv2d_balance_128, launched as bconv/benchmark-bconv.cu:516-540 does) on the standalone
+    conv configuration, 256 x 56 x 56 x 128 -> 128, 3x3, stride 1, SAME padding: its int32 sums
+    must equal tcbnn_conv_layer's accumulators everywhere and the CPU oracle's on the first
+    images; both timings are printed (run with -s)."""
+    R = orc.ref_lib()
+    if R is None or not hasattr(R, "ref_gpu_bconv128"):
+        pytest.skip("oracle/_ref/libref_bmm.so not built (reference tree absent at build time)")
+    N, H, Cc, O = 256, 56, 128, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(11)
+    x = torch.randint(0, 2, (N, H, H, Cc), device=cuda, generator=g, dtype=torch.int8).float() * 2 - 1
+    F = torch.randint(0, 2, (9, Cc, O), device=cuda, generator=g, dtype=torch.int8).float() * 2 - 1
+    ref_out = torch.zeros((H, H, N, O), dtype=torch.int32, device=cuda)
+    ms = C.c_float(0)
+    torch.cuda.synchronize()
+    rc = R.ref_gpu_bconv128(C.c_void_p(x.data_ptr()), C.c_void_p(F.data_ptr()), C.c_void_p(ref_out.data_ptr()),
+                            N, H, H, Cc, O, 3, 3, 1, 1, H, H, 5, C.byref(ms))
+    assert rc == 0
+    ref_nhwo = ref_out.permute(2, 0, 1, 3).contiguous()
+    d = ops.conv_desc(N, H, H, Cc, O, 3, 3)
+    xb = ops.pack_rows(x.reshape(N * H * H, Cc)).reshape(N, H, H, Cc // 32)
+    fb = ops.pack_conv_filter(F)
+    prep = ops.conv_prepare(d, fb)
+    thr = torch.zeros((O,), device=cuda)
+    out, _, acc = ops.conv_layer(d, xb, prep, thr, want_acc=True)
+    assert torch.equal(acc, ref_nhwo)
+    sub = 4
+    _, _, ea = orc.conv_layer(xb[:sub].cpu().numpy(), fb.cpu().numpy(), thr.cpu().numpy(), Cc, 3, 3, want_acc=True)
+    assert np.array_equal(ref_nhwo[:sub].cpu().numpy(), ea)
+    del acc, ref_out
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        ops.conv_layer(d, xb, prep, thr, out=out)
+    e0.record()
+    for _ in range(20):
+        ops.conv_layer(d, xb, prep, thr, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    t = e0.elapsed_time(e1) / 20
+    work = 2.0 * N * H * H * O * 9 * Cc
+    print("\nSAME_BOX_BITCONV " + json.dumps({
+        "BTC_Conv2d_balance_128": {"ms": ms.value, "tops": work / (ms.value * 1e-3) / 1e12},
+        "tcbnn_conv_layer": {"ms": t, "tops": work / (t * 1e-3) / 1e12}, "ratio": ms.value / t}))
+
+
 def test_reference_network_drivers_same_box(cuda, tmp_path):
     """The reference's unchanged drivers built with the reference's OWN headers (its WMMA b1
     kernels in one cooperative launch) for sm_100a into oracle/_ref/ref_<driver>, run once each on
