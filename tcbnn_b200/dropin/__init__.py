@@ -40,5 +40,13 @@ def write_weights(arrays, path):
             f.write("\n")
 
 
+def write_weights_binary(arrays, path):
+    """The same numbers in the same order as raw fp32 (a ".bin" name): what the drop-in's
+    tcbnn_dropin::Weights::from_binary / from_memory overloads of initialize() read."""
+    with open(path, "wb") as f:
+        for a in arrays:
+            np.asarray(a, dtype=np.float32).ravel().tofile(f)
+
+
 def weight_count(spec):
     return sum(int(np.prod(a.shape)) for a in models.synthetic_weights(spec, 0))

@@ -11,7 +11,11 @@
 //   conv R S C O stride pool ahead_fc save_residual inject(-1 or layer index) residual_channels residual_pool
 //   fc N
 //   out N
-// weights.txt : whitespace-separated floats in launch_array order (utility.h).
+// weights.txt : whitespace-separated floats in launch_array order (utility.h).  With the drop-in
+//   headers a name ending in ".bin" is read as raw fp32 in the same order (from the file, or, with
+//   TCBNN_WEIGHTS_IN_MEMORY set, loaded first and handed over as a host array).
+// TCBNN_RUNS=n launches the forward kernel n times on the same objects (layers store their
+//   outputs, so every run gives the same result); the last one is timed.
 // input.bin   : fp32, [B][K] for "in" networks, NCHW [B][3][H][W] otherwise.
 #include <cooperative_groups.h>
 #include <vector>
@@ -50,9 +54,26 @@ int main(int argc, char** argv) {
     const int device = argc > 5 ? atoi(argv[5]) : 0;
     CUDA_SAFE_CALL(cudaSetDevice(device));
     FILE* spec = fopen(argv[1], "r");
-    FILE* config_file = fopen(argv[2], "r");
     FILE* fin = fopen(argv[3], "rb");
+#ifdef TCBNN_DROPIN
+    const size_t len = strlen(argv[2]);
+    const bool binary = len > 4 && strcmp(argv[2] + len - 4, ".bin") == 0;
+    FILE* wfile = fopen(argv[2], binary ? "rb" : "r");
+    if (!spec || !wfile || !fin) { fprintf(stderr, "cannot open an input file\n"); return 2; }
+    std::vector<float> held;
+    if (binary && getenv("TCBNN_WEIGHTS_IN_MEMORY")) {
+        fseek(wfile, 0, SEEK_END);
+        held.resize((size_t)ftell(wfile) / sizeof(float));
+        fseek(wfile, 0, SEEK_SET);
+        if (fread(held.data(), sizeof(float), held.size(), wfile) != held.size()) return 2;
+    }
+    tcbnn_dropin::Weights config_file = !binary ? tcbnn_dropin::Weights::from_text(wfile)
+                                        : held.empty() ? tcbnn_dropin::Weights::from_binary(wfile)
+                                                       : tcbnn_dropin::Weights::from_memory(held.data(), held.size());
+#else
+    FILE* config_file = fopen(argv[2], "r");
     if (!spec || !config_file || !fin) { fprintf(stderr, "cannot open an input file\n"); return 2; }
+#endif
     int batch = 0;
     char word[64];
     if (fscanf(spec, "%63s %d", word, &batch) != 2 || std::string(word) != "batch") return 2;
@@ -122,6 +143,10 @@ int main(int argc, char** argv) {
     cudaFuncSetAttribute(run_network, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_memory);
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&numBlocksPerSm, run_network, numThreads, shared_memory);
     void* args[] = {&refs_gpu, &n};
+    const int runs = getenv("TCBNN_RUNS") ? atoi(getenv("TCBNN_RUNS")) : 1;
+    for (int i = 1; i < runs; i++)
+        CUDA_SAFE_CALL(cudaLaunchCooperativeKernel((void*)run_network, numBlocksPerSm * deviceProp.multiProcessorCount,
+                                                   numThreads, args, shared_memory));
     START_TIMER;
     CUDA_SAFE_CALL(cudaLaunchCooperativeKernel((void*)run_network, numBlocksPerSm * deviceProp.multiProcessorCount,
                                                numThreads, args, shared_memory));

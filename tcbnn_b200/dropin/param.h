@@ -3,7 +3,8 @@
 // B200 layer code in ../csrc/bnn_layers.cuh.
 //
 // What is kept: class and method names, argument order and defaults (param.h:115-1065), the
-// weight-file order consumed through launch_array, "initialize() returns the device-side copy
+// weight-file order consumed through launch_array (plus initialize() overloads that take the same
+// numbers from a binary file or from memory, tcbnn_dropin::Weights), "initialize() returns the device-side copy
 // that the driver's cooperative kernel receives", borrowed input / residual pointers, owned
 // outputs, exit-on-error.
 // What is different inside: activations are NHWC bit-packed words (no HWNC 8x128 tiling),
@@ -11,6 +12,7 @@
 // argument block the layer loops read on the device.
 #ifndef PARAM_H
 #define PARAM_H
+#define TCBNN_DROPIN 1
 
 #include "utility.h"
 #include "../csrc/bnn_layers.cuh"
@@ -30,11 +32,45 @@ __global__ void k_conv_prepare(const uin32* fbits, int O, int R, int S, int Cw, 
 inline int grid_for(size_t n) { size_t b = (n + 255) / 256; return (int)(b < 1 ? 1 : b > 4096 ? 4096 : b); }
 inline int fc_ld(int k) { return STEP128(k) * 4; }
 
-// reads `n` floats from the weight file and returns them in a fresh device buffer
-inline float* upload_from_file(FILE* cf, size_t n, float** host_keep) {
+// Where initialize() takes its numbers from.  The reference reads a text file of decimal floats
+// through launch_array (utility.h:188-196); the same values, in the same order, may also come
+// from a binary file of raw fp32 or from host memory, so that a caller that already holds the
+// weights need not print and re-parse them.  Running short is fatal, as in launch_array.
+struct Weights {
+    FILE* text;
+    FILE* binary;
+    const float* memory;
+    size_t left;
+    static Weights from_text(FILE* f) { Weights w = {f, NULL, NULL, 0}; return w; }
+    static Weights from_binary(FILE* f) {
+        if (f == NULL) { fprintf(stderr, "NULL pointer to the network configuration file.\n"); exit(1); }
+        Weights w = {NULL, f, NULL, 0};
+        return w;
+    }
+    static Weights from_memory(const float* p, size_t count) {
+        if (p == NULL) { fprintf(stderr, "NULL pointer to the network weights.\n"); exit(1); }
+        Weights w = {NULL, NULL, p, count};
+        return w;
+    }
+    void read(float* dst, size_t n) {
+        if (binary) {
+            const size_t got = fread(dst, sizeof(float), n, binary);
+            if (got != n) { fprintf(stderr, "network configuration file ended after %zu of %zu values.\n", got, n); exit(1); }
+        } else if (memory) {
+            if (left < n) { fprintf(stderr, "network weights ended after %zu of %zu values.\n", left, n); exit(1); }
+            memcpy(dst, memory, n * sizeof(float));
+            memory += n;
+            left -= n;
+        } else {
+            launch_array(text, dst, (unsigned)n);
+        }
+    }
+};
+// reads `n` floats from the weight source and returns them in a fresh device buffer
+inline float* upload_from_file(Weights& cf, size_t n, float** host_keep) {
     float* h = NULL;
     SAFE_ALOC_HOST(h, n * sizeof(float));
-    launch_array(cf, h, (unsigned)n);
+    cf.read(h, n);
     float* d = NULL;
     SAFE_ALOC_GPU(d, n * sizeof(float));
     CUDA_SAFE_CALL(cudaMemcpy(d, h, n * sizeof(float), cudaMemcpyHostToDevice));
@@ -136,6 +172,10 @@ public:
     // rows of the producer: a conv layer that feeds an FC layer pads each image to 128 bits
     void set_input_gpu(uin32* p) { input_gpu = p; input_ld = tcbnn_dropin::fc_ld(input_width); }
     Fc128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu) {
+        tcbnn_dropin::Weights w = tcbnn_dropin::Weights::from_text(config_file);
+        return initialize(w, prev_layer_gpu);
+    }
+    Fc128LayerParam* initialize(tcbnn_dropin::Weights& config_file, uin32* prev_layer_gpu) {
         float* w = tcbnn_dropin::upload_from_file(config_file, weight_size(), &weight);
         SAFE_ALOC_GPU(weight_gpu, weight_bit_bytes());
         tcbnn_dropin::k_pack_fc_weight<<<tcbnn_dropin::grid_for(weight_bit_bytes() / 4), 256>>>(
@@ -200,6 +240,10 @@ public:
     size_t bn_bytes() { return bn_size() * sizeof(float); }
     void set_input_gpu(uin32* p) { input_gpu = p; }
     Out128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu) {
+        tcbnn_dropin::Weights w = tcbnn_dropin::Weights::from_text(config_file);
+        return initialize(w, prev_layer_gpu);
+    }
+    Out128LayerParam* initialize(tcbnn_dropin::Weights& config_file, uin32* prev_layer_gpu) {
         float* w = tcbnn_dropin::upload_from_file(config_file, weight_size(), &weight);
         SAFE_ALOC_GPU(weight_gpu, weight_bit_bytes());
         tcbnn_dropin::k_pack_fc_weight<<<tcbnn_dropin::grid_for(weight_bit_bytes() / 4), 256>>>(
@@ -284,6 +328,10 @@ public:
     size_t residual_size() { return (size_t)PAD128(output_channels) * batch * output_height * pool_height * output_width * pool_width; }
     size_t residual_bytes() { return residual_size() * sizeof(int); }
     InConv128LayerParam* initialize(float* input, FILE* config_file) {
+        tcbnn_dropin::Weights w = tcbnn_dropin::Weights::from_text(config_file);
+        return initialize(input, w);
+    }
+    InConv128LayerParam* initialize(float* input, tcbnn_dropin::Weights& config_file) {
         CHECK_NULL_POINTER(input);
         this->input = input;
         SAFE_ALOC_GPU(input_gpu, input_bytes());
@@ -404,6 +452,10 @@ public:
         input_residual_channels = PAD128(residual_channels);
     }
     Conv128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu, int* input_residual_gpu = NULL) {
+        tcbnn_dropin::Weights w = tcbnn_dropin::Weights::from_text(config_file);
+        return initialize(w, prev_layer_gpu, input_residual_gpu);
+    }
+    Conv128LayerParam* initialize(tcbnn_dropin::Weights& config_file, uin32* prev_layer_gpu, int* input_residual_gpu = NULL) {
         float* f = tcbnn_dropin::upload_from_file(config_file, filter_size(), &filter);
         SAFE_ALOC_GPU(filter_gpu, filter_bit_bytes());
         tcbnn_dropin::k_pack_conv_filter<<<tcbnn_dropin::grid_for(filter_bit_bytes() / 4), 256>>>(

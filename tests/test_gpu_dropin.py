@@ -31,18 +31,26 @@ def _unpacked(act, layer):
     return orc.unpack_rows(np.ascontiguousarray(bits), O)
 
 
-def _run(spec, seed, tmp_path, cuda, runner=None):
+def _run(spec, seed, tmp_path, cuda, runner=None, weights="text", runs=1):
     """runner: the binary to run; default the generic driver built on the drop-in headers (the
-    reference-header build of the same driver is tests/test_gpu_reference_kernels.py's)."""
+    reference-header build of the same driver is tests/test_gpu_reference_kernels.py's).
+    weights: "text" (the reference's file format), "binary" (raw fp32 file) or "memory" (host
+    array); runs: forward launches on the same layer objects."""
     runner = runner or dbuild.build_runner()
     w = models.synthetic_weights(spec, seed)
     x = models.synthetic_input(spec, seed + 1)
     d = str(tmp_path)
     dropin.write_spec(spec, os.path.join(d, "spec.txt"))
-    dropin.write_weights(w, os.path.join(d, "weights.txt"))
+    wname = "weights.txt" if weights == "text" else "weights.bin"
+    if weights == "text":
+        dropin.write_weights(w, os.path.join(d, wname))
+    else:
+        dropin.write_weights_binary(w, os.path.join(d, wname))
     np.ascontiguousarray(x, dtype=np.float32).tofile(os.path.join(d, "input.bin"))
-    env = dict(os.environ, TCBNN_DUMP_DIR=d)
-    r = subprocess.run([runner, os.path.join(d, "spec.txt"), os.path.join(d, "weights.txt"),
+    env = dict(os.environ, TCBNN_DUMP_DIR=d, TCBNN_RUNS=str(runs))
+    if weights == "memory":
+        env["TCBNN_WEIGHTS_IN_MEMORY"] = "1"
+    r = subprocess.run([runner, os.path.join(d, "spec.txt"), os.path.join(d, wname),
                         os.path.join(d, "input.bin"), os.path.join(d, "logits.bin")],
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
@@ -73,6 +81,13 @@ def test_dropin_resnet18_small_image(cuda, tmp_path):
 
 def test_dropin_resnet_cifar(cuda, tmp_path):
     _run(models.resnet_cifar_spec(4), 43, tmp_path, cuda)
+
+
+def test_dropin_binary_weights_and_repeated_runs(cuda, tmp_path):
+    """initialize() from a raw fp32 file and from a host array (tcbnn_dropin::Weights), and three
+    forward launches on the same layer objects: same activations and logits as the oracle."""
+    _run(models.resnet_cifar_spec(4), 44, tmp_path, cuda, weights="binary", runs=3)
+    _run(models.vgg_cifar_spec(8), 45, tmp_path, cuda, weights="memory", runs=2)
 
 
 def test_reference_drivers_built_against_dropin_run(cuda, tmp_path):
