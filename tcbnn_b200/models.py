@@ -308,7 +308,9 @@ class Network:
             self.forward()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            # thread_local: only this thread's calls are checked during the capture; another
+            # thread (e.g. a communicator's watchdog polling its events) is left alone
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self.forward()
             graphs[key] = g
         g.replay()
