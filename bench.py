@@ -153,6 +153,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU arm")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # stdout carries the one JSON line: whatever NCCL_DEBUG makes NCCL print goes to stderr
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     tdist.init("nccl", dev)
 
     B = args.batch
