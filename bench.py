@@ -223,13 +223,12 @@ def main():
         def on_result(out):
             if world > 1:
                 tdist.gather_logits(out, gathered)
-            logits_host.copy_(out, non_blocking=True)
 
-        feeder.run([batch_host] * 2, on_result)
+        feeder.run([batch_host] * 2, on_result, logits_host)
         sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        feeder.run([batch_host] * args.steps, on_result)
+        feeder.run([batch_host] * args.steps, on_result, logits_host)   # ends by waiting for the last read
         e1.record()
         sync()
         return e0.elapsed_time(e1)

@@ -332,6 +332,9 @@ class HostFeeder:
         self.copy_stream = torch.cuda.Stream()
         self.copied = [torch.cuda.Event(), torch.cuda.Event()]
         self.free = [torch.cuda.Event(), torch.cuda.Event()]
+        self.read_stream = torch.cuda.Stream()
+        self.computed = torch.cuda.Event()
+        self.read_done = torch.cuda.Event()
         self.n = 0
         self.pending = None
 
@@ -342,13 +345,16 @@ class HostFeeder:
             self.bufs[slot].copy_(x_host.reshape(self.bufs[slot].shape), non_blocking=True)
             self.copied[slot].record(self.copy_stream)
 
-    def run(self, batches, on_result):
+    def run(self, batches, on_result=None, result_host=None):
         """batches: iterable of pinned host tensors; on_result(logits_device) is called after
-        each forward pass has been queued (it may queue the device->host read)."""
+        each forward pass has been queued.  result_host: pinned host tensor that receives every
+        batch's logits; that device->host read runs on a third stream, beside the next batch's
+        compute and input copy, and the next pass's output layer waits for it."""
         import torch
         main = torch.cuda.current_stream()
         for ev in self.free:
             ev.record(main)
+        self.read_done.record(main)
         it = iter(batches)
         nxt = next(it, None)
         slot = 0
@@ -362,6 +368,15 @@ class HostFeeder:
                 self._enqueue_copy(slot, nxt)
             main.wait_event(self.copied[cur_slot])
             self.first.input_gpu = self.bufs[cur_slot]
+            main.wait_event(self.read_done)          # the logits buffer is about to be rewritten
             out = self.net.forward_graph() if self.graph else self.net.forward()
             self.free[cur_slot].record(main)
-            on_result(out)
+            if on_result is not None:
+                on_result(out)
+            if result_host is not None:
+                self.computed.record(main)
+                with torch.cuda.stream(self.read_stream):
+                    self.read_stream.wait_event(self.computed)
+                    result_host.copy_(out, non_blocking=True)
+                    self.read_done.record(self.read_stream)
+        main.wait_event(self.read_done)

@@ -111,3 +111,27 @@ def test_forward_graph_replay_equals_eager_forward(cuda):
     assert torch.equal(g1, eager1) and not torch.equal(g1, g0)
     acts, _ = onet.run(spec, w, x1)
     np.testing.assert_allclose(g1.cpu().numpy(), acts[-1], rtol=1e-5, atol=1e-5)
+
+
+def test_host_feeder_overlapped_copies_give_each_batch_its_own_logits(cuda):
+    """models.HostFeeder: pinned host batches in, input copy of batch i+1 and logits read of
+    batch i beside the compute of the batch between them; every batch's logits equal those of
+    a plain forward pass on that batch, with and without graph replay."""
+    spec = models.resnet18_spec(4, image=64, classes=100)
+    w = models.synthetic_weights(spec, 70)
+    xs = [models.synthetic_input(spec, 71 + i) for i in range(4)]
+    expect = []
+    for x in xs:
+        expect.append(models.Network(spec, w, x, input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND).forward().cpu().numpy())
+    for graph in (False, True):
+        net = models.Network(spec, w, xs[0], input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND)
+        feeder = models.HostFeeder(net, graph=graph)
+        host = [torch.from_numpy(np.ascontiguousarray(x)).pin_memory() for x in xs]
+        last = torch.empty((4, 100), dtype=torch.float32).pin_memory()
+        got = []
+        feeder.run(host, lambda out: got.append(out.clone()), last)
+        torch.cuda.synchronize()
+        assert len(got) == len(xs)
+        for g, e in zip(got, expect):
+            assert np.array_equal(g.cpu().numpy(), e)
+        assert np.array_equal(last.numpy(), expect[-1])
