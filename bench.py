@@ -153,8 +153,12 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback); use --impl reference for the CPU arm")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    # stdout carries the one JSON line: whatever NCCL_DEBUG makes NCCL print goes to stderr
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # stdout carries the one JSON line and nothing else: from here on file descriptor 1 points at
+    # stderr (libraries such as NCCL print their version banner to it) and the line goes to the
+    # saved descriptor at the end
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     tdist.init("nccl", dev)
 
     B = args.batch
@@ -292,7 +296,7 @@ def main():
         }
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(args.cpu_images)
-        print(json.dumps(out))
+        os.write(json_fd, (json.dumps(out) + "\n").encode())
     tdist.finish()
 
 
