@@ -471,6 +471,52 @@ __device__ __forceinline__ void pack_rows(const float* x, int rows, int cols, in
     }
 }
 
+// bit i of the low byte of b -> bit 4 * i
+__device__ __forceinline__ uint32_t spread4(uint32_t b) {
+    uint32_t x = b & 0xFFu;
+    x = (x | (x << 12)) & 0x000F000Fu;
+    x = (x | (x << 6)) & 0x03030303u;
+    x = (x | (x << 3)) & 0x11111111u;
+    return x;
+}
+
+// The same packing for rows whose length is a multiple of 4 floats on a 16-byte aligned base: a
+// lane reads 16 bytes (four consecutive columns), a warp one 128-column block per load, and a
+// task is eight consecutive blocks of one row, all eight loads (4 KB) issued before the first is
+// used -- with 64 warps per SM that keeps up to 256 KB in flight.  Four ballots give one bit per
+// (lane, component); lane L interleaves eight lanes' four bits into word L & 3 of block L >> 2.
+// rows * ceil(blocks / 8) must fit in 31 bits (the caller checks).
+__device__ __forceinline__ void pack_rows_vec(const float* x, int rows, int cols, int ld_words,
+                                              uint32_t* out) {
+    constexpr int U = 8;
+    const int lane = threadIdx.x & 31;
+    const unsigned blocks = (unsigned)ld_words >> 2, chunks = (blocks + U - 1) / U;
+    const unsigned total = (unsigned)rows * chunks, step = (unsigned)grid_warps();
+    for (unsigned task = (unsigned)grid_warp(); task < total; task += step) {
+        const unsigned row = task / chunks, blk0 = (task - row * chunks) * U;
+        const float* xr = x + (size_t)row * cols;
+        float4 f[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int col = (int)(blk0 + u) * 128 + 4 * lane;
+            f[u] = col < cols ? __ldg(reinterpret_cast<const float4*>(xr + col)) : make_float4(-1.0f, -1.0f, -1.0f, -1.0f);
+        }
+        // lane L produces word L & 3 of block L >> 2: it keeps that block's four ballots
+        uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
+        const int myu = lane >> 2;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint32_t b0 = __ballot_sync(0xffffffffu, f[u].x >= 0), b1 = __ballot_sync(0xffffffffu, f[u].y >= 0);
+            const uint32_t b2 = __ballot_sync(0xffffffffu, f[u].z >= 0), b3 = __ballot_sync(0xffffffffu, f[u].w >= 0);
+            if (myu == u) { m0 = b0; m1 = b1; m2 = b2; m3 = b3; }
+        }
+        const int sh = 8 * (lane & 3);
+        const uint32_t v = spread4(m0 >> sh) | (spread4(m1 >> sh) << 1) | (spread4(m2 >> sh) << 2) |
+                           (spread4(m3 >> sh) << 3);           // column k of the word at bit k
+        if (blk0 + myu < blocks) out[(size_t)row * ld_words + blk0 * 4 + lane] = __brev(v);   // 128 contiguous bytes
+    }
+}
+
 // bit rows -> +-1 floats (UnPackFcOutput128FMT, param.h:87-104).
 __device__ __forceinline__ void unpack_rows(const uint32_t* in, int rows, int cols, int ld_words,
                                             float* out) {

@@ -69,6 +69,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 k_pack_rows(const float* x, int rows, int cols, int ld, uint32_t* out) {
     pack_rows(x, rows, cols, ld, out);
 }
+__global__ void __launch_bounds__(kThreads, 8)
+k_pack_rows_vec(const float* x, int rows, int cols, int ld, uint32_t* out) {
+    pack_rows_vec(x, rows, cols, ld, out);
+}
 __global__ void k_unpack_rows(const uint32_t* in, int rows, int cols, int ld, float* out) {
     unpack_rows(in, rows, cols, ld, out);
 }
@@ -692,8 +696,15 @@ int tcbnn_pack_rows(const float* x, int rows, int cols, int ld_words, uint32_t* 
     if ((uintptr_t)out & 15) return fail("pack_rows: output must be 16-byte aligned");
     int sms;
     if (sm_count(&sms)) return 1;
-    k_pack_rows<<<warp_grid((long long)rows * (ld_words / 4), sms), kThreads, 0, (cudaStream_t)stream>>>(
-        x, rows, cols, ld_words, out);
+    const long long tasks = (long long)rows * (ld_words / 4);
+    const long long vtasks = (long long)rows * ((ld_words / 4 + 7) / 8);
+    if ((cols & 3) == 0 && ((uintptr_t)x & 15) == 0 && vtasks < (1LL << 31)) {   // 16-byte loads, eight blocks per task
+        // memory-bound and light on registers: all 64 warps an SM holds (8 CTAs)
+        long long ctas = (vtasks + kThreads / 32 - 1) / (kThreads / 32);
+        if (ctas > 8LL * sms) ctas = 8LL * sms;
+        k_pack_rows_vec<<<(int)ctas, kThreads, 0, (cudaStream_t)stream>>>(x, rows, cols, ld_words, out);
+    } else
+        k_pack_rows<<<warp_grid(tasks, sms), kThreads, 0, (cudaStream_t)stream>>>(x, rows, cols, ld_words, out);
     return launch_check("pack_rows");
 }
 

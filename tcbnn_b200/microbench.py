@@ -39,9 +39,16 @@ def _time(fn, iters, warmup=3):
     return e0.elapsed_time(e1) / iters
 
 
+def _l_pack(x, out):
+    from . import lib as _lib
+    import ctypes as C
+    _lib.call("tcbnn_pack_rows", C.c_void_p(x.data_ptr()), x.shape[0], x.shape[1], out.shape[1],
+              C.c_void_p(out.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="c2", choices=["c1", "c2", "conv", "stem", "net"])
+    ap.add_argument("--case", default="c2", choices=["c1", "c2", "conv", "stem", "net", "pack"])
     ap.add_argument("--net", default="vgg_cifar",
                     choices=["mlp", "vgg_cifar", "resnet_cifar", "alexnet", "vgg16_imagenet", "resnet18"],
                     help="net: which reference driver's topology (C3 = mlp at batch 8192, C4 = vgg_cifar at 1024)")
@@ -81,6 +88,18 @@ def main():
         ms = sum(per.values())
         print(json.dumps({"case": "net", "net": a.net, "batch": a.batch, "ms": ms,
                           "images_per_s": a.batch / (ms * 1e-3), "layer_ms": {k: round(v, 4) for k, v in per.items()}}))
+        return
+    if a.case == "pack":
+        # the input layer (In128LayerFMT): fp32 rows -> bit rows.  Memory-bound: 4 bytes read and
+        # 1/8 byte written per value.  Rows x 784 features; the default 262144 rows (822 MB) do
+        # not fit in L2.
+        rows = a.batch if a.batch != 256 else 262144
+        x = torch.rand((rows, 784), device=dev) - 0.5
+        out = ops.pack_rows(x)
+        ms = _time(lambda: _l_pack(x, out), a.iters)
+        nbytes = x.numel() * 4 + out.numel() * 4
+        print(json.dumps({"case": "pack", "workload": "fp32 [%d][784] -> bit rows (tcbnn_pack_rows)" % rows, "ms": ms,
+                          "bytes": nbytes, "gb_per_s": nbytes / (ms * 1e-3) / 1e9}))
         return
     if a.case == "c1":
         M = N = 1024

@@ -22,7 +22,7 @@ def host_u32(t):
     return t.cpu().numpy().view(np.uint32)
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 1), (5, 70), (64, 784), (33, 1000), (8, 4096)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (5, 70), (64, 784), (33, 1000), (8, 4096), (20000, 260), (777, 130)])
 def test_pack_unpack_rows(cuda, rows, cols):
     g = util.rng(rows * 7 + cols)
     x = g.standard_normal((rows, cols)).astype(np.float32)
