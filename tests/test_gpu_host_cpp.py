@@ -1,0 +1,33 @@
+"""GPU parity of the C++ host classes on the C ABI (tcbnn_b200/host/tcbnn_host.hpp): the generic
+driver build/host/fast_runner builds each network with the reference's class names and
+constructor arguments and runs it through libtcbnn_b200.so layer by layer (tcgen05 kernels, the
+first layer compiled for its filter, hand-over between conv layers).  Logits and every layer's
+unpacked +-1 activations are compared with the CPU oracle."""
+import pytest
+
+from tcbnn_b200 import models
+from tcbnn_b200.host import build as hbuild
+from test_gpu_dropin import _run
+
+pytestmark = pytest.mark.gpu
+
+
+def test_host_cpp_mlp(cuda, tmp_path):
+    _run(models.mlp_spec(256), 80, tmp_path, cuda, runner=hbuild.build_fast_runner())
+
+
+def test_host_cpp_vgg_cifar_binary_weights(cuda, tmp_path):
+    _run(models.vgg_cifar_spec(8), 81, tmp_path, cuda, runner=hbuild.build_fast_runner(), weights="binary")
+
+
+def test_host_cpp_resnet18_small_image_repeated_runs(cuda, tmp_path):
+    _run(models.resnet18_spec(8, image=64, classes=100), 82, tmp_path, cuda, runner=hbuild.build_fast_runner(), runs=3)
+
+
+def test_host_cpp_resnet_cifar(cuda, tmp_path):
+    _run(models.resnet_cifar_spec(4), 83, tmp_path, cuda, runner=hbuild.build_fast_runner())
+
+
+def test_host_cpp_without_handover(cuda, tmp_path, monkeypatch):
+    monkeypatch.setenv("TCBNN_NO_HANDOVER", "1")
+    _run(models.resnet18_spec(4, image=64, classes=100), 84, tmp_path, cuda, runner=hbuild.build_fast_runner())
