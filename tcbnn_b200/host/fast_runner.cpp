@@ -12,7 +12,8 @@
 //   fc N
 //   out N
 // A weights name ending in ".bin" is raw fp32 in launch_array order, anything else the
-// reference's text format.  TCBNN_RUNS=n runs the forward pass n times (the last one is timed);
+// reference's text format.  TCBNN_RESIDUAL16=1 keeps the saved residuals as int16 (the caller's
+// promise that they fit; an overflow is reported and fails the run).  TCBNN_RUNS=n runs the forward pass n times (the last one is timed);
 // TCBNN_DUMP_DIR=<dir> also writes every layer's download_full_output() as layerNN.bin.
 #include <string>
 #include <vector>
@@ -57,6 +58,7 @@ int main(int argc, char** argv) {
     std::vector<float> images;
     uin32* prev = NULL;
     int H = 0, W = 0, K = 0;
+    const int res_bytes = getenv("TCBNN_RESIDUAL16") ? 2 : 4;
     while (fscanf(spec, "%63s", word) == 1) {
         const std::string t(word);
         Built b = {};
@@ -73,6 +75,7 @@ int main(int argc, char** argv) {
             if (fread(images.data(), sizeof(float), images.size(), fin) != images.size()) return 2;
             b.kind = K_INCONV;
             b.inconv = new InConv128LayerParam("Conv1", H, W, R, S, C, O, batch, st, st, true, pool, pool, save != 0);
+            b.inconv->set_residual_bytes(res_bytes);
             b.inconv->initialize(images.data(), config);
             prev = b.inconv->get_output_gpu(); H = b.inconv->output_height; W = b.inconv->output_width;
             K = H * W * O;
@@ -88,7 +91,8 @@ int main(int argc, char** argv) {
                 if (net[inj].kind == K_INCONV) { res = net[inj].inconv->get_output_residual_gpu(); res_ch = net[inj].inconv->output_channels; }
                 else { res = net[inj].conv->get_output_residual_gpu(); res_ch = net[inj].conv->output_channels; }
             }
-            b.conv->initialize(config, prev, res, res_ch);
+            b.conv->set_residual_bytes(res_bytes);
+            b.conv->initialize(config, prev, res, res_ch, res_bytes);
             prev = b.conv->get_output_gpu(); H = b.conv->output_height; W = b.conv->output_width;
             K = H * W * O;
         } else if (t == "fc") {
@@ -136,6 +140,11 @@ int main(int argc, char** argv) {
     TCBNN_HOST_CUDA(cudaEventElapsedTime(&ms, e0, e1));
     printf("{\"forward_ms\": %.4f, \"batch\": %d, \"layers\": %d}\n", ms, batch, (int)net.size());
 
+    for (size_t i = 0; i < net.size(); i++)
+        if (net[i].kind == K_CONV && net[i].conv->overflowed()) {
+            fprintf(stderr, "layer %zu: a residual does not fit in int16\n", i);
+            return 3;
+        }
     float* logits = net.back().out->download_output();
     FILE* fo = fopen(argv[4], "wb");
     if (!fo) return 2;

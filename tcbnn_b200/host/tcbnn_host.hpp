@@ -278,8 +278,8 @@ public:
                         int _filter_width, int _input_channels, int _output_channels, int _batch,
                         int _stride_height = 1, int _stride_width = 1, bool _padding = true,
                         int _pool_height = 1, int _pool_width = 1, bool _save_residual = false)
-        : save_residual(_save_residual), input_gpu(NULL), filter_gpu(NULL), bn_gpu(NULL), output_gpu(NULL),
-          output_residual_gpu(NULL), handle(NULL), next(NULL), next_planes(NULL) {
+        : save_residual(_save_residual), residual_bytes(4), input_gpu(NULL), filter_gpu(NULL), bn_gpu(NULL),
+          output_gpu(NULL), output_residual_gpu(NULL), handle(NULL), next(NULL), next_planes(NULL) {
         strncpy(name, _name, 7); name[7] = 0;
         if (_pool_height != _pool_width || _input_channels != 3) {
             fprintf(stderr, "%s: square pooling windows and 3 input channels only.\n", name);
@@ -293,6 +293,10 @@ public:
         output_height = desc.OH; output_width = desc.OW; output_channels = desc.O; batch = desc.B;
     }
     int Ow() const { return (desc.O + 31) / 32; }
+    // Extension: keep the saved residual as int16 instead of the reference's int (call before
+    // initialize()).  The caller vouches that R*S*3*max|pixel| < 32768; the residual layers are
+    // bound by this tensor's traffic, which it halves.
+    void set_residual_bytes(int bytes) { residual_bytes = bytes == 2 ? 2 : 4; }
     size_t input_size() const { return (size_t)desc.B * 3 * desc.H * desc.W; }
     size_t output_size() const { return (size_t)desc.B * desc.OH * desc.OW * desc.O; }
     InConv128LayerParam* initialize(const float* input, Weights& config) {
@@ -308,7 +312,8 @@ public:
         bn_gpu = config.upload(desc.O);
         output_gpu = dev_alloc<uin32>((size_t)desc.B * desc.OH * desc.OW * Ow());
         if (save_residual)
-            output_residual_gpu = dev_alloc<int>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O);
+            output_residual_gpu = (int*)dev_alloc<char>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O *
+                                                        residual_bytes);
         // the layer compiled for its filter, where the library offers it (at most 128 output channels)
         if (desc.O <= 128) TCBNN_HOST_CALL(tcbnn_inconv_specialize(&desc, filter_gpu, bn_gpu, NULL, &handle));
         return this;
@@ -318,12 +323,12 @@ public:
         const long long stride = (long long)desc.OH * desc.OW * Ow();
         if (handle)
             TCBNN_HOST_CALL(tcbnn_inconv_specialized_layer_x(handle, &desc, input_gpu, NULL, NULL, output_gpu, stride,
-                                                             output_residual_gpu, 4, NULL, next,
+                                                             output_residual_gpu, residual_bytes, NULL, next,
                                                              next_planes ? next_planes->ptr : NULL,
                                                              next_planes ? next_planes->bytes : 0, stream));
         else
             TCBNN_HOST_CALL(tcbnn_inconv_layer(&desc, input_gpu, filter_gpu, bn_gpu, output_gpu, stride,
-                                               output_residual_gpu, 4, NULL, stream));
+                                               output_residual_gpu, residual_bytes, NULL, stream));
     }
     float* get_input_gpu() { return input_gpu; }
     uin32* get_output_gpu() { return output_gpu; }
@@ -339,6 +344,7 @@ public:
     tcbnn_conv_desc desc;
     int output_height, output_width, output_channels, batch;
     bool save_residual;
+    int residual_bytes;
     float* input_gpu; uin32* filter_gpu; float* bn_gpu; uin32* output_gpu; int* output_residual_gpu;
     void* handle;
     const tcbnn_conv_desc* next;
@@ -358,7 +364,8 @@ public:
         : ahead_fc(_ahead_fc), save_residual(_save_residual), inject_residual(_inject_residual),
           residual_channels(_residual_channels), residual_pool(_residual_pool), filter_gpu(NULL), prepared_gpu(NULL),
           bn_gpu(NULL), input_gpu(NULL), output_gpu(NULL), input_residual_gpu(NULL), output_residual_gpu(NULL),
-          input_residual_channels(0), workspace(NULL), next(NULL), next_planes(NULL) {
+          input_residual_channels(0), residual_bytes(4), input_residual_bytes(4), workspace(NULL), next(NULL),
+          next_planes(NULL) {
         strncpy(name, _name, 7); name[7] = 0;
         if (_pool_height != _pool_width) { fprintf(stderr, "%s: square pooling windows only.\n", name); exit(-1); }
         memset(&desc, 0, sizeof desc);
@@ -375,9 +382,19 @@ public:
     int Ow() const { return (desc.O + 31) / 32; }
     size_t output_size() const { return (size_t)desc.B * desc.OH * desc.OW * desc.O; }
     size_t workspace_bytes() const { return tcbnn_conv_workspace_bytes(&desc); }
+    // Extension: save this layer's residual as int16 (call before initialize()).  The caller vouches
+    // that the running sum fits: |value| <= C*R*S + bound of the injected residual.  A value that
+    // does not fit raises status 2 (overflowed()).
+    void set_residual_bytes(int bytes) { residual_bytes = bytes == 2 ? 2 : 4; }
+    bool overflowed() {
+        int st = 0;
+        TCBNN_HOST_CALL(tcbnn_conv_status(&desc, prepared_gpu, &st));
+        return st == 2;
+    }
     // input_residual_channels_: channels per pixel of the injected tensor (the producer's O)
+    // input_residual_bytes_: element size of the injected tensor (its producer's set_residual_bytes)
     Conv128LayerParam* initialize(Weights& config, uin32* prev_layer_gpu, int* _input_residual_gpu = NULL,
-                                  int input_residual_channels_ = 0) {
+                                  int input_residual_channels_ = 0, int input_residual_bytes_ = 4) {
         const int RS = desc.R * desc.S;
         float* f = config.upload((size_t)RS * desc.C * desc.O);               // [R*S][C][O]
         filter_gpu = dev_alloc<uin32>((size_t)desc.O * RS * ((desc.C + 31) / 32));
@@ -391,7 +408,8 @@ public:
         bn_gpu = config.upload(desc.O);
         output_gpu = dev_alloc<uin32>((size_t)desc.B * out_image_stride);
         if (save_residual)
-            output_residual_gpu = dev_alloc<int>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O);
+            output_residual_gpu = (int*)dev_alloc<char>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O *
+                                                        residual_bytes);
         input_gpu = prev_layer_gpu;
         if (inject_residual) {
             if (!_input_residual_gpu || input_residual_channels_ <= 0) {
@@ -400,6 +418,7 @@ public:
             }
             input_residual_gpu = _input_residual_gpu;
             input_residual_channels = input_residual_channels_;
+            input_residual_bytes = input_residual_bytes_ == 2 ? 2 : 4;
         }
         return this;
     }
@@ -416,9 +435,10 @@ public:
         void* ws = input_planes.p ? input_planes.p->ptr : (workspace ? workspace->ptr : NULL);
         const size_t wsb = input_planes.p ? input_planes.p->bytes : (workspace ? workspace->bytes : 0);
         TCBNN_HOST_CALL(tcbnn_conv_layer_x(&desc, input_gpu, prepared_gpu, bn_gpu,
-                                           inject_residual ? input_residual_gpu : NULL, 4, input_residual_channels,
+                                           inject_residual ? input_residual_gpu : NULL, input_residual_bytes,
+                                           input_residual_channels,
                                            residual_channels, residual_pool ? 1 : 0, output_gpu, out_image_stride,
-                                           output_residual_gpu, 4, NULL, ws, wsb, input_planes.p ? 1 : 0, next,
+                                           output_residual_gpu, residual_bytes, NULL, ws, wsb, input_planes.p ? 1 : 0, next,
                                            next_planes ? next_planes->ptr : NULL, next_planes ? next_planes->bytes : 0,
                                            stream));
     }
@@ -441,7 +461,7 @@ public:
     bool residual_pool;
     uin32* filter_gpu; void* prepared_gpu; float* bn_gpu; uin32* input_gpu; uin32* output_gpu;
     int* input_residual_gpu; int* output_residual_gpu;
-    int input_residual_channels;
+    int input_residual_channels, residual_bytes, input_residual_bytes;
     Workspace* workspace;
     const tcbnn_conv_desc* next;
     Planes* next_planes;

@@ -31,3 +31,10 @@ def test_host_cpp_resnet_cifar(cuda, tmp_path):
 def test_host_cpp_without_handover(cuda, tmp_path, monkeypatch):
     monkeypatch.setenv("TCBNN_NO_HANDOVER", "1")
     _run(models.resnet18_spec(4, image=64, classes=100), 84, tmp_path, cuda, runner=hbuild.build_fast_runner())
+
+
+def test_host_cpp_int16_residuals(cuda, tmp_path, monkeypatch):
+    """set_residual_bytes(2) on every layer: same activations and logits (the synthetic images
+    keep the running sums far inside int16)."""
+    monkeypatch.setenv("TCBNN_RESIDUAL16", "1")
+    _run(models.resnet18_spec(4, image=64, classes=100), 85, tmp_path, cuda, runner=hbuild.build_fast_runner())
