@@ -62,7 +62,13 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def mark(self):
+        """Number of samples read so far (to delimit a window of the run)."""
+        return len(self.lines)
+
+    def stop(self, first=0, last=None):
+        """Summary of the samples [first, last) (marks); the whole record if that window holds
+        fewer than three samples (a timed region of a few tens of milliseconds)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -72,7 +78,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        window = self.lines[first:last]
+        whole = len(window) < 3
+        if whole:
+            window = self.lines
+        for ln in window:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -86,7 +96,8 @@ class ClockSampler:
                     reasons.add(n)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons),
+                "window": "warm-up, timed region and per-layer pass" if whole else "timed region and per-layer pass"}
 
 
 def run_reference(args, rank, world):
@@ -190,14 +201,17 @@ def main():
         tdist.barrier()
         torch.cuda.synchronize()
 
+    # clocks and throttle reasons are sampled every 20 ms from before the warm-up on (nvidia-smi
+    # needs a moment to start), and the samples of the timed window are picked out by marks
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     sync()
 
     # ---- device-resident throughput ------------------------------------------------------
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    mark0 = sampler.mark()
     # The timed region replays the forward pass from a CUDA graph (the same launches as one
     # submission).  A second pass of the same K steps, layer by layer with a CUDA event pair
     # around each, gives the per-layer times the roofline figures use.
@@ -213,7 +227,7 @@ def main():
     for _ in range(args.steps):
         step(events)
     sync()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(mark0, sampler.mark()) if rank == 0 else None
 
     # ---- end to end from host buffers ----------------------------------------------------
     # Every step copies its images from pinned host memory and reads its logits back; the copy
