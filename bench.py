@@ -5,10 +5,15 @@ imagenet_resnet.cu:223-325) at batch 1024 per GPU on synthetic 224x224 images.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
 
 One JSON line on stdout (rank 0).  `value` is images/s with the inputs already in HBM;
-`e2e` is the same pass driven from pinned host buffers (H2D of the fp32 images and D2H of the
-logits inside the timed region).  `--impl reference` times the CPU oracle (the reference has
-no CPU path of its own; the oracle is its restatement) on a bounded sample of the same
-workload with all host threads.
+`e2e` is the same pass driven from pinned host buffers (H2D of the images and D2H of the
+logits inside the timed region).  Outside the timed regions the run also: checks the logits of
+the full batch against the CPU oracle on the first images (`checked`; a mismatch exits non-zero),
+repeats the step for at least three seconds (`sustained`, with the SM clock seen), measures the
+plain concurrent host-to-device copy rate the end-to-end figure is bounded by (`h2d_ceiling`) and,
+on one GPU, times the reference's own unchanged ImageNet ResNet driver where it was built
+(`reference_gpu_same_box`).  `--impl reference` times the CPU oracle (the reference has no CPU
+path of its own; the oracle is its restatement) on a bounded sample of the same workload with
+all host threads.
 """
 import argparse
 import json
@@ -66,16 +71,20 @@ class ClockSampler:
         """Number of samples read so far (to delimit a window of the run)."""
         return len(self.lines)
 
-    def stop(self, first=0, last=None):
-        """Summary of the samples [first, last) (marks); the whole record if that window holds
-        fewer than three samples (a timed region of a few tens of milliseconds)."""
+    def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+
+    def summary(self, first=0, last=None, what="timed region and per-layer pass"):
+        """Summary of the samples [first, last) (marks); the whole record if that window holds
+        fewer than three samples (a timed region of a few tens of milliseconds)."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         window = self.lines[first:last]
@@ -97,7 +106,7 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "samples": len(sm), "reasons": sorted(reasons),
-                "window": "warm-up, timed region and per-layer pass" if whole else "timed region and per-layer pass"}
+                "window": "whole run so far" if whole else what}
 
 
 def run_reference(args, rank, world):
@@ -145,6 +154,8 @@ def main():
     ap.add_argument("--impl", default="tcbnn_b200", choices=["tcbnn_b200", "reference"])
     ap.add_argument("--cpu-images", type=int, default=64, help="images in the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sustain-seconds", type=float, default=3.0, help="length of the sustained loop (0 = skip)")
+    ap.add_argument("--check-images", type=int, default=16, help="images checked against the CPU oracle (0 = skip)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -170,17 +181,19 @@ def main():
     sys.stdout.flush()
     json_fd = os.dup(1)
     os.dup2(2, 1)
+    # before any pinned buffer exists: this rank's share of the cores next to its GPU
+    cores = tdist.pin_to_gpu_node(local, int(os.environ.get("LOCAL_WORLD_SIZE", world)))
     tdist.init("nccl", dev)
 
     B = args.batch
     spec = models.resnet18_spec(B)
     shapes = models.layer_shapes(spec)
     weights = models.synthetic_weights(spec, 1234)               # same weights on every rank
-    x_host = torch.from_numpy(models.synthetic_input(spec, tdist.shard_seed(4321, rank))).pin_memory()
+    x_np = models.synthetic_input(spec, tdist.shard_seed(4321, rank))
+    x_host = torch.from_numpy(x_np).pin_memory()
     net = models.Network(spec, weights, x_host, input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND)
-    del weights
     logits_host = torch.empty((B, 1000), dtype=torch.float32).pin_memory()
-    gathered = torch.empty((world * B, 1000), dtype=torch.float32, device=dev) if world > 1 else None
+    gather = tdist.OverlappedGather(B, 1000, torch.float32, dev, world)
 
     def step(events=None):
         if events is None:
@@ -193,16 +206,16 @@ def main():
                 e1.record()
                 events.append((l, e0, e1))
             out = net.layers[-1].get_output_gpu()
-        if world > 1:
-            tdist.gather_logits(out, gathered)
+        gather(out)               # N > 1: staged copy, then the all-gather on a side stream
         return out
 
     def sync():
+        gather.finish()
         tdist.barrier()
         torch.cuda.synchronize()
 
     # clocks and throttle reasons are sampled every 20 ms from before the warm-up on (nvidia-smi
-    # needs a moment to start), and the samples of the timed window are picked out by marks
+    # needs a moment to start), and the samples of each window are picked out by marks
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -220,6 +233,7 @@ def main():
     t0.record()
     for _ in range(args.steps):
         step()
+    gather.finish()
     t1.record()
     sync()
     ms = t0.elapsed_time(t1)
@@ -227,7 +241,32 @@ def main():
     for _ in range(args.steps):
         step(events)
     sync()
-    clocks = sampler.stop(mark0, sampler.mark()) if rank == 0 else None
+    clocks = sampler.summary(mark0, sampler.mark()) if rank == 0 else None
+    logits_resident = net.layers[-1].get_output_gpu().cpu().numpy()
+
+    # ---- the same step for at least three seconds ----------------------------------------
+    # The timed region above lasts a few tens of milliseconds, which the GPU runs at its maximum
+    # clock; this loop is long enough for the power management to settle.
+    n_sus = max(args.steps, int(args.sustain_seconds * 1e3 / (ms / args.steps)) + 1) if args.sustain_seconds > 0 else 0
+    sustained = None
+    if n_sus:
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync()
+        mark_s = sampler.mark()
+        s0.record()
+        for _ in range(n_sus):
+            step()
+        gather.finish()
+        s1.record()
+        sync()
+        ms_sus = tdist.max_over_ranks([s0.elapsed_time(s1)], dev)[0]
+        if rank == 0:
+            c = sampler.summary(mark_s, sampler.mark(), "sustained loop")
+            v = world * B * n_sus / (ms_sus * 1e-3)
+            sustained = {"value": v, "unit": UNIT, "steps": n_sus, "seconds": ms_sus * 1e-3,
+                         "ms_per_step": ms_sus / n_sus, "clocks": c,
+                         "value_at_max_clock": (v * c["sm_max_mhz"] / c["sm_mhz"]) if c.get("sm_mhz") else None,
+                         "note": "graph replays back to back; value_at_max_clock scales by max / median SM MHz"}
 
     # ---- end to end from host buffers ----------------------------------------------------
     # Every step copies its images from pinned host memory and reads its logits back; the copy
@@ -239,14 +278,14 @@ def main():
         feeder = models.HostFeeder(network)
 
         def on_result(out):
-            if world > 1:
-                tdist.gather_logits(out, gathered)
+            gather(out)
 
         feeder.run([batch_host] * 2, on_result, logits_host)
         sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         feeder.run([batch_host] * args.steps, on_result, logits_host)   # ends by waiting for the last read
+        gather.finish()
         e1.record()
         sync()
         return e0.elapsed_time(e1)
@@ -254,11 +293,33 @@ def main():
     ms_e2e_f32 = timed_feed(net, x_host)
     u8_np, lut = models.synthetic_input_u8(spec, tdist.shard_seed(4321, rank))
     x8_host = torch.from_numpy(u8_np).pin_memory()
-    net8 = models.Network(spec, models.synthetic_weights(spec, 1234), x8_host,
+    net8 = models.Network(spec, weights, x8_host,
                           input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND, input_lut=lut)
     ms_e2e = timed_feed(net8, x8_host)
+    logits_e2e = logits_host.numpy().copy()
 
-    ms, ms_e2e, ms_e2e_f32 = tdist.max_over_ranks([ms, ms_e2e, ms_e2e_f32], dev)
+    # ---- what the end-to-end figure is bounded by: the plain host-to-device copy ----------
+    # every rank copies its uint8 batch from pinned memory at the same time, nothing else runs
+    dst8 = torch.empty_like(net8.layers[0].input_gpu)
+    for _ in range(2):
+        dst8.copy_(x8_host, non_blocking=True)
+    sync()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(args.steps):
+        dst8.copy_(x8_host, non_blocking=True)
+    c1.record()
+    sync()
+    ms_copy = c0.elapsed_time(c1)
+
+    ms, ms_e2e, ms_e2e_f32, ms_copy = tdist.max_over_ranks([ms, ms_e2e, ms_e2e_f32, ms_copy], dev)
+
+    # ---- parity of this very run: full-batch logits against the CPU oracle ----------------
+    checked = None
+    if rank == 0 and args.check_images > 0:
+        checked = check_logits(spec, weights, x_np, args.check_images,
+                               {"device_resident": logits_resident, "e2e_uint8": logits_e2e})
+    sampler.stop()
 
     if rank == 0:
         conv_ms, launches = 0.0, 0
@@ -276,42 +337,108 @@ def main():
         ops_per_step = conv_ops(shapes) * B
         achieved = ops_per_step * args.steps / (conv_ms * 1e-3) / 1e12
         peak_b1 = ops.mma_peak(0, 32, 4000)
-        peak = ops.mma_peak(3, 1, 20000)
-        traffic = None
+        peak_i8 = ops.mma_peak(3, 1, 20000)
+        peak = ops.mma_peak(7, 1, 20000)
+        traffic, traffic_note = None, None
         tpath = os.path.join(ROOT, "profiles", "conv_traffic.json")
         if os.path.exists(tpath):
-            traffic = json.load(open(tpath)).get("dram_bytes_per_launch_avg")
+            tj = json.load(open(tpath))
+            traffic, traffic_note = tj.get("dram_bytes_per_launch_scaled"), tj.get("how")
+        value = world * B * args.steps / (ms * 1e-3)
+        e2e_value = world * B * args.steps / (ms_e2e * 1e-3)
+        ceiling = world * B * args.steps / (ms_copy * 1e-3)
         out = {
-            "metric": METRIC, "value": world * B * args.steps / (ms * 1e-3), "unit": UNIT,
+            "metric": METRIC, "value": value, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": world * B * args.steps / (ms * 1e-3) / PUBLISHED_IMAGES_PER_S,
+            "vs_baseline": value / PUBLISHED_IMAGES_PER_S,
             "dtype": "b1/int32", "data": "synthetic",
             "config": {"workload": "C5 ResNet-18 BNN 224x224 (reference driver topology), batch %d per GPU" % B,
                        "l2": "inputs (%.0f MB fp32 images per step) larger than L2" % (x_host.numel() * 4 / 1e6),
-                       "parallelism": "batch-sharded x%d, NCCL all-gather of logits" % world,
+                       "parallelism": "batch-sharded x%d, NCCL all-gather of logits on a side stream" % world,
+                       "cpu_cores_of_rank0": len(cores) if cores else None,
+                       "timed_region": "%d graph replays, %.3f s: a burst at the clock in `clocks`; `sustained` is the >= %.0f s figure"
+                                       % (args.steps, ms * 1e-3, args.sustain_seconds),
                        "baseline_note": "vs_baseline divides by the 5.6 K images/s the reference README quotes for a Turing GPU"},
-            "e2e": {"value": world * B * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+            "e2e": {"value": e2e_value, "unit": UNIT,
                     "h2d_bytes_per_step": x8_host.numel(), "d2h_bytes_per_step": logits_host.numel() * 4,
-                    "input": "uint8 NCHW images + [3][256] fp32 value table (normalisation fused into the first layer)"},
+                    "input": "uint8 NCHW images + [3][256] fp32 value table (normalisation fused into the first layer)",
+                    "frac_of_h2d_ceiling": e2e_value / ceiling},
+            "h2d_ceiling": {"value": ceiling, "unit": UNIT, "gb_per_s_per_gpu": x8_host.numel() * args.steps / (ms_copy * 1e-3) / 1e9,
+                            "what": "all ranks copying their uint8 batch from pinned host memory at once, nothing else running"},
             "e2e_fp32_images": {"value": world * B * args.steps / (ms_e2e_f32 * 1e-3), "unit": UNIT,
                                 "h2d_bytes_per_step": x_host.numel() * 4,
                                 "d2h_bytes_per_step": logits_host.numel() * 4,
                                 "input": "fp32 NCHW images, the reference's interface"},
             "gpu_launches": launches,
             "clocks": clocks,
+            "sustained": sustained,
+            "checked": checked,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s",
-                         "frac": achieved / peak, "traffic": traffic,
-                         "kernel": "tcgen05 int8 implicit-GEMM conv kernels k_conv_umma_ws / _pre / _as (%d layers per step)" % n_conv,
+                         "frac": achieved / peak, "traffic": traffic, "traffic_how": traffic_note,
+                         "kernel": "tcgen05 implicit-GEMM conv kernels k_conv_umma_pre (kind::mxf4) / _ws / _as (kind::i8) (%d layers per step)" % n_conv,
                          "timing": "CUDA event pairs around each layer, a second pass of the same %d steps right after the timed (graph-replayed) one" % args.steps,
-                         "peak_source": "tcgen05.mma kind::i8 128x256x32 issue rate measured in this run by tcbnn_mma_peak(3) (of measured)",
+                         "peak_source": "tcgen05.mma kind::mxf4 128x256x64 issue rate measured in this run by tcbnn_mma_peak(7) (of measured)",
+                         "i8_mma_peak": peak_i8, "frac_of_i8_mma_peak": achieved / peak_i8,
                          "b1_mma_peak": peak_b1, "frac_of_b1_mma_peak": achieved / peak_b1},
             "layer_ms": {k: round(v, 4) for k, v in per_layer.items()},
         }
+        if world == 1:
+            out["reference_gpu_same_box"] = reference_gpu_same_box(models, B / (ms / args.steps * 1e-3))
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(args.cpu_images)
         os.write(json_fd, (json.dumps(out) + "\n").encode())
     tdist.finish()
+    if checked is not None and not checked["ok"]:
+        raise SystemExit("bench.py: logits differ from the CPU oracle: %s" % json.dumps(checked))
+
+
+def check_logits(spec, weights, x_np, images, runs):
+    """The CPU oracle on the first `images` images of rank 0's batch against the logits the GPU
+    computed for them inside the full batch, for each of the named runs.  1e-5 relative."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import numpy as np
+    import networks as onet
+    import oracle as orc
+    L = orc.lib(native=True)
+    orc.use_all_cores(L)
+    n = min(images, x_np.shape[0])
+    acts, _ = onet.run(dict(spec, batch=n), weights, x_np[:n], L=L)
+    ref = acts[-1]
+    res = {"images": n, "rtol": 1e-5, "atol": 1e-5, "ok": True, "max_rel": {}}
+    for name, got in runs.items():
+        g = got[:n, :ref.shape[1]]
+        res["max_rel"][name] = float(np.max(np.abs(g - ref) / np.maximum(np.abs(ref), 1.0)))
+        if not np.allclose(g, ref, rtol=1e-5, atol=1e-5):
+            res["ok"] = False
+    return res
+
+
+def reference_gpu_same_box(models, our_images_per_s):
+    """The reference's own unchanged imagenet_resnet driver (its WMMA kernels, its headers) built
+    for sm_100a into oracle/_ref by the build step, run once here on a synthetic weight file: the
+    time it measures around its forward launch at its hard-coded batch of 512."""
+    import re
+    import tempfile
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_imagenet_resnet")
+    if not os.path.exists(exe):
+        return {"unavailable": "oracle/_ref/ref_imagenet_resnet was not built (the reference tree was absent at build time)"}
+    from tcbnn_b200 import dropin
+    try:
+        with tempfile.TemporaryDirectory() as d:
+            spec = models.resnet18_spec(512)
+            dropin.write_weights(models.synthetic_weights(spec, 5), os.path.join(d, "resnet_imagenet.csv"))
+            r = subprocess.run([exe], cwd=d, capture_output=True, text=True, timeout=600)
+        m = re.search(r"TCBNN_REF_INFERENCE_MS ([0-9.]+) (.*)", r.stdout)
+        if r.returncode != 0 or not m or m.group(2).strip() != "no error":
+            return {"unavailable": "the reference driver did not finish: rc %d %s" % (r.returncode, (r.stderr or r.stdout)[-200:])}
+        ref_ms = float(m.group(1))
+        v = 512 / (ref_ms * 1e-3)
+        return {"value": v, "unit": UNIT, "batch": 512, "ms": ref_ms,
+                "what": "reference imagenet_resnet.cu, unchanged, reference headers, compiled for sm_100a; one cold cooperative launch timed by its own events",
+                "tcbnn_b200_over_reference": our_images_per_s / v}
+    except (OSError, subprocess.SubprocessError) as e:
+        return {"unavailable": "could not run the reference driver: %s" % e}
 
 
 def cpu_baseline(images):

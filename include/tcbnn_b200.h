@@ -49,14 +49,20 @@ size_t tcbnn_gemm_workspace_bytes(int M, int N, int K);
 /* Which kernel the GEMM family uses: 0 = automatic, 1 = always the warp-level b1 MMA kernel.
  * Process-wide; for tests and measurements.  tcbnn_gemm_status reads the tcgen05 GEMM kernel's
  * device-side status word (synchronises): 0 = fine, 1 = a bounded wait inside it gave up and the
- * last results are not valid.  No reference counterparts. */
+ * results since the last reading are not valid; reading a non-zero status clears it.  No reference
+ * counterparts. */
 int tcbnn_set_gemm_path(int path);
 int tcbnn_gemm_status(int* status);
 /* How many kernels a GEMM-family call of this shape launches when given a workspace of that size
  * (1, 2 with split K, 4 on the tcgen05 path); for callers that account for their launches. */
 int tcbnn_gemm_launches(int M, int N, int K, size_t workspace_bytes);
 
-/* C[m][n] = K - 2*popc(A[m] xor B[n]), int32 [M][ldc].
+/* GEMM family (the next three entry points): the pad bits of every row of A and of B / W -- the
+ * bits past element K up to the leading dimension -- must be zero, as tcbnn_pack_rows,
+ * tcbnn_pack_fc_weight and the layer outputs leave them.  (The warp-level kernel counts whole
+ * 64-bit words and relies on equal pads cancelling; the tcgen05 kernel masks them; which one runs
+ * depends on shape and workspace, so non-zero pads give shape-dependent results.)
+ * C[m][n] = K - 2*popc(A[m] xor B[n]), int32 [M][ldc].
  * BMMA / BMMAS_new, bmm/tensorcore_kernel.cu:138-356 (C = K - 2*acc at :331). */
 int tcbnn_bgemm(const uint32_t* A, const uint32_t* B, int M, int N, int K, int lda, int ldb,
                 int32_t* C, int ldc, void* workspace, size_t workspace_bytes, void* stream);
@@ -165,7 +171,8 @@ int tcbnn_set_conv_path(int path);
 int tcbnn_conv_set_trace(void* device_buffer);
 /* Reads the layer's device-side status word (synchronises): 0 = fine, 1 = a bounded wait inside
  * the tcgen05 kernel gave up and the layer's output is not valid, 2 = a residual value did not
- * fit the int16 element size the caller chose. */
+ * fit the int16 element size the caller chose.  The word collects failures of every call since
+ * tcbnn_conv_prepare or the last reading; reading a non-zero status clears it. */
 int tcbnn_conv_status(const tcbnn_conv_desc* d, const void* prepared, int* status);
 
 /* First layer on fp32 NCHW input [B][3][H][W] (d->C must be 3).
@@ -179,11 +186,16 @@ int tcbnn_inconv_layer(const tcbnn_conv_desc* d, const float* x, const uint32_t*
 /* No counterpart in the reference.  Same result as tcbnn_fc_layer, for callers that must not
  * allocate device memory around the call: a process whose own arena already holds all of the
  * GPU's memory (so a cudaMalloc for a workspace would fail or fragment it), or a serving loop
- * that cannot afford the device-wide synchronisation an allocation implies.  The split-K
- * partial sums go to a fixed array inside the library (tcbnn_noalloc_scratch_bytes() bytes,
- * 8 MiB; resident on every GPU that loads the library until the process exits) instead of a
- * caller workspace.  The call itself performs no cudaMalloc / cudaFree and uses no allocating
- * library routine.
+ * that cannot afford the device-wide synchronisation an allocation implies.  The scratch the
+ * layer needs (the split-K partial sums; for large problems, when they fit, the +-1 byte copies of
+ * both operands that the tcgen05 kernel reads, as with a caller workspace) goes to a fixed array
+ * inside the library (tcbnn_noalloc_scratch_bytes() bytes, 8 MiB; resident on every GPU that
+ * loads the library until the process exits) instead of a caller workspace.  The call itself
+ * performs no cudaMalloc / cudaFree and uses no allocating library routine.
+ *   - The array is part of the library's device code: the CUDA runtime places it on a device
+ *     when the library's code is first used there.  A caller whose arena takes all of the GPU's
+ *     memory must make one call into the library on that device (any entry point that launches,
+ *     or this one) BEFORE the arena is created, or the 8 MiB will not be there to place.
  *   - Shapes whose split-K partials (splits * M * N * 4 bytes) exceed the array are rejected
  *     with an error.
  *   - The first call on each device looks up the array's device address (with that device
@@ -246,7 +258,9 @@ int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, lo
  * ignored).  Kinds 4-6 measure what the issuing thread's bookkeeping costs a tcgen05 stream of
  * 128x128x32 MMAs issued in groups of warps_per_sm: 4 = nothing between the groups, 5 = a lone
  * lane doing mbarrier.try_wait + tcgen05.commit per group, 6 = the converged warp doing
- * mbarrier.test_wait and the elect.sync lane issuing and committing.  Returns tera-ops/s
+ * mbarrier.test_wait and the elect.sync lane issuing and committing.  Kind 7 = tcgen05.mma
+ * kind::mxf4 128x256x64 (e2m1 operands +-1.0, unit ue8m0 block scales, fp32 accumulators), with the
+ * accumulators checked against the exact sum; at most 2^18 iterations.  Returns tera-ops/s
  * (2*m*n*k per MMA) in *tops.
  * Synchronises the device.  The reference's counterpart is the WMMA latency probe
  * bmm/bmma_op_test/main_test.cu:35-220 and its TOPS formula at :368. */

@@ -16,6 +16,16 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def default_ref_root():
+    """Where the reference tree (pnnl/TCBNN) is looked for when no --ref-root is given: the
+    TCBNN_REF_ROOT environment variable, else a folder named `reference` beside this repository.
+    Nothing is built from it when it does not exist."""
+    env = os.environ.get("TCBNN_REF_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def _run(cmd):
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
@@ -39,7 +49,8 @@ def build_oracle(native=False):
     return out
 
 
-def build_ref(ref_root="/root/reference"):
+def build_ref(ref_root=None):
+    ref_root = ref_root or default_ref_root()
     tc = os.path.join(ref_root, "bmm", "tensorcore_kernel.cu")
     mt = os.path.join(ref_root, "bmm", "bmma_op_test", "main_test.cu")
     bc = os.path.join(ref_root, "bconv", "bmma_kernel.cu")
@@ -64,12 +75,13 @@ def build_ref(ref_root="/root/reference"):
 REF_DRIVERS = ["mnist_mlp", "cifar10_vgg", "cifar10_resnet", "imagenet_resnet"]
 
 
-def build_ref_drivers(ref_root="/root/reference"):
+def build_ref_drivers(ref_root=None):
     """The reference's unchanged drivers with the reference's own headers (WMMA b1 kernels) for
     sm_100a: _ref/ref_<driver>.  Compiled from the sources where they lie (nothing is copied);
     only the dataset readers are replaced (seeded synthetic images, the drop-in's
     synthetic_data.cpp, libjpeg stubbed) and ref_driver_shim.h is force-included so that the
     drivers print the time they measure.  Flags as the reference Makefile (:15)."""
+    ref_root = ref_root or default_ref_root()
     if not os.path.exists(os.path.join(ref_root, "kernel.cuh")):
         return []
     outdir = os.path.join(HERE, "_ref")
@@ -94,12 +106,13 @@ def build_ref_drivers(ref_root="/root/reference"):
         return [b for b in pool.map(one, REF_DRIVERS) if b]
 
 
-def build_ref_runner(ref_root="/root/reference"):
+def build_ref_runner(ref_root=None):
     """tcbnn_b200/dropin/net_runner.cu (this repository's generic driver on the reference's public
     API: network from a text description, one cooperative kernel, logits and every layer's
     download_full_output() to files) compiled against the REFERENCE's own utility.h / param.h /
     kernel.cuh: _ref/ref_net_runner, the layer-by-layer pin of the oracle.  The runner source is
     staged next to the binary so that its quote-includes resolve to the reference's headers."""
+    ref_root = ref_root or default_ref_root()
     if not os.path.exists(os.path.join(ref_root, "kernel.cuh")):
         return None
     import shutil
@@ -120,7 +133,7 @@ def build_ref_runner(ref_root="/root/reference"):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--native", action="store_true")
-    ap.add_argument("--ref-root", default="/root/reference")
+    ap.add_argument("--ref-root", default=None, help="reference tree (default: $TCBNN_REF_ROOT, else ../reference)")
     a = ap.parse_args()
     print(build_oracle(False))
     if a.native:

@@ -182,6 +182,61 @@ __device__ __forceinline__ uint4 expand16(uint32_t h) {
     return make_uint4(v[0], v[1], v[2], v[3]);
 }
 
+// ---- 4-bit operands: tcgen05.mma kind::mxf4 ------------------------------------------------
+// +1 / -1 are exact in e2m1 (0x2 / 0xA), zero is 0x0, and with unit ue8m0 block scales (byte 0x7F)
+// the fp32 accumulator of a +-1 contraction is the exact integer sum (every partial sum is an
+// integer far below 2^24).  An MMA is 128 x N x 64: twice the MAC rate of kind::i8 at half the
+// operand bytes (measured by tcbnn_mma_peak kind 7).  Layout as for int8, K-major without
+// swizzle, except that a 16-byte core-matrix row now holds 32 channels and one MMA spans two of
+// them (`lbo` apart).
+// 8 packed bits -> 8 nibbles (bit i -> nibble i; 1 -> +1.0, 0 -> -1.0)
+__host__ __device__ __forceinline__ uint32_t expand8_f4(uint32_t b) {
+    uint32_t x = b & 0xFFu;
+    x = (x | (x << 12)) & 0x000F000Fu;
+    x = (x | (x << 6)) & 0x03030303u;
+    x = (x | (x << 3)) & 0x11111111u;
+    return 0xAAAAAAAAu ^ (x << 3);
+}
+// 32 packed bits -> 16 bytes; bits 31..24 (the chunk's channels 0-7) land in .x, 7..0 in .w.
+// Activations and filters both go through this function, so the order inside a word cancels.
+__host__ __device__ __forceinline__ uint4 expand32_f4(uint32_t w) {
+    return make_uint4(expand8_f4(w >> 24), expand8_f4(w >> 16), expand8_f4(w >> 8), expand8_f4(w));
+}
+// Instruction descriptor of the block-scaled kinds: e2m1 x e2m1, ue8m0 scales, K-major, M = 128,
+// K = 64, scale-factor ids 0.
+__host__ __device__ constexpr uint32_t idesc_f4(int n) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+}
+// D[tmem] (+)= A * B with the scale factors read from tensor memory at sfa / sfb; descriptors as
+// (low, high) register pairs like mma_i8_split.
+__device__ __forceinline__ void mma_f4_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                             uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t sfa, uint32_t sfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], da, db, %5, [%7], [%8], p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate),
+          "r"(sfa), "r"(sfb));
+}
+// Columns [col, col + 32) of the calling warp's 32 lanes of tensor memory := unit scales (every
+// byte 0x7F), so a scale reads as 1.0 wherever in the region the hardware looks it up.  Whole
+// warp; warps 0-3 of a warpgroup cover the 128 lanes between them (warp w -> lanes 32*(w%4)..).
+__device__ __forceinline__ void tmem_fill_unit_scales(uint32_t tmem, uint32_t col) {
+    const uint32_t base = tmem + ((uint32_t)(((threadIdx.x >> 5) & 3) * 32) << 16) + col;
+#pragma unroll
+    for (int c = 0; c < 32; c += 8)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};"
+                     ::"r"(base + c), "r"(0x7F7F7F7Fu) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// fp32 accumulator holding an integer of magnitude below 2^22 -> that integer, exactly
+__device__ __forceinline__ int f4_acc_to_int(int raw) {
+    return __float_as_int(__int_as_float(raw) + 12582912.0f) - 0x4B400000;
+}
+
 // Four consecutive residual channels (element index i, a multiple of 4) widened to int32.
 __device__ __forceinline__ int4 ld_res4(const void* p, int bytes, size_t i) {
     if (bytes == 2) {

@@ -1,14 +1,18 @@
-// tcgen05 binary convolution fed from a pre-expanded input (stride 1, C <= 128).
+// tcgen05 binary convolution fed from a pre-expanded input (stride 1, C <= 512), 4-bit operands:
+// tcgen05.mma kind::mxf4 on +-1.0 as e2m1 with unit block scales (bconv_umma.cuh), 128 x NT x 64
+// per instruction -- one MMA per filter tap and 64-channel block.
 //
 // In bconv_umma_ws.cuh seven warps of every CTA turn packed bits into +-1 bytes, stage by
 // stage, next to the epilogue warps; with 16 warps per SM that chain of dependent scalar
-// instructions is what the narrow layers (64 / 128 channels) wait for.  Here the expansion is a
-// separate streaming pass (expand_raster below: full occupancy, HBM-bound, 8 bytes in and 64 out
-// per pixel and 64-channel block) that writes the layer's input as +-1 bytes straight in the
-// layout the MMA wants: for every 16-channel chunk a plane [raster position][16 bytes] over the
-// zero-padded virtual raster of bconv_umma.cuh, zeros on the dead bands.  A tile's patch is
-// then four contiguous runs per 64-channel block, which one thread fetches with bulk
-// asynchronous copies (cp.async.bulk + mbarrier complete_tx).  The CTA becomes
+// instructions is what the layers wait for.  Here the expansion is done by whoever produces the
+// input -- the previous layer's epilogue, or a separate streaming pass (expand_raster below: full
+// occupancy, HBM-bound, 8 bytes in and 32 out per pixel and 64-channel block) -- which writes it
+// as +-1 nibbles straight in the layout the MMA wants: for every 32-channel chunk a plane
+// [raster position][16 bytes] over the zero-padded virtual raster of bconv_umma.cuh, zeros on the
+// dead bands.  A tile's patch is then two contiguous runs per 64-channel block, which one thread
+// fetches with bulk asynchronous copies (cp.async.bulk + mbarrier complete_tx).  With half a byte
+// per channel the filter block of 128 output channels stays resident up to 256 input channels
+// (64 output channels at 512), so the wide layers run filter-stationary too.  The CTA becomes
 //
 //   warps 0-15  epilogue   : warp w reads TMEM lanes 32*(w%4).., columns (w/4) * NT/4 ..
 //   warp  16    loader     : one lane, bulk copies of the patch planes into the stage ring
@@ -35,11 +39,11 @@ __host__ __device__ inline long long pre_plane_positions(long long NV, int npos,
     return ((front + ((NV + 127) / 128) * 128 + npos + 7) & ~7LL);
 }
 __host__ __device__ inline size_t pre_smem_bytes(int npos, int C, int RS, int nt, int stages) {
-    return (size_t)stages * 4 * npos * 16 + (size_t)RS * C * nt + nt * 4 + RS * 8 + 40 * 8 + 64;
+    return (size_t)stages * 2 * npos * 16 + (size_t)RS * C * nt / 2 + nt * 4 + RS * 8 + 40 * 8 + 64;
 }
 
-// packed bits [B][H][W][C/32] -> planes [C/16][plane_positions][16 B] of +-1 bytes, zero where the
-// raster position is padding or outside the batch
+// packed bits [B][H][W][C/32] -> planes [C/32][plane_positions][16 B] of +-1 nibbles, zero where
+// the raster position is padding or outside the batch
 __device__ __forceinline__ void expand_raster(const ConvWsArgs& a, uint4* planes, long long plane_positions,
                                               long long front) {
     const int NCB = a.C >> 6, Cw = a.C >> 5;
@@ -49,41 +53,39 @@ __device__ __forceinline__ void expand_raster(const ConvWsArgs& a, uint4* planes
         const int cb = (int)(i / plane_positions);
         const long long slot = i - (long long)cb * plane_positions;
         const long long gq = slot - front;
-        uint4 e0 = make_uint4(0u, 0u, 0u, 0u), e1 = e0, e2 = e0, e3 = e0;
+        uint4 e0 = make_uint4(0u, 0u, 0u, 0u), e1 = e0;
         if (gq >= 0 && gq < a.NV) {
             const int vy = fastdiv((int)gq, a.pw_mul, a.pw_sh), vx = (int)gq - vy * a.PW;
             const int n = fastdiv(vy, a.vh_mul, a.vh_sh), vr = vy - n * a.VH;
             if (vr < a.H && vx < a.W) {
                 const uint2 b = ldg64(a.in + ((size_t)(n * a.H + vr) * a.W + vx) * Cw + cb * 2);
-                e0 = expand16(b.x >> 16); e1 = expand16(b.x & 0xFFFFu);
-                e2 = expand16(b.y >> 16); e3 = expand16(b.y & 0xFFFFu);
+                e0 = expand32_f4(b.x); e1 = expand32_f4(b.y);
             }
         }
-        uint4* dst = planes + (size_t)(cb * 4) * plane_positions + slot;
+        uint4* dst = planes + (size_t)(cb * 2) * plane_positions + slot;
         dst[0] = e0;
         dst[(size_t)plane_positions] = e1;
-        dst[(size_t)2 * plane_positions] = e2;
-        dst[(size_t)3 * plane_positions] = e3;
     }
 }
 
 template <int NT>
 __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
-    // All 512 columns of tensor memory serve as accumulators (8 at NT = 64) and the patch ring is
-    // as deep as shared memory allows, so that no role waits on another's latency.
-    constexpr uint32_t TM_COLS = 512;
-    constexpr int NACC = NT >= 128 ? 2 : ((512 / NT) > 8 ? 8 : (512 / NT));   // measured: deeper does not pay at NT = 128
+    // Tensor memory: accumulators (7 at NT = 64) below column 480, the unit block scales of the
+    // 4-bit MMA above it; the patch ring is as deep as shared memory allows, so that no role waits
+    // on another's latency.
+    constexpr uint32_t TM_COLS = 512, SF_COL = 480;
+    constexpr int NACC = NT >= 128 ? 2 : ((SF_COL / NT) > 8 ? 8 : (SF_COL / NT));   // measured: deeper does not pay at NT = 128
     const int NSTAGE = a.pre_stages;
     constexpr int COLS = NT / 4;                      // accumulator columns per epilogue thread
     static_assert(COLS == 8 || COLS == 16 || COLS == 32, "n-tile of 32, 64 or 128");
     constexpr int LOAD_WARP = kPreEpiThreads / 32, MMA_WARP = LOAD_WARP + 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int RS = a.R * a.S, NCB = a.C >> 6;
-    const uint32_t stage_bytes = 4u * a.NPOS * 16u;
+    const uint32_t stage_bytes = 2u * a.NPOS * 16u;           // two 32-channel chunk planes
 
     unsigned char* sAraw = smem;
     uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
-    int* sThr = reinterpret_cast<int*>(sB + (size_t)RS * (a.C >> 4) * NT);
+    int* sThr = reinterpret_cast<int*>(sB + (size_t)RS * (a.C >> 5) * NT);
     uint32_t* sTapK = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sThr + NT) + 7) & ~(uintptr_t)7);
     uint64_t* sBar = reinterpret_cast<uint64_t*>(sTapK + 2 * RS);
     // barriers: a_full[8], a_empty[8], acc_full[8], acc_empty[8]
@@ -109,8 +111,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     }
     if (warp == MMA_WARP) tmem_alloc(smem_u32(sTmem), TM_COLS);
     {
-        const uint4* src = a.wi8 + (size_t)nt * RS * (a.C >> 4) * NT;
-        const int nB = RS * (a.C >> 4) * NT;
+        const uint4* src = a.wf4 + (size_t)nt * RS * (a.C >> 5) * NT;
+        const int nB = RS * (a.C >> 5) * NT;
         for (int i = tid; i < nB; i += kPreThreads) sB[i] = __ldg(src + i);
         for (int i = tid; i < NT; i += kPreThreads) {
             // integer form of  !((float)v < thr)  (kernel.cuh:795-796): v >= ceil(thr)
@@ -122,9 +124,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             sThr[i] = it;
         }
         for (int t = tid; t < RS; t += kPreThreads) {
-            const uint32_t byte_off = (uint32_t)((t / a.S) * a.PW + (t % a.S)) * 16u;
-            sTapK[2 * t] = byte_off >> 4;
-            sTapK[2 * t + 1] = (byte_off + 2u * (uint32_t)a.NPOS * 16u) >> 4;
+            sTapK[t] = (uint32_t)((t / a.S) * a.PW + (t % a.S));     // patch offset in 16-byte units
         }
     }
     fence_proxy_async();
@@ -132,6 +132,10 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *sTmem;
+    if (warp < 4) tmem_fill_unit_scales(tmem, SF_COL);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
     const WsWait wait{sAbort, a.err_flag};
 
     if (warp == LOAD_WARP) {
@@ -149,9 +153,9 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     mbar_expect_tx(BAR_AFULL(s), stage_bytes);
                     const uint32_t dst = smem_u32(sAraw + (size_t)s * stage_bytes);
 #pragma unroll
-                    for (int c = 0; c < 4; c++)
+                    for (int c = 0; c < 2; c++)
                         bulk_g2s(dst + c * (uint32_t)a.NPOS * 16u,
-                                 a.pre + (size_t)(cb * 4 + c) * a.pre_positions + slot0,
+                                 a.pre + (size_t)(cb * 2 + c) * a.pre_positions + slot0,
                                  (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
                     if (++s == NSTAGE) { s = 0; sph ^= 1; }
                 }
@@ -182,8 +186,9 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             const uint64_t descB0 = smem_desc(smem_u32(sB), lboB, 128u);
             const uint32_t aHi = (uint32_t)(descA0 >> 32), bHi = (uint32_t)(descB0 >> 32);
             const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0;
-            const uint32_t stepB = (2u * lboB) >> 4, stepStage = stage_bytes >> 4;
-            constexpr uint32_t IDESC = idesc_i8(NT);
+            const uint32_t stepB = (2u * lboB) >> 4, stepStage = stage_bytes >> 4;   // one tap = two chunks of B
+            constexpr uint32_t IDESC = idesc_f4(NT);
+            const uint32_t sfa = tmem + SF_COL, sfb = tmem + SF_COL + 16;
             const bool rs9 = RS == 9;
             uint32_t it = 0, tc = 0, sph = 0, bph = 0;
             int s = 0, b = 0;
@@ -205,20 +210,17 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     if (leader) {
                     if (rs9) {
 #pragma unroll
-                        for (int i = 0; i < 18; i++) {
-                            // tap (r, s), k-step ks: patch offset (r*PW + s) positions, + two chunk planes
-                            const int t = i >> 1, ks = i & 1;
-                            const uint32_t aoff = (uint32_t)((t / 3) * a.PW + (t % 3)) + ks * 2u * (uint32_t)a.NPOS;
-                            mma_i8_split(d, aLo + aoff, aHi, bLo + i * stepB, bHi, IDESC, i == 0 ? acc : 1u);
+                        for (int t = 0; t < 9; t++) {
+                            // tap (r, s): patch offset (r*PW + s) positions
+                            const uint32_t aoff = (uint32_t)((t / 3) * a.PW + (t % 3));
+                            mma_f4_split(d, aLo + aoff, aHi, bLo + t * stepB, bHi, IDESC, t == 0 ? acc : 1u, sfa, sfb);
                         }
-                        bLo += 18 * stepB;
+                        bLo += 9 * stepB;
                     } else {
                         for (int t = 0; t < RS; t++) {
-                            const uint2 ao = *reinterpret_cast<const uint2*>(sTapK + 2 * t);
-                            mma_i8_split(d, aLo + ao.x, aHi, bLo, bHi, IDESC, acc);
-                            mma_i8_split(d, aLo + ao.y, aHi, bLo + stepB, bHi, IDESC, 1u);
+                            mma_f4_split(d, aLo + sTapK[t], aHi, bLo, bHi, IDESC, acc, sfa, sfb);
                             acc = 1;
-                            bLo += 2 * stepB;
+                            bLo += stepB;
                         }
                     }
                     acc = 1;
@@ -320,6 +322,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_CEMPTY(b));
             if (++b == NACC) { b = 0; bph ^= 1; }
+#pragma unroll
+            for (int j = 0; j < COLS; j++) v[j] = f4_acc_to_int(v[j]);     // fp32 accumulators, exact integers
             if (q.live && a.acc_out) {
                 int4* dst = reinterpret_cast<int4*>(a.acc_out + q.opix * a.O + o0);
 #pragma unroll

@@ -30,6 +30,7 @@ namespace umma {
 struct ConvWsArgs {
     const uint32_t* in;       // [B][H][W][C/32]
     const uint4* wi8;         // [n-tile][64-ch block][tap][4 chunks][NT][16 B]
+    const uint4* wf4;         // 4-bit form for bconv_umma_pre.cuh: [n-tile][64-ch block][tap][2 chunks][NT][16 B]
     const float* thr;         // [O]
     int B, H, W, C, O, R, S, pad_h, pad_w, stride;
     int OHg, OWg;             // outputs per image (pre-pool == post-pool here)
@@ -44,7 +45,7 @@ struct ConvWsArgs {
     const uint4* pre;         // pre-expanded input planes (bconv_umma_pre.cuh), else null
     long long pre_positions, pre_front;
     int pre_stages;           // patch ring depth of that kernel
-    // optional: also write the output as +-1 bytes into the next layer's input planes
+    // optional: also write the output as +-1 nibbles into the next layer's input planes
     // (bconv_umma_pre.cuh layout over THAT layer's raster; dead slots stay as the caller zeroed them)
     uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
     const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
@@ -98,23 +99,38 @@ __host__ inline void fastdiv_setup(int d, uint32_t* mul, uint32_t* sh) {
     *mul = (uint32_t)((((unsigned long long)1 << (31 + s)) + d - 1) / d);
 }
 
-// Writes the +-1 bytes of `nbits` output channels (8, 16 or 32; first channel o0, a multiple of
-// nbits; channel c at bit nbits-1-c of `word`) of output pixel (n, y, x) into the next layer's planes.
+// filter bits [O][R*S][Cw] -> e2m1 nibble blocks in the order bconv_umma_pre.cuh keeps them in
+// shared memory: [n-tile][64-ch block][tap][32-ch chunk][n][16 B]
+__device__ __forceinline__ void prepare_filter_f4(const uint32_t* fbits, int O, int RS, int C,
+                                                  int nt, uint4* out) {
+    const int Cw = C >> 5, ncb = C >> 6;
+    const long long total = (long long)O * RS * Cw;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int n = (int)(i % nt);
+        long long r = i / nt;
+        const int c2 = (int)(r & 1); r >>= 1;
+        const int tap = (int)(r % RS); r /= RS;
+        const int cb = (int)(r % ncb);
+        const int tile = (int)(r / ncb);
+        const int o = tile * nt + n;
+        out[i] = expand32_f4(fbits[((size_t)o * RS + tap) * Cw + cb * 2 + c2]);
+    }
+}
+
+// Writes the +-1 nibbles of `nbits` output channels (8, 16 or 32; first channel o0, a multiple of
+// nbits; channel c at bit nbits-1-c of `word`) of output pixel (n, y, x) into the next layer's
+// planes: one 16-byte slot per raster position and 32-channel chunk (expand32_f4 order).
 __device__ __forceinline__ void store_next_planes(const ConvWsArgs& a, int n, int y, int x, int o0,
                                                   uint32_t word, int nbits) {
-    uint4* base = a.nxt + (size_t)(o0 >> 4) * a.nxt_positions + a.nxt_front +
+    uint4* base = a.nxt + (size_t)(o0 >> 5) * a.nxt_positions + a.nxt_front +
                   ((long long)n * a.nxt_VH + y) * a.nxt_PW + x;
     if (nbits == 32) {
-        base[0] = expand16(word >> 16);
-        base[(size_t)a.nxt_positions] = expand16(word & 0xFFFFu);
-    } else if (nbits == 16) {
-        base[0] = expand16(word & 0xFFFFu);
-    } else {                                    // 8 channels: half of a 16-channel chunk
-        const bool high = (o0 & 8) == 0;        // channels 0-7 of the chunk sit in bits 15..8
-        const uint4 e = expand16(high ? (word & 0xFFu) << 8 : (word & 0xFFu));
-        uint2* half = reinterpret_cast<uint2*>(base);
-        if (high) half[1] = make_uint2(e.z, e.w);
-        else half[0] = make_uint2(e.x, e.y);
+        base[0] = expand32_f4(word);
+    } else if (nbits == 16) {                   // half a chunk: channels 0-15 are its first 8 bytes
+        reinterpret_cast<uint2*>(base)[(o0 >> 4) & 1] = make_uint2(expand8_f4(word >> 8), expand8_f4(word));
+    } else {                                    // 8 channels: one 32-bit word of the slot
+        reinterpret_cast<uint32_t*>(base)[(o0 >> 3) & 3] = expand8_f4(word);
     }
 }
 

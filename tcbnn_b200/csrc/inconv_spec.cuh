@@ -44,7 +44,7 @@ struct SpecArgs {
     int res_out_bytes, res_out_ld;
     float* acc_out;
     unsigned total;            // pre-pool pixels
-    // optional: the output also as +-1 bytes in the next layer's input planes (bconv_umma_pre.cuh)
+    // optional: the output also as +-1 nibbles in the next layer's input planes (bconv_umma_pre.cuh)
     uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
 };
 
@@ -82,13 +82,13 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
          "  uint32_t* out; long long out_image_stride; void* res_out; int res_out_bytes, res_out_ld;\n"
          "  float* acc_out; unsigned total;\n"
          "  uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH; };\n"
-         // 16 packed bits -> 16 bytes of +1 / -1, the byte order the conv kernels' filters use
-         "__device__ __forceinline__ uint4 expand16(uint32_t h) {\n"
-         "  uint32_t v[4];\n"
-         "#pragma unroll\n"
-         "  for (int g = 0; g < 4; g++) { const uint32_t nb = (h >> (4 * g)) & 0xFu;\n"
-         "    const uint32_t y = (nb * 0x00204081u) & 0x01010101u; v[g] = ~(y * 0xFEu); }\n"
-         "  return make_uint4(v[0], v[1], v[2], v[3]); }\n";
+         // 32 packed bits -> 32 nibbles of +1 / -1 (e2m1), the order the conv kernels' filters use
+         // (expand32_f4 in bconv_umma.cuh)
+         "__device__ __forceinline__ uint32_t expand8_f4(uint32_t b) {\n"
+         "  uint32_t x = b & 0xFFu; x = (x | (x << 12)) & 0x000F000Fu; x = (x | (x << 6)) & 0x03030303u;\n"
+         "  x = (x | (x << 3)) & 0x11111111u; return 0xAAAAAAAAu ^ (x << 3); }\n"
+         "__device__ __forceinline__ uint4 expand32_f4(uint32_t w) {\n"
+         "  return make_uint4(expand8_f4(w >> 24), expand8_f4(w >> 16), expand8_f4(w >> 8), expand8_f4(w)); }\n";
     for (int half = 0; half < nhalf; half++) {
     const int OB = 64 * half, O = Oall - OB < 64 ? Oall - OB : 64;
     // VEC (stride 4 only, image rows a multiple of 4 pixels, aligned base): a thread's taps of one
@@ -181,8 +181,8 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
     s += "\n";
     emit(s, "     if (c.nxt) { uint4* pl = c.nxt + c.nxt_front + ((long long)n * c.nxt_VH + (y / %d)) * c.nxt_PW + (x / %d);\n",
          h.pool, h.pool);
-    for (int k = 0; k < (O + 15) / 16; k++)
-        emit(s, "       pl[(size_t)%d * c.nxt_positions] = expand16((w%d >> %d) & 0xFFFFu);\n", OB / 16 + k, k / 2, (k & 1) ? 0 : 16);
+    for (int k = 0; k < (O + 31) / 32; k++)
+        emit(s, "       pl[(size_t)%d * c.nxt_positions] = expand32_f4(w%d);\n", OB / 32 + k, k);
     s += "     }\n   } }\n";
     // residual = (int)acc (kernel.cuh:666-668), optional fp32 accumulators
     s += " const size_t opix = ((size_t)n * P + y) * Q + x;\n"

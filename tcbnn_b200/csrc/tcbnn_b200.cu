@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstdarg>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 using namespace tcbnn;
@@ -39,13 +40,32 @@ int sm_count(int* sms) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail("no CUDA device: %s", cudaGetErrorString(e));
-    static int cache[64] = {0};
-    if (dev < 64 && cache[dev]) { *sms = cache[dev]; return 0; }
+    // per-device caches are shared by every host thread that drives a GPU of its own
+    static std::atomic<int> cache[64];
+    if (dev >= 0 && dev < 64) {
+        const int c = cache[dev].load(std::memory_order_relaxed);
+        if (c) { *sms = c; return 0; }
+    }
     int n = 0;
     e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess || n <= 0) return fail("cannot query SM count: %s", cudaGetErrorString(e));
-    if (dev < 64) cache[dev] = n;
+    if (dev >= 0 && dev < 64) cache[dev].store(n, std::memory_order_relaxed);
     *sms = n;
+    return 0;
+}
+
+// First-use configuration of a kernel on the current device (opt-in shared memory size): done once
+// per device, under a lock, because callers may drive several GPUs from threads of one process.
+std::mutex g_configure_mutex;
+template <class F>
+int configure_once(bool (&done)[64], F&& configure) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(g_configure_mutex);
+    if (dev >= 0 && dev < 64 && done[dev]) return 0;
+    const cudaError_t e = configure();
+    if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    if (dev >= 0 && dev < 64) done[dev] = true;
     return 0;
 }
 
@@ -158,13 +178,10 @@ GemmUmmaPlan gemm_umma_plan(int M, int N, int K, int sms) {
 
 int run_gemm_umma(const GemmArgs& g, const GemmUmmaPlan& p, void* workspace, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)umma::kGemmSmem);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured[dev] = true;
-    }
+    if (configure_once(configured, [] {
+            return cudaFuncSetAttribute(k_gemm_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)umma::kGemmSmem);
+        }))
+        return 1;
     char* w = (char*)workspace;
     k_expand_rows<<<elementwise_grid((long long)p.MT * p.KB * 512, sms), 256, 0, st>>>(g.A, g.M, g.lda, g.K, p.MT, p.KB,
                                                                                      (uint4*)(w + p.off_ea));
@@ -175,14 +192,19 @@ int run_gemm_umma(const GemmArgs& g, const GemmUmmaPlan& p, void* workspace, int
     a.ea = (const unsigned char*)(w + p.off_ea); a.ew = (const unsigned char*)(w + p.off_ew);
     a.M = g.M; a.N = g.N; a.KB = p.KB; a.MT = p.MT; a.NT = p.NT; a.splits = p.splits; a.per = p.per;
     a.partial = (int32_t*)(w + p.off_partial);
-    static int* status_addr[64] = {nullptr};
-    if (dev >= 64 || !status_addr[dev]) {
-        int* q = nullptr;
-        CUDA_TRY(cudaGetSymbolAddress((void**)&q, g_gemm_status));
-        if (dev < 64) status_addr[dev] = q;
-        a.status = q;
-    } else {
-        a.status = status_addr[dev];
+    {
+        static int* status_addr[64] = {nullptr};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::lock_guard<std::mutex> lock(g_configure_mutex);
+        if (dev < 0 || dev >= 64 || !status_addr[dev]) {
+            int* q = nullptr;
+            CUDA_TRY(cudaGetSymbolAddress((void**)&q, g_gemm_status));
+            if (dev >= 0 && dev < 64) status_addr[dev] = q;
+            a.status = q;
+        } else {
+            a.status = status_addr[dev];
+        }
     }
     k_gemm_umma<<<((p.MT + 1) / 2) * p.NT * p.splits, umma::kGemmThreads, umma::kGemmSmem, st>>>(a);
     if (launch_check("gemm (tcgen05)")) return 1;
@@ -245,6 +267,8 @@ struct PreparedLayout {
     size_t pre_bytes;     // workspace size, 0 when the layer is not eligible
     size_t pre_smem;
     int pre_stages;
+    int pre_nt;           // its n-tile (output channels of the resident filter block)
+    size_t off_wf4;       // its filter copy: e2m1 nibbles
     long long pre_positions, pre_front;
     int as_npos;          // 0 when the layer is not eligible
     size_t pool_bytes;    // scratch the activation-stationary kernel can use to pre-pool a residual
@@ -289,6 +313,7 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
     L.umma_pw = L.umma_vh = L.umma_back_y = L.umma_back_x = 0;
     L.as_npos = 0; L.as_smem = 0; L.as_slots = 0; L.off_wi8_as = o;
     L.pre_bytes = 0; L.pre_smem = 0; L.pre_stages = 0; L.pool_bytes = 0; L.pre_positions = 0; L.pre_front = 0;
+    L.pre_nt = 0; L.off_wf4 = o;
     // (a pooled layer runs the tcgen05 kernels on its pre-pool grid, followed by an OR-pooling pass)
     const int OHu = d->OH * d->pool, OWu = d->OW * d->pool;
     if (d->stride_h == d->stride_w && (d->stride_h == 1 || d->stride_h == 2) &&
@@ -318,28 +343,23 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
                 break;
             }
             L.ws_ok = L.umma_nt != 0;
-            if (!L.umma_nt && st == 1 && d->C <= 128 && (npos * 16) < (1 << 18)) {
-                // images too wide for the in-CTA expansion (its patch is limited by the expander
-                // threads): the loader-fed kernel alone can still take the layer
-                for (int nt = 128; nt >= 32; nt >>= 1) {
+            if (st == 1 && d->C <= 512 && (npos * 16) < (1 << 18)) {
+                // loader-fed 4-bit kernel: the largest n-tile whose filter block leaves room for a
+                // patch ring of at least three stages
+                for (int nt = 128; nt >= 32 && !L.pre_nt; nt >>= 1) {
                     if (d->O % nt) continue;
-                    if (umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, 2) > 227 * 1024) continue;
-                    L.umma_nt = nt; L.umma_npos = npos;
+                    int stages = nt >= 128 ? 4 : umma::kPreMaxStages;
+                    while (stages > 3 && umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, stages) > 227 * 1024) stages--;
+                    const size_t smem_pre = umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, stages);
+                    if (smem_pre > 227 * 1024) continue;
+                    L.pre_nt = nt; L.pre_stages = stages; L.pre_smem = smem_pre;
+                    L.umma_npos = npos;
                     L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
-                    o += (size_t)d->R * d->S * d->C * d->O;      o = (o + 255) & ~(size_t)255;
-                    break;
-                }
-            }
-            if (L.umma_nt && st == 1 && d->C <= 128 && L.umma_nt <= 128) {
-                int stages = L.umma_nt >= 128 ? 3 : umma::kPreMaxStages;
-                while (stages > 2 && umma::pre_smem_bytes(npos, d->C, d->R * d->S, L.umma_nt, stages) > 227 * 1024) stages--;
-                const size_t smem_pre = umma::pre_smem_bytes(npos, d->C, d->R * d->S, L.umma_nt, stages);
-                L.pre_stages = stages;
-                if (smem_pre <= 227 * 1024) {
                     L.pre_front = umma::pre_front(back_y, back_x, PW);
                     L.pre_positions = umma::pre_plane_positions(nv, npos, L.pre_front);
-                    L.pre_bytes = (size_t)d->C * (size_t)L.pre_positions;     // C/16 planes x 16 bytes
-                    L.pre_smem = smem_pre;
+                    L.pre_bytes = (size_t)(d->C / 32) * (size_t)L.pre_positions * 16;    // C/32 planes x 16 bytes
+                    L.off_wf4 = o;
+                    o += (size_t)d->R * d->S * d->C * d->O / 2;  o = (o + 255) & ~(size_t)255;
                 }
             }
             // wide layers: keep 256 positions x all channels resident, stream the filter
@@ -363,11 +383,21 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
             }
         }
     }
+    // the loader-fed kernel pre-pools an injected residual too (scratch behind its planes)
+    if (L.pre_nt && d->pool == 1) L.pool_bytes = (size_t)d->B * d->OH * d->OW * d->O * 2;
     L.prepool_bytes = 0;
-    if (d->pool != 1 && (L.umma_nt || L.as_npos))
+    if (d->pool != 1 && (L.umma_nt || L.as_npos || L.pre_nt))
         L.prepool_bytes = ((size_t)d->B * OHu * OWu * ((d->O + 31) / 32) * 4 + 255) & ~(size_t)255;
     L.bytes = o;
     return L;
+}
+
+// Scratch in front of a pooled layer's pre-pool bits: the input planes of the loader-fed kernel
+// followed by its pooled-residual scratch, or the activation-stationary kernel's pooled residual.
+size_t planes_padded(const PreparedLayout& L) { return (L.pre_bytes + 255) & ~(size_t)255; }
+size_t main_ws_bytes(const PreparedLayout& L) {
+    if (L.pre_bytes) return planes_padded(L) + ((L.pool_bytes + 255) & ~(size_t)255);
+    return (L.pool_bytes + 255) & ~(size_t)255;
 }
 
 template <int PPT>
@@ -379,14 +409,10 @@ __global__ void __launch_bounds__(kInconvThreads) k_inconv_tiled(InConvArgs c) {
 template <int PPT>
 int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_inconv_tiled<PPT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured[dev] = true;
-    }
+    if (configure_once(configured, [] {
+            return cudaFuncSetAttribute(k_inconv_tiled<PPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        }))
+        return 1;
     int per_sm = (int)((220 * 1024) / (smem + 1024));
     if (per_sm > 8) per_sm = 8;
     if (per_sm < 1) per_sm = 1;
@@ -408,18 +434,17 @@ __global__ void __launch_bounds__(umma::kWsThreads, 1) k_conv_umma_ws(umma::Conv
 __global__ void k_prepare_filter_ws(const uint32_t* fbits, int O, int RS, int C, int nt, uint4* out) {
     umma::prepare_filter_ws(fbits, O, RS, C, nt, out);
 }
+__global__ void k_prepare_filter_f4(const uint32_t* fbits, int O, int RS, int C, int nt, uint4* out) {
+    umma::prepare_filter_f4(fbits, O, RS, C, nt, out);
+}
 
 template <int NT, int STRIDE>
 int launch_conv_umma_ws(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_conv_umma_ws<NT, STRIDE>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured[dev] = true;
-    }
+    if (configure_once(configured, [] {
+            return cudaFuncSetAttribute(k_conv_umma_ws<NT, STRIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        }))
+        return 1;
     a.ntiles_n = a.O / NT;
     if (a.ntiles_n > sms) return fail("conv_layer: more n-tiles than SMs");
     const long long mtiles = (a.NV + 127) / 128;
@@ -442,14 +467,10 @@ __global__ void __launch_bounds__(256) k_expand_raster(umma::ConvWsArgs a, uint4
 template <int NT>
 int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st, bool expand) {
     static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_conv_umma_pre<NT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured[dev] = true;
-    }
+    if (configure_once(configured, [] {
+            return cudaFuncSetAttribute(k_conv_umma_pre<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        }))
+        return 1;
     if (expand) {
         const long long units = a.pre_positions * (a.C >> 6);
         k_expand_raster<<<elementwise_grid(units, sms), 256, 0, st>>>(a, const_cast<uint4*>(a.pre), a.pre_positions,
@@ -514,14 +535,10 @@ __global__ void __launch_bounds__(umma::kAsThreads, 1) k_conv_umma_as(umma::Conv
 
 int launch_conv_umma_as(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_conv_umma_as,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e != cudaSuccess) return fail("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        configured[dev] = true;
-    }
+    if (configure_once(configured, [] {
+            return cudaFuncSetAttribute(k_conv_umma_as, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        }))
+        return 1;
     // Split the n-tiles of a task over several work items when that fills the last wave of
     // CTAs better (the patch is then expanded once per part, which is cheap).
     const long long ntasks = (a.NV + 255) / 256;
@@ -602,6 +619,66 @@ __global__ void __launch_bounds__(128) k_umma_peak(int iters, long long* cycles,
     umma::tc_fence_before();
     __syncthreads();
     if (threadIdx.x < 32) umma::tmem_dealloc(tm, 256);
+}
+
+// tcgen05.mma kind::mxf4 (e2m1 operands, ue8m0 block scales, fp32 accumulate) M=128 N=256 K=64,
+// back to back like k_umma_peak.  +-1.0 is exact in e2m1 (0x2 / 0xA) and a unit scale is the
+// ue8m0 byte 0x7F; the scale region of tensor memory is filled with that byte throughout, so every
+// scale reads as 1.0 wherever the hardware looks.  A is all +1, B all -1: every accumulator must
+// end at -64 * iters, which the kernel checks on one row per warp (sample[]).
+__global__ void __launch_bounds__(128) k_umma_peak_mxf4(int iters, long long* cycles, int* err, float* sample) {
+    extern __shared__ __align__(1024) unsigned char peak_smem[];
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tm;
+    if (threadIdx.x < 32) umma::tmem_alloc(umma::smem_u32(&tm), 512);
+    if (threadIdx.x == 0) umma::mbar_init(umma::smem_u32(&bar), 1);
+    for (int i = threadIdx.x; i < 16384 / 4; i += blockDim.x) ((uint32_t*)peak_smem)[i] = 0x22222222u;            // A: +1
+    for (int i = threadIdx.x; i < 32768 / 4; i += blockDim.x) ((uint32_t*)(peak_smem + 16384))[i] = 0xAAAAAAAAu;  // B: -1
+    umma::fence_proxy_async();
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    const uint32_t tmem = tm;
+    {   // unit scales: columns 256..511 of this warp's 32 lanes
+        const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) * 32) << 16;
+        for (int c = 256; c < 512; c += 8)
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};"
+                         ::"r"(tmem + lane_base + c), "r"(0x7F7F7F7Fu) : "memory");
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    if (threadIdx.x == 0) {
+        // K-major, no swizzle: a 16-byte row of a core matrix holds 32 elements; K = 64 is two core
+        // matrices `lbo` apart
+        const uint64_t da = umma::smem_desc(umma::smem_u32(peak_smem), 128 * 16, 128);
+        const uint64_t db = umma::smem_desc(umma::smem_u32(peak_smem + 16384), 256 * 16, 128);
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+        const long long t0 = clock64();
+        for (int i = 0; i < iters; i++) {
+            const uint32_t acc = i ? 1u : 0u;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "setp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+                ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc), "r"(tmem + 256u), "r"(tmem + 384u) : "memory");
+        }
+        umma::mma_commit(umma::smem_u32(&bar));
+        if (!umma::mbar_wait(umma::smem_u32(&bar), 0, err)) { /* status already recorded */ }
+        if (blockIdx.x == 0) cycles[0] = clock64() - t0;
+    }
+    __syncthreads();
+    umma::tc_fence_after();
+    {
+        int r[8];
+        umma::tmem_ld8(tmem + ((uint32_t)((threadIdx.x >> 5) * 32) << 16) + 248u, r);
+        umma::tmem_ld_wait();
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 5) sample[threadIdx.x >> 5] = __int_as_float(r[7]);
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) umma::tmem_dealloc(tmem, 512);
 }
 
 // What the issuing thread's bookkeeping costs: 128x128x32 MMAs in groups of `group`, with per
@@ -772,6 +849,10 @@ int tcbnn_gemm_status(int* status) {
     if (!status) return fail("gemm_status: null pointer");
     CUDA_TRY(cudaDeviceSynchronize());
     CUDA_TRY(cudaMemcpyFromSymbol(status, g_gemm_status, sizeof(int)));
+    if (*status) {                                       // reading a failure clears it
+        const int zero = 0;
+        CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
+    }
     return 0;
 }
 
@@ -837,6 +918,12 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
             filter_bits, d->O, d->R * d->S, d->C, L.umma_nt, (uint4*)(p + L.off_wi8));
         if (launch_check("conv_prepare (int8 filter)")) return 1;
     }
+    if (L.pre_nt) {
+        const long long units = (long long)d->O * d->R * d->S * (d->C / 32);
+        k_prepare_filter_f4<<<elementwise_grid(units, sms), 256, 0, (cudaStream_t)stream>>>(
+            filter_bits, d->O, d->R * d->S, d->C, L.pre_nt, (uint4*)(p + L.off_wf4));
+        if (launch_check("conv_prepare (4-bit filter)")) return 1;
+    }
     if (L.as_npos && (!L.umma_nt || L.off_wi8_as != L.off_wi8)) {
         const long long units = (long long)d->O * d->R * d->S * (d->C / 16);
         k_prepare_filter_ws<<<elementwise_grid(units, sms), 256, 0, (cudaStream_t)stream>>>(
@@ -849,7 +936,7 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
 size_t tcbnn_conv_workspace_bytes(const tcbnn_conv_desc* d) {
     if (conv_check(d, true)) return 0;
     const PreparedLayout L = prepared_layout(d);
-    return (L.pre_bytes > L.pool_bytes ? L.pre_bytes : L.pool_bytes) + L.prepool_bytes;
+    return main_ws_bytes(L) + L.prepool_bytes;
 }
 
 size_t tcbnn_conv_planes_bytes(const tcbnn_conv_desc* d) {
@@ -927,8 +1014,8 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
     if ((uintptr_t)in & 7) return fail("conv_layer: input must be 8-byte aligned");
     const PreparedLayout L = prepared_layout(d);
     const char* p = (const char*)prepared;
-    const bool use_as = L.as_npos && g_conv_path != 3;
     const bool use_pre = L.pre_bytes && workspace && g_conv_path != 3;
+    const bool use_as = L.as_npos && g_conv_path != 3 && !use_pre;
     const bool have_tc = use_as || use_pre || L.ws_ok;
     if (g_conv_path >= 2 && !have_tc) return fail("conv_layer: layer is not eligible for the tcgen05 path (or needs its workspace)");
     // the tcgen05 epilogue moves residuals in 4-channel vectors
@@ -936,7 +1023,7 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
                                         ((uintptr_t)res_in & 15) == 0);
     if (g_conv_path >= 2 && !res_vec_ok) return fail("conv_layer: residual layout not eligible for the tcgen05 path");
     // a pooled layer needs room behind the kernel's own scratch for its pre-pool bits
-    const size_t main_ws = L.pre_bytes > L.pool_bytes ? L.pre_bytes : L.pool_bytes;
+    const size_t main_ws = main_ws_bytes(L);
     const bool pooled = d->pool != 1;
     const bool pooled_ok = !pooled || (workspace && workspace_bytes >= main_ws + L.prepool_bytes &&
                                        ((uintptr_t)workspace & 255) == 0);
@@ -950,7 +1037,7 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
       cudaStream_t st = (cudaStream_t)stream;
       auto launch_tc = [&]() -> int {
         umma::ConvWsArgs a;
-        a.in = in; a.wi8 = (const uint4*)(p + L.off_wi8); a.thr = thr;
+        a.in = in; a.wi8 = (const uint4*)(p + L.off_wi8); a.wf4 = (const uint4*)(p + L.off_wf4); a.thr = thr;
         a.B = d->B; a.H = d->H; a.W = d->W; a.C = d->C; a.O = d->O; a.R = d->R; a.S = d->S;
         a.pad_h = d->pad_h; a.pad_w = d->pad_w; a.stride = d->stride_h;
         a.OHg = P; a.OWg = Q;
@@ -970,7 +1057,7 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         a.pre = nullptr; a.pre_positions = 0; a.pre_front = 0;
         a.pre_stages = 0;
         a.nxt = nullptr; a.nxt_positions = 0; a.nxt_front = 0; a.nxt_PW = 0; a.nxt_VH = 0;
-        if (nx && !use_as && !pooled) {
+        if (nx && !use_as && !pooled) {     // (a pooled layer's kernel sees the pre-pool grid)
             a.nxt = nx->planes; a.nxt_positions = nx->positions; a.nxt_front = nx->front;
             a.nxt_PW = nx->PW; a.nxt_VH = nx->VH;
             *fed = true;
@@ -997,9 +1084,21 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
             if ((uintptr_t)workspace & 255) return fail("conv_layer: workspace must be 256-byte aligned");
             a.pre = (const uint4*)workspace; a.pre_positions = L.pre_positions; a.pre_front = L.pre_front;
             a.pre_stages = L.pre_stages;
-            if (L.umma_nt == 32) return launch_conv_umma_pre<32>(a, L.pre_smem, sms, st, !workspace_ready);
-            if (L.umma_nt == 64) return launch_conv_umma_pre<64>(a, L.pre_smem, sms, st, !workspace_ready);
-            if (L.umma_nt == 128) return launch_conv_umma_pre<128>(a, L.pre_smem, sms, st, !workspace_ready);
+            // a pooled int16 residual is reduced by a streaming pass first when the workspace has
+            // the room behind the planes: four scattered loads per value in the epilogue cost more
+            const size_t pooled_res_bytes = (size_t)d->B * d->OH * d->OW * (size_t)res_in_ch * 2;
+            if (res_in && residual_pool && res_in_bytes == 2 && res_in_ch % 8 == 0 && !pooled &&
+                pooled_res_bytes <= L.pool_bytes && workspace_bytes >= planes_padded(L) + pooled_res_bytes) {
+                char* pooled_res = (char*)workspace + planes_padded(L);
+                const long long units = (long long)d->B * d->OH * d->OW * (res_in_ch / 8);
+                k_pool_residual16<<<elementwise_grid(units, sms), 256, 0, st>>>((const uint4*)res_in, (uint4*)pooled_res,
+                                                                             d->B, d->OH, d->OW, res_in_ch / 8);
+                if (launch_check("conv_layer (residual pooling)")) return 1;
+                a.res_in = pooled_res; a.residual_pool = 0;
+            }
+            if (L.pre_nt == 32) return launch_conv_umma_pre<32>(a, L.pre_smem, sms, st, !workspace_ready);
+            if (L.pre_nt == 64) return launch_conv_umma_pre<64>(a, L.pre_smem, sms, st, !workspace_ready);
+            if (L.pre_nt == 128) return launch_conv_umma_pre<128>(a, L.pre_smem, sms, st, !workspace_ready);
         }
 #define TCBNN_WS_CASE(NN, SS) \
         if (L.umma_nt == NN && d->stride_h == SS) return launch_conv_umma_ws<NN, SS>(a, L.umma_smem, sms, st);
@@ -1080,6 +1179,8 @@ int tcbnn_conv_status(const tcbnn_conv_desc* d, const void* prepared, int* statu
     if (!status) return fail("conv_status: null status");
     const PreparedLayout L = prepared_layout(d);
     CUDA_TRY(cudaMemcpy(status, (const char*)prepared + L.off_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status)                                         // reading a failure clears it
+        CUDA_TRY(cudaMemset((char*)const_cast<void*>(prepared) + L.off_err, 0, sizeof(int)));
     return 0;
 }
 
@@ -1218,7 +1319,7 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
     // aligned row loads when the geometry allows (stride 4, rows a multiple of 4 pixels, aligned base)
     const bool vec = h->sw == 4 && d->W % 4 == 0 && (x ? ((uintptr_t)x & 15) == 0 : ((uintptr_t)x8 & 3) == 0);
     const int variant = (x ? 0 : 2) + (vec ? 1 : 0);
-    if (!h->kernel[variant] && spec_build(h, variant, false)) return 1;       // first use: compile it
+    if (spec_build(h, variant, false)) return 1;       // first use compiles it (checked under the handle's lock)
     CUDA_TRY(cudaLaunchKernel((const void*)h->kernel[variant], dim3(grid, (h->O + 63) / 64), dim3(spec::kSpecThreads),
                               params, 0, (cudaStream_t)stream));
     return launch_check("inconv_specialized_layer");
@@ -1251,7 +1352,7 @@ int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, lo
 }
 
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
-    if (!tops || iters <= 0 || warps_per_sm <= 0 || kind < 0 || kind > 6) return fail("mma_peak: bad arguments");
+    if (!tops || iters <= 0 || warps_per_sm <= 0 || kind < 0 || kind > 7) return fail("mma_peak: bad arguments");
     int sms;
     if (sm_count(&sms)) return 1;
     cudaEvent_t e0, e1;
@@ -1260,14 +1361,16 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
     float best = 1e30f;
     if (kind >= 3) {
         long long* buf = nullptr;
-        CUDA_TRY(cudaMalloc(&buf, 16));
-        CUDA_TRY(cudaMemset(buf, 0, 16));
+        CUDA_TRY(cudaMalloc(&buf, 32));
+        CUDA_TRY(cudaMemset(buf, 0, 32));
+        if (kind == 7 && iters > (1 << 18)) return fail("mma_peak: at most 2^18 iterations for kind 7 (exact fp32 sums)");
+        CUDA_TRY(cudaFuncSetAttribute(k_umma_peak_mxf4, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
         CUDA_TRY(cudaFuncSetAttribute(k_umma_peak, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
         CUDA_TRY(cudaFuncSetAttribute(k_umma_issue<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
         CUDA_TRY(cudaFuncSetAttribute(k_umma_issue<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
         CUDA_TRY(cudaFuncSetAttribute(k_umma_issue<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024));
         const int group = warps_per_sm;            // kinds 4-6: MMAs per wait/commit group
-        if (kind > 3) iters = (iters / group) * group;
+        if (kind > 3 && kind < 7) iters = (iters / group) * group;
         if (iters <= 0) return fail("mma_peak: fewer iterations than MMAs per group");
         for (int rep = 0; rep < 4; rep++) {
             cudaEventRecord(e0);
@@ -1275,6 +1378,7 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
             if (kind == 4) k_umma_issue<0><<<sms, 128, 48 * 1024>>>(iters, group, buf, (int*)(buf + 1));
             if (kind == 5) k_umma_issue<1><<<sms, 128, 48 * 1024>>>(iters, group, buf, (int*)(buf + 1));
             if (kind == 6) k_umma_issue<2><<<sms, 128, 48 * 1024>>>(iters, group, buf, (int*)(buf + 1));
+            if (kind == 7) k_umma_peak_mxf4<<<sms, 128, 48 * 1024>>>(iters, buf, (int*)(buf + 1), (float*)(buf + 2));
             cudaEventRecord(e1);
             CUDA_TRY(cudaEventSynchronize(e1));
             float ms = 0;
@@ -1283,10 +1387,20 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
         }
         int status = 0;
         CUDA_TRY(cudaMemcpy(&status, buf + 1, sizeof(int), cudaMemcpyDeviceToHost));
+        float sample[4] = {0, 0, 0, 0};
+        CUDA_TRY(cudaMemcpy(sample, buf + 2, sizeof(sample), cudaMemcpyDeviceToHost));
         cudaFree(buf);
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);
         if (status) return fail("mma_peak: a bounded wait in the tcgen05 probe gave up");
+        if (kind == 7) {
+            for (int w = 0; w < 4; w++)
+                if (sample[w] != -64.0f * iters)
+                    return fail("mma_peak: kind::mxf4 accumulator is %g, expected %g (+-1 operands, unit scales)",
+                                (double)sample[w], -64.0 * iters);
+            *tops = (double)sms * iters * 2.0 * 128 * 256 * 64 / (best * 1e-3) / 1e12;
+            return 0;
+        }
         *tops = (double)sms * iters * 2.0 * 128 * (kind == 3 ? 256 : 128) * 32 / (best * 1e-3) / 1e12;
         return 0;
     }

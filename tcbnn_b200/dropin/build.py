@@ -55,7 +55,13 @@ def build_runner():
     return out
 
 
-def build_reference_drivers(ref_root="/root/reference"):
+def default_ref_root():
+    """$TCBNN_REF_ROOT, else a folder named `reference` beside this repository."""
+    return os.environ.get("TCBNN_REF_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
+
+
+def build_reference_drivers(ref_root=None):
+    ref_root = ref_root or default_ref_root()
     if not os.path.exists(os.path.join(ref_root, "data.h")):
         return []
     os.makedirs(OUT, exist_ok=True)
@@ -80,7 +86,7 @@ def build_reference_drivers(ref_root="/root/reference"):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-root", default="/root/reference")
+    ap.add_argument("--ref-root", default=None)
     a = ap.parse_args()
     print(build_runner())
     for b in build_reference_drivers(a.ref_root):

@@ -348,8 +348,8 @@ class Conv128LayerParam:
         expansion pass too unless its producer filled the planes."""
         has_ws = ops.conv_workspace(self.desc, self.input_gpu.device) is not None
         own_expand = self.input_planes is None and ops.new_planes_bytes(self.desc) > 0
-        pools_residual = (ops.new_planes_bytes(self.desc) == 0 and self.inject_residual and self.residual_pool and
-                          has_ws)
+        pools_residual = (self.inject_residual and self.residual_pool and has_ws and self.desc.pool == 1 and
+                          self.input_residual_gpu is not None and self.input_residual_gpu.dtype == torch.int16)
         pools_output = self.desc.pool != 1 and has_ws          # tcgen05 on the pre-pool grid + OR-pooling pass
         return 1 + int(own_expand) + int(pools_residual) + int(pools_output)
 

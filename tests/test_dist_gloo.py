@@ -24,6 +24,13 @@ def _worker(rank, world, port, q):
     b, e = d.shard_range(8, rank, world)
     local = torch.arange(b, e, dtype=torch.float32).reshape(-1, 1).repeat(1, 3) + 0.5
     full = d.gather_logits(local)
+    og = d.OverlappedGather(local.shape[0], local.shape[1], local.dtype, "cpu", world)
+    assert og(local).tolist() == full.tolist() and og.finish().tolist() == full.tolist()
+    try:
+        d.shard_range(7, rank, world)            # a batch that does not split evenly is refused
+        raise AssertionError("uneven shard accepted")
+    except ValueError:
+        pass
     times = d.max_over_ranks([1.0 + rank, 5.0 - rank])
     member = torch.tensor([[1.0, -2.0 + 5 * rank, 3.0 - rank], [0.5 * rank, 0.0, -1.0]])
     voted = d.ensemble_max(member.clone())

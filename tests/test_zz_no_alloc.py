@@ -6,7 +6,9 @@ synchronisation is not acceptable.  For them the library keeps the split-K scrat
 array of its own.  This file checks, through the C ABI, that the entry point gives exactly the
 bits of the workspace-taking one on two calls in a row (the second with different inputs, so
 stale scratch contents from the first call would show), and that a shape whose partial sums do
-not fit the array is refused with a clear message.  It is named to be collected last.
+not fit the array is refused with a clear message.  The bits are also compared with the CPU
+oracle, and the free device memory is read before and after a call that follows the first one:
+a call that allocated anything would show there.  It is named to be collected last.
 """
 import ctypes as C
 
@@ -14,6 +16,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle as orc
 import util
 from tcbnn_b200 import lib, ops
 
@@ -26,7 +29,7 @@ def _case(g, M, N, K, cuda):
     W = util.mask_row_pad(util.rand_words(g, (N, ld)), K)
     thr = (g.standard_normal(N) * np.sqrt(K)).astype(np.float32)
     to = lambda a: torch.from_numpy(a.view(np.int32) if a.dtype == np.uint32 else a).to(cuda)
-    return to(A), to(W), to(thr)
+    return to(A), to(W), to(thr), orc.fc_layer(A, W, thr, K)
 
 
 def _noalloc(A, W, thr, K):
@@ -43,19 +46,34 @@ def test_noalloc_matches_workspace_variant_twice(cuda):
     M, N, K = 256, 128, 8192                      # few tiles, long K: the split-K path
     need = lib.load().tcbnn_gemm_workspace_bytes(M, N, K)
     assert 0 < need <= lib.load().tcbnn_noalloc_scratch_bytes()
-    for _ in range(2):
-        A, W, thr = _case(g, M, N, K, cuda)
+    for call in range(2):
+        A, W, thr, expect = _case(g, M, N, K, cuda)
         ws = ops.gemm_workspace(M, N, K, cuda)
         ref = ops.fc_layer(A, W, thr, K, workspace=ws)
         got = _noalloc(A, W, thr, K)
         torch.cuda.synchronize()
         assert torch.equal(got, ref)              # packed bits: exact
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), expect)      # and the CPU oracle's
+        if call == 1:
+            # the array's address is known by now: a further call must leave the device's free
+            # memory exactly as it found it (the output buffer is allocated before the reading)
+            out = torch.zeros((M, ops.step128_words(N)), dtype=torch.int32, device=cuda)
+            torch.cuda.synchronize()
+            free0, _ = torch.cuda.mem_get_info()
+            lib.call("tcbnn_fc_layer_noalloc", ops._ptr(A), ops._ptr(W), ops._ptr(thr), M, K, N, A.shape[1],
+                     W.shape[1], ops._ptr(out), out.shape[1], ops._stream())
+            torch.cuda.synchronize()
+            free1, _ = torch.cuda.mem_get_info()
+            assert free1 == free0
+            assert torch.equal(out, ref)
 
 
 def test_noalloc_small_shape_without_split(cuda):
     g = util.rng(7)
-    A, W, thr = _case(g, 64, 40, 200, cuda)
-    assert torch.equal(_noalloc(A, W, thr, 200), ops.fc_layer(A, W, thr, 200))
+    A, W, thr, expect = _case(g, 64, 40, 200, cuda)
+    got = _noalloc(A, W, thr, 200)
+    assert torch.equal(got, ops.fc_layer(A, W, thr, 200))
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), expect)
 
 
 def test_noalloc_rejects_oversized_shape(cuda):
