@@ -159,7 +159,9 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
  * is eligible, else the warp-level b1 MMA), 1 = always the b1 MMA, 2 = tcgen05 or an error,
  * 3 = as 2 but only the filter-stationary tcgen05 kernel with its in-kernel bit expansion (wide
  * stride-1 layers otherwise take the activation-stationary kernel, narrow ones with a workspace the
- * kernel fed from a pre-expanded input).
+ * kernel fed from a pre-expanded input), 4 = as 0 but the loader-fed kernel moves int16 residual
+ * rows straight between registers and global memory, never staging them in shared memory, 5 = as 0
+ * but staging them wherever the tensors allow (0 stages them where that measured faster).
  * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);

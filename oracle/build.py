@@ -72,7 +72,7 @@ def build_ref(ref_root=None):
     return out
 
 
-REF_DRIVERS = ["mnist_mlp", "cifar10_vgg", "cifar10_resnet", "imagenet_resnet"]
+REF_DRIVERS = ["mnist_mlp", "cifar10_vgg", "cifar10_resnet", "imagenet_resnet", "alexnet", "imagenet_vgg"]
 
 
 def build_ref_drivers(ref_root=None):

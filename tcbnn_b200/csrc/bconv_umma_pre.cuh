@@ -38,37 +38,52 @@ __host__ __device__ inline long long pre_front(int back_y, int back_x, int PW) {
 __host__ __device__ inline long long pre_plane_positions(long long NV, int npos, long long front) {
     return ((front + ((NV + 127) / 128) * 128 + npos + 7) & ~7LL);
 }
-__host__ __device__ inline size_t pre_smem_bytes(int npos, int C, int RS, int nt, int stages) {
-    return (size_t)stages * 2 * npos * 16 + (size_t)RS * C * nt / 2 + nt * 4 + RS * 8 + 40 * 8 + 64;
+// nplane: 1 for stride 1, 4 for stride 2 (the input's four row / column parity planes)
+__host__ __device__ inline size_t pre_smem_bytes(int npos, int C, int RS, int nt, int stages, int nplane) {
+    return (size_t)stages * nplane * 2 * npos * 16 + (size_t)RS * C * nt / 2 + nt * 4 + RS * 8 + 40 * 8 + 64;
 }
+// two buffers of a tile's int16 residual rows (128 rows x nt channels), staged in shared memory
+__host__ __device__ inline size_t pre_res_stage_bytes(int nt) { return (size_t)2 * 128 * nt * 2 + 128; }
 
-// packed bits [B][H][W][C/32] -> planes [C/32][plane_positions][16 B] of +-1 nibbles, zero where
-// the raster position is padding or outside the batch
+// packed bits [B][H][W][C/32] -> planes [C/32][nplane][plane_positions][16 B] of +-1 nibbles, zero
+// where the raster position is padding or outside the batch.  Stride 1: one plane, the raster of
+// the input.  Stride 2: four planes, plane (py, px) holds input pixel (2*vr + py, 2*vx + px) at
+// raster position (vr, vx) of the OUTPUT grid, so that a filter tap is again a fixed offset.
 __device__ __forceinline__ void expand_raster(const ConvWsArgs& a, uint4* planes, long long plane_positions,
                                               long long front) {
     const int NCB = a.C >> 6, Cw = a.C >> 5;
-    const long long total = plane_positions * NCB;
+    const int nplane = a.stride == 2 ? 4 : 1;
+    const long long total = plane_positions * NCB * nplane;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
-        const int cb = (int)(i / plane_positions);
-        const long long slot = i - (long long)cb * plane_positions;
+        const int cp = (int)(i / plane_positions);             // (channel block, plane)
+        const int cb = cp / nplane, pl = cp - cb * nplane;
+        const long long slot = i - (long long)cp * plane_positions;
         const long long gq = slot - front;
         uint4 e0 = make_uint4(0u, 0u, 0u, 0u), e1 = e0;
         if (gq >= 0 && gq < a.NV) {
             const int vy = fastdiv((int)gq, a.pw_mul, a.pw_sh), vx = (int)gq - vy * a.PW;
             const int n = fastdiv(vy, a.vh_mul, a.vh_sh), vr = vy - n * a.VH;
-            if (vr < a.H && vx < a.W) {
-                const uint2 b = ldg64(a.in + ((size_t)(n * a.H + vr) * a.W + vx) * Cw + cb * 2);
+            const int iy = nplane == 4 ? 2 * vr + (pl >> 1) : vr, ix = nplane == 4 ? 2 * vx + (pl & 1) : vx;
+            if (vr < a.OHg && vx < a.OWg && iy < a.H && ix < a.W) {
+                const uint2 b = ldg64(a.in + ((size_t)(n * a.H + iy) * a.W + ix) * Cw + cb * 2);
                 e0 = expand32_f4(b.x); e1 = expand32_f4(b.y);
             }
         }
-        uint4* dst = planes + (size_t)(cb * 2) * plane_positions + slot;
+        uint4* dst = planes + ((size_t)(cb * 2) * nplane + pl) * plane_positions + slot;
         dst[0] = e0;
-        dst[(size_t)plane_positions] = e1;
+        dst[(size_t)nplane * plane_positions] = e1;
     }
 }
 
-template <int NT>
+// RSTAGE: int16 residual rows travel through shared memory.  A tile's live pixels are consecutive
+// rows of the residual tensors, so all 512 epilogue threads move them as whole 128-byte lines
+// (cp.async in, 16-byte stores out: 4 lines per instruction) into a buffer whose 16-byte chunks are
+// XOR-swizzled by row, and every thread then reads / overwrites its own pixel's chunks there without
+// bank conflicts.  The incoming rows of the next tile fly while this tile is computed; the
+// outgoing rows leave one tile late.  (Without it each lane moves 16-byte pieces of its own row: 32
+// lines per instruction, which made L1TEX the busiest unit of these layers.)
+template <int NT, bool RSTAGE>
 __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     // Tensor memory: accumulators (7 at NT = 64) below column 480, the unit block scales of the
     // 4-bit MMA above it; the patch ring is as deep as shared memory allows, so that no role waits
@@ -81,17 +96,21 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     constexpr int LOAD_WARP = kPreEpiThreads / 32, MMA_WARP = LOAD_WARP + 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int RS = a.R * a.S, NCB = a.C >> 6;
-    const uint32_t stage_bytes = 2u * a.NPOS * 16u;           // two 32-channel chunk planes
+    const int NPLANE = a.stride == 2 ? 4 : 1;
+    const uint32_t plane_bytes = 2u * a.NPOS * 16u;           // two 32-channel chunk planes
+    const uint32_t stage_bytes = NPLANE * plane_bytes;
 
     unsigned char* sAraw = smem;
     uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
     int* sThr = reinterpret_cast<int*>(sB + (size_t)RS * (a.C >> 5) * NT);
     uint32_t* sTapK = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sThr + NT) + 7) & ~(uintptr_t)7);
     uint64_t* sBar = reinterpret_cast<uint64_t*>(sTapK + 2 * RS);
-    // barriers: a_full[8], a_empty[8], acc_full[8], acc_empty[8]
-    uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 32);
+    // barriers: a_full[8], a_empty[8], acc_full[8], acc_empty[8], epilogue rendezvous
+    uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 40);
     volatile int* sAbort = reinterpret_cast<volatile int*>(sTmem + 1);
+    unsigned char* sRes = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sTmem + 2) + 127) & ~(uintptr_t)127);
     const uint32_t bar0 = smem_u32(sBar);
+    const uint32_t BAR_EPI = bar0 + 8u * 32;           // the epilogue warps' own rendezvous (RSTAGE)
     auto BAR_AFULL = [&](int s) { return bar0 + 8u * s; };
     auto BAR_AEMPTY = [&](int s) { return bar0 + 8u * (8 + s); };
     auto BAR_CFULL = [&](int b) { return bar0 + 8u * (16 + b); };
@@ -106,6 +125,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     if (tid == 0) {
         for (int s = 0; s < 8; s++) { mbar_init(BAR_AFULL(s), 1); mbar_init(BAR_AEMPTY(s), 1); }
         for (int b = 0; b < 8; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), kPreEpiThreads / 32); }
+        mbar_init(BAR_EPI, kPreEpiThreads / 32);
         *sAbort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -124,7 +144,16 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             sThr[i] = it;
         }
         for (int t = tid; t < RS; t += kPreThreads) {
-            sTapK[t] = (uint32_t)((t / a.S) * a.PW + (t % a.S));     // patch offset in 16-byte units
+            // offset of the tap's operand inside a stage, in 16-byte units
+            const int r = t / a.S, sx = t % a.S;
+            if (NPLANE == 4) {
+                const int ty = r - a.pad_h, tx = sx - a.pad_w;
+                const int py = ty & 1, px = tx & 1;
+                const int dy = (ty - py) / 2, dx = (tx - px) / 2;
+                sTapK[t] = (uint32_t)(py * 2 + px) * (plane_bytes >> 4) + (uint32_t)((dy + a.back_y) * a.PW + (dx + a.back_x));
+            } else {
+                sTapK[t] = (uint32_t)(r * a.PW + sx);
+            }
         }
     }
     fence_proxy_async();
@@ -152,11 +181,12 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     if (!ok) break;
                     mbar_expect_tx(BAR_AFULL(s), stage_bytes);
                     const uint32_t dst = smem_u32(sAraw + (size_t)s * stage_bytes);
+                    for (int pl = 0; pl < NPLANE; pl++)
 #pragma unroll
-                    for (int c = 0; c < 2; c++)
-                        bulk_g2s(dst + c * (uint32_t)a.NPOS * 16u,
-                                 a.pre + (size_t)(cb * 2 + c) * a.pre_positions + slot0,
-                                 (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
+                        for (int c = 0; c < 2; c++)
+                            bulk_g2s(dst + (uint32_t)(pl * 2 + c) * (uint32_t)a.NPOS * 16u,
+                                     a.pre + ((size_t)(cb * 2 + c) * NPLANE + pl) * a.pre_positions + slot0,
+                                     (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
                     if (++s == NSTAGE) { s = 0; sph ^= 1; }
                 }
             }
@@ -190,6 +220,9 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             constexpr uint32_t IDESC = idesc_f4(NT);
             const uint32_t sfa = tmem + SF_COL, sfb = tmem + SF_COL + 16;
             const bool rs9 = RS == 9;
+            uint32_t tapk[9];                              // 3x3 filters: the tap offsets in registers
+#pragma unroll
+            for (int t = 0; t < 9; t++) tapk[t] = rs9 ? sTapK[t] : 0u;
             uint32_t it = 0, tc = 0, sph = 0, bph = 0;
             int s = 0, b = 0;
             bool ok = true;
@@ -210,11 +243,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     if (leader) {
                     if (rs9) {
 #pragma unroll
-                        for (int t = 0; t < 9; t++) {
-                            // tap (r, s): patch offset (r*PW + s) positions
-                            const uint32_t aoff = (uint32_t)((t / 3) * a.PW + (t % 3));
-                            mma_f4_split(d, aLo + aoff, aHi, bLo + t * stepB, bHi, IDESC, t == 0 ? acc : 1u, sfa, sfb);
-                        }
+                        for (int t = 0; t < 9; t++)
+                            mma_f4_split(d, aLo + tapk[t], aHi, bLo + t * stepB, bHi, IDESC, t == 0 ? acc : 1u, sfa, sfb);
                         bLo += 9 * stepB;
                     } else {
                         for (int t = 0; t < RS; t++) {
@@ -241,7 +271,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         const int Ow = (a.O + 31) >> 5;
         const int lim = a.res_in ? min(a.residual_channels, a.res_in_ch) : 0;
         const int o0 = obase + cg * COLS;                  // this thread's first output channel
-        const bool res16 = a.res_in && a.res_in_bytes == 2 && (a.res_in_ch & 7) == 0 && (lim & 7) == 0;
+        const bool res16 = !RSTAGE && a.res_in && a.res_in_bytes == 2 && (a.res_in_ch & 7) == 0 && (lim & 7) == 0;
         uint32_t tc = 0;
         bool ok = true, overflow = false;
         long long tr_w = 0;
@@ -259,6 +289,59 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             }
             q.opix = ((size_t)q.n * a.OHg + q.y) * a.OWg + q.x;
             return q;
+        };
+        // ---- staged residual rows (RSTAGE; the host enables it only for int16 tensors, an n-tile
+        //      that lies entirely inside or outside the injected channels, NT of 64 or 128) --------
+        constexpr uint32_t ROWB = NT * 2;                  // bytes of one pixel's residual segment
+        constexpr int NCOPY = (128 * ROWB) / (kPreEpiThreads * 16);     // 16-byte pieces per thread and tile
+        const bool st_in = RSTAGE && a.res_in && obase < lim;
+        const bool st_out = RSTAGE && a.res_out;
+        // output pixels in front of raster position p (live pixels are consecutive tensor rows)
+        auto live_before = [&](int p) -> long long {
+            if (p >= NV) return (long long)a.B * a.OHg * a.OWg;
+            const int vy = fastdiv(p, a.pw_mul, a.pw_sh), x = p - vy * a.PW;
+            const int n = fastdiv(vy, a.vh_mul, a.vh_sh), y = vy - n * a.VH;
+            return ((long long)n * a.OHg + min(y, a.OHg)) * a.OWg + (y < a.OHg ? min(x, a.OWg) : 0);
+        };
+        // shared-memory address of 16-byte chunk `c` of staged row `r`: chunks XOR-swizzled by row
+        auto st_addr = [&](int buf, int r, int c) -> uint32_t {
+            return smem_u32(sRes) + (uint32_t)buf * (128u * ROWB) + (uint32_t)r * ROWB +
+                   (uint32_t)(((c & ~7) | ((c ^ r) & 7)) << 4);
+        };
+        auto issue_in = [&](long long p0, int nl, int buf) {   // cp.async of a tile's incoming rows
+            if (!st_in) return;
+            const char* g = reinterpret_cast<const char*>(a.res_in) + ((size_t)p0 * a.res_in_ch + obase) * 2;
+#pragma unroll
+            for (int k = 0; k < NCOPY; k++) {
+                const uint32_t off = (uint32_t)(tid + k * kPreEpiThreads) * 16u;
+                const int r = off / ROWB, c = (off % ROWB) >> 4;
+                if (r < nl)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(st_addr(buf, r, c)),
+                                 "l"(g + (size_t)r * a.res_in_ch * 2 + (c << 4)) : "memory");
+            }
+        };
+        auto store_out = [&](long long p0, int nl, int buf) {  // a tile's outgoing rows, whole lines
+            if (!st_out) return;
+            char* g = reinterpret_cast<char*>(a.res_out) + ((size_t)p0 * a.O + obase) * 2;
+#pragma unroll
+            for (int k = 0; k < NCOPY; k++) {
+                const uint32_t off = (uint32_t)(tid + k * kPreEpiThreads) * 16u;
+                const int r = off / ROWB, c = (off % ROWB) >> 4;
+                if (r < nl) {
+                    uint4 v4;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v4.x), "=r"(v4.y), "=r"(v4.z), "=r"(v4.w)
+                                 : "r"(st_addr(buf, r, c)) : "memory");
+                    *reinterpret_cast<uint4*>(g + (size_t)r * a.O * 2 + (c << 4)) = v4;
+                }
+            }
+        };
+        uint32_t eph = 0;                                  // phase of the epilogue rendezvous
+        auto rendezvous = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(BAR_EPI);
+            const bool r = wait(BAR_EPI, eph);
+            eph ^= 1;
+            return r;
         };
         // int16 residual of channels [o0, o0+COLS) of one pixel, packed (zeros where nothing is
         // injected); 2x2 max for pooled residuals (kernel.cuh:773-783)
@@ -296,12 +379,34 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     r[j] = (q.live && o0 + 8 * j < lim) ? __ldg(reinterpret_cast<const uint4*>(s + 8 * j)) : z;
             }
         };
+        auto add16 = [&](int (&v)[COLS], const uint4 (&r)[NQ]) {
+#pragma unroll
+            for (int j = 0; j < NQ; j++) {
+                v[8 * j] += (int)(short)(r[j].x & 0xFFFFu);
+                v[8 * j + 1] += (int)(short)(r[j].x >> 16);
+                v[8 * j + 2] += (int)(short)(r[j].y & 0xFFFFu);
+                v[8 * j + 3] += (int)(short)(r[j].y >> 16);
+                v[8 * j + 4] += (int)(short)(r[j].z & 0xFFFFu);
+                v[8 * j + 5] += (int)(short)(r[j].z >> 16);
+                v[8 * j + 6] += (int)(short)(r[j].w & 0xFFFFu);
+                v[8 * j + 7] += (int)(short)(r[j].w >> 16);
+            }
+        };
         uint4 rnext[NQ];
 #pragma unroll
         for (int j = 0; j < NQ; j++) rnext[j] = make_uint4(0u, 0u, 0u, 0u);
         Pix cur = locate(mfirst);
         if (res16 && mfirst < mtiles) fetch16(rnext, cur);
-        int b = 0;
+        // first pixel and number of live pixels of the current, the previous and the next tile
+        long long p0_cur = 0, p0_prev = 0, p0_next = 0;
+        int nl_cur = 0, nl_prev = -1, nl_next = 0;
+        if (RSTAGE && mfirst < mtiles) {
+            p0_cur = live_before(mfirst * 128);
+            nl_cur = (int)(live_before(mfirst * 128 + 128) - p0_cur);
+            issue_in(p0_cur, nl_cur, 0);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        int b = 0, mprev = -1;
         uint32_t bph = 0;
         for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
             const Pix q = cur;
@@ -330,18 +435,32 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 for (int j = 0; j < COLS / 4; j++)
                     dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
-            if (res16) {
-#pragma unroll
-                for (int j = 0; j < NQ; j++) {
-                    v[8 * j] += (int)(short)(rcur[j].x & 0xFFFFu);
-                    v[8 * j + 1] += (int)(short)(rcur[j].x >> 16);
-                    v[8 * j + 2] += (int)(short)(rcur[j].y & 0xFFFFu);
-                    v[8 * j + 3] += (int)(short)(rcur[j].y >> 16);
-                    v[8 * j + 4] += (int)(short)(rcur[j].z & 0xFFFFu);
-                    v[8 * j + 5] += (int)(short)(rcur[j].z >> 16);
-                    v[8 * j + 6] += (int)(short)(rcur[j].w & 0xFFFFu);
-                    v[8 * j + 7] += (int)(short)(rcur[j].w >> 16);
+            const int sbuf = (int)(tc & 1);
+            int lrow = 0;
+            if (RSTAGE) {
+                // this tile's incoming rows have landed (mine: wait_group; everyone's: rendezvous),
+                // and every thread has written its part of the previous tile's outgoing rows
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                ok = rendezvous();
+                if (!ok) break;
+                if (nl_prev >= 0) store_out(p0_prev, nl_prev, sbuf ^ 1);
+                if (m + mstep < mtiles) {
+                    p0_next = live_before((m + mstep) * 128);
+                    nl_next = (int)(live_before((m + mstep) * 128 + 128) - p0_next);
+                    issue_in(p0_next, nl_next, sbuf ^ 1);  // the buffer this thread has just drained
                 }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                lrow = (int)((long long)q.opix - p0_cur);
+                if (st_in && q.live) {
+                    uint4 r[NQ];
+#pragma unroll
+                    for (int j = 0; j < NQ; j++)
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[j].x), "=r"(r[j].y), "=r"(r[j].z), "=r"(r[j].w)
+                                     : "r"(st_addr(sbuf, lrow, cg * NQ + j)) : "memory");
+                    add16(v, r);
+                }
+            } else if (res16) {
+                add16(v, rcur);
             } else if (a.res_in && q.live && o0 < lim) {
 #pragma unroll
                 for (int j = 0; j < COLS / 4; j++) {
@@ -385,7 +504,11 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                             ovf |= (uint32_t)(lo ^ (lo >> 31)) | (uint32_t)(hi ^ (hi >> 31));
                             w[kk] = ((uint32_t)lo & 0xFFFFu) | ((uint32_t)hi << 16);
                         }
-                        dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                        if (RSTAGE)                        // into the staged row, in place of what was read
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_addr(sbuf, lrow, cg * NQ + j)),
+                                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        else
+                            dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                     overflow |= ovf > 32767u;              // some value outside [-32768, 32767]
                 } else {
@@ -404,6 +527,13 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 else wp[3 - ((o0 & 31) >> 3)] = (unsigned char)word;
                 if (a.nxt) store_next_planes(a, q.n, q.y, q.x, o0, word, COLS);
             }
+            mprev = m;
+            p0_prev = p0_cur; nl_prev = nl_cur;
+            p0_cur = p0_next; nl_cur = nl_next;
+        }
+        if (RSTAGE) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");      // nothing of this thread's in flight at exit
+            if (ok && mprev >= 0 && rendezvous()) store_out(p0_prev, nl_prev, (int)((tc - 1) & 1));
         }
         if (overflow) atomicExch(a.err_flag, 2);
         if (a.trace && blockIdx.x == 0 && tid == 0) { a.trace[6] = clock64() - tr_t0; a.trace[7] = tr_w; a.trace[8] = tc; }

@@ -48,6 +48,7 @@ struct ConvWsArgs {
     // optional: also write the output as +-1 nibbles into the next layer's input planes
     // (bconv_umma_pre.cuh layout over THAT layer's raster; dead slots stay as the caller zeroed them)
     uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
+    int nxt_nplane;           // 1, or 4 when that layer has stride 2 (one plane per row / column parity)
     const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
     uint32_t* out; long long out_image_stride;
     void* res_out; int res_out_bytes; int32_t* acc_out;
@@ -123,7 +124,12 @@ __device__ __forceinline__ void prepare_filter_f4(const uint32_t* fbits, int O, 
 // planes: one 16-byte slot per raster position and 32-channel chunk (expand32_f4 order).
 __device__ __forceinline__ void store_next_planes(const ConvWsArgs& a, int n, int y, int x, int o0,
                                                   uint32_t word, int nbits) {
-    uint4* base = a.nxt + (size_t)(o0 >> 5) * a.nxt_positions + a.nxt_front +
+    int pl = 0;
+    if (a.nxt_nplane == 4) {                    // stride-2 consumer: pixel (y, x) lives in plane (y&1, x&1) at (y/2, x/2)
+        pl = (y & 1) * 2 + (x & 1);
+        y >>= 1; x >>= 1;
+    }
+    uint4* base = a.nxt + ((size_t)(o0 >> 5) * a.nxt_nplane + pl) * a.nxt_positions + a.nxt_front +
                   ((long long)n * a.nxt_VH + y) * a.nxt_PW + x;
     if (nbits == 32) {
         base[0] = expand32_f4(word);

@@ -343,21 +343,22 @@ PreparedLayout prepared_layout(const tcbnn_conv_desc* d) {
                 break;
             }
             L.ws_ok = L.umma_nt != 0;
-            if (st == 1 && d->C <= 512 && (npos * 16) < (1 << 18)) {
+            const int nplane = st == 2 ? 4 : 1;
+            if (d->C <= 512 && (nplane * 2 * npos * 16) < (1 << 18)) {
                 // loader-fed 4-bit kernel: the largest n-tile whose filter block leaves room for a
                 // patch ring of at least three stages
                 for (int nt = 128; nt >= 32 && !L.pre_nt; nt >>= 1) {
                     if (d->O % nt) continue;
                     int stages = nt >= 128 ? 4 : umma::kPreMaxStages;
-                    while (stages > 3 && umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, stages) > 227 * 1024) stages--;
-                    const size_t smem_pre = umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, stages);
+                    while (stages > 3 && umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, stages, nplane) > 227 * 1024) stages--;
+                    const size_t smem_pre = umma::pre_smem_bytes(npos, d->C, d->R * d->S, nt, stages, nplane);
                     if (smem_pre > 227 * 1024) continue;
                     L.pre_nt = nt; L.pre_stages = stages; L.pre_smem = smem_pre;
                     L.umma_npos = npos;
                     L.umma_pw = PW; L.umma_vh = VH; L.umma_back_y = back_y; L.umma_back_x = back_x;
                     L.pre_front = umma::pre_front(back_y, back_x, PW);
                     L.pre_positions = umma::pre_plane_positions(nv, npos, L.pre_front);
-                    L.pre_bytes = (size_t)(d->C / 32) * (size_t)L.pre_positions * 16;    // C/32 planes x 16 bytes
+                    L.pre_bytes = (size_t)(d->C / 32) * nplane * (size_t)L.pre_positions * 16;    // C/32 x nplane planes of 16-byte slots
                     L.off_wf4 = o;
                     o += (size_t)d->R * d->S * d->C * d->O / 2;  o = (o + 255) & ~(size_t)255;
                 }
@@ -424,6 +425,7 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
 }
 
 long long* g_conv_trace = nullptr;   // device buffer for per-role cycle counters, or null
+int g_conv_res_stage = 1; // loader-fed kernel: stage int16 residual rows in shared memory when possible
 int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible), 3 = 2 without the activation-stationary kernel
 
 template <int NT, int STRIDE>
@@ -454,36 +456,65 @@ int launch_conv_umma_ws(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t 
     return launch_check("conv_layer (tcgen05)");
 }
 
-template <int NT>
+template <int NT, bool RSTAGE>
 __global__ void __launch_bounds__(umma::kPreThreads, 1) k_conv_umma_pre(umma::ConvWsArgs a) {
     extern __shared__ __align__(128) unsigned char dyn_smem_pre[];
-    umma::conv_umma_pre_cta<NT>(a, dyn_smem_pre);
+    umma::conv_umma_pre_cta<NT, RSTAGE>(a, dyn_smem_pre);
 }
 __global__ void __launch_bounds__(256) k_expand_raster(umma::ConvWsArgs a, uint4* planes, long long positions,
                                                        long long front) {
     umma::expand_raster(a, planes, positions, front);
 }
 
-template <int NT>
-int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st, bool expand) {
+template <int NT, bool RSTAGE>
+int launch_conv_umma_pre_k(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
     if (configure_once(configured, [] {
-            return cudaFuncSetAttribute(k_conv_umma_pre<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            return cudaFuncSetAttribute(k_conv_umma_pre<NT, RSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         }))
         return 1;
-    if (expand) {
-        const long long units = a.pre_positions * (a.C >> 6);
-        k_expand_raster<<<elementwise_grid(units, sms), 256, 0, st>>>(a, const_cast<uint4*>(a.pre), a.pre_positions,
-                                                                   a.pre_front);
-        if (launch_check("conv_layer (input expansion)")) return 1;
-    }
     a.ntiles_n = a.O / NT;
     if (a.ntiles_n > sms) return fail("conv_layer: more n-tiles than SMs");
     const long long mtiles = (a.NV + 127) / 128;
     long long per = sms / a.ntiles_n;
     if (per > mtiles) per = mtiles;
-    k_conv_umma_pre<NT><<<(int)(per * a.ntiles_n), umma::kPreThreads, smem, st>>>(a);
+    k_conv_umma_pre<NT, RSTAGE><<<(int)(per * a.ntiles_n), umma::kPreThreads, smem, st>>>(a);
     return launch_check("conv_layer (tcgen05, pre-expanded input)");
+}
+
+// npos, C, RS of the layer are needed to size the patch ring again when the residual rows are staged
+template <int NT>
+int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st, bool expand) {
+    if (expand) {
+        const long long units = a.pre_positions * (a.C >> 6) * (a.stride == 2 ? 4 : 1);
+        k_expand_raster<<<elementwise_grid(units, sms), 256, 0, st>>>(a, const_cast<uint4*>(a.pre), a.pre_positions,
+                                                                   a.pre_front);
+        if (launch_check("conv_layer (input expansion)")) return 1;
+    }
+    if constexpr (NT >= 64) {
+        // int16 residual rows through shared memory (see conv_umma_pre_cta) when the tensors allow
+        // it and the two row buffers fit beside a patch ring of at least two stages.  Measured at
+        // batch 1024 (staged / direct): 28 x 28 x 128 0.186 / 0.215 ms, 14 x 14 x 256 0.112 /
+        // 0.138, 7 x 7 x 512 0.127 / 0.120, 56 x 56 x 64 (n-tile 64) 0.425 / 0.327 -- the once-per-tile
+        // rendezvous of the 16 epilogue warps costs more than the narrow rows save there.
+        const int lim = a.res_in ? (a.residual_channels < a.res_in_ch ? a.residual_channels : a.res_in_ch) : 0;
+        const bool in_ok = !a.res_in || (a.res_in_bytes == 2 && !a.residual_pool && a.res_in_ch % 8 == 0 &&
+                                         ((uintptr_t)a.res_in & 15) == 0 && (lim % NT == 0 || lim >= a.O));
+        const bool out_ok = !a.res_out || (a.res_out_bytes == 2 && ((uintptr_t)a.res_out & 15) == 0);
+        if ((a.res_in || a.res_out) && in_ok && out_ok && g_conv_res_stage && (NT >= 128 || g_conv_res_stage == 2)) {
+            int stages = a.pre_stages;
+            const int RS = a.R * a.S;
+            const int nplane = a.stride == 2 ? 4 : 1;
+            while (stages > 2 && umma::pre_smem_bytes(a.NPOS, a.C, RS, NT, stages, nplane) + umma::pre_res_stage_bytes(NT) > 227 * 1024)
+                stages--;
+            const size_t need = umma::pre_smem_bytes(a.NPOS, a.C, RS, NT, stages, nplane) + umma::pre_res_stage_bytes(NT);
+            if (need <= 227 * 1024) {
+                a.pre_stages = stages;
+                return launch_conv_umma_pre_k<NT, true>(a, need, sms, st);
+            }
+        }
+    }
+    return launch_conv_umma_pre_k<NT, false>(a, smem, sms, st);
 }
 
 // 2x2 max of an int16 residual [B][2P][2Q][ch] -> [B][P][Q][ch] (kernel.cuh:773-783), 8 channels
@@ -965,7 +996,7 @@ int tcbnn_conv_layer_w(const tcbnn_conv_desc* d, const uint32_t* in, const void*
 }
 
 // the next layer's input planes, as its descriptor lays them out
-struct NextPlanes { uint4* planes; long long positions, front; int PW, VH; };
+struct NextPlanes { uint4* planes; long long positions, front; int PW, VH, nplane; };
 
 // Checks that `next` can take `d`'s output as pre-expanded input and describes its planes.
 static int next_planes_of(const tcbnn_conv_desc* d, int out_h, int out_w, const tcbnn_conv_desc* next,
@@ -979,7 +1010,7 @@ static int next_planes_of(const tcbnn_conv_desc* d, int out_h, int out_w, const 
     if (!planes || planes_bytes < N.pre_bytes) return fail("next layer's planes: %zu bytes given, %zu needed", planes_bytes, N.pre_bytes);
     if ((uintptr_t)planes & 255) return fail("next layer's planes must be 256-byte aligned");
     nx->planes = (uint4*)planes; nx->positions = N.pre_positions; nx->front = N.pre_front;
-    nx->PW = N.umma_pw; nx->VH = N.umma_vh;
+    nx->PW = N.umma_pw; nx->VH = N.umma_vh; nx->nplane = next->stride_h == 2 ? 4 : 1;
     return 0;
 }
 
@@ -988,12 +1019,13 @@ static int next_planes_of(const tcbnn_conv_desc* d, int out_h, int out_w, const 
 static int expand_for_next(const tcbnn_conv_desc* next, const uint32_t* bits, const NextPlanes& nx, cudaStream_t st) {
     umma::ConvWsArgs a = {};
     a.in = bits; a.B = next->B; a.H = next->H; a.W = next->W; a.C = next->C;
+    a.stride = next->stride_h; a.OHg = next->OH * next->pool; a.OWg = next->OW * next->pool;
     a.PW = nx.PW; a.VH = nx.VH; a.NV = (long long)next->B * nx.VH * nx.PW;
     umma::fastdiv_setup(a.PW, &a.pw_mul, &a.pw_sh);
     umma::fastdiv_setup(a.VH, &a.vh_mul, &a.vh_sh);
     int sms;
     if (sm_count(&sms)) return 1;
-    k_expand_raster<<<elementwise_grid(nx.positions * (next->C >> 6), sms), 256, 0, st>>>(a, nx.planes, nx.positions, nx.front);
+    k_expand_raster<<<elementwise_grid(nx.positions * (next->C >> 6) * nx.nplane, sms), 256, 0, st>>>(a, nx.planes, nx.positions, nx.front);
     return launch_check("expansion for the next layer");
 }
 
@@ -1056,10 +1088,10 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         a.trace = g_conv_trace;
         a.pre = nullptr; a.pre_positions = 0; a.pre_front = 0;
         a.pre_stages = 0;
-        a.nxt = nullptr; a.nxt_positions = 0; a.nxt_front = 0; a.nxt_PW = 0; a.nxt_VH = 0;
+        a.nxt = nullptr; a.nxt_positions = 0; a.nxt_front = 0; a.nxt_PW = 0; a.nxt_VH = 0; a.nxt_nplane = 1;
         if (nx && !use_as && !pooled) {     // (a pooled layer's kernel sees the pre-pool grid)
             a.nxt = nx->planes; a.nxt_positions = nx->positions; a.nxt_front = nx->front;
-            a.nxt_PW = nx->PW; a.nxt_VH = nx->VH;
+            a.nxt_PW = nx->PW; a.nxt_VH = nx->VH; a.nxt_nplane = nx->nplane;
             *fed = true;
         }
         if (use_as) {
@@ -1163,9 +1195,11 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
 }
 
 int tcbnn_set_conv_path(int path) {
-    if (path < 0 || path > 3)
-        return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05, 3 = tcgen05 filter-stationary kernel only");
-    g_conv_path = path;
+    if (path < 0 || path > 5)
+        return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05, 3 = tcgen05 filter-stationary kernel only, "
+                    "4 / 5 = automatic with residual staging never / wherever possible");
+    g_conv_path = path >= 4 ? 0 : path;
+    g_conv_res_stage = path == 4 ? 0 : path == 5 ? 2 : 1;
     return 0;
 }
 
@@ -1309,10 +1343,15 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
     c.res_out_bytes = res_out_bytes; c.res_out_ld = d->O; c.acc_out = acc_out;
     c.total = (unsigned)((long long)d->B * d->OH * d->OW * d->pool * d->pool);
     c.nxt = nullptr; c.nxt_positions = 0; c.nxt_front = 0; c.nxt_PW = 0; c.nxt_VH = 0;
+    NextPlanes nx;
+    bool expand_after = false;
     if (next) {
-        NextPlanes nx;
         if (next_planes_of(d, d->OH, d->OW, next, next_planes, next_planes_bytes, &nx)) return 1;
-        c.nxt = nx.planes; c.nxt_positions = nx.positions; c.nxt_front = nx.front; c.nxt_PW = nx.PW; c.nxt_VH = nx.VH;
+        if (nx.nplane == 1) {
+            c.nxt = nx.planes; c.nxt_positions = nx.positions; c.nxt_front = nx.front; c.nxt_PW = nx.PW; c.nxt_VH = nx.VH;
+        } else {
+            expand_after = true;                  // the generated kernel writes stride-1 planes only
+        }
     }
     void* params[] = {&c};
     const unsigned grid = (c.total + spec::kSpecThreads - 1) / spec::kSpecThreads;
@@ -1322,7 +1361,9 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
     if (spec_build(h, variant, false)) return 1;       // first use compiles it (checked under the handle's lock)
     CUDA_TRY(cudaLaunchKernel((const void*)h->kernel[variant], dim3(grid, (h->O + 63) / 64), dim3(spec::kSpecThreads),
                               params, 0, (cudaStream_t)stream));
-    return launch_check("inconv_specialized_layer");
+    if (launch_check("inconv_specialized_layer")) return 1;
+    if (expand_after) return expand_for_next(next, out, nx, (cudaStream_t)stream);
+    return 0;
 }
 
 int tcbnn_inconv_release(void* handle) {

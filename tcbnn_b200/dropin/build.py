@@ -4,8 +4,12 @@
 
 build/dropin/net_runner        : tcbnn_b200/dropin/net_runner.cu (generic cooperative-kernel driver)
 build/dropin/<driver>          : the reference's own, UNCHANGED driver sources (mnist_mlp.cu,
-    cifar10_vgg.cu, cifar10_resnet.cu, imagenet_resnet.cu) compiled against the drop-in
-    utility.h / param.h / kernel.cuh.  The sources are copied at build time into the git-ignored
+    cifar10_vgg.cu, cifar10_resnet.cu, imagenet_resnet.cu, alexnet.cu, imagenet_vgg.cu and the
+    OpenMP-thread-per-GPU benn_scaleup.cu) compiled against the drop-in utility.h / param.h /
+    kernel.cuh and linked with libtcbnn_b200.so (the drop-in routes the drivers' network launch
+    to the library's kernels, see param.h).  With shim=<header> the binaries are named
+    <driver>_shim and are built with that header force-included (the tests pass one that makes a
+    driver print the time it measures and dump the logits it downloads).  The sources are copied at build time into the git-ignored
     build/ folder (a driver's `#include "param.h"` looks in its own folder first, so it must not
     sit next to the reference headers), together with the reference's data.h; the dataset readers
     are replaced by synthetic_data.cpp and libjpeg by empty stub headers.  Skipped when the
@@ -23,7 +27,11 @@ OUT = os.path.join(ROOT, "build", "dropin")
 # -maxrregcount=64 as in the reference Makefile (Makefile:15): the drivers launch 1024-thread blocks
 NVCC = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-rdc=true",
         "-maxrregcount=64", "-w"]
-DRIVERS = ["mnist_mlp", "cifar10_vgg", "cifar10_resnet", "imagenet_resnet"]
+DRIVERS = ["mnist_mlp", "cifar10_vgg", "cifar10_resnet", "imagenet_resnet", "alexnet", "imagenet_vgg", "benn_scaleup"]
+PKG = os.path.dirname(HERE)
+# the drivers call into libtcbnn_b200.so; found at run time relative to the binary (build/dropin/)
+LINK = ["-L", PKG, "-ltcbnn_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../tcbnn_b200"]
+EXTRA = {"benn_scaleup": ["-Xcompiler", "-fopenmp", "-lnccl"]}
 
 
 def _run(cmd):
@@ -43,7 +51,8 @@ def _stale(target, deps):
 def _headers():
     csrc = os.path.join(os.path.dirname(HERE), "csrc")
     return [os.path.join(HERE, f) for f in ("utility.h", "param.h", "kernel.cuh")] + \
-           [os.path.join(csrc, f) for f in ("bnn_layers.cuh", "bnn_warp.cuh")]
+           [os.path.join(csrc, f) for f in ("bnn_layers.cuh", "bnn_warp.cuh")] + \
+           [os.path.join(ROOT, "include", "tcbnn_b200.h")]
 
 
 def build_runner():
@@ -51,7 +60,7 @@ def build_runner():
     src = os.path.join(HERE, "net_runner.cu")
     out = os.path.join(OUT, "net_runner")
     if _stale(out, [src] + _headers()):
-        _run(NVCC + ["-I", HERE, "-o", out, src])
+        _run(NVCC + ["-I", HERE, "-o", out, src] + LINK)
     return out
 
 
@@ -60,8 +69,9 @@ def default_ref_root():
     return os.environ.get("TCBNN_REF_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
-def build_reference_drivers(ref_root=None):
+def build_reference_drivers(ref_root=None, shim=None):
     ref_root = ref_root or default_ref_root()
+    shim_h = shim
     if not os.path.exists(os.path.join(ref_root, "data.h")):
         return []
     os.makedirs(OUT, exist_ok=True)
@@ -74,10 +84,17 @@ def build_reference_drivers(ref_root=None):
         if not os.path.exists(src):
             return None
         staged = os.path.join(OUT, name + ".cu")
-        out = os.path.join(OUT, name)
-        if _stale(out, [src, data_src] + _headers()):
+        out = os.path.join(OUT, name + ("_shim" if shim else ""))
+        if _stale(out, [src, data_src] + _headers() + ([shim_h] if shim else [])):
             shutil.copyfile(src, staged)
-            _run(NVCC + ["-I", OUT, "-I", HERE, "-I", os.path.join(HERE, "stubs"), "-o", out, staged, data_src])
+            try:
+                _run(NVCC + (["-include", shim_h] if shim else []) +
+                     ["-I", OUT, "-I", HERE, "-I", os.path.join(HERE, "stubs"), "-o", out, staged, data_src] +
+                     LINK + EXTRA.get(name, []))
+            except RuntimeError:
+                if name in EXTRA:          # needs OpenMP and the NCCL headers: optional
+                    return None
+                raise
         return out
 
     with ThreadPoolExecutor(max_workers=len(DRIVERS)) as pool:      # the compiles are independent
@@ -87,7 +104,8 @@ def build_reference_drivers(ref_root=None):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref-root", default=None)
+    ap.add_argument("--shim", default=None, help="header to force-include (builds <driver>_shim)")
     a = ap.parse_args()
     print(build_runner())
-    for b in build_reference_drivers(a.ref_root):
+    for b in build_reference_drivers(a.ref_root, a.shim):
         print(b)

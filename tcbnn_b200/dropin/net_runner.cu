@@ -16,6 +16,12 @@
 //   TCBNN_WEIGHTS_IN_MEMORY set, loaded first and handed over as a host array).
 // TCBNN_RUNS=n launches the forward kernel n times on the same objects (layers store their
 //   outputs, so every run gives the same result); the last one is timed.
+// TCBNN_LIVE_BATCH=n (drop-in headers only): after the first runs on the full batch the same objects
+//   are switched to the first n images (set_batch) for the last, timed run; logits and dumps then
+//   hold n images.
+// TCBNN_RUNNER_FAST (drop-in headers only): instead of the cooperative kernel, queue every layer
+//   through the C ABI of libtcbnn_b200.so, the way the drop-in does for a driver whose kernel
+//   takes its layer objects as arguments (tcbnn_dropin::launch_network in param.h).
 // input.bin   : fp32, [B][K] for "in" networks, NCHW [B][3][H][W] otherwise.
 #include <cooperative_groups.h>
 #include <vector>
@@ -144,21 +150,50 @@ int main(int argc, char** argv) {
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&numBlocksPerSm, run_network, numThreads, shared_memory);
     void* args[] = {&refs_gpu, &n};
     const int runs = getenv("TCBNN_RUNS") ? atoi(getenv("TCBNN_RUNS")) : 1;
-    for (int i = 1; i < runs; i++)
+    bool fast = false;
+#ifdef TCBNN_DROPIN
+    fast = getenv("TCBNN_RUNNER_FAST") != NULL;
+#endif
+    auto forward = [&]() {
+#ifdef TCBNN_DROPIN
+        if (fast) {
+            for (size_t i = 0; i < refs.size(); i++)
+                if (!tcbnn_dropin::forward_registered(refs[i].gpu, 0, false)) {
+                    fprintf(stderr, "layer %zu cannot take the fast path\n", i);
+                    exit(2);
+                }
+            return;
+        }
+#endif
         CUDA_SAFE_CALL(cudaLaunchCooperativeKernel((void*)run_network, numBlocksPerSm * deviceProp.multiProcessorCount,
                                                    numThreads, args, shared_memory));
+    };
+    for (int i = 1; i < runs; i++) forward();
+    int live = batch;
+#ifdef TCBNN_DROPIN
+    if (getenv("TCBNN_LIVE_BATCH")) {
+        live = atoi(getenv("TCBNN_LIVE_BATCH"));
+        CUDA_SAFE_CALL(cudaDeviceSynchronize());
+        for (size_t i = 0; i < net.size(); i++) {
+            if (net[i].in) net[i].in->set_batch(live);
+            if (net[i].inconv) net[i].inconv->set_batch(live);
+            if (net[i].conv) net[i].conv->set_batch(live);
+            if (net[i].fc) net[i].fc->set_batch(live);
+            if (net[i].out) net[i].out->set_batch(live);
+        }
+    }
+#endif
     START_TIMER;
-    CUDA_SAFE_CALL(cudaLaunchCooperativeKernel((void*)run_network, numBlocksPerSm * deviceProp.multiProcessorCount,
-                                               numThreads, args, shared_memory));
+    forward();
     STOP_TIMER;
     CUDA_CHECK_KERNEL();
     CUDA_SAFE_CALL(cudaDeviceSynchronize());
-    printf("{\"forward_ms\": %.4f, \"batch\": %d, \"layers\": %d, \"blocks\": %d}\n", milliseconds, batch, n,
-           numBlocksPerSm * deviceProp.multiProcessorCount);
+    printf("{\"forward_ms\": %.4f, \"batch\": %d, \"layers\": %d, \"blocks\": %d, \"fast\": %d}\n", milliseconds, batch, n,
+           numBlocksPerSm * deviceProp.multiProcessorCount, fast ? 1 : 0);
 
     float* logits = net.back().out->download_output();
     FILE* fo = fopen(argv[4], "wb");
-    fwrite(logits, sizeof(float), (size_t)batch * K, fo);
+    fwrite(logits, sizeof(float), (size_t)live * K, fo);
     fclose(fo);
     // also dump every layer's +-1 activations when asked (parity checks)
     if (getenv("TCBNN_DUMP_DIR")) {

@@ -10,12 +10,30 @@
 // What is different inside: activations are NHWC bit-packed words (no HWNC 8x128 tiling),
 // residuals are NHWC int32 with the reference's PAD128 channel stride, sizes are computed in size_t, and every object carries the
 // argument block the layer loops read on the device.
+//
+// Two ways to run the network the driver has built, chosen when the driver launches its kernel:
+//  * the fast path (default): the driver's cudaLaunchCooperativeKernel(net, grid, block, args, ...)
+//    is routed to tcbnn_dropin::launch_network (end of this file).  Every initialize() has
+//    registered its object under the device pointer it returned, so the kernel's argument list --
+//    which IS the layer list, in layer order, in all of the reference's drivers -- is mapped back
+//    to the objects and each layer is queued through the C ABI of libtcbnn_b200.so
+//    (include/tcbnn_b200.h: tcgen05 convolutions and GEMM, the first layer compiled for its
+//    filter, int16 residual rows where the running sum provably fits).  The driver source stays
+//    as it is; it is linked with -ltcbnn_b200.
+//  * the driver's own cooperative kernel on the warp-level b1 layer loops (kernel.cuh), when the
+//    environment variable TCBNN_DROPIN_COOPERATIVE is set or when an argument of the launch is
+//    not a registered layer object.
+// The two paths lay the saved residuals out differently inside the same buffers, so one process
+// uses one of them.
 #ifndef PARAM_H
 #define PARAM_H
 #define TCBNN_DROPIN 1
 
+#include <mutex>
+#include <vector>
 #include "utility.h"
 #include "../csrc/bnn_layers.cuh"
+#include "../../include/tcbnn_b200.h"
 
 const int dev = 0;
 
@@ -31,6 +49,75 @@ __global__ void k_conv_prepare(const uin32* fbits, int O, int R, int S, int Cw, 
 }
 inline int grid_for(size_t n) { size_t b = (n + 255) / 256; return (int)(b < 1 ? 1 : b > 4096 ? 4096 : b); }
 inline int fc_ld(int k) { return STEP128(k) * 4; }
+
+#define TCBNN_FAST_CALL(call)                                                                      \
+    do {                                                                                           \
+        if ((call) != 0) {                                                                         \
+            fprintf(stderr, "%s failed at %s:%i : %s\n", #call, __FILE__, __LINE__, tcbnn_last_error()); \
+            exit(-1);                                                                              \
+        }                                                                                          \
+    } while (0)
+
+// Every initialised layer object, findable by the pointers a driver passes around: the device
+// copy initialize() returned (the kernel argument), its output bits (the next layer's input) and
+// its saved residual (a later layer's injected residual).  Drivers may build one network per GPU
+// from one host thread each (benn_scaleup.cu:231-234), so the list is locked and keyed by device.
+enum LayerKind { kLayerIn, kLayerFc, kLayerOut, kLayerInConv, kLayerConv };
+struct RegisteredLayer {
+    int device;
+    LayerKind kind;
+    void* host;                 // the XLayerParam object
+    const void* gpu_struct;
+    const void* output_gpu;
+    const void* residual_gpu;
+};
+inline std::vector<RegisteredLayer>& layer_list() { static std::vector<RegisteredLayer> v; return v; }
+inline std::mutex& layer_mutex() { static std::mutex m; return m; }
+inline int current_device() { int d = 0; CUDA_SAFE_CALL(cudaGetDevice(&d)); return d; }
+inline void register_layer(LayerKind kind, void* host, const void* gpu_struct, const void* output_gpu,
+                           const void* residual_gpu) {
+    std::lock_guard<std::mutex> lock(layer_mutex());
+    RegisteredLayer r = {current_device(), kind, host, gpu_struct, output_gpu, residual_gpu};
+    layer_list().push_back(r);
+}
+inline void unregister_layer(void* host) {
+    std::lock_guard<std::mutex> lock(layer_mutex());
+    std::vector<RegisteredLayer>& v = layer_list();
+    for (size_t i = 0; i < v.size(); i++)
+        if (v[i].host == host) { v.erase(v.begin() + i); return; }
+}
+// which: 0 = by kernel argument, 1 = by output bits, 2 = by saved residual
+inline bool find_layer(int which, const void* p, RegisteredLayer* out) {
+    if (p == NULL) return false;
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(layer_mutex());
+    const std::vector<RegisteredLayer>& v = layer_list();
+    for (size_t i = v.size(); i-- > 0;) {
+        const void* q = which == 0 ? v[i].gpu_struct : which == 1 ? v[i].output_gpu : v[i].residual_gpu;
+        if (v[i].device == dev && q == p) { *out = v[i]; return true; }
+    }
+    return false;
+}
+
+// Scratch the C-ABI layer calls may use during a call (split-K partial sums, expanded GEMM
+// operands, a conv layer's expanded input): one buffer per device, grown by initialize() to the
+// largest request, shared by all layers since they run one after the other on one stream.
+struct DeviceScratch { void* ptr; size_t bytes; };
+inline DeviceScratch* scratch_of_device() {
+    static DeviceScratch s[64];
+    const int d = current_device();
+    if (d < 0 || d >= 64) { fprintf(stderr, "device ordinal %d not supported.\n", d); exit(-1); }
+    return &s[d];
+}
+inline void scratch_reserve(size_t bytes) {
+    std::lock_guard<std::mutex> lock(layer_mutex());
+    DeviceScratch* s = scratch_of_device();
+    if (bytes <= s->bytes) return;
+    if (s->ptr) CUDA_SAFE_CALL(cudaFree(s->ptr));
+    CUDA_SAFE_CALL(cudaMalloc(&s->ptr, bytes));
+    CUDA_SAFE_CALL(cudaMemset(s->ptr, 0, bytes));
+    s->bytes = bytes;
+}
 
 // Where initialize() takes its numbers from.  The reference reads a text file of decimal floats
 // through launch_array (utility.h:188-196); the same values, in the same order, may also come
@@ -128,7 +215,20 @@ public:
         CHECK_NULL_POINTER(output_gpu);
         SAFE_ALOC_GPU(gpu, sizeof(In128LayerParam));
         CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(In128LayerParam), cudaMemcpyHostToDevice));
+        tcbnn_dropin::register_layer(tcbnn_dropin::kLayerIn, this, gpu, output_gpu, NULL);
         return gpu;
+    }
+    // the layer through the C ABI (the fast path of tcbnn_dropin::launch_network)
+    void forward(cudaStream_t stream) {
+        TCBNN_FAST_CALL(tcbnn_pack_rows(input_gpu, input_height, input_width, ld(), output_gpu, stream));
+    }
+    // Extension (the reference fixes the batch at construction): from now on the object processes
+    // the first n rows, n at most the constructor's input_height; buffers keep their size.
+    void set_batch(int n) {
+        if (max_rows == 0) max_rows = input_height;
+        if (n <= 0 || n > max_rows) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, max_rows); exit(-1); }
+        input_height = output_height = n;
+        if (gpu) CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(In128LayerParam), cudaMemcpyHostToDevice));
     }
     void set_output_gpu(uin32* p) { output_gpu = p; }
     uin32* get_output_gpu() { return output_gpu; }
@@ -139,6 +239,7 @@ public:
     }
     float* download_full_output() { return tcbnn_dropin::unpack_to_host(output_gpu, output_height, output_width, ld()); }
     void release() {
+        tcbnn_dropin::unregister_layer(this);
         SAFE_FREE_GPU(input_gpu); SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(gpu); SAFE_FREE_HOST(output);
     }
     ~In128LayerParam() { release(); }
@@ -147,6 +248,7 @@ public:
     int input_width, input_height, output_width, output_height;
     In128LayerParam* gpu;
     char name[8];
+    int max_rows = 0;           // the constructor's row count once set_batch has been used
 };
 
 // hidden FC layer (param.h:224-385)
@@ -197,7 +299,21 @@ public:
         args.p0 = bn_gpu; args.p1 = NULL; args.splits = 1; args.partial = NULL;
         SAFE_ALOC_GPU(gpu, sizeof(Fc128LayerParam));
         CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Fc128LayerParam), cudaMemcpyHostToDevice));
+        tcbnn_dropin::scratch_reserve(tcbnn_gemm_workspace_bytes(input_height, weight_width, input_width));
+        tcbnn_dropin::register_layer(tcbnn_dropin::kLayerFc, this, gpu, output_gpu, NULL);
         return gpu;
+    }
+    void set_batch(int n) {             // see In128LayerParam::set_batch
+        if (max_rows == 0) max_rows = input_height;
+        if (n <= 0 || n > max_rows) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, max_rows); exit(-1); }
+        input_height = output_height = n;
+        args.M = n;
+        if (gpu) CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Fc128LayerParam), cudaMemcpyHostToDevice));
+    }
+    void forward(cudaStream_t stream) {
+        tcbnn_dropin::DeviceScratch* ws = tcbnn_dropin::scratch_of_device();
+        TCBNN_FAST_CALL(tcbnn_fc_layer(input_gpu, weight_gpu, bn_gpu, input_height, input_width, weight_width, input_ld,
+                                       tcbnn_dropin::fc_ld(weight_height), output_gpu, ld(), ws->ptr, ws->bytes, stream));
     }
     uin32* get_output_gpu() { return output_gpu; }
     uin32* download_output() {
@@ -207,6 +323,7 @@ public:
     }
     float* download_full_output() { return tcbnn_dropin::unpack_to_host(output_gpu, output_height, output_width, ld()); }
     void release() {
+        tcbnn_dropin::unregister_layer(this);
         SAFE_FREE_HOST(weight); SAFE_FREE_HOST(bn); SAFE_FREE_HOST(output);
         SAFE_FREE_GPU(weight_gpu); SAFE_FREE_GPU(bn_gpu); SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(gpu);
     }
@@ -219,6 +336,7 @@ public:
     tcbnn::GemmArgs args;
     Fc128LayerParam* gpu;
     char name[8];
+    int max_rows = 0;
 };
 
 // output layer (param.h:388-531)
@@ -267,7 +385,22 @@ public:
         args.splits = 1; args.partial = NULL;
         SAFE_ALOC_GPU(gpu, sizeof(Out128LayerParam));
         CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Out128LayerParam), cudaMemcpyHostToDevice));
+        tcbnn_dropin::scratch_reserve(tcbnn_gemm_workspace_bytes(input_height, weight_width, input_width));
+        tcbnn_dropin::register_layer(tcbnn_dropin::kLayerOut, this, gpu, output_gpu, NULL);
         return gpu;
+    }
+    void set_batch(int n) {             // see In128LayerParam::set_batch
+        if (max_rows == 0) max_rows = input_height;
+        if (n <= 0 || n > max_rows) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, max_rows); exit(-1); }
+        input_height = output_height = n;
+        args.M = n;
+        if (gpu) CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Out128LayerParam), cudaMemcpyHostToDevice));
+    }
+    void forward(cudaStream_t stream) {
+        tcbnn_dropin::DeviceScratch* ws = tcbnn_dropin::scratch_of_device();
+        TCBNN_FAST_CALL(tcbnn_out_layer(input_gpu, weight_gpu, bn_scale_gpu, bn_bias_gpu, input_height, input_width,
+                                        weight_width, tcbnn_dropin::fc_ld(input_width), tcbnn_dropin::fc_ld(weight_height),
+                                        output_gpu, weight_width, ws->ptr, ws->bytes, stream));
     }
     float* get_output_gpu() { return output_gpu; }
     float* download_output() {
@@ -276,6 +409,7 @@ public:
         return output;
     }
     void release() {
+        tcbnn_dropin::unregister_layer(this);
         SAFE_FREE_HOST(weight); SAFE_FREE_HOST(bn_scale); SAFE_FREE_HOST(bn_bias); SAFE_FREE_HOST(output);
         SAFE_FREE_GPU(weight_gpu); SAFE_FREE_GPU(bn_scale_gpu); SAFE_FREE_GPU(bn_bias_gpu);
         SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(gpu);
@@ -288,6 +422,7 @@ public:
     tcbnn::GemmArgs args;
     Out128LayerParam* gpu;
     char name[8];
+    int max_rows = 0;
 };
 
 // first conv layer on fp32 NCHW images (param.h:701-870)
@@ -302,7 +437,8 @@ public:
           filter_height(_filter_height), output(NULL), output_gpu(NULL), output_channels(_output_channels),
           padding(_padding), bn(NULL), bn_gpu(NULL), batch(_batch), stride_height(_stride_height),
           stride_width(_stride_width), pool_width(_pool_width), pool_height(_pool_height),
-          save_residual(_save_residual), output_residual_gpu(NULL), gpu(NULL) {
+          save_residual(_save_residual), output_residual_gpu(NULL), gpu(NULL), fast_handle(NULL),
+          fast_res_bytes(4), fast_res_bound(-1), fast_next(NULL), fast_next_planes(NULL), fast_next_planes_bytes(0) {
         strncpy(name, _name, 8);
         tcbnn_dropin::conv_geometry(input_height, input_width, filter_height, filter_width, stride_height,
                                     stride_width, padding, pool_height, pool_width, &pad_h, &pad_w,
@@ -349,7 +485,49 @@ public:
             SAFE_ALOC_GPU(output_residual_gpu, residual_bytes());
             CUDA_SAFE_CALL(cudaMemset(output_residual_gpu, 0, residual_bytes()));
         }
+        fast_setup();
         return ready();
+    }
+    // ---- the fast path (tcbnn_dropin::launch_network): the layer through the C ABI ----------------
+    // The saved residual is kept as int16 when R*S*3*max|pixel| (the images are at hand here) fits;
+    // the kernel is compiled for this layer's filter and run once now, so that the driver's timed
+    // launch does not pay for the compilation.
+    void fast_setup() {
+        memset(&fast_desc, 0, sizeof fast_desc);
+        fast_desc.B = batch; fast_desc.H = input_height; fast_desc.W = input_width; fast_desc.C = 3;
+        fast_desc.O = output_channels; fast_desc.R = filter_height; fast_desc.S = filter_width;
+        fast_desc.stride_h = stride_height; fast_desc.stride_w = stride_width; fast_desc.padding = padding ? 1 : 0;
+        fast_desc.pool = pool_height;
+        TCBNN_FAST_CALL(tcbnn_conv_shape(&fast_desc));
+        float amax = 0.f;
+        for (size_t i = 0; i < input_size(); i++) { const float v = input[i] < 0 ? -input[i] : input[i]; if (v > amax) amax = v; }
+        const double bound = (double)filter_height * filter_width * 3 * amax * 1.001 + 2;
+        fast_res_bound = bound < 2e9 ? (long long)bound : -1;
+        fast_res_bytes = (fast_res_bound >= 0 && fast_res_bound <= 32767) ? 2 : 4;
+        if (tcbnn_inconv_specialize(&fast_desc, filter_gpu, bn_gpu, NULL, &fast_handle) != 0) fast_handle = NULL;
+        if (fast_handle) {                                 // compile now, outside any timed launch
+            forward(0);
+            CUDA_SAFE_CALL(cudaDeviceSynchronize());
+            CUDA_SAFE_CALL(cudaMemset(output_gpu, 0, output_bit_bytes()));
+            if (save_residual) CUDA_SAFE_CALL(cudaMemset(output_residual_gpu, 0, residual_bytes()));
+        }
+    }
+    void set_batch(int n) {             // see In128LayerParam::set_batch
+        if (max_batch == 0) max_batch = batch;
+        if (n <= 0 || n > max_batch) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, max_batch); exit(-1); }
+        batch = n; args.B = n; fast_desc.B = n;
+        if (gpu) CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(InConv128LayerParam), cudaMemcpyHostToDevice));
+    }
+    void forward(cudaStream_t stream) {
+        const long long stride = (long long)output_height * output_width * STEP32(output_channels);
+        void* res = save_residual ? (void*)output_residual_gpu : NULL;
+        if (fast_handle)
+            TCBNN_FAST_CALL(tcbnn_inconv_specialized_layer_x(fast_handle, &fast_desc, input_gpu, NULL, NULL, output_gpu,
+                                                             stride, res, fast_res_bytes, NULL, fast_next, fast_next_planes,
+                                                             fast_next_planes_bytes, stream));
+        else
+            TCBNN_FAST_CALL(tcbnn_inconv_layer(&fast_desc, input_gpu, filter_gpu, bn_gpu, output_gpu, stride, res,
+                                               fast_res_bytes, NULL, stream));
     }
     InConv128LayerParam* ready() {
         CHECK_NULL_POINTER(input_gpu);
@@ -365,6 +543,7 @@ public:
         args.res_out_ld = PAD128(output_channels); args.acc_out = NULL;
         SAFE_ALOC_GPU(gpu, sizeof(InConv128LayerParam));
         CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(InConv128LayerParam), cudaMemcpyHostToDevice));
+        tcbnn_dropin::register_layer(tcbnn_dropin::kLayerInConv, this, gpu, output_gpu, output_residual_gpu);
         return gpu;
     }
     uin32* get_output_gpu() { return output_gpu; }
@@ -380,6 +559,8 @@ public:
                                             output_channels, STEP32(output_channels));
     }
     void release() {
+        tcbnn_dropin::unregister_layer(this);
+        if (fast_handle) { tcbnn_inconv_release(fast_handle); fast_handle = NULL; }
         SAFE_FREE_HOST(filter); SAFE_FREE_HOST(bn); SAFE_FREE_HOST(output);
         SAFE_FREE_GPU(input_gpu); SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(filter_gpu); SAFE_FREE_GPU(bn_gpu);
         SAFE_FREE_GPU(gpu); SAFE_FREE_GPU(output_residual_gpu);
@@ -394,6 +575,16 @@ public:
     tcbnn::InConvArgs args;
     InConv128LayerParam* gpu;
     char name[8];
+    // fast path: descriptor, compiled kernel, element size and bound of the saved residual, and the
+    // consumer whose pre-expanded input this layer also writes (set by that consumer's initialize())
+    tcbnn_conv_desc fast_desc;
+    void* fast_handle;
+    int fast_res_bytes;
+    long long fast_res_bound;
+    const tcbnn_conv_desc* fast_next;
+    void* fast_next_planes;
+    size_t fast_next_planes_bytes;
+    int max_batch = 0;
 };
 
 // binary conv layer (param.h:872-1065)
@@ -412,7 +603,9 @@ public:
           padding(_padding), pool_width(_pool_width), pool_height(_pool_height), ahead_fc(_ahead_fc),
           save_residual(_save_residual), output_residual_gpu(NULL), inject_residual(_inject_residual),
           input_residual_gpu(NULL), residual_channels(_residual_channels), residual_pool(_residual_pool),
-          prepared_gpu(NULL), input_residual_channels(0), gpu(NULL) {
+          prepared_gpu(NULL), input_residual_channels(0), gpu(NULL), fast_ok(false), fast_prepared(NULL),
+          fast_planes(NULL), fast_planes_bytes(0), fast_res_in_ch(0), fast_res_in_bytes(4), fast_res_bytes(4),
+          fast_res_bound(-1), fast_next(NULL), fast_next_planes(NULL), fast_next_planes_bytes(0) {
         strncpy(name, _name, 8);
         tcbnn_dropin::conv_geometry(input_height, input_width, filter_height, filter_width, stride_height,
                                     stride_width, padding, pool_height, pool_width, &pad_h, &pad_w,
@@ -479,7 +672,90 @@ public:
             CUDA_SAFE_CALL(cudaMemset(output_residual_gpu, 0, residual_bytes()));
         }
         if (inject_residual) set_input_residual_gpu(input_residual_gpu);
+        fast_setup();
         return ready();
+    }
+    // ---- the fast path (tcbnn_dropin::launch_network): the layer through the C ABI ----------------
+    // Found through the registry: the producer of the input bits (when it can, it also writes this
+    // layer's pre-expanded input, and this layer skips its expansion pass) and the producer of the
+    // injected residual (its channel count, element size and bound).  The saved residual is int16
+    // when C*R*S + the injected bound fits.  Without a registered residual producer the layer --
+    // and with it the whole network -- stays on the driver's cooperative kernel.
+    void fast_setup() {
+        memset(&fast_desc, 0, sizeof fast_desc);
+        fast_desc.B = batch; fast_desc.H = input_height; fast_desc.W = input_width; fast_desc.C = input_channels;
+        fast_desc.O = output_channels; fast_desc.R = filter_height; fast_desc.S = filter_width;
+        fast_desc.stride_h = stride_height; fast_desc.stride_w = stride_width; fast_desc.padding = padding ? 1 : 0;
+        fast_desc.pool = pool_height;
+        TCBNN_FAST_CALL(tcbnn_conv_shape(&fast_desc));
+        const size_t pb = tcbnn_conv_prepared_bytes(&fast_desc);
+        SAFE_ALOC_GPU(fast_prepared, pb ? pb : 1);
+        TCBNN_FAST_CALL(tcbnn_conv_prepare(&fast_desc, filter_gpu, fast_prepared, NULL));
+        CUDA_SAFE_CALL(cudaDeviceSynchronize());
+        tcbnn_dropin::scratch_reserve(tcbnn_conv_workspace_bytes(&fast_desc));
+        fast_ok = true;
+        long long in_bound = 0;
+        if (inject_residual) {
+            tcbnn_dropin::RegisteredLayer r;
+            if (!tcbnn_dropin::find_layer(2, input_residual_gpu, &r)) {
+                fast_ok = false;
+            } else if (r.kind == tcbnn_dropin::kLayerInConv) {
+                InConv128LayerParam* p = (InConv128LayerParam*)r.host;
+                fast_res_in_ch = p->output_channels; fast_res_in_bytes = p->fast_res_bytes; in_bound = p->fast_res_bound;
+            } else {
+                Conv128LayerParam* p = (Conv128LayerParam*)r.host;
+                fast_res_in_ch = p->output_channels; fast_res_in_bytes = p->fast_res_bytes; in_bound = p->fast_res_bound;
+            }
+        }
+        const long long fan = (long long)input_channels * filter_height * filter_width;
+        fast_res_bound = in_bound < 0 ? -1 : fan + in_bound;
+        fast_res_bytes = (fast_res_bound >= 0 && fast_res_bound <= 32767) ? 2 : 4;
+        // hand-over of the pre-expanded input from the producing layer
+        tcbnn_dropin::RegisteredLayer pr;
+        const size_t planes = tcbnn_conv_planes_bytes(&fast_desc);
+        if (planes && tcbnn_dropin::find_layer(1, input_gpu, &pr)) {
+            const tcbnn_conv_desc** slot = NULL; void** pslot = NULL; size_t* bslot = NULL;
+            if (pr.kind == tcbnn_dropin::kLayerInConv) {
+                InConv128LayerParam* p = (InConv128LayerParam*)pr.host;
+                if (p->fast_handle && p->fast_next == NULL) { slot = &p->fast_next; pslot = &p->fast_next_planes; bslot = &p->fast_next_planes_bytes; }
+            } else if (pr.kind == tcbnn_dropin::kLayerConv) {
+                Conv128LayerParam* p = (Conv128LayerParam*)pr.host;
+                if (p->pool_height == 1 && !p->ahead_fc && p->fast_next == NULL) { slot = &p->fast_next; pslot = &p->fast_next_planes; bslot = &p->fast_next_planes_bytes; }
+            }
+            if (slot) {
+                const size_t ws = tcbnn_conv_workspace_bytes(&fast_desc);
+                fast_planes_bytes = planes > ws ? planes : ws;
+                SAFE_ALOC_GPU(fast_planes, fast_planes_bytes);
+                CUDA_SAFE_CALL(cudaMemset(fast_planes, 0, fast_planes_bytes));
+                *slot = &fast_desc; *pslot = fast_planes; *bslot = fast_planes_bytes;
+            }
+        }
+    }
+    // see In128LayerParam::set_batch; the planes a producer fills are cleared, because their layout
+    // depends on the batch and their padding positions must read as zero
+    void set_batch(int n) {
+        if (max_batch == 0) max_batch = batch;
+        if (n <= 0 || n > max_batch) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, max_batch); exit(-1); }
+        if (n != batch && fast_planes) CUDA_SAFE_CALL(cudaMemset(fast_planes, 0, fast_planes_bytes));
+        batch = n; args.B = n; fast_desc.B = n;
+        if (gpu) CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Conv128LayerParam), cudaMemcpyHostToDevice));
+    }
+    void forward(cudaStream_t stream) {
+        tcbnn_dropin::DeviceScratch* sc = tcbnn_dropin::scratch_of_device();
+        void* ws = fast_planes ? fast_planes : sc->ptr;
+        const size_t wsb = fast_planes ? fast_planes_bytes : sc->bytes;
+        TCBNN_FAST_CALL(tcbnn_conv_layer_x(&fast_desc, input_gpu, fast_prepared, bn_gpu,
+                                           inject_residual ? (const void*)input_residual_gpu : NULL, fast_res_in_bytes,
+                                           fast_res_in_ch, residual_channels, residual_pool ? 1 : 0, output_gpu,
+                                           (long long)image_words(), save_residual ? (void*)output_residual_gpu : NULL,
+                                           fast_res_bytes, NULL, ws, wsb, fast_planes ? 1 : 0, fast_next, fast_next_planes,
+                                           fast_next_planes_bytes, stream));
+    }
+    // 2 after a forward pass in which a residual value did not fit the int16 rows chosen above
+    int fast_status() {
+        int st = 0;
+        TCBNN_FAST_CALL(tcbnn_conv_status(&fast_desc, fast_prepared, &st));
+        return st;
     }
     Conv128LayerParam* ready() {
         CHECK_NULL_POINTER(input_gpu);
@@ -503,6 +779,7 @@ public:
         args.res_out_ld = PAD128(output_channels); args.acc_out = NULL;
         SAFE_ALOC_GPU(gpu, sizeof(Conv128LayerParam));
         CUDA_SAFE_CALL(cudaMemcpy(gpu, this, sizeof(Conv128LayerParam), cudaMemcpyHostToDevice));
+        tcbnn_dropin::register_layer(tcbnn_dropin::kLayerConv, this, gpu, output_gpu, output_residual_gpu);
         return gpu;
     }
     uin32* get_output_gpu() { return output_gpu; }
@@ -521,9 +798,10 @@ public:
                                             output_channels, Ow());
     }
     void release() {
+        tcbnn_dropin::unregister_layer(this);
         SAFE_FREE_HOST(filter); SAFE_FREE_HOST(bn); SAFE_FREE_HOST(output);
         SAFE_FREE_GPU(output_gpu); SAFE_FREE_GPU(filter_gpu); SAFE_FREE_GPU(prepared_gpu); SAFE_FREE_GPU(bn_gpu);
-        SAFE_FREE_GPU(gpu); SAFE_FREE_GPU(output_residual_gpu);
+        SAFE_FREE_GPU(gpu); SAFE_FREE_GPU(output_residual_gpu); SAFE_FREE_GPU(fast_prepared); SAFE_FREE_GPU(fast_planes);
     }
     ~Conv128LayerParam() { release(); }
 public:
@@ -537,6 +815,67 @@ public:
     tcbnn::ConvArgs args;
     Conv128LayerParam* gpu;
     char name[8];
+    // fast path (see fast_setup)
+    tcbnn_conv_desc fast_desc;
+    bool fast_ok;
+    void* fast_prepared;
+    void* fast_planes;                  // this layer's pre-expanded input, filled by its producer
+    size_t fast_planes_bytes;
+    int fast_res_in_ch, fast_res_in_bytes, fast_res_bytes;
+    long long fast_res_bound;
+    const tcbnn_conv_desc* fast_next;   // the consumer whose planes this layer fills
+    void* fast_next_planes;
+    size_t fast_next_planes_bytes;
+    int max_batch = 0;
 };
+
+namespace tcbnn_dropin {
+// Queues the registered layer object behind a kernel argument through the C ABI.  false: not a
+// registered layer, or one that cannot take the fast path.
+inline bool forward_registered(const void* gpu_struct, cudaStream_t stream, bool dry_run) {
+    RegisteredLayer r;
+    if (!find_layer(0, gpu_struct, &r)) return false;
+    switch (r.kind) {
+        case kLayerIn: if (!dry_run) ((In128LayerParam*)r.host)->forward(stream); return true;
+        case kLayerFc: if (!dry_run) ((Fc128LayerParam*)r.host)->forward(stream); return true;
+        case kLayerOut: if (!dry_run) ((Out128LayerParam*)r.host)->forward(stream); return true;
+        case kLayerInConv: if (!dry_run) ((InConv128LayerParam*)r.host)->forward(stream); return true;
+        default:
+            if (!((Conv128LayerParam*)r.host)->fast_ok) return false;
+            if (!dry_run) ((Conv128LayerParam*)r.host)->forward(stream);
+            return true;
+    }
+}
+
+// What the drivers' cudaLaunchCooperativeKernel(net, grid, block, args, smem, stream) becomes (macro
+// below).  The reference's network kernels take their layer objects as arguments, one per layer
+// and in layer order (imagenet_resnet.cu:34-53, 338-357; the same in every driver): when every
+// argument is a registered object, the layers are queued one by one through the C ABI on `stream`
+// and the kernel itself is not launched.  Otherwise -- another kind of kernel, an unknown
+// pointer, or TCBNN_DROPIN_COOPERATIVE set -- the launch goes through unchanged.
+inline cudaError_t launch_network(const void* func, dim3 grid, dim3 block, void** args, size_t smem = 0,
+                                  cudaStream_t stream = 0) {
+    if (getenv("TCBNN_DROPIN_COOPERATIVE") == NULL && args != NULL) {
+        size_t nparams = 0, off = 0, size = 0;
+        bool all = true;
+        while (cudaFuncGetParamInfo(func, nparams, &off, &size) == cudaSuccess) {
+            if (size != sizeof(void*) || !forward_registered(*(void**)args[nparams], stream, true)) { all = false; break; }
+            nparams++;
+        }
+        cudaGetLastError();                              // the probe past the last parameter leaves an error behind
+        if (all && nparams > 0) {
+            for (size_t i = 0; i < nparams; i++) forward_registered(*(void**)args[i], stream, false);
+            return cudaGetLastError();
+        }
+    }
+    return (cudaLaunchCooperativeKernel)(func, grid, block, args, smem, stream);
+}
+template <class T>
+inline cudaError_t launch_network(T* func, dim3 grid, dim3 block, void** args, size_t smem = 0, cudaStream_t stream = 0) {
+    return launch_network((const void*)func, grid, block, args, smem, stream);
+}
+}  // namespace tcbnn_dropin
+
+#define cudaLaunchCooperativeKernel(...) tcbnn_dropin::launch_network(__VA_ARGS__)
 
 #endif

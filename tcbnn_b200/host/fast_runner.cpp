@@ -15,6 +15,10 @@
 // reference's text format.  TCBNN_RESIDUAL16=1 keeps the saved residuals as int16 (the caller's
 // promise that they fit; an overflow is reported and fails the run).  TCBNN_RUNS=n runs the forward pass n times (the last one is timed);
 // TCBNN_DUMP_DIR=<dir> also writes every layer's download_full_output() as layerNN.bin.
+// TCBNN_TEXT_SIGNATURES=1 (text weights) builds the layers through the reference's own
+// initialize(FILE*, ...) signatures.  TCBNN_LIVE_BATCH=n: after the first runs on the full batch the
+// same objects are switched to the first n images (set_batch) for the last, timed run; logits and
+// dumps then hold n images.
 #include <string>
 #include <vector>
 #include "tcbnn_host.hpp"
@@ -59,6 +63,7 @@ int main(int argc, char** argv) {
     uin32* prev = NULL;
     int H = 0, W = 0, K = 0;
     const int res_bytes = getenv("TCBNN_RESIDUAL16") ? 2 : 4;
+    const bool text_sig = getenv("TCBNN_TEXT_SIGNATURES") != NULL && !binary;
     while (fscanf(spec, "%63s", word) == 1) {
         const std::string t(word);
         Built b = {};
@@ -76,7 +81,7 @@ int main(int argc, char** argv) {
             b.kind = K_INCONV;
             b.inconv = new InConv128LayerParam("Conv1", H, W, R, S, C, O, batch, st, st, true, pool, pool, save != 0);
             b.inconv->set_residual_bytes(res_bytes);
-            b.inconv->initialize(images.data(), config);
+            if (text_sig) b.inconv->initialize(images.data(), wfile); else b.inconv->initialize(images.data(), config);
             prev = b.inconv->get_output_gpu(); H = b.inconv->output_height; W = b.inconv->output_width;
             K = H * W * O;
         } else if (t == "conv") {
@@ -92,17 +97,19 @@ int main(int argc, char** argv) {
                 else { res = net[inj].conv->get_output_residual_gpu(); res_ch = net[inj].conv->output_channels; }
             }
             b.conv->set_residual_bytes(res_bytes);
-            b.conv->initialize(config, prev, res, res_ch, res_bytes);
+            if (text_sig) b.conv->initialize(wfile, prev, res); else b.conv->initialize(config, prev, res, res_ch, res_bytes);
             prev = b.conv->get_output_gpu(); H = b.conv->output_height; W = b.conv->output_width;
             K = H * W * O;
         } else if (t == "fc") {
             int N; if (fscanf(spec, "%d", &N) != 1) return 2;
             b.kind = K_FC; b.fc = new Fc128LayerParam("Fc", batch, K, N);
-            b.fc->initialize(config, prev); prev = b.fc->get_output_gpu(); K = N;
+            if (text_sig) b.fc->initialize(wfile, prev); else b.fc->initialize(config, prev);
+            prev = b.fc->get_output_gpu(); K = N;
         } else if (t == "out") {
             int N; if (fscanf(spec, "%d", &N) != 1) return 2;
             b.kind = K_OUT; b.out = new Out128LayerParam("Fout", batch, K, N);
-            b.out->initialize(config, prev); K = N;
+            if (text_sig) b.out->initialize(wfile, prev); else b.out->initialize(config, prev);
+            K = N;
         } else { fprintf(stderr, "unknown layer %s\n", word); return 2; }
         net.push_back(b);
     }
@@ -129,6 +136,18 @@ int main(int argc, char** argv) {
     TCBNN_HOST_CUDA(cudaStreamCreate(&st));
     const int runs = getenv("TCBNN_RUNS") ? atoi(getenv("TCBNN_RUNS")) : 1;
     for (int i = 1; i < runs; i++) forward(net, st);
+    int live = batch;
+    if (getenv("TCBNN_LIVE_BATCH")) {
+        live = atoi(getenv("TCBNN_LIVE_BATCH"));
+        TCBNN_HOST_CUDA(cudaStreamSynchronize(st));
+        for (size_t i = 0; i < net.size(); i++) {
+            if (net[i].in) net[i].in->set_batch(live);
+            if (net[i].inconv) net[i].inconv->set_batch(live);
+            if (net[i].conv) net[i].conv->set_batch(live);
+            if (net[i].fc) net[i].fc->set_batch(live);
+            if (net[i].out) net[i].out->set_batch(live);
+        }
+    }
     cudaEvent_t e0, e1;
     TCBNN_HOST_CUDA(cudaEventCreate(&e0));
     TCBNN_HOST_CUDA(cudaEventCreate(&e1));
@@ -138,7 +157,7 @@ int main(int argc, char** argv) {
     TCBNN_HOST_CUDA(cudaStreamSynchronize(st));
     float ms = 0;
     TCBNN_HOST_CUDA(cudaEventElapsedTime(&ms, e0, e1));
-    printf("{\"forward_ms\": %.4f, \"batch\": %d, \"layers\": %d}\n", ms, batch, (int)net.size());
+    printf("{\"forward_ms\": %.4f, \"batch\": %d, \"layers\": %d, \"live\": %d}\n", ms, batch, (int)net.size(), live);
 
     for (size_t i = 0; i < net.size(); i++)
         if (net[i].kind == K_CONV && net[i].conv->overflowed()) {
@@ -148,7 +167,7 @@ int main(int argc, char** argv) {
     float* logits = net.back().out->download_output();
     FILE* fo = fopen(argv[4], "wb");
     if (!fo) return 2;
-    fwrite(logits, sizeof(float), (size_t)batch * K, fo);
+    fwrite(logits, sizeof(float), (size_t)live * K, fo);
     fclose(fo);
     if (getenv("TCBNN_DUMP_DIR")) {
         for (size_t i = 0; i + 1 < net.size(); i++) {
@@ -157,6 +176,7 @@ int main(int argc, char** argv) {
             if (net[i].kind == K_FC) { full = net[i].fc->download_full_output(); cnt = net[i].fc->output_size(); }
             if (net[i].kind == K_INCONV) { full = net[i].inconv->download_full_output(); cnt = net[i].inconv->output_size(); }
             if (net[i].kind == K_CONV) { full = net[i].conv->download_full_output(); cnt = net[i].conv->output_size(); }
+            cnt = cnt / batch * live;
             char path[512];
             snprintf(path, sizeof(path), "%s/layer%02zu.bin", getenv("TCBNN_DUMP_DIR"), i);
             FILE* f = fopen(path, "wb");

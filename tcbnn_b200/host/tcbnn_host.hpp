@@ -13,13 +13,17 @@
 // Differences from the reference a caller sees: packed layouts are the library's (NHWC words;
 // the unpacked +-1 values, residuals and logits are the reference's); layers store their outputs,
 // so the same objects run any number of passes; weights come from a text file in launch_array
-// order, a raw fp32 file or a host array (Weights).
+// order (initialize(FILE*, ...), the reference's own signatures, so that a driver's layer lines
+// stay as they are), a raw fp32 file or a host array (Weights); the batch given to a constructor
+// is the largest the object will see and set_batch(n) makes the following passes process the first
+// n images in the same buffers.
 #ifndef TCBNN_HOST_HPP
 #define TCBNN_HOST_HPP
 
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <vector>
 #include <cuda_runtime.h>
 #include "tcbnn_b200.h"
@@ -54,6 +58,30 @@ inline T* dev_alloc(size_t count, bool zero = true) {
     TCBNN_HOST_CUDA(cudaMalloc((void**)&p, (count ? count : 1) * sizeof(T)));
     if (zero) TCBNN_HOST_CUDA(cudaMemset(p, 0, (count ? count : 1) * sizeof(T)));
     return p;
+}
+
+// What a layer that saves its residual tells the layers that inject it: the reference hands over
+// a bare int* (param.h:944), so channel count and element size travel through this table.
+struct ResidualInfo { const void* ptr; int channels; int bytes; };
+inline std::vector<ResidualInfo>& residual_table() { static std::vector<ResidualInfo> t; return t; }
+inline std::mutex& residual_mutex() { static std::mutex m; return m; }
+inline void publish_residual(const void* ptr, int channels, int bytes) {
+    std::lock_guard<std::mutex> lock(residual_mutex());
+    ResidualInfo r = {ptr, channels, bytes};
+    residual_table().push_back(r);
+}
+inline void retract_residual(const void* ptr) {
+    std::lock_guard<std::mutex> lock(residual_mutex());
+    std::vector<ResidualInfo>& t = residual_table();
+    for (size_t i = 0; i < t.size(); i++)
+        if (t[i].ptr == ptr) { t.erase(t.begin() + i); return; }
+}
+inline bool lookup_residual(const void* ptr, int* channels, int* bytes) {
+    std::lock_guard<std::mutex> lock(residual_mutex());
+    const std::vector<ResidualInfo>& t = residual_table();
+    for (size_t i = t.size(); i-- > 0;)
+        if (t[i].ptr == ptr) { *channels = t[i].channels; *bytes = t[i].bytes; return true; }
+    return false;
 }
 
 // Where initialize() takes its numbers from: the reference's text file (launch_array,
@@ -140,8 +168,16 @@ class In128LayerParam {
 public:
     In128LayerParam(const char* _name, int _input_height, int _input_width)
         : input_height(_input_height), input_width(_input_width), output_height(_input_height),
-          output_width(_input_width), input_gpu(NULL), output_gpu(NULL) {
+          output_width(_input_width), input_gpu(NULL), output_gpu(NULL), live(_input_height) {
         strncpy(name, _name, 7); name[7] = 0;
+    }
+    // the following passes process the first n rows (n <= the constructor's input_height)
+    void set_batch(int n) {
+        if (n <= 0 || n > input_height) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, input_height); exit(-1); }
+        live = n;
+    }
+    void set_input(const float* input, int rows) {
+        TCBNN_HOST_CUDA(cudaMemcpy(input_gpu, input, (size_t)rows * input_width * sizeof(float), cudaMemcpyHostToDevice));
     }
     int ld() const { return step128_words(output_width); }
     size_t output_size() const { return (size_t)output_height * output_width; }
@@ -153,15 +189,16 @@ public:
         return this;
     }
     void forward(cudaStream_t stream = 0) {
-        TCBNN_HOST_CALL(tcbnn_pack_rows(input_gpu, input_height, input_width, ld(), output_gpu, stream));
+        TCBNN_HOST_CALL(tcbnn_pack_rows(input_gpu, live, input_width, ld(), output_gpu, stream));
     }
     float* get_input_gpu() { return input_gpu; }
     uin32* get_output_gpu() { return output_gpu; }
-    float* download_full_output() { return unpack_to_host(output_gpu, 1, 0, output_height, output_width, ld()); }
+    float* download_full_output() { return unpack_to_host(output_gpu, 1, 0, live, output_width, ld()); }
     ~In128LayerParam() { cudaFree(input_gpu); cudaFree(output_gpu); }
     int input_height, input_width, output_height, output_width;
     float* input_gpu;
     uin32* output_gpu;
+    int live;
     char name[8];
 };
 
@@ -171,13 +208,22 @@ public:
     Fc128LayerParam(const char* _name, int _input_height, int _input_width, int _weight_width)
         : input_height(_input_height), input_width(_input_width), weight_height(_input_width),
           weight_width(_weight_width), output_height(_input_height), output_width(_weight_width),
-          weight_gpu(NULL), bn_gpu(NULL), input_gpu(NULL), output_gpu(NULL), workspace(NULL) {
+          weight_gpu(NULL), bn_gpu(NULL), input_gpu(NULL), output_gpu(NULL), workspace(NULL), live(_input_height) {
         strncpy(name, _name, 7); name[7] = 0;
     }
     int ld() const { return step128_words(output_width); }
     int ldw() const { return step128_words(weight_height); }
     size_t output_size() const { return (size_t)output_height * output_width; }
     size_t workspace_bytes() const { return tcbnn_gemm_workspace_bytes(input_height, weight_width, input_width); }
+    void set_batch(int n) {
+        if (n <= 0 || n > input_height) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, input_height); exit(-1); }
+        live = n;
+    }
+    // the reference's signature (param.h:270): weights from its text file
+    Fc128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu) {
+        Weights w = Weights::from_text(config_file);
+        return initialize(w, prev_layer_gpu);
+    }
     Fc128LayerParam* initialize(Weights& config, uin32* prev_layer_gpu) {
         float* w = config.upload((size_t)weight_height * weight_width);          // [K][N]
         weight_gpu = dev_alloc<uin32>((size_t)weight_width * ldw());
@@ -191,16 +237,17 @@ public:
     }
     void set_workspace(Workspace* w) { workspace = w; }
     void forward(cudaStream_t stream = 0) {
-        TCBNN_HOST_CALL(tcbnn_fc_layer(input_gpu, weight_gpu, bn_gpu, input_height, input_width, weight_width,
+        TCBNN_HOST_CALL(tcbnn_fc_layer(input_gpu, weight_gpu, bn_gpu, live, input_width, weight_width,
                                        step128_words(input_width), ldw(), output_gpu, ld(),
                                        workspace ? workspace->ptr : NULL, workspace ? workspace->bytes : 0, stream));
     }
     uin32* get_output_gpu() { return output_gpu; }
-    float* download_full_output() { return unpack_to_host(output_gpu, 1, 0, output_height, output_width, ld()); }
+    float* download_full_output() { return unpack_to_host(output_gpu, 1, 0, live, output_width, ld()); }
     ~Fc128LayerParam() { cudaFree(weight_gpu); cudaFree(bn_gpu); cudaFree(output_gpu); }
     int input_height, input_width, weight_height, weight_width, output_height, output_width;
     uin32* weight_gpu; float* bn_gpu; uin32* input_gpu; uin32* output_gpu;
     Workspace* workspace;
+    int live;
     char name[8];
 };
 
@@ -211,12 +258,21 @@ public:
         : input_height(_input_height), input_width(_input_width), weight_height(_input_width),
           weight_width(_weight_width), output_height(_input_height), output_width(_weight_width),
           weight_gpu(NULL), bn_scale_gpu(NULL), bn_bias_gpu(NULL), input_gpu(NULL), output_gpu(NULL),
-          output(NULL), workspace(NULL) {
+          output(NULL), workspace(NULL), live(_input_height) {
         strncpy(name, _name, 7); name[7] = 0;
     }
     int ldw() const { return step128_words(weight_height); }
     size_t output_size() const { return (size_t)output_height * output_width; }
     size_t workspace_bytes() const { return tcbnn_gemm_workspace_bytes(input_height, weight_width, input_width); }
+    void set_batch(int n) {
+        if (n <= 0 || n > input_height) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, input_height); exit(-1); }
+        live = n;
+    }
+    // the reference's signature (param.h:439)
+    Out128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu) {
+        Weights w = Weights::from_text(config_file);
+        return initialize(w, prev_layer_gpu);
+    }
     Out128LayerParam* initialize(Weights& config, uin32* prev_layer_gpu) {
         float* w = config.upload((size_t)weight_height * weight_width);
         weight_gpu = dev_alloc<uin32>((size_t)weight_width * ldw());
@@ -231,7 +287,7 @@ public:
     }
     void set_workspace(Workspace* w) { workspace = w; }
     void forward(cudaStream_t stream = 0) {
-        TCBNN_HOST_CALL(tcbnn_out_layer(input_gpu, weight_gpu, bn_scale_gpu, bn_bias_gpu, input_height, input_width,
+        TCBNN_HOST_CALL(tcbnn_out_layer(input_gpu, weight_gpu, bn_scale_gpu, bn_bias_gpu, live, input_width,
                                         weight_width, step128_words(input_width), ldw(), output_gpu, weight_width,
                                         workspace ? workspace->ptr : NULL, workspace ? workspace->bytes : 0, stream));
     }
@@ -248,6 +304,7 @@ public:
     int input_height, input_width, weight_height, weight_width, output_height, output_width;
     uin32* weight_gpu; float* bn_scale_gpu; float* bn_bias_gpu; uin32* input_gpu; float* output_gpu; float* output;
     Workspace* workspace;
+    int live;                  // rows of the live batch: the first `live` rows of the output are current
     char name[8];
 };
 
@@ -298,7 +355,20 @@ public:
     // bound by this tensor's traffic, which it halves.
     void set_residual_bytes(int bytes) { residual_bytes = bytes == 2 ? 2 : 4; }
     size_t input_size() const { return (size_t)desc.B * 3 * desc.H * desc.W; }
-    size_t output_size() const { return (size_t)desc.B * desc.OH * desc.OW * desc.O; }
+    size_t output_size() const { return (size_t)batch * desc.OH * desc.OW * desc.O; }   // at the constructor's batch
+    // the following passes process the first n images (n <= the constructor's batch)
+    void set_batch(int n) {
+        if (n <= 0 || n > batch) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, batch); exit(-1); }
+        desc.B = n;
+    }
+    void set_input(const float* input, int images) {
+        TCBNN_HOST_CUDA(cudaMemcpy(input_gpu, input, (size_t)images * 3 * desc.H * desc.W * sizeof(float), cudaMemcpyHostToDevice));
+    }
+    // the reference's signature (param.h:760)
+    InConv128LayerParam* initialize(const float* input, FILE* config_file) {
+        Weights w = Weights::from_text(config_file);
+        return initialize(input, w);
+    }
     InConv128LayerParam* initialize(const float* input, Weights& config) {
         if (!input) { fprintf(stderr, "NULL pointer.\n"); exit(-1); }
         input_gpu = dev_alloc<float>(input_size(), false);
@@ -311,9 +381,11 @@ public:
         TCBNN_HOST_CUDA(cudaFree(f));
         bn_gpu = config.upload(desc.O);
         output_gpu = dev_alloc<uin32>((size_t)desc.B * desc.OH * desc.OW * Ow());
-        if (save_residual)
+        if (save_residual) {
             output_residual_gpu = (int*)dev_alloc<char>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O *
                                                         residual_bytes);
+            publish_residual(output_residual_gpu, desc.O, residual_bytes);
+        }
         // the layer compiled for its filter, where the library offers it (at most 128 output channels)
         if (desc.O <= 128) TCBNN_HOST_CALL(tcbnn_inconv_specialize(&desc, filter_gpu, bn_gpu, NULL, &handle));
         return this;
@@ -337,6 +409,7 @@ public:
         return unpack_to_host(output_gpu, 1, 0, desc.B * desc.OH * desc.OW, desc.O, Ow());
     }
     ~InConv128LayerParam() {
+        if (output_residual_gpu) retract_residual(output_residual_gpu);
         cudaFree(input_gpu); cudaFree(filter_gpu); cudaFree(bn_gpu); cudaFree(output_gpu); cudaFree(output_residual_gpu);
         if (handle) tcbnn_inconv_release(handle);
         delete next_planes;
@@ -380,7 +453,7 @@ public:
         out_image_stride = ahead_fc ? step128_words(words * 32) : words;
     }
     int Ow() const { return (desc.O + 31) / 32; }
-    size_t output_size() const { return (size_t)desc.B * desc.OH * desc.OW * desc.O; }
+    size_t output_size() const { return (size_t)batch * desc.OH * desc.OW * desc.O; }   // at the constructor's batch
     size_t workspace_bytes() const { return tcbnn_conv_workspace_bytes(&desc); }
     // Extension: save this layer's residual as int16 (call before initialize()).  The caller vouches
     // that the running sum fits: |value| <= C*R*S + bound of the injected residual.  A value that
@@ -390,6 +463,25 @@ public:
         int st = 0;
         TCBNN_HOST_CALL(tcbnn_conv_status(&desc, prepared_gpu, &st));
         return st == 2;
+    }
+    // the following passes process the first n images (n <= the constructor's batch); planes a
+    // producer fills are cleared, because their layout depends on the batch and their padding
+    // positions must read as zero
+    void set_batch(int n) {
+        if (n <= 0 || n > batch) { fprintf(stderr, "%s: batch %d outside 1..%d.\n", name, n, batch); exit(-1); }
+        if (n != desc.B && input_planes.p) TCBNN_HOST_CUDA(cudaMemset(input_planes.p->ptr, 0, input_planes.p->bytes));
+        desc.B = n;
+    }
+    // the reference's signature (param.h:944): weights from its text file; channel count and element
+    // size of the injected residual are those its producer published
+    Conv128LayerParam* initialize(FILE* config_file, uin32* prev_layer_gpu, int* _input_residual_gpu = NULL) {
+        Weights w = Weights::from_text(config_file);
+        int ch = 0, bytes = 4;
+        if (inject_residual && !lookup_residual(_input_residual_gpu, &ch, &bytes)) {
+            fprintf(stderr, "%s: the injected residual is not the saved residual of an initialised layer.\n", name);
+            exit(-1);
+        }
+        return initialize(w, prev_layer_gpu, _input_residual_gpu, ch, bytes);
     }
     // input_residual_channels_: channels per pixel of the injected tensor (the producer's O)
     // input_residual_bytes_: element size of the injected tensor (its producer's set_residual_bytes)
@@ -407,9 +499,11 @@ public:
         TCBNN_HOST_CUDA(cudaDeviceSynchronize());
         bn_gpu = config.upload(desc.O);
         output_gpu = dev_alloc<uin32>((size_t)desc.B * out_image_stride);
-        if (save_residual)
+        if (save_residual) {
             output_residual_gpu = (int*)dev_alloc<char>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O *
                                                         residual_bytes);
+            publish_residual(output_residual_gpu, desc.O, residual_bytes);
+        }
         input_gpu = prev_layer_gpu;
         if (inject_residual) {
             if (!_input_residual_gpu || input_residual_channels_ <= 0) {
@@ -448,6 +542,7 @@ public:
         return unpack_to_host(output_gpu, desc.B, out_image_stride, desc.OH * desc.OW, desc.O, Ow());
     }
     ~Conv128LayerParam() {
+        if (output_residual_gpu) retract_residual(output_residual_gpu);
         cudaFree(filter_gpu); cudaFree(prepared_gpu); cudaFree(bn_gpu); cudaFree(output_gpu); cudaFree(output_residual_gpu);
         delete next_planes;
     }

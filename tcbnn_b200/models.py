@@ -288,6 +288,14 @@ class Network:
     def set_input(self, x):
         self.layers[0].set_input(x)
 
+    def set_batch(self, n):
+        """Run the following passes on the first n images (n <= the batch the network was built
+        for) without rebuilding anything: buffers keep their size, kernels take the live batch.
+        The logits of the live images are the first n rows of the output."""
+        for l in self.layers:
+            l.set_batch(n)
+        self.live_batch = n
+
     def forward(self):
         for l in self.layers:
             l.forward()
@@ -301,7 +309,7 @@ class Network:
         work and the gaps between the launches go away."""
         import torch
         first = self.layers[0]
-        key = first.input_gpu.data_ptr()
+        key = (first.input_gpu.data_ptr(), getattr(self, "live_batch", None))
         graphs = self.__dict__.setdefault("_graphs", {})
         g = graphs.get(key)
         if g is None:

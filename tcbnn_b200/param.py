@@ -8,7 +8,11 @@ C ABI.  Differences that follow from the B200 design, not from the interface:
   * every layer is a separate launch on the current stream (forward()), outputs are written
     with stores, so a layer object can be run any number of times;
   * weights come from a `config` object with read(n) -> n floats in the order launch_array
-    consumes them (utility.h:188-196): filter/weight first, then thresholds.
+    consumes them (utility.h:188-196): filter/weight first, then thresholds;
+  * the batch given to the constructor is the LARGEST batch the object will see: set_batch(n)
+    (n <= that) makes the following forward() calls process the first n images in the same
+    buffers, so a serving loop with a ragged last batch keeps its layer objects (the reference
+    fixes the batch at construction, param.h:875-881).
 """
 import numpy as np
 import torch
@@ -70,6 +74,13 @@ class In128LayerParam:
         self.input_height = self.output_height = input_height
         self.input_width = self.output_width = input_width
         self.input_gpu = self.output_gpu = None
+        self.live = input_height
+
+    def set_batch(self, n):
+        """Process the first n rows from now on (n <= the constructor's input_height)."""
+        if not 0 < n <= self.input_height:
+            raise ValueError("%s: batch %d outside 1..%d" % (self.name, n, self.input_height))
+        self.live = n
 
     def initialize(self, input):
         dev = _dev()
@@ -81,10 +92,11 @@ class In128LayerParam:
 
     def set_input(self, input):
         src = input if torch.is_tensor(input) else torch.from_numpy(np.ascontiguousarray(input, dtype=np.float32))
-        self.input_gpu.copy_(src.reshape(self.input_height, self.input_width), non_blocking=True)
+        src = src.reshape(-1, self.input_width)
+        self.input_gpu[:src.shape[0]].copy_(src, non_blocking=True)
 
     def forward(self):
-        ops._l.call("tcbnn_pack_rows", ops._ptr(self.input_gpu), self.input_height, self.input_width,
+        ops._l.call("tcbnn_pack_rows", ops._ptr(self.input_gpu), self.live, self.input_width,
                     self.output_gpu.shape[1], ops._ptr(self.output_gpu), ops._stream())
 
     def get_output_gpu(self):
@@ -106,6 +118,12 @@ class Fc128LayerParam:
         self.input_width = self.weight_height = input_width
         self.weight_width = self.output_width = self.bn_width = weight_width
         self.weight_gpu = self.bn_gpu = self.input_gpu = self.output_gpu = None
+        self.live = input_height
+
+    def set_batch(self, n):
+        if not 0 < n <= self.input_height:
+            raise ValueError("%s: batch %d outside 1..%d" % (self.name, n, self.input_height))
+        self.live = n
 
     def initialize(self, config, prev_layer_gpu):
         dev = _dev()
@@ -131,8 +149,8 @@ class Fc128LayerParam:
         return self.launches
 
     def forward(self):
-        ops.fc_layer(self.input_gpu, self.weight_gpu, self.bn_gpu, self.input_width,
-                     out=self.output_gpu, workspace=self.workspace)
+        ops.fc_layer(self.input_gpu[:self.live], self.weight_gpu, self.bn_gpu, self.input_width,
+                     out=self.output_gpu[:self.live], workspace=self.workspace)
 
     def get_output_gpu(self):
         return self.output_gpu
@@ -153,6 +171,12 @@ class Out128LayerParam:
         self.input_width = self.weight_height = input_width
         self.weight_width = self.output_width = weight_width
         self.weight_gpu = self.input_gpu = self.output_gpu = None
+        self.live = input_height
+
+    def set_batch(self, n):
+        if not 0 < n <= self.input_height:
+            raise ValueError("%s: batch %d outside 1..%d" % (self.name, n, self.input_height))
+        self.live = n
 
     def initialize(self, config, prev_layer_gpu):
         dev = _dev()
@@ -173,14 +197,14 @@ class Out128LayerParam:
         return self.launches
 
     def forward(self):
-        ops.out_layer(self.input_gpu, self.weight_gpu, self.bn_scale_gpu, self.bn_bias_gpu,
-                      self.input_width, out=self.output_gpu, workspace=self.workspace)
+        ops.out_layer(self.input_gpu[:self.live], self.weight_gpu, self.bn_scale_gpu, self.bn_bias_gpu,
+                      self.input_width, out=self.output_gpu[:self.live], workspace=self.workspace)
 
     def get_output_gpu(self):
         return self.output_gpu
 
     def download_output(self):
-        return self.output_gpu.cpu().numpy()
+        return self.output_gpu[:self.live].cpu().numpy()
 
 
 class InConv128LayerParam:
@@ -247,11 +271,19 @@ class InConv128LayerParam:
 
     next_layer = None      # (consumer's descriptor, its planes): see Conv128LayerParam
 
+    def set_batch(self, n):
+        """Process the first n images from now on (n <= the constructor's batch); the compiled
+        kernel does not depend on the batch."""
+        if not 0 < n <= self.batch:
+            raise ValueError("%s: batch %d outside 1..%d" % (self.name, n, self.batch))
+        self.desc.B = n
+
     def set_input(self, input):
         src = input if torch.is_tensor(input) else torch.from_numpy(np.ascontiguousarray(input))
         if src.dtype != self.input_gpu.dtype:
             raise ValueError("%s: input dtype %s, layer was initialised for %s" % (self.name, src.dtype, self.input_gpu.dtype))
-        self.input_gpu.copy_(src.reshape(self.input_gpu.shape), non_blocking=True)
+        src = src.reshape((-1,) + tuple(self.input_gpu.shape[1:]))
+        self.input_gpu[:src.shape[0]].copy_(src, non_blocking=True)
 
     def forward(self):
         ops.inconv_layer(self.desc, self.input_gpu, self.filter_gpu, self.bn_gpu, out=self.output_gpu,
@@ -271,7 +303,7 @@ class InConv128LayerParam:
     def download_full_output(self):
         d = self.desc
         rows = d.B * d.OH * d.OW
-        return ops.unpack_rows(self.output_gpu.reshape(rows, -1), d.O).reshape(d.B, d.OH, d.OW, d.O).cpu().numpy()
+        return ops.unpack_rows(self.output_gpu[:d.B].reshape(rows, -1), d.O).reshape(d.B, d.OH, d.OW, d.O).cpu().numpy()
 
 
 class Conv128LayerParam:
@@ -328,9 +360,19 @@ class Conv128LayerParam:
             self.set_input_residual_gpu(input_residual_gpu)
         return self
 
+    def set_batch(self, n):
+        """Process the first n images from now on (n <= the constructor's batch).  The layout of the
+        pre-expanded input planes depends on the batch, so planes a producer fills are cleared
+        (their padding positions must read as zero)."""
+        if not 0 < n <= self.batch:
+            raise ValueError("%s: batch %d outside 1..%d" % (self.name, n, self.batch))
+        if n != self.desc.B and self.input_planes is not None:
+            self.input_planes.zero_()
+        self.desc.B = n
+
     def set_input_gpu(self, t):
         d = self.desc
-        self.input_gpu = t.reshape(d.B, d.H, d.W, (d.C + 31) // 32)
+        self.input_gpu = t.reshape(self.batch, d.H, d.W, (d.C + 31) // 32)
 
     def set_input_residual_gpu(self, t):
         if t is None:
@@ -374,5 +416,5 @@ class Conv128LayerParam:
     def download_full_output(self):
         d = self.desc
         Ow = (d.O + 31) // 32
-        bits = self.output_gpu[:, :d.OH * d.OW * Ow].reshape(d.B * d.OH * d.OW, Ow).contiguous()
+        bits = self.output_gpu[:d.B, :d.OH * d.OW * Ow].reshape(d.B * d.OH * d.OW, Ow).contiguous()
         return ops.unpack_rows(bits, d.O).reshape(d.B, d.OH, d.OW, d.O).cpu().numpy()

@@ -38,3 +38,14 @@ def test_host_cpp_int16_residuals(cuda, tmp_path, monkeypatch):
     keep the running sums far inside int16)."""
     monkeypatch.setenv("TCBNN_RESIDUAL16", "1")
     _run(models.resnet18_spec(4, image=64, classes=100), 85, tmp_path, cuda, runner=hbuild.build_fast_runner())
+
+
+def test_host_cpp_reference_signatures_and_ragged_batch(cuda, tmp_path):
+    """The layer lines of a reference driver compile against the host classes as they are:
+    initialize(FILE*, prev [, residual]) with the residual's channel count and element size looked
+    up from its producer.  The same objects then run the first 5 of their 8 images (set_batch)."""
+    _run(models.resnet18_spec(8, image=64, classes=100), 86, tmp_path, cuda, runner=hbuild.build_fast_runner(),
+         extra_env={"TCBNN_TEXT_SIGNATURES": "1"})
+    _run(models.resnet18_spec(8, image=64, classes=100), 87, tmp_path, cuda, runner=hbuild.build_fast_runner(),
+         runs=2, live=5, extra_env={"TCBNN_TEXT_SIGNATURES": "1", "TCBNN_RESIDUAL16": "1"})
+    _run(models.vgg_cifar_spec(8), 88, tmp_path, cuda, runner=hbuild.build_fast_runner(), runs=2, live=3)

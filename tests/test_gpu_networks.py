@@ -135,3 +135,31 @@ def test_host_feeder_overlapped_copies_give_each_batch_its_own_logits(cuda):
         for g, e in zip(got, expect):
             assert np.array_equal(g.cpu().numpy(), e)
         assert np.array_equal(last.numpy(), expect[-1])
+
+
+@pytest.mark.parametrize("which", ["resnet18", "vgg_cifar", "mlp"])
+def test_set_batch_runs_ragged_batches_on_the_same_objects(cuda, which):
+    """Layer objects built for 8 images process 5, then 8, then 3 images (Network.set_batch)
+    without being rebuilt: every layer's bits and the logits of the live images equal the oracle's
+    on exactly those images (the reference fixes the batch at construction, param.h:875-881)."""
+    spec = {"resnet18": models.resnet18_spec(8, image=64, classes=100), "vgg_cifar": models.vgg_cifar_spec(8),
+            "mlp": models.mlp_spec(8)}[which]
+    w = models.synthetic_weights(spec, 80)
+    bound = models.SYNTHETIC_IMAGE_ABS_BOUND if which == "resnet18" else None
+    net = models.Network(spec, w, models.synthetic_input(spec, 81), input_abs_bound=bound)
+    net.forward()
+    for step, n in enumerate((5, 8, 3)):
+        x = models.synthetic_input(spec, 90 + step, batch=n)
+        net.set_batch(n)
+        net.set_input(x)
+        logits = (net.forward_graph() if step else net.forward())[:n].cpu().numpy()
+        acts, ress = onet.run(dict(spec, batch=n), w, x)
+        for i, (layer, a, r) in enumerate(zip(net.layers[:-1], acts[:-1], ress[:-1])):
+            got = layer.get_output_gpu()[:n].cpu().numpy().view(np.uint32)
+            assert np.array_equal(got.reshape(a.shape), a), "batch %d layer %d %s bits" % (n, i, layer.name)
+            if r is not None:
+                gr = layer.get_output_residual_gpu()[:n].cpu().numpy().astype(np.int32)
+                assert np.array_equal(gr, r), "batch %d layer %d %s residual" % (n, i, layer.name)
+        np.testing.assert_allclose(logits, acts[-1], rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError):
+        net.set_batch(9)
