@@ -268,6 +268,15 @@ int tcbnn_inconv_specialize_selftest(const tcbnn_conv_desc* d, unsigned seed, lo
  * bmm/bmma_op_test/main_test.cu:35-220 and its TOPS formula at :368. */
 int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops);
 
+/* Failure-handling probe.  Every wait inside the tcgen05 kernels is bounded: a role that waits
+ * for a partner which never arrives gives up after a fixed number of polls, records status 1
+ * (tcbnn_conv_status / tcbnn_gemm_status), the kernel drains, frees its tensor memory and returns.
+ * This call runs that path in isolation: one CTA allocates tensor memory, waits `polls` times on an
+ * mbarrier nobody arrives at, gives up, records *status = 1, frees its tensor memory and returns.
+ * Synchronises.  The device context stays usable (the next call works as usual).  The reference has
+ * no counterpart: its error handling is exit() on a failed CUDA call (utility.h:57-101). */
+int tcbnn_wait_probe(int polls, int* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,7 +27,12 @@ namespace tcbnn {
 namespace umma {
 
 constexpr int kPreEpiThreads = 512;
-constexpr int kPreThreads = kPreEpiThreads + 64;
+// One MMA-issuing warp.  (Two issuers on alternate tiles were tried and are wrong as well as no
+// faster: an mbarrier wait names its phase by parity only, so a waiter must see every phase of a
+// barrier; with two consumers alternating on the same ring slot the one that runs ahead finds the
+// parity of the phase before last already complete and reads a slot that has not been refilled.)
+constexpr int kPreMmaWarps = 1;
+constexpr int kPreThreads = kPreEpiThreads + 32 + 32 * kPreMmaWarps;
 constexpr int kPreMaxStages = 8;           // patch ring depth is chosen by the host from the shared memory left
 
 // positions of zero padding in front of the planes (a tile's patch starts up to back_y*PW+back_x
@@ -40,7 +45,7 @@ __host__ __device__ inline long long pre_plane_positions(long long NV, int npos,
 }
 // nplane: 1 for stride 1, 4 for stride 2 (the input's four row / column parity planes)
 __host__ __device__ inline size_t pre_smem_bytes(int npos, int C, int RS, int nt, int stages, int nplane) {
-    return (size_t)stages * nplane * 2 * npos * 16 + (size_t)RS * C * nt / 2 + nt * 4 + RS * 8 + 40 * 8 + 64;
+    return (size_t)stages * nplane * 2 * npos * 16 + (size_t)RS * C * nt / 2 + nt * 8 + RS * 8 + 40 * 8 + 64;
 }
 // two buffers of a tile's int16 residual rows (128 rows x nt channels), staged in shared memory
 __host__ __device__ inline size_t pre_res_stage_bytes(int nt) { return (size_t)2 * 128 * nt * 2 + 128; }
@@ -76,15 +81,25 @@ __device__ __forceinline__ void expand_raster(const ConvWsArgs& a, uint4* planes
     }
 }
 
-// RSTAGE: int16 residual rows travel through shared memory.  A tile's live pixels are consecutive
-// rows of the residual tensors, so all 512 epilogue threads move them as whole 128-byte lines
-// (cp.async in, 16-byte stores out: 4 lines per instruction) into a buffer whose 16-byte chunks are
-// XOR-swizzled by row, and every thread then reads / overwrites its own pixel's chunks there without
-// bank conflicts.  The incoming rows of the next tile fly while this tile is computed; the
-// outgoing rows leave one tile late.  (Without it each lane moves 16-byte pieces of its own row: 32
+// Staged epilogue: int16 residual rows travel through shared memory.  The four epilogue warps that
+// share 32 rows of a tile (same TMEM lane quadrant, different column groups) form a group: the live
+// pixels among its rows are consecutive rows of the residual tensors, so the group's 128 threads
+// move them as whole 128-byte lines (cp.async in, 16-byte stores out: 4 lines per instruction) into
+// a buffer of its own whose 16-byte chunks are XOR-swizzled by row, and every thread then reads /
+// overwrites its own pixel's chunks there without bank conflicts.  The incoming rows of the next
+// tile fly while this tile is computed; the outgoing rows leave one tile late; the four groups
+// meet only among themselves (one mbarrier each), never CTA-wide.  (Without it each lane moves 16-byte pieces of its own row: 32
 // lines per instruction, which made L1TEX the busiest unit of these layers.)
-template <int NT, bool RSTAGE>
+//
+// EPI selects the epilogue the kernel is compiled with, so that each carries only its own
+// registers (18 warps leave 96 per thread): 0 = plain (no residual in or out, no integer output:
+// the fp32 accumulator is compared with the fp32 threshold as it is), 1 = residual rows moved
+// directly between registers and global memory (any element size, pooled residuals, partial
+// channel ranges), 2 = staged int16 residual rows as described above.
+constexpr int kEpiPlain = 0, kEpiDirect = 1, kEpiStaged = 2;
+template <int NT, int EPI>
 __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
+    constexpr bool RSTAGE = EPI == kEpiStaged;
     // Tensor memory: accumulators (7 at NT = 64) below column 480, the unit block scales of the
     // 4-bit MMA above it; the patch ring is as deep as shared memory allows, so that no role waits
     // on another's latency.
@@ -103,14 +118,16 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     unsigned char* sAraw = smem;
     uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
     int* sThr = reinterpret_cast<int*>(sB + (size_t)RS * (a.C >> 5) * NT);
-    uint32_t* sTapK = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sThr + NT) + 7) & ~(uintptr_t)7);
+    float* sThrF = reinterpret_cast<float*>(sThr + NT);       // the thresholds as given (fp32)
+    uint32_t* sTapK = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sThrF + NT) + 7) & ~(uintptr_t)7);
     uint64_t* sBar = reinterpret_cast<uint64_t*>(sTapK + 2 * RS);
-    // barriers: a_full[8], a_empty[8], acc_full[8], acc_empty[8], epilogue rendezvous
+    // barriers: a_full[8], a_empty[8], acc_full[8], acc_empty[8], epilogue groups [4], drain
     uint32_t* sTmem = reinterpret_cast<uint32_t*>(sBar + 40);
     volatile int* sAbort = reinterpret_cast<volatile int*>(sTmem + 1);
     unsigned char* sRes = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(sTmem + 2) + 127) & ~(uintptr_t)127);
     const uint32_t bar0 = smem_u32(sBar);
-    const uint32_t BAR_EPI = bar0 + 8u * 32;           // the epilogue warps' own rendezvous (RSTAGE)
+    auto BAR_EPI = [&](int g) { return bar0 + 8u * (32 + g); };    // rendezvous of an epilogue group (staged epilogue)
+    const uint32_t BAR_DRAIN = bar0 + 8u * 36;         // MMAs still in flight when the issuer gives up
     auto BAR_AFULL = [&](int s) { return bar0 + 8u * s; };
     auto BAR_AEMPTY = [&](int s) { return bar0 + 8u * (8 + s); };
     auto BAR_CFULL = [&](int b) { return bar0 + 8u * (16 + b); };
@@ -125,7 +142,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     if (tid == 0) {
         for (int s = 0; s < 8; s++) { mbar_init(BAR_AFULL(s), 1); mbar_init(BAR_AEMPTY(s), 1); }
         for (int b = 0; b < 8; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), kPreEpiThreads / 32); }
-        mbar_init(BAR_EPI, kPreEpiThreads / 32);
+        for (int g = 0; g < 4; g++) mbar_init(BAR_EPI(g), kPreEpiThreads / 128);
+        mbar_init(BAR_DRAIN, 1);
         *sAbort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -137,11 +155,14 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         for (int i = tid; i < NT; i += kPreThreads) {
             // integer form of  !((float)v < thr)  (kernel.cuh:795-796): v >= ceil(thr)
             int it = INT_MIN;
+            float tf = __int_as_float(0x7FC00000);       // NaN: never "less", the bit is always set
             if (obase + i < a.O) {
                 const float t = __ldg(a.thr + obase + i);
+                tf = t;
                 if (t == t) it = t >= 2147483520.0f ? INT_MAX : t <= -2147483648.0f ? INT_MIN : (int)ceilf(t);
             }
             sThr[i] = it;
+            sThrF[i] = tf;
         }
         for (int t = tid; t < RS; t += kPreThreads) {
             // offset of the tap's operand inside a stage, in 16-byte units
@@ -177,7 +198,9 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             for (int m = mfirst; m < mtiles && ok; m += mstep) {
                 const long long slot0 = (long long)m * 128 - back + a.pre_front;
                 for (int cb = 0; cb < NCB; cb++, it++) {
-                    ok = wait(BAR_AEMPTY(s), sph ^ 1);
+                    // the ring is several tiles deep: this lane mostly waits for a slot, and sleeps
+                    // between polls so that it does not take issue slots from the epilogue warps
+                    ok = wait.relaxed(BAR_AEMPTY(s), sph ^ 1);
                     if (!ok) break;
                     mbar_expect_tx(BAR_AFULL(s), stage_bytes);
                     const uint32_t dst = smem_u32(sAraw + (size_t)s * stage_bytes);
@@ -202,8 +225,9 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             }
         }
         __syncwarp();
-    } else if (warp == MMA_WARP) {
+    } else if (warp >= MMA_WARP && warp < MMA_WARP + kPreMmaWarps) {
         // =============================== MMA issuer =========================================
+        // (ring slot, accumulator and their barrier phases follow from the tile's index tc)
         // The whole warp runs the control flow converged and polls the barriers, and one elected
         // lane issues: what the issuing thread executes between two MMAs is time the tensor pipe
         // idles, and a lone lane in a diverged warp pays far more per branch and per wait.
@@ -223,19 +247,24 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             uint32_t tapk[9];                              // 3x3 filters: the tap offsets in registers
 #pragma unroll
             for (int t = 0; t < 9; t++) tapk[t] = rs9 ? sTapK[t] : 0u;
-            uint32_t it = 0, tc = 0, sph = 0, bph = 0;
-            int s = 0, b = 0;
+            const uint32_t w2 = (uint32_t)(warp - MMA_WARP);
+            uint32_t it = 0;
             bool ok = true;
             long long tr_wc = 0, tr_wa = 0;
             const long long tr_t0 = clock64();
-            for (int m = mfirst; m < mtiles && ok; m += mstep, tc++) {
+            for (uint32_t tc = w2; (long long)mfirst + (long long)tc * mstep < mtiles && ok; tc += kPreMmaWarps) {
+                const int b = (int)(tc % NACC);
+                const uint32_t bph = (tc / NACC) & 1u;
                 ok = a.trace ? wait.timed(BAR_CEMPTY(b), bph ^ 1, tr_wc) : wait.spin(BAR_CEMPTY(b), bph ^ 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + b * NT;
                 uint32_t acc = 0;
                 uint32_t bLo = bLo0;
+                it = tc * NCB;
                 for (int cb = 0; cb < NCB && ok; cb++, it++) {
+                    const int s = (int)(it % (uint32_t)NSTAGE);
+                    const uint32_t sph = (it / (uint32_t)NSTAGE) & 1u;
                     ok = a.trace ? wait.timed(BAR_AFULL(s), sph, tr_wa) : wait.spin(BAR_AFULL(s), sph);
                     if (!ok) break;
                     tc_fence_after();
@@ -256,12 +285,16 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     acc = 1;
                     mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
                     }
-                    if (++s == NSTAGE) { s = 0; sph ^= 1; }
                 }
                 if (ok && leader) mma_commit(BAR_CFULL(b));       // accumulator complete
-                if (++b == NACC) { b = 0; bph ^= 1; }
             }
-            if (a.trace && blockIdx.x == 0 && leader) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[2] = it; }
+            if (!ok && leader) {
+                // giving up: the MMAs already issued must have finished before tensor memory is freed
+                mma_commit(BAR_DRAIN);
+                for (int i = 0; i < (1 << 20); i++)
+                    if (mbar_try_wait(BAR_DRAIN, 0)) break;
+            }
+            if (a.trace && blockIdx.x == 0 && leader && w2 == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[2] = it; }
         }
         __syncwarp();
     } else if (tid < kPreEpiThreads) {
@@ -271,7 +304,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         const int Ow = (a.O + 31) >> 5;
         const int lim = a.res_in ? min(a.residual_channels, a.res_in_ch) : 0;
         const int o0 = obase + cg * COLS;                  // this thread's first output channel
-        const bool res16 = !RSTAGE && a.res_in && a.res_in_bytes == 2 && (a.res_in_ch & 7) == 0 && (lim & 7) == 0;
+        const bool res16 = EPI == kEpiDirect && a.res_in && a.res_in_bytes == 2 && (a.res_in_ch & 7) == 0 && (lim & 7) == 0;
         uint32_t tc = 0;
         bool ok = true, overflow = false;
         long long tr_w = 0;
@@ -293,7 +326,9 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         // ---- staged residual rows (RSTAGE; the host enables it only for int16 tensors, an n-tile
         //      that lies entirely inside or outside the injected channels, NT of 64 or 128) --------
         constexpr uint32_t ROWB = NT * 2;                  // bytes of one pixel's residual segment
-        constexpr int NCOPY = (128 * ROWB) / (kPreEpiThreads * 16);     // 16-byte pieces per thread and tile
+        constexpr int NCOPY = (32 * ROWB) / (128 * 16);    // 16-byte pieces per thread and tile (group: 32 rows, 128 threads)
+        const int gtid = cg * 32 + lane;                   // this thread's index in its group
+        const int grow0 = quad * 32;                       // the group's first row of a tile
         const bool st_in = RSTAGE && a.res_in && obase < lim;
         const bool st_out = RSTAGE && a.res_out;
         // output pixels in front of raster position p (live pixels are consecutive tensor rows)
@@ -305,7 +340,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         };
         // shared-memory address of 16-byte chunk `c` of staged row `r`: chunks XOR-swizzled by row
         auto st_addr = [&](int buf, int r, int c) -> uint32_t {
-            return smem_u32(sRes) + (uint32_t)buf * (128u * ROWB) + (uint32_t)r * ROWB +
+            return smem_u32(sRes) + (uint32_t)(quad * 2 + buf) * (32u * ROWB) + (uint32_t)r * ROWB +
                    (uint32_t)(((c & ~7) | ((c ^ r) & 7)) << 4);
         };
         auto issue_in = [&](long long p0, int nl, int buf) {   // cp.async of a tile's incoming rows
@@ -313,7 +348,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             const char* g = reinterpret_cast<const char*>(a.res_in) + ((size_t)p0 * a.res_in_ch + obase) * 2;
 #pragma unroll
             for (int k = 0; k < NCOPY; k++) {
-                const uint32_t off = (uint32_t)(tid + k * kPreEpiThreads) * 16u;
+                const uint32_t off = (uint32_t)(gtid + k * 128) * 16u;
                 const int r = off / ROWB, c = (off % ROWB) >> 4;
                 if (r < nl)
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(st_addr(buf, r, c)),
@@ -325,7 +360,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             char* g = reinterpret_cast<char*>(a.res_out) + ((size_t)p0 * a.O + obase) * 2;
 #pragma unroll
             for (int k = 0; k < NCOPY; k++) {
-                const uint32_t off = (uint32_t)(tid + k * kPreEpiThreads) * 16u;
+                const uint32_t off = (uint32_t)(gtid + k * 128) * 16u;
                 const int r = off / ROWB, c = (off % ROWB) >> 4;
                 if (r < nl) {
                     uint4 v4;
@@ -338,8 +373,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         uint32_t eph = 0;                                  // phase of the epilogue rendezvous
         auto rendezvous = [&]() -> bool {
             __syncwarp();
-            if (lane == 0) mbar_arrive(BAR_EPI);
-            const bool r = wait(BAR_EPI, eph);
+            if (lane == 0) mbar_arrive(BAR_EPI(quad));
+            const bool r = wait(BAR_EPI(quad), eph);
             eph ^= 1;
             return r;
         };
@@ -392,17 +427,28 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 v[8 * j + 7] += (int)(short)(r[j].w >> 16);
             }
         };
+        // packed output bits (and the next layer's planes) of this thread's channels of one pixel
+        auto store_bits = [&](const Pix& q, uint32_t word) {
+            // bits of channel o live at bit 31 - o%32 of word o/32 (little-endian bytes)
+            unsigned char* wp = reinterpret_cast<unsigned char*>(
+                a.out + (size_t)q.n * a.out_image_stride + ((size_t)q.y * a.OWg + q.x) * Ow + (o0 >> 5));
+            if (COLS == 32) *reinterpret_cast<uint32_t*>(wp) = word;
+            else if (COLS == 16) *reinterpret_cast<unsigned short*>(wp + ((o0 & 16) ? 0 : 2)) = (unsigned short)word;
+            else wp[3 - ((o0 & 31) >> 3)] = (unsigned char)word;
+            if (a.nxt) store_next_planes(a, q.n, q.y, q.x, o0, word, COLS);
+        };
+        constexpr bool plain = EPI == kEpiPlain;
         uint4 rnext[NQ];
 #pragma unroll
         for (int j = 0; j < NQ; j++) rnext[j] = make_uint4(0u, 0u, 0u, 0u);
         Pix cur = locate(mfirst);
         if (res16 && mfirst < mtiles) fetch16(rnext, cur);
-        // first pixel and number of live pixels of the current, the previous and the next tile
+        // first pixel and number of live pixels of the group's rows of the current, previous and next tile
         long long p0_cur = 0, p0_prev = 0, p0_next = 0;
         int nl_cur = 0, nl_prev = -1, nl_next = 0;
         if (RSTAGE && mfirst < mtiles) {
-            p0_cur = live_before(mfirst * 128);
-            nl_cur = (int)(live_before(mfirst * 128 + 128) - p0_cur);
+            p0_cur = live_before(mfirst * 128 + grow0);
+            nl_cur = (int)(live_before(mfirst * 128 + grow0 + 32) - p0_cur);
             issue_in(p0_cur, nl_cur, 0);
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -427,6 +473,23 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_CEMPTY(b));
             if (++b == NACC) { b = 0; bph ^= 1; }
+            if (plain) {
+                // no residual and no integer output: the reference's comparison as it stands,
+                // !((float)value < threshold) (kernel.cuh:795-796), on the fp32 accumulator
+                uint32_t word = 0;
+                const float4* tf4 = reinterpret_cast<const float4*>(sThrF + cg * COLS);
+#pragma unroll
+                for (int j = 0; j < COLS / 4; j++) {
+                    const float4 th = tf4[j];
+                    if (!(__int_as_float(v[4 * j]) < th.x)) word |= (1u << (COLS - 1)) >> (4 * j);
+                    if (!(__int_as_float(v[4 * j + 1]) < th.y)) word |= (1u << (COLS - 1)) >> (4 * j + 1);
+                    if (!(__int_as_float(v[4 * j + 2]) < th.z)) word |= (1u << (COLS - 1)) >> (4 * j + 2);
+                    if (!(__int_as_float(v[4 * j + 3]) < th.w)) word |= (1u << (COLS - 1)) >> (4 * j + 3);
+                }
+                if (q.live) store_bits(q, word);
+                mprev = m;
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < COLS; j++) v[j] = f4_acc_to_int(v[j]);     // fp32 accumulators, exact integers
             if (q.live && a.acc_out) {
@@ -445,8 +508,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 if (!ok) break;
                 if (nl_prev >= 0) store_out(p0_prev, nl_prev, sbuf ^ 1);
                 if (m + mstep < mtiles) {
-                    p0_next = live_before((m + mstep) * 128);
-                    nl_next = (int)(live_before((m + mstep) * 128 + 128) - p0_next);
+                    p0_next = live_before((m + mstep) * 128 + grow0);
+                    nl_next = (int)(live_before((m + mstep) * 128 + grow0 + 32) - p0_next);
                     issue_in(p0_next, nl_next, sbuf ^ 1);  // the buffer this thread has just drained
                 }
                 asm volatile("cp.async.commit_group;" ::: "memory");
@@ -518,15 +581,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                         dst[j] = make_int4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
             }
-            if (q.live) {
-                // bits of channel o live at bit 31 - o%32 of word o/32 (little-endian bytes)
-                unsigned char* wp = reinterpret_cast<unsigned char*>(
-                    a.out + (size_t)q.n * a.out_image_stride + ((size_t)q.y * a.OWg + q.x) * Ow + (o0 >> 5));
-                if (COLS == 32) *reinterpret_cast<uint32_t*>(wp) = word;
-                else if (COLS == 16) *reinterpret_cast<unsigned short*>(wp + ((o0 & 16) ? 0 : 2)) = (unsigned short)word;
-                else wp[3 - ((o0 & 31) >> 3)] = (unsigned char)word;
-                if (a.nxt) store_next_planes(a, q.n, q.y, q.x, o0, word, COLS);
-            }
+            if (q.live) store_bits(q, word);
             mprev = m;
             p0_prev = p0_cur; nl_prev = nl_cur;
             p0_cur = p0_next; nl_cur = nl_next;

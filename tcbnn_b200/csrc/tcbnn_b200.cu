@@ -456,21 +456,21 @@ int launch_conv_umma_ws(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t 
     return launch_check("conv_layer (tcgen05)");
 }
 
-template <int NT, bool RSTAGE>
+template <int NT, int EPI>
 __global__ void __launch_bounds__(umma::kPreThreads, 1) k_conv_umma_pre(umma::ConvWsArgs a) {
     extern __shared__ __align__(128) unsigned char dyn_smem_pre[];
-    umma::conv_umma_pre_cta<NT, RSTAGE>(a, dyn_smem_pre);
+    umma::conv_umma_pre_cta<NT, EPI>(a, dyn_smem_pre);
 }
 __global__ void __launch_bounds__(256) k_expand_raster(umma::ConvWsArgs a, uint4* planes, long long positions,
                                                        long long front) {
     umma::expand_raster(a, planes, positions, front);
 }
 
-template <int NT, bool RSTAGE>
+template <int NT, int EPI>
 int launch_conv_umma_pre_k(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
     if (configure_once(configured, [] {
-            return cudaFuncSetAttribute(k_conv_umma_pre<NT, RSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            return cudaFuncSetAttribute(k_conv_umma_pre<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         }))
         return 1;
     a.ntiles_n = a.O / NT;
@@ -478,7 +478,7 @@ int launch_conv_umma_pre_k(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream
     const long long mtiles = (a.NV + 127) / 128;
     long long per = sms / a.ntiles_n;
     if (per > mtiles) per = mtiles;
-    k_conv_umma_pre<NT, RSTAGE><<<(int)(per * a.ntiles_n), umma::kPreThreads, smem, st>>>(a);
+    k_conv_umma_pre<NT, EPI><<<(int)(per * a.ntiles_n), umma::kPreThreads, smem, st>>>(a);
     return launch_check("conv_layer (tcgen05, pre-expanded input)");
 }
 
@@ -510,11 +510,12 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
             const size_t need = umma::pre_smem_bytes(a.NPOS, a.C, RS, NT, stages, nplane) + umma::pre_res_stage_bytes(NT);
             if (need <= 227 * 1024) {
                 a.pre_stages = stages;
-                return launch_conv_umma_pre_k<NT, true>(a, need, sms, st);
+                return launch_conv_umma_pre_k<NT, umma::kEpiStaged>(a, need, sms, st);
             }
         }
     }
-    return launch_conv_umma_pre_k<NT, false>(a, smem, sms, st);
+    if (!a.res_in && !a.res_out && !a.acc_out) return launch_conv_umma_pre_k<NT, umma::kEpiPlain>(a, smem, sms, st);
+    return launch_conv_umma_pre_k<NT, umma::kEpiDirect>(a, smem, sms, st);
 }
 
 // 2x2 max of an int16 residual [B][2P][2Q][ch] -> [B][P][Q][ch] (kernel.cuh:773-783), 8 channels
@@ -760,6 +761,34 @@ __global__ void __launch_bounds__(128) k_umma_issue(int iters, int group, long l
     umma::tc_fence_before();
     __syncthreads();
     if (threadIdx.x < 32) umma::tmem_dealloc(tm, 256);
+}
+
+// ---- what a wait that gives up looks like ----------------------------------------------------
+// One CTA allocates tensor memory like the conv kernels, initialises an mbarrier that expects one
+// arrival, and polls it `polls` times with the kernels' own poll instruction.  Nobody arrives: the wait runs out, the thread records status 1, the CTA frees its
+// tensor memory and returns -- the path every bounded wait of the tcgen05 kernels takes when its
+// partner never shows up.  Nothing faults and nothing hangs; the context stays usable.
+__global__ void __launch_bounds__(128) k_wait_probe(int polls, int* status, int* polled) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tm;
+    if (threadIdx.x < 32) umma::tmem_alloc(umma::smem_u32(&tm), 32);
+    if (threadIdx.x == 0) {
+        umma::mbar_init(umma::smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    if (threadIdx.x == 0) {
+        int i = 0;
+        bool done = false;
+        for (; i < polls && !done; i++) done = umma::mbar_try_wait(umma::smem_u32(&bar), 0);
+        *polled = i;
+        if (!done) atomicExch(status, 1);
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) umma::tmem_dealloc(tm, 32);
 }
 
 // ---- fixed scratch for callers that cannot allocate ---------------------------------------
@@ -1464,6 +1493,22 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
     cudaFree(sink);
     const double ops = (kind == 2 ? 2.0 * 16 * 8 * 32 : 2.0 * 16 * 8 * 256);
     *tops = (double)ctas * (threads / 32) * iters * 8 * ops / (best * 1e-3) / 1e12;
+    return 0;
+}
+
+int tcbnn_wait_probe(int polls, int* status) {
+    if (!status || polls <= 0 || polls > (1 << 24)) return fail("wait_probe: polls must be in 1..2^24");
+    int* buf = nullptr;
+    CUDA_TRY(cudaMalloc(&buf, 8));
+    CUDA_TRY(cudaMemset(buf, 0, 8));
+    k_wait_probe<<<1, 128>>>(polls, buf, buf + 1);
+    if (launch_check("wait_probe")) { cudaFree(buf); return 1; }
+    int host[2] = {0, 0};
+    const cudaError_t e = cudaMemcpy(host, buf, sizeof host, cudaMemcpyDeviceToHost);   // synchronises
+    cudaFree(buf);
+    if (e != cudaSuccess) return fail("wait_probe: %s", cudaGetErrorString(e));
+    if (host[0] == 1 && host[1] != polls) return fail("wait_probe: gave up after %d of %d polls", host[1], polls);
+    *status = host[0];
     return 0;
 }
 

@@ -61,6 +61,7 @@ SIGNATURES = {
     "tcbnn_inconv_specialize_selftest": (_I, [C.POINTER(ConvDesc), C.c_uint, C.POINTER(C.c_longlong)]),
     "tcbnn_inconv_layer_u8": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_mma_peak": (_I, [_I, _I, _I, C.POINTER(C.c_double)]),
+    "tcbnn_wait_probe": (_I, [_I, C.POINTER(C.c_int)]),
 }
 
 _lib = None

@@ -325,7 +325,8 @@ UMMA_CASES = [
 
 @pytest.mark.parametrize("case", UMMA_CASES)
 def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
-    """Both conv kernels (tcgen05 int8 implicit GEMM, warp-level b1 MMA) against the oracle."""
+    """The conv kernels (tcgen05 implicit GEMM on 4-bit and on int8 operands, warp-level b1 MMA) and
+    the epilogue variants of the loader-fed one against the oracle."""
     B, H, W, C, O, R, resmode = case[:7]
     st = case[7] if len(case) > 7 else 1
     g = util.rng(sum(case[:6]))
@@ -348,7 +349,8 @@ def test_conv_layer_tcgen05_and_b1_paths_agree_with_oracle(cuda, case):
     try:
         # 5x5 filters over 256 channels do not fit the filter-stationary kernel's shared memory
         # ... and 200-pixel rows do not fit its patch
-        for path in ((2, 1) if ((R == 5 and C >= 256) or W >= 160) else (2, 3, 1)):
+        # path 5: automatic choice with the int16 residual rows staged in shared memory wherever possible
+        for path in ((2, 5, 1) if ((R == 5 and C >= 256) or W >= 160) else (2, 5, 3, 1)):
             ops.set_conv_path(path)
             go, gr, ga = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda),
                                         res_in=dev(res_in, cuda) if res_in is not None else None,
@@ -482,3 +484,32 @@ def test_tcgen05_path_refuses_ineligible_layer(cuda):
             ops.conv_layer(d, x, prep, thr)
     finally:
         ops.set_conv_path(0)
+
+
+def test_bounded_wait_gives_up_and_the_context_stays_usable(cuda):
+    """A wait on a barrier nobody arrives at runs out after its poll limit, the kernel records
+    status 1, frees its tensor memory and returns (tcbnn_wait_probe runs that path of the tcgen05
+    kernels in isolation); the next tcgen05 convolution on the same context is bit-exact and
+    reports status 0."""
+    import ctypes as C
+    from tcbnn_b200 import lib
+    st = C.c_int(-1)
+    lib.call("tcbnn_wait_probe", 1 << 16, C.byref(st))
+    assert st.value == 1
+    g = util.rng(99)
+    B, H, Cc, O = 2, 12, 64, 64
+    x = util.rand_words(g, (B, H, H, Cc // 32))
+    f = util.rand_words(g, (O, 9, Cc // 32))
+    thr = (g.standard_normal(O) * 24).astype(np.float32)
+    d = ops.conv_desc(B, H, H, Cc, O, 3, 3)
+    prep = ops.conv_prepare(d, dev(f, cuda))
+    try:
+        ops.set_conv_path(2)
+        out, _, _ = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda))
+    finally:
+        ops.set_conv_path(0)
+    eb, _, _ = orc.conv_layer(x, f, thr, Cc, 3, 3)
+    assert np.array_equal(host_u32(out).reshape(eb.shape), eb)
+    assert ops.conv_status(d, prep) == 0
+    lib.call("tcbnn_wait_probe", 1 << 10, C.byref(st))       # and once more after real work
+    assert st.value == 1

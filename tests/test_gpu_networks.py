@@ -163,3 +163,22 @@ def test_set_batch_runs_ragged_batches_on_the_same_objects(cuda, which):
         np.testing.assert_allclose(logits, acts[-1], rtol=1e-5, atol=1e-5)
     with pytest.raises(ValueError):
         net.set_batch(9)
+
+
+@pytest.mark.parametrize("which,sub", [("mlp", 512), ("vgg_cifar", 32)])
+def test_baseline_batch_logits_against_oracle_slice(cuda, which, sub):
+    """The MLP at batch 8192 and the CIFAR VGG at batch 1024 (the standalone network
+    configurations at their full batch): the logits of the first images must equal the CPU
+    oracle's on exactly those images (every image is processed independently), and all logits
+    must be finite.  1e-5 relative."""
+    spec = models.mlp_spec(8192) if which == "mlp" else models.vgg_cifar_spec(1024)
+    w = models.synthetic_weights(spec, 110)
+    x = models.synthetic_input(spec, 111)
+    net = models.Network(spec, w, x)
+    logits = net.forward_graph().cpu().numpy()
+    assert np.all(np.isfinite(logits))
+    acts, _ = onet.run(dict(spec, batch=sub), w, x[:sub])
+    np.testing.assert_allclose(logits[:sub], acts[-1], rtol=1e-5, atol=1e-5)
+    # and the last images, which sit in the last tiles of every layer
+    acts, _ = onet.run(dict(spec, batch=sub), w, x[-sub:])
+    np.testing.assert_allclose(logits[-sub:], acts[-1], rtol=1e-5, atol=1e-5)

@@ -187,3 +187,45 @@ def test_oracle_matches_reference_implementation_layer_by_layer(cuda, tmp_path, 
             "resnet18_small": models.resnet18_spec(8, image=64, classes=100),
             "resnet_cifar": models.resnet_cifar_spec(8)}[which]
     _run(spec, 60, tmp_path, cuda, runner=_ref_runner())
+
+
+def test_standalone_conv_full_size_with_thresholds(cuda):
+    """The standalone conv configuration at full size with its thresholds: 256 x 56 x 56 x 128 ->
+    128, 3x3, stride 1, SAME padding, per-channel fp32 thresholds N(0, 8) (8 is the standard
+    deviation).  Packed output bits and int32 accumulators against the CPU oracle on the first and
+    last 8 images, the accumulators of ALL images against the reference's own kernel where it was
+    built, and the packed bits of all images against the accumulators thresholded in torch."""
+    N, H, Cc, O = 256, 56, 128, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(2)
+    x = torch.randint(0, 2, (N, H, H, Cc), device=cuda, generator=g, dtype=torch.int8).float() * 2 - 1
+    g.manual_seed(3)
+    F = torch.randint(0, 2, (9, Cc, O), device=cuda, generator=g, dtype=torch.int8).float() * 2 - 1
+    g.manual_seed(4)
+    thr = torch.randn((O,), device=cuda, generator=g) * 8.0
+    d = ops.conv_desc(N, H, H, Cc, O, 3, 3)
+    xb = ops.pack_rows(x.reshape(N * H * H, Cc)).reshape(N, H, H, Cc // 32)
+    fb = ops.pack_conv_filter(F)
+    prep = ops.conv_prepare(d, fb)
+    out, _, acc = ops.conv_layer(d, xb, prep, thr, want_acc=True)
+    assert ops.conv_status(d, prep) == 0
+    sub = 8
+    for sl in (slice(0, sub), slice(N - sub, N)):
+        eb, _, ea = orc.conv_layer(xb[sl].cpu().numpy(), fb.cpu().numpy(), thr.cpu().numpy(), Cc, 3, 3, want_acc=True)
+        assert np.array_equal(acc[sl].cpu().numpy(), ea)
+        assert np.array_equal(out[sl].cpu().numpy().view(np.uint32).reshape(eb.shape), eb)
+    # all images: bit o of a pixel is !((float)acc < thr[o]) (kernel.cuh:795-796)
+    bits = ~(acc.float() < thr.view(1, 1, 1, O))
+    weights = (2 ** torch.arange(31, -1, -1, device=cuda, dtype=torch.int64)).view(1, 1, 1, 1, 32)
+    words = (bits.view(N, H, H, O // 32, 32).to(torch.int64) * weights).sum(-1)
+    got = out.view(N, H, H, O // 32).to(torch.int64) & 0xFFFFFFFF
+    assert torch.equal(got, words)
+    R = orc.ref_lib()
+    if R is not None and hasattr(R, "ref_gpu_bconv128"):
+        ref_out = torch.zeros((H, H, N, O), dtype=torch.int32, device=cuda)
+        ms = C.c_float(0)
+        torch.cuda.synchronize()
+        rc = R.ref_gpu_bconv128(C.c_void_p(x.data_ptr()), C.c_void_p(F.data_ptr()), C.c_void_p(ref_out.data_ptr()),
+                                N, H, H, Cc, O, 3, 3, 1, 1, H, H, 1, C.byref(ms))
+        assert rc == 0
+        assert torch.equal(acc, ref_out.permute(2, 0, 1, 3).contiguous())
