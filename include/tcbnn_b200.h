@@ -98,13 +98,26 @@ size_t tcbnn_conv_prepared_bytes(const tcbnn_conv_desc* d);
 int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, void* prepared,
                        void* stream);
 
+/* Element formats of residual tensors: the res_in_bytes / res_out_bytes arguments below.
+ * TCBNN_RES_INT16_CHUNKED is int16 laid out by 8-channel chunk, [ceil(ch/8)][pixels][8] with
+ * pixels = B*P*Q of that tensor (element (pixel p, channel c) at ((c/8)*pixels + p)*8 + c%8): one
+ * thread per pixel then reads and writes whole lines across a warp, which the residual layers with
+ * narrow channel counts are bound by.  It is read and written only by the loader-fed tcgen05
+ * kernel (layers with tcbnn_conv_planes_bytes != 0 called with their workspace, pool == 1, channel
+ * counts in multiples of 8; other calls fail) and written by tcbnn_inconv_specialized_layer;
+ * tcbnn_conv_prefers_chunked_residual says for which layers it is the faster choice. */
+#define TCBNN_RES_INT32 4
+#define TCBNN_RES_INT16 2
+#define TCBNN_RES_INT16_CHUNKED 18
+int tcbnn_conv_prefers_chunked_residual(const tcbnn_conv_desc* d);
+
 /* Binary conv layer with threshold / OR-pool / residual / repack fused.
  * Conv128LayerFMT, kernel.cuh:676-827.
  *   in   [B][H][W][Cw]; out: image b at out + b*out_image_stride words, [OH][OW][Ow]
  *        (out_image_stride > OH*OW*Ow lets the next FC layer see padded rows: ahead_fc)
  *   res_in  (optional) [B][P or 2P][Q or 2Q][res_in_ch], int32 or int16 elements
- *           (res_in_bytes = 4 or 2); injected for o < residual_channels; residual_pool takes
- *           the max over the 2x2 window
+ *           (res_in_bytes = 4 or 2, or TCBNN_RES_INT16_CHUNKED for the chunk-major layout);
+ *           injected for o < residual_channels; residual_pool takes the max over the 2x2 window
  *   res_out (optional) [B][P][Q][O], int32 or int16 (res_out_bytes): value after injection
  *           (save_residual).  int16 halves the dominant HBM traffic of the residual layers;
  *           the caller picks it when the running sum is known to fit (|value| <= C*R*S +
@@ -161,7 +174,9 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
  * stride-1 layers otherwise take the activation-stationary kernel, narrow ones with a workspace the
  * kernel fed from a pre-expanded input), 4 = as 0 but the loader-fed kernel moves int16 residual
  * rows straight between registers and global memory, never staging them in shared memory, 5 = as 0
- * but staging them wherever the tensors allow (0 stages them where that measured faster).
+ * but staging them wherever the tensors allow (0 stages them where that measured faster), 6 = as
+ * 0 but the loader-fed kernel always runs one CTA per SM (0 runs layers with an n-tile of 64 as
+ * two smaller CTAs per SM when they fit).
  * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);

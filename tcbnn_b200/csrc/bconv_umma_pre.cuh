@@ -26,13 +26,19 @@
 namespace tcbnn {
 namespace umma {
 
-constexpr int kPreEpiThreads = 512;
+constexpr int kPreEpiThreads = 512;         // epilogue threads of the one-CTA-per-SM form (16 warps)
 // One MMA-issuing warp.  (Two issuers on alternate tiles were tried and are wrong as well as no
 // faster: an mbarrier wait names its phase by parity only, so a waiter must see every phase of a
 // barrier; with two consumers alternating on the same ring slot the one that runs ahead finds the
 // parity of the phase before last already complete and reads a slot that has not been refilled.)
 constexpr int kPreMmaWarps = 1;
 constexpr int kPreThreads = kPreEpiThreads + 32 + 32 * kPreMmaWarps;
+// EPIW, the kernel's third template argument, is the number of epilogue warps: 16 (one CTA per SM,
+// all of tensor memory) or 8 (n-tile 64 only: each thread then takes 32 columns instead of 16, the
+// CTA allocates half of tensor memory and two CTAs share an SM -- twice the independent
+// loader / issuer / epilogue pipelines, so that one CTA's barrier round trips and epilogue
+// latency are covered by the other's work, and half the per-thread bookkeeping per output).
+__host__ __device__ constexpr int pre_threads(int epiw) { return epiw * 32 + 32 + 32 * kPreMmaWarps; }
 constexpr int kPreMaxStages = 8;           // patch ring depth is chosen by the host from the shared memory left
 
 // positions of zero padding in front of the planes (a tile's patch starts up to back_y*PW+back_x
@@ -97,18 +103,20 @@ __device__ __forceinline__ void expand_raster(const ConvWsArgs& a, uint4* planes
 // directly between registers and global memory (any element size, pooled residuals, partial
 // channel ranges), 2 = staged int16 residual rows as described above.
 constexpr int kEpiPlain = 0, kEpiDirect = 1, kEpiStaged = 2;
-template <int NT, int EPI>
+template <int NT, int EPI, int EPIW>
 __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     constexpr bool RSTAGE = EPI == kEpiStaged;
+    constexpr int kEpiThreads = EPIW * 32, kThreadsCta = pre_threads(EPIW);
+    static_assert(EPIW == 16 || (EPIW == 8 && NT == 64 && EPI != kEpiStaged), "8 epilogue warps: n-tile 64, no staging");
     // Tensor memory: accumulators (7 at NT = 64) below column 480, the unit block scales of the
     // 4-bit MMA above it; the patch ring is as deep as shared memory allows, so that no role waits
     // on another's latency.
-    constexpr uint32_t TM_COLS = 512, SF_COL = 480;
+    constexpr uint32_t TM_COLS = EPIW == 16 ? 512 : 256, SF_COL = TM_COLS - 32;
     constexpr int NACC = NT >= 128 ? 2 : ((SF_COL / NT) > 8 ? 8 : (SF_COL / NT));   // measured: deeper does not pay at NT = 128
     const int NSTAGE = a.pre_stages;
-    constexpr int COLS = NT / 4;                      // accumulator columns per epilogue thread
+    constexpr int COLS = NT / (EPIW / 4);             // accumulator columns per epilogue thread
     static_assert(COLS == 8 || COLS == 16 || COLS == 32, "n-tile of 32, 64 or 128");
-    constexpr int LOAD_WARP = kPreEpiThreads / 32, MMA_WARP = LOAD_WARP + 1;
+    constexpr int LOAD_WARP = EPIW, MMA_WARP = LOAD_WARP + 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int RS = a.R * a.S, NCB = a.C >> 6;
     const int NPLANE = a.stride == 2 ? 4 : 1;
@@ -141,8 +149,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
 
     if (tid == 0) {
         for (int s = 0; s < 8; s++) { mbar_init(BAR_AFULL(s), 1); mbar_init(BAR_AEMPTY(s), 1); }
-        for (int b = 0; b < 8; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), kPreEpiThreads / 32); }
-        for (int g = 0; g < 4; g++) mbar_init(BAR_EPI(g), kPreEpiThreads / 128);
+        for (int b = 0; b < 8; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), EPIW); }
+        for (int g = 0; g < 4; g++) mbar_init(BAR_EPI(g), EPIW / 4);
         mbar_init(BAR_DRAIN, 1);
         *sAbort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -151,8 +159,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     {
         const uint4* src = a.wf4 + (size_t)nt * RS * (a.C >> 5) * NT;
         const int nB = RS * (a.C >> 5) * NT;
-        for (int i = tid; i < nB; i += kPreThreads) sB[i] = __ldg(src + i);
-        for (int i = tid; i < NT; i += kPreThreads) {
+        for (int i = tid; i < nB; i += kThreadsCta) sB[i] = __ldg(src + i);
+        for (int i = tid; i < NT; i += kThreadsCta) {
             // integer form of  !((float)v < thr)  (kernel.cuh:795-796): v >= ceil(thr)
             int it = INT_MIN;
             float tf = __int_as_float(0x7FC00000);       // NaN: never "less", the bit is always set
@@ -164,7 +172,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             sThr[i] = it;
             sThrF[i] = tf;
         }
-        for (int t = tid; t < RS; t += kPreThreads) {
+        for (int t = tid; t < RS; t += kThreadsCta) {
             // offset of the tap's operand inside a stage, in 16-byte units
             const int r = t / a.S, sx = t % a.S;
             if (NPLANE == 4) {
@@ -297,7 +305,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             if (a.trace && blockIdx.x == 0 && leader && w2 == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[2] = it; }
         }
         __syncwarp();
-    } else if (tid < kPreEpiThreads) {
+    } else if (tid < kEpiThreads) {
         // =============================== epilogue ===========================================
         constexpr int NQ = COLS / 8;                       // 8-channel groups (one uint4 of int16) per thread
         const int row = tid & 127, quad = warp & 3, cg = warp >> 2;
@@ -343,14 +351,19 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             return smem_u32(sRes) + (uint32_t)(quad * 2 + buf) * (32u * ROWB) + (uint32_t)r * ROWB +
                    (uint32_t)(((c & ~7) | ((c ^ r) & 7)) << 4);
         };
+        // bytes of a pixel's incoming segment: the whole n-tile, or the part of it that receives a
+        // residual (a producer with fewer channels, e.g. 64 of this layer's 128); a multiple of 16
+        const uint32_t rowb_in = st_in ? (uint32_t)min(NT, lim - obase) * 2u : ROWB;
         auto issue_in = [&](long long p0, int nl, int buf) {   // cp.async of a tile's incoming rows
             if (!st_in) return;
             const char* g = reinterpret_cast<const char*>(a.res_in) + ((size_t)p0 * a.res_in_ch + obase) * 2;
 #pragma unroll
             for (int k = 0; k < NCOPY; k++) {
+                // the same thread -> (row, chunk) map as store_out: a thread refills exactly the
+                // bytes it has just drained, whatever the width of the incoming rows
                 const uint32_t off = (uint32_t)(gtid + k * 128) * 16u;
                 const int r = off / ROWB, c = (off % ROWB) >> 4;
-                if (r < nl)
+                if (r < nl && (uint32_t)(c << 4) < rowb_in)
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(st_addr(buf, r, c)),
                                  "l"(g + (size_t)r * a.res_in_ch * 2 + (c << 4)) : "memory");
             }
@@ -383,7 +396,30 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         auto fetch16 = [&](uint4 (&r)[NQ], const Pix& q) {
             const short* base = reinterpret_cast<const short*>(a.res_in);
             const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-            if (a.residual_pool) {
+            if (a.res_in_chunked) {
+                // [channel chunk][pixel][8 channels]: consecutive lanes (pixels) read consecutive
+                // 16 bytes, so a warp's load touches four whole lines instead of 32 pieces of lines
+                const uint4* cb = reinterpret_cast<const uint4*>(a.res_in) + (size_t)(o0 >> 3) * a.res_in_npix;
+                if (a.residual_pool) {
+                    const size_t i00 = ((size_t)q.n * 2 * a.OHg + 2 * q.y) * 2 * a.OWg + 2 * q.x, rw = (size_t)2 * a.OWg;
+#pragma unroll
+                    for (int j = 0; j < NQ; j++) {
+                        r[j] = z;
+                        if (q.live && o0 + 8 * j < lim) {
+                            const uint4* p = cb + (size_t)j * a.res_in_npix + i00;
+                            const uint4 w0 = __ldg(p), w1 = __ldg(p + 1), w2 = __ldg(p + rw), w3 = __ldg(p + rw + 1);
+                            r[j].x = __vmaxs2(__vmaxs2(w0.x, w1.x), __vmaxs2(w2.x, w3.x));
+                            r[j].y = __vmaxs2(__vmaxs2(w0.y, w1.y), __vmaxs2(w2.y, w3.y));
+                            r[j].z = __vmaxs2(__vmaxs2(w0.z, w1.z), __vmaxs2(w2.z, w3.z));
+                            r[j].w = __vmaxs2(__vmaxs2(w0.w, w1.w), __vmaxs2(w2.w, w3.w));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NQ; j++)
+                        r[j] = (q.live && o0 + 8 * j < lim) ? __ldg(cb + (size_t)j * a.res_in_npix + q.opix) : z;
+                }
+            } else if (a.residual_pool) {
                 const size_t b00 = (((size_t)q.n * 2 * a.OHg + 2 * q.y) * 2 * a.OWg + 2 * q.x) * a.res_in_ch + o0;
                 const size_t rowp = (size_t)2 * a.OWg * a.res_in_ch;
 #pragma unroll
@@ -514,12 +550,15 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 }
                 asm volatile("cp.async.commit_group;" ::: "memory");
                 lrow = (int)((long long)q.opix - p0_cur);
-                if (st_in && q.live) {
+                if (st_in && q.live && o0 < lim) {
                     uint4 r[NQ];
 #pragma unroll
-                    for (int j = 0; j < NQ; j++)
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[j].x), "=r"(r[j].y), "=r"(r[j].z), "=r"(r[j].w)
-                                     : "r"(st_addr(sbuf, lrow, cg * NQ + j)) : "memory");
+                    for (int j = 0; j < NQ; j++) {
+                        r[j] = make_uint4(0u, 0u, 0u, 0u);
+                        if (o0 + 8 * j < lim)
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[j].x), "=r"(r[j].y), "=r"(r[j].z), "=r"(r[j].w)
+                                         : "r"(st_addr(sbuf, lrow, cg * NQ + j)) : "memory");
+                    }
                     add16(v, r);
                 }
             } else if (res16) {
@@ -570,6 +609,9 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                         if (RSTAGE)                        // into the staged row, in place of what was read
                             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(st_addr(sbuf, lrow, cg * NQ + j)),
                                          "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        else if (a.res_out_chunked)
+                            reinterpret_cast<uint4*>(a.res_out)[(size_t)((o0 >> 3) + j) * a.res_out_npix + q.opix] =
+                                make_uint4(w[0], w[1], w[2], w[3]);
                         else
                             dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
                     }

@@ -50,6 +50,9 @@ struct ConvWsArgs {
     uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
     int nxt_nplane;           // 1, or 4 when that layer has stride 2 (one plane per row / column parity)
     const void* res_in; int res_in_bytes, res_in_ch, residual_channels, residual_pool;
+    // int16 residual tensors may be laid out by 8-channel chunk, [ch/8][pixels][8], instead of NHWC
+    // (bconv_umma_pre.cuh, direct epilogue only): npix = pixels of the whole tensor
+    int res_in_chunked, res_out_chunked; long long res_in_npix, res_out_npix;
     uint32_t* out; long long out_image_stride;
     void* res_out; int res_out_bytes; int32_t* acc_out;
     int* err_flag;

@@ -46,6 +46,7 @@ struct SpecArgs {
     unsigned total;            // pre-pool pixels
     // optional: the output also as +-1 nibbles in the next layer's input planes (bconv_umma_pre.cuh)
     uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;
+    int res_out_chunked;      // int16 residual laid out [channel chunk of 8][pixel][8] instead of NHWC
 };
 
 // One kernel per (input type, load style), compiled when first used: a 7x7x64 kernel takes
@@ -81,7 +82,7 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
          "struct SpecArgs { const float* x; const unsigned char* x8; const float* lut; int B, H, W, OH, OW;\n"
          "  uint32_t* out; long long out_image_stride; void* res_out; int res_out_bytes, res_out_ld;\n"
          "  float* acc_out; unsigned total;\n"
-         "  uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH; };\n"
+         "  uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH; int res_out_chunked; };\n"
          // 32 packed bits -> 32 nibbles of +1 / -1 (e2m1), the order the conv kernels' filters use
          // (expand32_f4 in bconv_umma.cuh)
          "__device__ __forceinline__ uint32_t expand8_f4(uint32_t b) {\n"
@@ -155,11 +156,17 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
                  "    } }\n"
                  "   const float pp = __fadd_rn(f0, f1), pm = __fadd_rn(f0, -f1);\n"
                  "   const float v7 = __fadd_rn(pp, f2), v6 = __fadd_rn(pp, -f2), v5 = __fadd_rn(pm, f2), v4 = __fadd_rn(pm, -f2);\n";
-            for (int o = 0; o < O; o++) {
-                const int k = codes[(size_t)t * Oall + OB + o];
-                if (k >= 4) emit(s, "   a%d = __fadd_rn(a%d, v%d);\n", o, o, k);
-                else emit(s, "   a%d = __fadd_rn(a%d, -v%d);\n", o, o, 7 - k);     // pattern k is minus pattern 7-k
-            }
+            // The adds of one tap are independent of each other (one per channel), so their order is
+            // free: they are emitted grouped by the magnitude they add, consecutive instructions then
+            // share a source register and the assembler can serve it from the operand reuse cache
+            // instead of the register file (fewer bank conflicts next to the accumulator reads).
+            for (int mag = 4; mag < 8; mag++)
+                for (int o = 0; o < O; o++) {
+                    const int k = codes[(size_t)t * Oall + OB + o];
+                    if ((k >= 4 ? k : 7 - k) != mag) continue;
+                    if (k >= 4) emit(s, "   a%d = __fadd_rn(a%d, v%d);\n", o, o, k);
+                    else emit(s, "   a%d = __fadd_rn(a%d, -v%d);\n", o, o, 7 - k);     // pattern k is minus pattern 7-k
+                }
             s += "  }\n";
         }
         s += " }\n";
@@ -190,6 +197,16 @@ inline std::string generate_source(const SpecHandle& h, const std::vector<unsign
          "  if (c.res_out_bytes == 2) {\n"
          "   short* r = reinterpret_cast<short*>(c.res_out) + opix * c.res_out_ld + OBASE;\n";
     if (O % 8 == 0) {
+        // chunk-major layout [channel chunk of 8][pixel][8]: consecutive threads (pixels) store
+        // consecutive 16 bytes, whole lines per warp
+        emit(s, "   if (c.res_out_chunked) {\n    uint4* d4 = reinterpret_cast<uint4*>(c.res_out) + (size_t)%d * c.total + opix;\n", OB / 8);
+        for (int j = 0; j < O / 8; j++) {
+            emit(s, "    d4[(size_t)%d * c.total] = make_uint4(", j);
+            for (int k = 0; k < 4; k++)
+                emit(s, "((uint32_t)(int)a%d & 0xFFFFu) | ((uint32_t)(int)a%d << 16)%s", 8 * j + 2 * k, 8 * j + 2 * k + 1,
+                     k < 3 ? ", " : ");\n");
+        }
+        s += "   } else\n";
         s += "   if ((c.res_out_ld & 7) == 0 && (reinterpret_cast<size_t>(c.res_out) & 15) == 0) {\n"
              "    uint4* d4 = reinterpret_cast<uint4*>(r);\n";
         for (int j = 0; j < O / 8; j++) {

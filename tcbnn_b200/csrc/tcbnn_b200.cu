@@ -425,6 +425,7 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
 }
 
 long long* g_conv_trace = nullptr;   // device buffer for per-role cycle counters, or null
+int g_conv_two_ctas = 1;  // loader-fed kernel, n-tile 64: two CTAs of eight epilogue warps per SM when they fit
 int g_conv_res_stage = 1; // loader-fed kernel: stage int16 residual rows in shared memory when possible
 int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible), 3 = 2 without the activation-stationary kernel
 
@@ -456,30 +457,51 @@ int launch_conv_umma_ws(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t 
     return launch_check("conv_layer (tcgen05)");
 }
 
-template <int NT, int EPI>
-__global__ void __launch_bounds__(umma::kPreThreads, 1) k_conv_umma_pre(umma::ConvWsArgs a) {
+template <int NT, int EPI, int EPIW>
+__global__ void __launch_bounds__(umma::pre_threads(EPIW), EPIW == 8 ? 2 : 1) k_conv_umma_pre(umma::ConvWsArgs a) {
     extern __shared__ __align__(128) unsigned char dyn_smem_pre[];
-    umma::conv_umma_pre_cta<NT, EPI>(a, dyn_smem_pre);
+    umma::conv_umma_pre_cta<NT, EPI, EPIW>(a, dyn_smem_pre);
 }
 __global__ void __launch_bounds__(256) k_expand_raster(umma::ConvWsArgs a, uint4* planes, long long positions,
                                                        long long front) {
     umma::expand_raster(a, planes, positions, front);
 }
 
-template <int NT, int EPI>
+template <int NT, int EPI, int EPIW>
 int launch_conv_umma_pre_k(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
     if (configure_once(configured, [] {
-            return cudaFuncSetAttribute(k_conv_umma_pre<NT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            return cudaFuncSetAttribute(k_conv_umma_pre<NT, EPI, EPIW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        EPIW == 8 ? 113 * 1024 : 227 * 1024);
         }))
         return 1;
     a.ntiles_n = a.O / NT;
     if (a.ntiles_n > sms) return fail("conv_layer: more n-tiles than SMs");
     const long long mtiles = (a.NV + 127) / 128;
-    long long per = sms / a.ntiles_n;
+    long long per = (long long)(EPIW == 8 ? 2 : 1) * sms / a.ntiles_n;    // CTAs per n-tile: one or two per SM
     if (per > mtiles) per = mtiles;
-    k_conv_umma_pre<NT, EPI><<<(int)(per * a.ntiles_n), umma::kPreThreads, smem, st>>>(a);
+    k_conv_umma_pre<NT, EPI, EPIW><<<(int)(per * a.ntiles_n), umma::pre_threads(EPIW), smem, st>>>(a);
     return launch_check("conv_layer (tcgen05, pre-expanded input)");
+}
+
+// n-tile 64, plain epilogue: two CTAs of eight epilogue warps per SM when the filter block and a
+// patch ring of at least three stages fit half of the shared memory.  Measured at batch 1024,
+// 56 x 56 x 64 -> 64: 0.119 ms against 0.154 with one CTA; with residual rows moved directly the
+// two-CTA form loses (0.40 against 0.33: 32 columns of residual per thread spill), so those
+// layers stay on one CTA of sixteen epilogue warps.
+template <int EPI>
+int launch_conv_umma_pre_64(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
+    if (g_conv_two_ctas && (EPI == umma::kEpiPlain || g_conv_two_ctas == 2)) {
+        int stages = a.pre_stages;
+        const int nplane = a.stride == 2 ? 4 : 1;
+        while (stages > 3 && umma::pre_smem_bytes(a.NPOS, a.C, a.R * a.S, 64, stages, nplane) > 113 * 1024) stages--;
+        const size_t need = umma::pre_smem_bytes(a.NPOS, a.C, a.R * a.S, 64, stages, nplane);
+        if (need <= 113 * 1024) {
+            a.pre_stages = stages;
+            return launch_conv_umma_pre_k<64, EPI, 8>(a, need, sms, st);
+        }
+    }
+    return launch_conv_umma_pre_k<64, EPI, 16>(a, smem, sms, st);
 }
 
 // npos, C, RS of the layer are needed to size the patch ring again when the residual rows are staged
@@ -498,9 +520,9 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
         // 0.138, 7 x 7 x 512 0.127 / 0.120, 56 x 56 x 64 (n-tile 64) 0.425 / 0.327 -- the once-per-tile
         // rendezvous of the 16 epilogue warps costs more than the narrow rows save there.
         const int lim = a.res_in ? (a.residual_channels < a.res_in_ch ? a.residual_channels : a.res_in_ch) : 0;
-        const bool in_ok = !a.res_in || (a.res_in_bytes == 2 && !a.residual_pool && a.res_in_ch % 8 == 0 &&
-                                         ((uintptr_t)a.res_in & 15) == 0 && (lim % NT == 0 || lim >= a.O));
-        const bool out_ok = !a.res_out || (a.res_out_bytes == 2 && ((uintptr_t)a.res_out & 15) == 0);
+        const bool in_ok = !a.res_in || (a.res_in_bytes == 2 && !a.res_in_chunked && !a.residual_pool && a.res_in_ch % 8 == 0 &&
+                                         ((uintptr_t)a.res_in & 15) == 0 && lim % 8 == 0);
+        const bool out_ok = !a.res_out || (a.res_out_bytes == 2 && !a.res_out_chunked && ((uintptr_t)a.res_out & 15) == 0);
         if ((a.res_in || a.res_out) && in_ok && out_ok && g_conv_res_stage && (NT >= 128 || g_conv_res_stage == 2)) {
             int stages = a.pre_stages;
             const int RS = a.R * a.S;
@@ -510,12 +532,67 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
             const size_t need = umma::pre_smem_bytes(a.NPOS, a.C, RS, NT, stages, nplane) + umma::pre_res_stage_bytes(NT);
             if (need <= 227 * 1024) {
                 a.pre_stages = stages;
-                return launch_conv_umma_pre_k<NT, umma::kEpiStaged>(a, need, sms, st);
+                return launch_conv_umma_pre_k<NT, umma::kEpiStaged, 16>(a, need, sms, st);
             }
         }
     }
-    if (!a.res_in && !a.res_out && !a.acc_out) return launch_conv_umma_pre_k<NT, umma::kEpiPlain>(a, smem, sms, st);
-    return launch_conv_umma_pre_k<NT, umma::kEpiDirect>(a, smem, sms, st);
+    const bool plain = !a.res_in && !a.res_out && !a.acc_out;
+    if constexpr (NT == 64) {
+        return plain ? launch_conv_umma_pre_64<umma::kEpiPlain>(a, smem, sms, st)
+                     : launch_conv_umma_pre_64<umma::kEpiDirect>(a, smem, sms, st);
+    } else {
+        return plain ? launch_conv_umma_pre_k<NT, umma::kEpiPlain, 16>(a, smem, sms, st)
+                     : launch_conv_umma_pre_k<NT, umma::kEpiDirect, 16>(a, smem, sms, st);
+    }
+}
+
+// The *_bytes arguments of the conv entry points name the residual's element format: 4 = int32
+// NHWC, 2 = int16 NHWC, TCBNN_RES_INT16_CHUNKED = int16 laid out by 8-channel chunk.
+bool residual_format(int code, int* bytes, int* chunked) {
+    *chunked = code == TCBNN_RES_INT16_CHUNKED;
+    *bytes = *chunked ? 2 : code;
+    return code == 2 || code == 4 || code == TCBNN_RES_INT16_CHUNKED;
+}
+
+// 2x2 max of a chunked int16 residual [ch/8][B*2P*2Q][8] -> NHWC [B][P][Q][ch].  A block takes 32
+// consecutive output pixels x all chunks: it reads chunk by chunk (consecutive lanes = consecutive
+// pixels: whole lines), turns the tile through shared memory (16-byte slots XOR-swizzled by pixel),
+// and writes pixel by pixel (consecutive lanes = consecutive chunks of a row: whole lines again).
+constexpr int kPoolChunkedMaxCh8 = 32;
+__global__ void __launch_bounds__(256) k_pool_residual16_chunked(const uint4* in, uint4* out, int B, int P, int Q, int ch8) {
+    __shared__ uint4 tile[32 * kPoolChunkedMaxCh8];
+    const long long npix = (long long)B * P * Q, npix_in = npix * 4;
+    const long long ntiles = (npix + 31) / 32;
+    const int units = 32 * ch8;
+    const int swz = (ch8 & (ch8 - 1)) == 0 ? (ch8 < 8 ? ch8 - 1 : 7) : 0;    // power-of-two chunk counts only
+    for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const long long pix0 = t * 32;
+        for (int u = threadIdx.x; u < units; u += 256) {
+            const int c = u >> 5, pl = u & 31;
+            const long long pix = pix0 + pl;
+            uint4 m = make_uint4(0u, 0u, 0u, 0u);
+            if (pix < npix) {
+                long long r = pix;
+                const int x = (int)(r % Q); r /= Q;
+                const int y = (int)(r % P);
+                const long long n = r / P;
+                const uint4* s0 = in + (long long)c * npix_in + (n * 2 * P + 2 * y) * 2 * Q + 2 * x;
+                const uint4* s1 = s0 + 2 * Q;
+                const uint4 a = __ldg(s0), b = __ldg(s0 + 1), e = __ldg(s1), f = __ldg(s1 + 1);
+                m.x = __vmaxs2(__vmaxs2(a.x, b.x), __vmaxs2(e.x, f.x));
+                m.y = __vmaxs2(__vmaxs2(a.y, b.y), __vmaxs2(e.y, f.y));
+                m.z = __vmaxs2(__vmaxs2(a.z, b.z), __vmaxs2(e.z, f.z));
+                m.w = __vmaxs2(__vmaxs2(a.w, b.w), __vmaxs2(e.w, f.w));
+            }
+            tile[pl * ch8 + (c ^ (pl & swz))] = m;
+        }
+        __syncthreads();
+        for (int u = threadIdx.x; u < units; u += 256) {
+            const int pl = u / ch8, c = u - pl * ch8;
+            if (pix0 + pl < npix) out[(pix0 + pl) * ch8 + c] = tile[pl * ch8 + (c ^ (pl & swz))];
+        }
+        __syncthreads();
+    }
 }
 
 // 2x2 max of an int16 residual [B][2P][2Q][ch] -> [B][P][Q][ch] (kernel.cuh:773-783), 8 channels
@@ -1070,12 +1147,28 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("conv_layer: out_image_stride too small");
     if ((res_out || res_in) && d->pool != 1) return fail("conv_layer: residuals need pool == 1");
     if (res_in && (res_in_ch <= 0 || residual_channels <= 0)) return fail("conv_layer: residual channel counts must be positive");
-    if (res_in && res_in_bytes != 2 && res_in_bytes != 4) return fail("conv_layer: res_in_bytes must be 2 or 4");
-    if (res_out && res_out_bytes != 2 && res_out_bytes != 4) return fail("conv_layer: res_out_bytes must be 2 or 4");
+    int res_in_chunked = 0, res_out_chunked = 0;
+    if (res_in && !residual_format(res_in_bytes, &res_in_bytes, &res_in_chunked))
+        return fail("conv_layer: res_in_bytes must be 2, 4 or TCBNN_RES_INT16_CHUNKED");
+    if (res_out && !residual_format(res_out_bytes, &res_out_bytes, &res_out_chunked))
+        return fail("conv_layer: res_out_bytes must be 2, 4 or TCBNN_RES_INT16_CHUNKED");
+    if (!res_in) res_in_chunked = 0;
+    if (!res_out) res_out_chunked = 0;
     if ((uintptr_t)in & 7) return fail("conv_layer: input must be 8-byte aligned");
     const PreparedLayout L = prepared_layout(d);
     const char* p = (const char*)prepared;
     const bool use_pre = L.pre_bytes && workspace && g_conv_path != 3;
+    if (res_in_chunked || res_out_chunked) {
+        // only the loader-fed kernel reads and writes that layout
+        if (!use_pre || g_conv_path == 1 || d->pool != 1)
+            return fail("conv_layer: chunked residuals need the loader-fed tcgen05 kernel (a layer with tcbnn_conv_planes_bytes != 0, "
+                        "called with its workspace, no pooling)");
+        const int lim_in = residual_channels < res_in_ch ? residual_channels : res_in_ch;
+        if (res_in_chunked && (res_in_ch % 8 || lim_in % 8 || ((uintptr_t)res_in & 15)))
+            return fail("conv_layer: a chunked residual needs channel counts in multiples of 8 and a 16-byte aligned tensor");
+        if (res_out_chunked && (d->O % 8 || ((uintptr_t)res_out & 15)))
+            return fail("conv_layer: a chunked residual needs channel counts in multiples of 8 and a 16-byte aligned tensor");
+    }
     const bool use_as = L.as_npos && g_conv_path != 3 && !use_pre;
     const bool have_tc = use_as || use_pre || L.ws_ok;
     if (g_conv_path >= 2 && !have_tc) return fail("conv_layer: layer is not eligible for the tcgen05 path (or needs its workspace)");
@@ -1108,6 +1201,9 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         umma::fastdiv_setup(a.PW, &a.pw_mul, &a.pw_sh);
         umma::fastdiv_setup(a.VH, &a.vh_mul, &a.vh_sh);
         a.res_in = res_in; a.res_in_bytes = res_in_bytes; a.res_in_ch = res_in_ch;
+        a.res_in_chunked = res_in_chunked; a.res_out_chunked = res_out_chunked;
+        a.res_in_npix = (long long)d->B * d->OH * d->OW * (residual_pool ? 4 : 1);
+        a.res_out_npix = (long long)d->B * d->OH * d->OW;
         a.residual_channels = residual_channels; a.residual_pool = residual_pool;
         a.out = pooled ? prepool : out;
         a.out_image_stride = pooled ? (long long)P * Q * Ow : out_image_stride;
@@ -1149,13 +1245,19 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
             // the room behind the planes: four scattered loads per value in the epilogue cost more
             const size_t pooled_res_bytes = (size_t)d->B * d->OH * d->OW * (size_t)res_in_ch * 2;
             if (res_in && residual_pool && res_in_bytes == 2 && res_in_ch % 8 == 0 && !pooled &&
+                (!res_in_chunked || res_in_ch / 8 <= kPoolChunkedMaxCh8) &&
                 pooled_res_bytes <= L.pool_bytes && workspace_bytes >= planes_padded(L) + pooled_res_bytes) {
                 char* pooled_res = (char*)workspace + planes_padded(L);
                 const long long units = (long long)d->B * d->OH * d->OW * (res_in_ch / 8);
-                k_pool_residual16<<<elementwise_grid(units, sms), 256, 0, st>>>((const uint4*)res_in, (uint4*)pooled_res,
-                                                                             d->B, d->OH, d->OW, res_in_ch / 8);
+                if (res_in_chunked)
+                    k_pool_residual16_chunked<<<elementwise_grid(units, sms), 256, 0, st>>>(
+                        (const uint4*)res_in, (uint4*)pooled_res, d->B, d->OH, d->OW, res_in_ch / 8);   // (res_in_ch / 8 <= 32: checked above)
+                else
+                    k_pool_residual16<<<elementwise_grid(units, sms), 256, 0, st>>>((const uint4*)res_in, (uint4*)pooled_res,
+                                                                                 d->B, d->OH, d->OW, res_in_ch / 8);
                 if (launch_check("conv_layer (residual pooling)")) return 1;
                 a.res_in = pooled_res; a.residual_pool = 0;
+                a.res_in_chunked = 0; a.res_in_npix = (long long)d->B * d->OH * d->OW;     // the pooled copy is NHWC
             }
             if (L.pre_nt == 32) return launch_conv_umma_pre<32>(a, L.pre_smem, sms, st, !workspace_ready);
             if (L.pre_nt == 64) return launch_conv_umma_pre<64>(a, L.pre_smem, sms, st, !workspace_ready);
@@ -1176,6 +1278,8 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
       }
       return 0;
     }
+    if (res_in_chunked || res_out_chunked)
+        return fail("conv_layer: this call cannot take the tcgen05 path it needs for chunked residuals (alignment, residual layout)");
     ConvArgs c;
     c.in = in;
     c.wq = (const uint32_t*)(p + L.off_wq);
@@ -1223,12 +1327,20 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
     return 0;
 }
 
+int tcbnn_conv_prefers_chunked_residual(const tcbnn_conv_desc* d) {
+    if (conv_check(d, true)) return 0;
+    const PreparedLayout L = prepared_layout(d);
+    // the layers whose epilogue moves residual rows directly: n-tile 64 (wider ones stage NHWC rows)
+    return L.pre_nt == 64 && d->pool == 1 && d->O % 8 == 0 ? 1 : 0;
+}
+
 int tcbnn_set_conv_path(int path) {
-    if (path < 0 || path > 5)
+    if (path < 0 || path > 6)
         return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05, 3 = tcgen05 filter-stationary kernel only, "
-                    "4 / 5 = automatic with residual staging never / wherever possible");
+                    "4 / 5 = automatic with residual staging never / wherever possible, 6 = automatic, one CTA per SM only");
     g_conv_path = path >= 4 ? 0 : path;
     g_conv_res_stage = path == 4 ? 0 : path == 5 ? 2 : 1;
+    g_conv_two_ctas = path == 6 ? 0 : 1;
     return 0;
 }
 
@@ -1363,13 +1475,18 @@ int tcbnn_inconv_specialized_layer_x(void* handle, const tcbnn_conv_desc* d, con
         return fail("inconv_specialized_layer: descriptor does not match the one the kernel was built for");
     if ((x != nullptr) == (x8 != nullptr)) return fail("inconv_specialized_layer: give fp32 images or uint8 images");
     if (x8 && !lut) return fail("inconv_specialized_layer: uint8 images need the value table");
-    if (res_out && res_out_bytes != 2 && res_out_bytes != 4) return fail("inconv_specialized_layer: res_out_bytes must be 2 or 4");
+    int res_out_chunked = 0;
+    if (res_out && !residual_format(res_out_bytes, &res_out_bytes, &res_out_chunked))
+        return fail("inconv_specialized_layer: res_out_bytes must be 2, 4 or TCBNN_RES_INT16_CHUNKED");
+    if (res_out && res_out_chunked && (d->O % 8 || d->pool != 1 || ((uintptr_t)res_out & 15)))
+        return fail("inconv_specialized_layer: a chunked residual needs a multiple of 8 channels, no pooling and a 16-byte aligned tensor");
     const int Ow = (d->O + 31) / 32;
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("inconv_specialized_layer: out_image_stride too small");
     spec::SpecArgs c;
     c.x = x; c.x8 = x8; c.lut = lut; c.B = d->B; c.H = d->H; c.W = d->W; c.OH = d->OH; c.OW = d->OW;
     c.out = out; c.out_image_stride = out_image_stride; c.res_out = res_out;
     c.res_out_bytes = res_out_bytes; c.res_out_ld = d->O; c.acc_out = acc_out;
+    c.res_out_chunked = res_out ? res_out_chunked : 0;
     c.total = (unsigned)((long long)d->B * d->OH * d->OW * d->pool * d->pool);
     c.nxt = nullptr; c.nxt_positions = 0; c.nxt_front = 0; c.nxt_PW = 0; c.nxt_VH = 0;
     NextPlanes nx;

@@ -438,7 +438,8 @@ public:
           padding(_padding), bn(NULL), bn_gpu(NULL), batch(_batch), stride_height(_stride_height),
           stride_width(_stride_width), pool_width(_pool_width), pool_height(_pool_height),
           save_residual(_save_residual), output_residual_gpu(NULL), gpu(NULL), fast_handle(NULL),
-          fast_res_bytes(4), fast_res_bound(-1), fast_next(NULL), fast_next_planes(NULL), fast_next_planes_bytes(0) {
+          fast_res_bytes(4), fast_res_bound(-1), fast_next(NULL), fast_next_planes(NULL), fast_next_planes_bytes(0),
+          fast_res_chunked(false), fast_res_consumers(0) {
         strncpy(name, _name, 8);
         tcbnn_dropin::conv_geometry(input_height, input_width, filter_height, filter_width, stride_height,
                                     stride_width, padding, pool_height, pool_width, &pad_h, &pad_w,
@@ -523,8 +524,8 @@ public:
         void* res = save_residual ? (void*)output_residual_gpu : NULL;
         if (fast_handle)
             TCBNN_FAST_CALL(tcbnn_inconv_specialized_layer_x(fast_handle, &fast_desc, input_gpu, NULL, NULL, output_gpu,
-                                                             stride, res, fast_res_bytes, NULL, fast_next, fast_next_planes,
-                                                             fast_next_planes_bytes, stream));
+                                                             stride, res, fast_res_chunked ? TCBNN_RES_INT16_CHUNKED : fast_res_bytes,
+                                                             NULL, fast_next, fast_next_planes, fast_next_planes_bytes, stream));
         else
             TCBNN_FAST_CALL(tcbnn_inconv_layer(&fast_desc, input_gpu, filter_gpu, bn_gpu, output_gpu, stride, res,
                                                fast_res_bytes, NULL, stream));
@@ -584,6 +585,13 @@ public:
     const tcbnn_conv_desc* fast_next;
     void* fast_next_planes;
     size_t fast_next_planes_bytes;
+    // the saved int16 residual in the library's chunk-major layout (TCBNN_RES_INT16_CHUNKED): chosen
+    // by the first layer that injects it, when both sides handle it
+    bool fast_res_chunked;
+    int fast_res_consumers;
+    bool fast_can_write_chunked() const {
+        return fast_handle != NULL && fast_res_bytes == 2 && output_channels % 8 == 0 && pool_height == 1;
+    }
     int max_batch = 0;
 };
 
@@ -605,7 +613,8 @@ public:
           input_residual_gpu(NULL), residual_channels(_residual_channels), residual_pool(_residual_pool),
           prepared_gpu(NULL), input_residual_channels(0), gpu(NULL), fast_ok(false), fast_prepared(NULL),
           fast_planes(NULL), fast_planes_bytes(0), fast_res_in_ch(0), fast_res_in_bytes(4), fast_res_bytes(4),
-          fast_res_bound(-1), fast_next(NULL), fast_next_planes(NULL), fast_next_planes_bytes(0) {
+          fast_res_bound(-1), fast_next(NULL), fast_next_planes(NULL), fast_next_planes_bytes(0),
+          fast_res_chunked(false), fast_res_in_chunked(false), fast_res_consumers(0) {
         strncpy(name, _name, 8);
         tcbnn_dropin::conv_geometry(input_height, input_width, filter_height, filter_width, stride_height,
                                     stride_width, padding, pool_height, pool_width, &pad_h, &pad_w,
@@ -696,15 +705,24 @@ public:
         fast_ok = true;
         long long in_bound = 0;
         if (inject_residual) {
+            // can this layer read a chunk-major residual?  (directly, or through the pooling pass)
+            const bool c_can = pool_height == 1 && tcbnn_conv_planes_bytes(&fast_desc) != 0 &&
+                               (residual_pool || tcbnn_conv_prefers_chunked_residual(&fast_desc));
             tcbnn_dropin::RegisteredLayer r;
             if (!tcbnn_dropin::find_layer(2, input_residual_gpu, &r)) {
                 fast_ok = false;
             } else if (r.kind == tcbnn_dropin::kLayerInConv) {
                 InConv128LayerParam* p = (InConv128LayerParam*)r.host;
                 fast_res_in_ch = p->output_channels; fast_res_in_bytes = p->fast_res_bytes; in_bound = p->fast_res_bound;
+                if (p->fast_res_consumers++ == 0) p->fast_res_chunked = p->fast_can_write_chunked() && c_can;
+                else if (p->fast_res_chunked && !c_can) fast_ok = false;
+                fast_res_in_chunked = p->fast_res_chunked;
             } else {
                 Conv128LayerParam* p = (Conv128LayerParam*)r.host;
                 fast_res_in_ch = p->output_channels; fast_res_in_bytes = p->fast_res_bytes; in_bound = p->fast_res_bound;
+                if (p->fast_res_consumers++ == 0) p->fast_res_chunked = p->fast_can_write_chunked() && c_can;
+                else if (p->fast_res_chunked && !c_can) fast_ok = false;
+                fast_res_in_chunked = p->fast_res_chunked;
             }
         }
         const long long fan = (long long)input_channels * filter_height * filter_width;
@@ -745,11 +763,12 @@ public:
         void* ws = fast_planes ? fast_planes : sc->ptr;
         const size_t wsb = fast_planes ? fast_planes_bytes : sc->bytes;
         TCBNN_FAST_CALL(tcbnn_conv_layer_x(&fast_desc, input_gpu, fast_prepared, bn_gpu,
-                                           inject_residual ? (const void*)input_residual_gpu : NULL, fast_res_in_bytes,
+                                           inject_residual ? (const void*)input_residual_gpu : NULL,
+                                           fast_res_in_chunked ? TCBNN_RES_INT16_CHUNKED : fast_res_in_bytes,
                                            fast_res_in_ch, residual_channels, residual_pool ? 1 : 0, output_gpu,
                                            (long long)image_words(), save_residual ? (void*)output_residual_gpu : NULL,
-                                           fast_res_bytes, NULL, ws, wsb, fast_planes ? 1 : 0, fast_next, fast_next_planes,
-                                           fast_next_planes_bytes, stream));
+                                           fast_res_chunked ? TCBNN_RES_INT16_CHUNKED : fast_res_bytes, NULL, ws, wsb,
+                                           fast_planes ? 1 : 0, fast_next, fast_next_planes, fast_next_planes_bytes, stream));
     }
     // 2 after a forward pass in which a residual value did not fit the int16 rows chosen above
     int fast_status() {
@@ -826,6 +845,13 @@ public:
     const tcbnn_conv_desc* fast_next;   // the consumer whose planes this layer fills
     void* fast_next_planes;
     size_t fast_next_planes_bytes;
+    // chunk-major int16 residual tensors (TCBNN_RES_INT16_CHUNKED): this layer's saved one, chosen by
+    // the first layer that injects it, and the injected one
+    bool fast_res_chunked, fast_res_in_chunked;
+    int fast_res_consumers;
+    bool fast_can_write_chunked() {
+        return save_residual && fast_res_bytes == 2 && pool_height == 1 && tcbnn_conv_prefers_chunked_residual(&fast_desc) != 0;
+    }
     int max_batch = 0;
 };
 

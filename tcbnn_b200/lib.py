@@ -62,7 +62,10 @@ SIGNATURES = {
     "tcbnn_inconv_layer_u8": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_mma_peak": (_I, [_I, _I, _I, C.POINTER(C.c_double)]),
     "tcbnn_wait_probe": (_I, [_I, C.POINTER(C.c_int)]),
+    "tcbnn_conv_prefers_chunked_residual": (_I, [C.POINTER(ConvDesc)]),
 }
+
+RES_INT32, RES_INT16, RES_INT16_CHUNKED = 4, 2, 18      # TCBNN_RES_* of the header
 
 _lib = None
 

@@ -59,6 +59,8 @@ def main():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--residual", action="store_true", help="c2: also save the int32 residual")
+    ap.add_argument("--chunked", action="store_true",
+                    help="conv --residual: int16 residuals in the chunk-major layout (TCBNN_RES_INT16_CHUNKED)")
     ap.add_argument("--no-peak", action="store_true")
     ap.add_argument("--specialized", action="store_true", help="stem: the kernel compiled for the filter")
     a = ap.parse_args()
@@ -137,10 +139,12 @@ def main():
         if a.residual:
             rin = torch.randint(-500, 500, (Bn, d.OH, d.OW, O), dtype=torch.int16, device=dev, generator=g)
             rout = torch.empty((Bn, d.OH, d.OW, O), dtype=torch.int16, device=dev)
+        ch = bool(a.chunked and a.residual)
         ms = _time(lambda: ops.conv_layer(d, x, prep, thr, res_in=rin, residual_channels=O if rin is not None else 0,
-                                          out=out, res_out_buf=rout), a.iters)
+                                          out=out, res_out_buf=rout, res_in_chunked=ch, res_out_chunked=ch), a.iters)
         work = 2.0 * Bn * d.OH * d.OW * O * 9 * C
-        desc = "bit conv %dx%dx%dx%d -> %d, 3x3 stride %d%s" % (Bn, H, H, C, O, st, " + int16 residual in/out" if a.residual else "")
+        desc = "bit conv %dx%dx%dx%d -> %d, 3x3 stride %d%s%s" % (Bn, H, H, C, O, st, " + int16 residual in/out" if a.residual else "",
+                                                                " (chunk-major)" if ch else "")
     else:
         Bn, H, C, O = a.batch, 56, 128, 128
         d = ops.conv_desc(Bn, H, H, C, O, 3, 3)

@@ -262,6 +262,7 @@ class Network:
             prev = obj
         if handover:
             self._wire_handover()
+            self._wire_residual_layouts()
 
     def _wire_handover(self):
         """Consecutive conv layers: where the consumer runs on a pre-expanded input, its producer
@@ -284,6 +285,22 @@ class Network:
                 continue
             prod.next_layer = (cons.desc, planes)
             cons.input_planes = planes
+
+    def _wire_residual_layouts(self):
+        """An int16 residual tensor is kept in the chunk-major layout (TCBNN_RES_INT16_CHUNKED)
+        when the layer that saves it and every layer that injects it move residual rows directly
+        between registers and memory: one thread per pixel then touches whole lines per warp."""
+        consumers = {}
+        for l in self.layers:
+            if type(l).__name__ == "Conv128LayerParam" and l.inject_residual:
+                for p in self.layers:
+                    if getattr(p, "output_residual_gpu", None) is l.input_residual_gpu and p.output_residual_gpu is not None:
+                        consumers.setdefault(id(p), (p, []))[1].append(l)
+        for p, cons in consumers.values():
+            if p.can_write_chunked_residual() and all(c.can_read_chunked_residual() for c in cons):
+                p.residual_chunked = True
+                for c in cons:
+                    c.input_residual_chunked = True
 
     def set_input(self, x):
         self.layers[0].set_input(x)

@@ -163,9 +163,10 @@ def conv_workspace(d, device):
 def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_pool=False,
                out=None, out_image_stride=None, save_residual=False, want_acc=False,
                res_out_buf=None, residual_dtype=torch.int32, workspace=None, workspace_ready=False,
-               next_layer=None):
+               next_layer=None, res_in_chunked=False, res_out_chunked=False):
     """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out).
-    Residual tensors may be torch.int32 or torch.int16.
+    Residual tensors may be torch.int32 or torch.int16; res_in_chunked / res_out_chunked: the
+    int16 tensor is laid out by 8-channel chunk (TCBNN_RES_INT16_CHUNKED, see chunked_to_nhwc).
     workspace: uint8 scratch tensor for tcbnn_conv_layer_w; None = the shared one of
     conv_workspace(); False = none (tcbnn_conv_layer).
     next_layer: (descriptor, planes tensor) of the layer consuming this output: the layer also
@@ -187,10 +188,10 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
     acc_out = torch.empty((d.B, P, Q, d.O), dtype=torch.int32, device=x.device) if want_acc else None
     res_in_ch = res_in.shape[-1] if res_in is not None else 0
     args = (C.byref(d), _ptr(x), _ptr(prepared), _ptr(thr), _ptr(res_in),
-            res_in.element_size() if res_in is not None else 4,
+            _residual_code(res_in, res_in_chunked),
             res_in_ch, residual_channels, int(bool(residual_pool)), _ptr(out),
             C.c_longlong(stride), _ptr(res_out),
-            res_out.element_size() if res_out is not None else 4, _ptr(acc_out))
+            _residual_code(res_out, res_out_chunked), _ptr(acc_out))
     if next_layer is not None or workspace_ready:
         nd, npl = next_layer if next_layer is not None else (None, None)
         _l.call("tcbnn_conv_layer_x", *args, _ptr(workspace),
@@ -202,6 +203,35 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
     else:
         _l.call("tcbnn_conv_layer", *args, _stream())
     return out, res_out, acc_out
+
+
+def _residual_code(t, chunked):
+    """The *_bytes argument of the conv entry points for a residual tensor."""
+    if t is None:
+        return 4
+    if chunked:
+        if t.dtype != torch.int16:
+            raise _l.TcbnnError("chunked residuals are int16")
+        return _l.RES_INT16_CHUNKED
+    return t.element_size()
+
+
+def conv_prefers_chunked_residual(d):
+    """True for layers whose epilogue is fastest on residual tensors laid out by 8-channel chunk."""
+    return bool(_l.load().tcbnn_conv_prefers_chunked_residual(C.byref(d)))
+
+
+def chunked_to_nhwc(t):
+    """A [B][P][Q][ch] int16 tensor whose memory holds the chunk-major layout [ch/8][B*P*Q][8]
+    (TCBNN_RES_INT16_CHUNKED) -> the same values as a proper NHWC tensor."""
+    B, P, Q, ch = t.shape
+    return t.reshape(ch // 8, B * P * Q, 8).permute(1, 0, 2).reshape(B, P, Q, ch).contiguous()
+
+
+def nhwc_to_chunked(t):
+    """The inverse: NHWC values -> a tensor of the same shape whose memory is chunk-major."""
+    B, P, Q, ch = t.shape
+    return t.reshape(B * P * Q, ch // 8, 8).permute(1, 0, 2).contiguous().reshape(B, P, Q, ch)
 
 
 def new_planes_bytes(d):
@@ -246,7 +276,7 @@ def inconv_specialize(d, filter_bits, thr):
 
 def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_residual=False,
                  want_acc=False, res_out_buf=None, residual_dtype=torch.int32, lut=None,
-                 specialized=None, next_layer=None):
+                 specialized=None, next_layer=None, res_out_chunked=False):
     """x: fp32 [B][3][H][W], or uint8 [B][3][H][W] together with lut (fp32 [3][256], the value
     of every byte per channel).  specialized: an InconvSpecialized built from the same filter
     and thresholds (filter_bits and thr are then not read).  Returns (out_bits, res_out, acc_out)."""
@@ -270,7 +300,7 @@ def inconv_layer(d, x, filter_bits, thr, out=None, out_image_stride=None, save_r
         _l.call("tcbnn_inconv_specialized_layer_x", specialized.handle, C.byref(d),
                 None if u8 else _ptr(x), _ptr(x) if u8 else None, _ptr(lut), _ptr(out),
                 C.c_longlong(stride), _ptr(res_out),
-                res_out.element_size() if res_out is not None else 4, _ptr(acc_out),
+                _residual_code(res_out, res_out_chunked), _ptr(acc_out),
                 C.byref(nd) if nd is not None else None, _ptr(npl),
                 C.c_size_t(npl.numel() if npl is not None else 0), _stream())
     elif lut is not None:

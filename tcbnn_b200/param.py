@@ -60,6 +60,13 @@ def _residual_dtype(bound):
     return torch.int16 if (bound is not None and bound <= 32767) else torch.int32
 
 
+def _live_chunked(t, live):
+    """A residual buffer sized for the constructor's batch that holds the chunk-major layout of the
+    first `live` images: the view whose memory is exactly that layout."""
+    B, P, Q, ch = t.shape
+    return t.reshape(-1)[:live * P * Q * ch].reshape(live, P, Q, ch)
+
+
 def _dev():
     if not torch.cuda.is_available():
         raise RuntimeError("tcbnn_b200 needs a CUDA device; there is no CPU path")
@@ -270,6 +277,22 @@ class InConv128LayerParam:
         return self
 
     next_layer = None      # (consumer's descriptor, its planes): see Conv128LayerParam
+    # The saved int16 residual is laid out by 8-channel chunk (TCBNN_RES_INT16_CHUNKED) instead of
+    # NHWC: set by models.Network when this layer and the residual's consumers all handle it.
+    residual_chunked = False
+
+    def can_write_chunked_residual(self):
+        d = self.desc
+        return (self.specialized is not None and self.output_residual_gpu is not None and
+                self.output_residual_gpu.dtype == torch.int16 and d.O % 8 == 0 and d.pool == 1)
+
+    def download_output_residual(self):
+        """The saved residual as int32 NHWC [B][P][Q][O] on the host, whatever its device layout."""
+        d = self.desc
+        t = self.output_residual_gpu
+        if self.residual_chunked:
+            t = ops.chunked_to_nhwc(_live_chunked(t, d.B))
+        return t[:d.B].cpu().numpy().astype(np.int32)
 
     def set_batch(self, n):
         """Process the first n images from now on (n <= the constructor's batch); the compiled
@@ -289,7 +312,8 @@ class InConv128LayerParam:
         ops.inconv_layer(self.desc, self.input_gpu, self.filter_gpu, self.bn_gpu, out=self.output_gpu,
                          res_out_buf=self.output_residual_gpu, lut=self.input_lut_gpu,
                          specialized=self.specialized,
-                         next_layer=self.next_layer if self.specialized is not None else None)
+                         next_layer=self.next_layer if self.specialized is not None else None,
+                         res_out_chunked=self.residual_chunked)
 
     def get_output_gpu(self):
         return self.output_gpu
@@ -384,6 +408,29 @@ class Conv128LayerParam:
     # layer's planes when its producer fills them.
     next_layer = None
     input_planes = None
+    # chunk-major int16 residual tensors (TCBNN_RES_INT16_CHUNKED), wired by models.Network
+    residual_chunked = False            # this layer's saved residual
+    input_residual_chunked = False      # the injected one
+
+    def can_write_chunked_residual(self):
+        return (self.output_residual_gpu is not None and self.output_residual_gpu.dtype == torch.int16 and
+                ops.conv_prefers_chunked_residual(self.desc) and self.has_workspace())
+
+    def can_read_chunked_residual(self):
+        if self.desc.pool != 1 or not self.has_workspace() or ops.new_planes_bytes(self.desc) == 0:
+            return False
+        return bool(self.residual_pool) or ops.conv_prefers_chunked_residual(self.desc)
+
+    def has_workspace(self):
+        return ops.conv_workspace(self.desc, self.input_gpu.device) is not None
+
+    def download_output_residual(self):
+        """The saved residual as int32 NHWC [B][P][Q][O] on the host, whatever its device layout."""
+        d = self.desc
+        t = self.output_residual_gpu
+        if self.residual_chunked:
+            t = ops.chunked_to_nhwc(_live_chunked(t, d.B))
+        return t[:d.B].cpu().numpy().astype(np.int32)
 
     def kernel_launches(self):
         """Kernels one forward() launches: a layer that runs on a pre-expanded input launches the
@@ -402,7 +449,9 @@ class Conv128LayerParam:
                        out=self.output_gpu, out_image_stride=self.out_image_stride,
                        res_out_buf=self.output_residual_gpu,
                        workspace=self.input_planes, workspace_ready=self.input_planes is not None,
-                       next_layer=self.next_layer)
+                       next_layer=self.next_layer,
+                       res_in_chunked=self.input_residual_chunked and self.inject_residual,
+                       res_out_chunked=self.residual_chunked)
 
     def get_output_gpu(self):
         return self.output_gpu

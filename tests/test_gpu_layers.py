@@ -513,3 +513,74 @@ def test_bounded_wait_gives_up_and_the_context_stays_usable(cuda):
     assert ops.conv_status(d, prep) == 0
     lib.call("tcbnn_wait_probe", 1 << 10, C.byref(st))       # and once more after real work
     assert st.value == 1
+
+
+CHUNKED_CASES = [
+    # B, H, W, C, O, residual: "plain" (same grid) or "pool" (2x2 max of a [2H][2W][O/2] tensor)
+    (3, 9, 11, 64, 64, "plain"),        # n-tile 64: the direct epilogue, two images straddle tiles
+    (2, 56, 56, 64, 64, "plain"),
+    (5, 6, 6, 128, 64, "plain"),
+    (2, 8, 8, 128, 128, "pool"),        # pooled chunked input through the pooling pass, NHWC output
+    (2, 7, 9, 64, 64, "pool"),          # pooled chunked input read in the epilogue when there is no room ... or the pass
+]
+
+
+@pytest.mark.parametrize("case", CHUNKED_CASES)
+def test_conv_layer_chunked_int16_residuals(cuda, case):
+    """int16 residual tensors laid out by 8-channel chunk (TCBNN_RES_INT16_CHUNKED) in and out of
+    the loader-fed kernel: same values as the oracle's NHWC tensors; calls that cannot honour the
+    layout fail instead of misreading it."""
+    B, H, W, C, O, mode = case
+    g = util.rng(sum(case[:5]) + 5)
+    Cw = C // 32
+    x = util.rand_words(g, (B, H, W, Cw))
+    f = util.rand_words(g, (O, 9, Cw))
+    thr = (g.standard_normal(O) * np.sqrt(C * 9) * 0.5).astype(np.float32)
+    if mode == "plain":
+        res_in = g.integers(-300, 300, size=(B, H, W, O)).astype(np.int32)
+        rc, rpool = O, False
+    else:
+        res_in = g.integers(-300, 300, size=(B, 2 * H, 2 * W, O // 2)).astype(np.int32)
+        rc, rpool = O // 2, True
+    eo, er, _ = orc.conv_layer(x, f, thr, C, 3, 3, 1, 1, True, 1, res_in=res_in, residual_channels=rc,
+                               residual_pool=rpool, save_residual=True)
+    d = ops.conv_desc(B, H, W, C, O, 3, 3)
+    prep = ops.conv_prepare(d, dev(f, cuda))
+    r16 = ops.nhwc_to_chunked(dev(res_in.astype(np.int16), cuda))
+    out_chunked = ops.conv_prefers_chunked_residual(d)
+    go, gr, _ = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16, residual_channels=rc,
+                               residual_pool=rpool, save_residual=True, residual_dtype=torch.int16,
+                               res_in_chunked=True, res_out_chunked=out_chunked)
+    assert ops.conv_status(d, prep) == 0
+    if out_chunked:
+        gr = ops.chunked_to_nhwc(gr)
+    assert np.array_equal(gr.cpu().numpy().astype(np.int32), er)
+    assert np.array_equal(host_u32(go), eo)
+    if rpool:
+        # a workspace with room for the planes only: no pooling pass, the epilogue takes the 2x2
+        # maximum from the chunked tensor itself
+        ws = torch.zeros((ops.new_planes_bytes(d),), dtype=torch.uint8, device=cuda)
+        go, gr, _ = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16, residual_channels=rc,
+                                   residual_pool=True, save_residual=True, residual_dtype=torch.int16,
+                                   res_in_chunked=True, workspace=ws)
+        assert np.array_equal(gr.cpu().numpy().astype(np.int32), er) and np.array_equal(host_u32(go), eo)
+    # without its workspace the layer runs on a kernel that does not know the layout: refused
+    with pytest.raises(Exception):
+        ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16, residual_channels=rc, residual_pool=rpool,
+                       workspace=False, res_in_chunked=True)
+
+
+def test_specialized_first_layer_writes_chunked_residual(cuda):
+    g = util.rng(123)
+    B, H = 3, 36
+    d = ops.conv_desc(B, H, H, 3, 64, 7, 7, 4, 4)
+    x = g.standard_normal((B, 3, H, H)).astype(np.float32)
+    F = util.rand_pm1(g, (49, 3, 64))
+    thr = (g.standard_normal(64) * 6).astype(np.float32)
+    fb = ops.pack_inconv_filter(dev(F, cuda))
+    spec = ops.inconv_specialize(d, fb, dev(thr, cuda))
+    _, r_nhwc, _ = ops.inconv_layer(d, dev(x, cuda), fb, dev(thr, cuda), save_residual=True,
+                                    residual_dtype=torch.int16, specialized=spec)
+    _, r_chunk, _ = ops.inconv_layer(d, dev(x, cuda), fb, dev(thr, cuda), save_residual=True,
+                                     residual_dtype=torch.int16, specialized=spec, res_out_chunked=True)
+    assert torch.equal(ops.chunked_to_nhwc(r_chunk), r_nhwc)

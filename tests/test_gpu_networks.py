@@ -22,10 +22,9 @@ def _compare(spec, seed, cuda, input_abs_bound=None):
             got = got.view(np.uint32)
             assert np.array_equal(got.reshape(a.shape), a), "layer %d %s bits" % (i, layer.name)
         if r is not None:
-            gr = layer.get_output_residual_gpu()
             if input_abs_bound is not None:
-                assert gr.dtype == torch.int16
-            gr = gr.cpu().numpy().astype(np.int32)
+                assert layer.get_output_residual_gpu().dtype == torch.int16
+            gr = layer.download_output_residual()          # int32 NHWC whatever the device layout
             assert np.array_equal(gr, r), "layer %d %s residual" % (i, layer.name)
     ref = acts[-1]
     got = logits.cpu().numpy()
@@ -65,6 +64,18 @@ def test_resnet18_224(cuda):
 def test_resnet18_224_int16_residuals(cuda):
     # same network with the stated input bound: residual chain stored as int16, values identical
     _compare(models.resnet18_spec(3), 31, cuda, input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND)
+
+
+def test_resnet18_chunked_residual_layout_is_wired_where_it_pays(cuda):
+    """With int16 residuals the three 56 x 56 x 64 residual tensors (first layer -> L1B1C2 -> L1B2C2
+    -> pooled into L2B1C2) are kept in the chunk-major layout; the wider ones stay NHWC."""
+    spec = models.resnet18_spec(2)
+    net = models.Network(spec, models.synthetic_weights(spec, 32), models.synthetic_input(spec, 33),
+                         input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND)
+    by = {l.name: l for l in net.layers}
+    assert by["Conv1"].residual_chunked and by["L1B1C2"].residual_chunked and by["L1B2C2"].residual_chunked
+    assert by["L1B1C2"].input_residual_chunked and by["L1B2C2"].input_residual_chunked and by["L2B1C2"].input_residual_chunked
+    assert not by["L2B1C2"].residual_chunked and not by["L3B2C2"].residual_chunked
 
 
 def test_resnet18_both_conv_kernels(cuda):
@@ -158,7 +169,7 @@ def test_set_batch_runs_ragged_batches_on_the_same_objects(cuda, which):
             got = layer.get_output_gpu()[:n].cpu().numpy().view(np.uint32)
             assert np.array_equal(got.reshape(a.shape), a), "batch %d layer %d %s bits" % (n, i, layer.name)
             if r is not None:
-                gr = layer.get_output_residual_gpu()[:n].cpu().numpy().astype(np.int32)
+                gr = layer.download_output_residual()
                 assert np.array_equal(gr, r), "batch %d layer %d %s residual" % (n, i, layer.name)
         np.testing.assert_allclose(logits, acts[-1], rtol=1e-5, atol=1e-5)
     with pytest.raises(ValueError):
