@@ -41,8 +41,8 @@ int tcbnn_pack_conv_filter(const float* F, int RS, int C, int O, uint32_t* out, 
 int tcbnn_pack_inconv_filter(const float* F, int RS, int O, uint32_t* out, void* stream);
 
 /* Scratch a GEMM-family call can use: partial sums to split K when M x N alone leaves SMs idle
- * and, for large problems (M >= 128, N >= 64, K >= 2048, M*N*K >= 2^31), both operands written
- * out as +-1 bytes for the tcgen05 int8 kernel (csrc/bgemm_umma.cuh), which is then used.
+ * and, for large problems (M >= 128, N >= 64, 512 <= K < 2^22, M*N*K >= 2^30), both operands
+ * written out as +-1 4-bit values for the tcgen05 kernel (csrc/bgemm_umma.cuh), which is then used.
  * Passing NULL / 0 is always allowed (warp-level b1 MMA kernel, no split); the buffer must be
  * 256-byte aligned for the tcgen05 kernel to be taken. */
 size_t tcbnn_gemm_workspace_bytes(int M, int N, int K);
@@ -53,8 +53,16 @@ size_t tcbnn_gemm_workspace_bytes(int M, int N, int K);
  * counterparts. */
 int tcbnn_set_gemm_path(int path);
 int tcbnn_gemm_status(int* status);
+/* Overrides what the tcgen05 GEMM derives from its cost model: `pair` 1 = CTAs own 256 x 128
+ * tiles, 0 = 128 x 128, -1 = automatic; `splits` 1..32 = that many slices of K (1: the GEMM's own
+ * epilogue finishes the layer; more: int32 partial sums and a finishing pass), -1 = automatic.
+ * A forced plan also waives the M*N*K >= 2^30 rule.  A workspace sized by
+ * tcbnn_gemm_workspace_bytes AFTER this call fits the forced plan.
+ * Process-wide; for tests and measurements.  No reference counterpart. */
+int tcbnn_set_gemm_plan(int pair, int splits);
 /* How many kernels a GEMM-family call of this shape launches when given a workspace of that size
- * (1, 2 with split K, 4 on the tcgen05 path); for callers that account for their launches. */
+ * (warp-level kernel: 1, or 2 with split K; tcgen05 path: 2 = operand expansion and a GEMM that
+ * finishes the layer, 3 with split K); for callers that account for their launches. */
 int tcbnn_gemm_launches(int M, int N, int K, size_t workspace_bytes);
 
 /* GEMM family (the next three entry points): the pad bits of every row of A and of B / W -- the
@@ -184,7 +192,11 @@ int tcbnn_set_conv_path(int path);
  * while `device_buffer` (at least 16 int64, device memory) is set, CTA 0 of every tcgen05 conv
  * launch writes cycle counters: [0] expander total, [1] expander waiting for a free stage,
  * [2] stages, [3] MMA issuer total, [4] waiting for a free accumulator, [5] waiting for a full
- * stage, [6] epilogue total, [7] waiting for a full accumulator, [8] tiles.  NULL turns it off. */
+ * stage, [6] epilogue total, [7] waiting for a full accumulator, [8] tiles; CTA 0 of every
+ * tcgen05 GEMM launch writes [9] the CTA from entry to exit, [10] loader waiting for a free stage,
+ * [11] MMA issuer total, [12] waiting for a full stage, [13] epilogue waiting for the accumulator,
+ * [14] k-blocks, [15] epilogue after the accumulator arrived.
+ * NULL turns it off. */
 int tcbnn_conv_set_trace(void* device_buffer);
 /* Reads the layer's device-side status word (synchronises): 0 = fine, 1 = a bounded wait inside
  * the tcgen05 kernel gave up and the layer's output is not valid, 2 = a residual value did not
@@ -291,6 +303,14 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops);
  * Synchronises.  The device context stays usable (the next call works as usual).  The reference has
  * no counterpart: its error handling is exit() on a failed CUDA call (utility.h:57-101). */
 int tcbnn_wait_probe(int polls, int* status);
+/* Measurement aid: `ctas` CTAs (one per SM up to the SM count) each run `iters` rounds in which
+ * one thread of each of `warps` warps issues `depth` bulk copies (cp.async.bulk, global -> shared,
+ * completion on an mbarrier) of `bytes` back to back over an L2-resident buffer and then waits for
+ * them.  Returns, for the slowest CTA, the clocks an issuing thread spent per copy and the bytes
+ * per SM clock over issue + wait -- what the loaders of the tcgen05 kernels can be fed with.
+ * Allocates and frees its buffer; every wait is bounded.  No reference counterpart. */
+int tcbnn_bulk_copy_rate(int bytes, int depth, int warps, int ctas, int iters, double* issue_clocks_per_copy,
+                         double* bytes_per_clock);
 
 #ifdef __cplusplus
 }

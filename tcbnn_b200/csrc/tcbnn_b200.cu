@@ -14,6 +14,7 @@
 #include <cstring>
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 using namespace tcbnn;
 
@@ -137,41 +138,72 @@ int gemm_splits(int M, int N, int K, int sms) {
 }
 
 // ---- tcgen05 bit GEMM (bgemm_umma.cuh) -----------------------------------------------------
+long long* g_conv_trace = nullptr;   // device buffer for per-role cycle counters, or null
+int g_gemm_force_pair = -1, g_gemm_force_splits = -1;   // tcbnn_set_gemm_plan: -1 = from the model
 __device__ int g_gemm_status;        // 1 after a bounded wait inside k_gemm_umma gave up
 
-__global__ void __launch_bounds__(256) k_expand_rows(const uint32_t* bits, int rows, int ld, int K, int RT, int KB,
-                                                     uint4* out) {
-    umma::expand_rows(bits, rows, ld, K, RT, KB, out);
+__global__ void __launch_bounds__(256) k_expand_rows(const uint32_t* a_bits, int a_rows, int a_ld, int RT_a,
+                                                     const uint32_t* w_bits, int w_rows, int w_ld, int RT_w,
+                                                     int K, int KB, uint4* out_a, uint4* out_w) {
+    umma::expand_rows_pair(a_bits, a_rows, a_ld, RT_a, w_bits, w_rows, w_ld, RT_w, K, KB, out_a, out_w);
 }
+template <bool PAIR>
 __global__ void __launch_bounds__(umma::kGemmThreads, 1) k_gemm_umma(umma::GemmUmmaArgs g) {
     extern __shared__ __align__(128) unsigned char dyn_smem_gemm[];
-    umma::gemm_umma_cta(g, dyn_smem_gemm);
+    umma::gemm_umma_cta<PAIR>(g, dyn_smem_gemm);
 }
 
 struct GemmUmmaPlan {
     bool use;
+    bool pair;            // 256 x 128 tiles (two sub-tiles of A per CTA) instead of 128 x 128
+    int stages;           // ring depth; fixes the dynamic shared memory and with it the CTAs per SM
     int MT, NT, KB, splits, per;
     size_t off_ea, off_ew, off_partial, bytes;
 };
 
-// The tcgen05 path pays two expansion passes and a finishing pass: worth it for large problems.
+// Tile shape and split count of the tcgen05 path from a clock model of its launches, calibrated
+// on the kernel's own cycle counters (tcbnn_conv_set_trace): a k-block costs a lone 128 x 128 CTA
+// about 150 clocks, each of two such CTAs sharing an SM 250, a 256 x 128 CTA 180 (the loads, not
+// the MMAs, set the pace); set-up and epilogue cost a CTA 6500, 8000 and 11000 clocks; more than
+// one split adds the finishing launch and the partial sums' round trip.
 GemmUmmaPlan gemm_umma_plan(int M, int N, int K, int sms) {
     GemmUmmaPlan p = {};
-    // (measured: 8192x1024x1024 is faster on the b1 kernel, 1024x1024x4096 and up on this one)
-    p.use = M >= 128 && N >= 64 && K >= 2048 && (long long)M * N * K >= (1LL << 31);
+    // below 2^30 multiply-adds the single launch of the warp-level kernel wins (measured; a plan
+    // forced through tcbnn_set_gemm_plan waives that); the fp32 accumulators hold K exactly up to 2^22
+    const bool forced = g_gemm_force_pair >= 0 || g_gemm_force_splits > 0;
+    p.use = M >= 128 && N >= 64 && K >= 512 && K < (1 << 22) && ((long long)M * N * K >= (1LL << 30) || forced);
     if (!p.use) return p;
     p.MT = (M + 127) / 128; p.NT = (N + 127) / 128; p.KB = (K + 63) / 64;
-    const int tiles = ((p.MT + 1) / 2) * p.NT;
-    int splits = sms / tiles;
-    if (splits < 1) splits = 1;
-    if (splits > p.KB / 4) splits = p.KB / 4;           // at least 4 k-blocks per split
-    if (splits < 1) splits = 1;
-    p.per = (p.KB + splits - 1) / splits;
-    p.splits = (p.KB + p.per - 1) / p.per;              // no empty split
+    double best = 1e30;
+    for (int pair = 0; pair < 2; pair++) {
+        if (g_gemm_force_pair >= 0 && pair != g_gemm_force_pair) continue;
+        if (pair && p.MT < 2 && g_gemm_force_pair < 0) continue;
+        const long long tiles = (long long)(pair ? (p.MT + 1) / 2 : p.MT) * p.NT;
+        for (int want = 1; want <= 32 && (want <= (p.KB + 3) / 4 || g_gemm_force_splits > 0); want++) {
+            const int per = (p.KB + want - 1) / want;
+            const int splits = (p.KB + per - 1) / per;                    // no empty split
+            if (splits != want && want > 1) continue;
+            if (g_gemm_force_splits > 0 && want != (g_gemm_force_splits < p.KB ? g_gemm_force_splits : p.KB)) continue;
+            const long long ctas = tiles * splits;
+            const bool shared_sm = !pair && ctas > sms;                   // two 128 x 128 CTAs per SM
+            const long long resident = (long long)sms * (shared_sm ? 2 : 1);
+            const long long waves = (ctas + resident - 1) / resident;
+            const double kblock = pair ? 180.0 : (shared_sm ? 250.0 : 150.0);
+            const double fixed = pair ? 11000.0 : (shared_sm ? 8000.0 : 6500.0);
+            double clk = (double)waves * (per * kblock + fixed);
+            if (splits > 1) clk += 12000.0 + 6.0 * splits * (double)M * N * 4.0 / 3000.0;
+            if (clk < best) { best = clk; p.pair = pair != 0; p.splits = splits; p.per = per; }
+        }
+    }
+    if (p.splits < 1) { p.use = false; return p; }      // a forced plan no slicing of K gives
+    {
+        const long long ctas = (long long)(p.pair ? (p.MT + 1) / 2 : p.MT) * p.NT * p.splits;
+        p.stages = p.pair ? 4 : (ctas > sms ? 3 : 6);
+    }
     size_t o = 0;
     p.off_ea = o;      o += (size_t)p.MT * p.KB * umma::kGemmUnit;  o = (o + 255) & ~(size_t)255;
     p.off_ew = o;      o += (size_t)p.NT * p.KB * umma::kGemmUnit;  o = (o + 255) & ~(size_t)255;
-    p.off_partial = o; o += (size_t)p.splits * M * N * sizeof(int32_t);
+    p.off_partial = o; o += p.splits > 1 ? (size_t)p.splits * M * N * sizeof(int32_t) : 0;
     p.bytes = o;
     return p;
 }
@@ -179,19 +211,24 @@ GemmUmmaPlan gemm_umma_plan(int M, int N, int K, int sms) {
 int run_gemm_umma(const GemmArgs& g, const GemmUmmaPlan& p, void* workspace, int sms, cudaStream_t st) {
     static bool configured[64] = {false};
     if (configure_once(configured, [] {
-            return cudaFuncSetAttribute(k_gemm_umma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)umma::kGemmSmem);
+            cudaError_t e = cudaFuncSetAttribute(k_gemm_umma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)umma::gemm_smem(true, 4));
+            if (e != cudaSuccess) return e;
+            return cudaFuncSetAttribute(k_gemm_umma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)umma::gemm_smem(false, 6));
         }))
         return 1;
     char* w = (char*)workspace;
-    k_expand_rows<<<elementwise_grid((long long)p.MT * p.KB * 512, sms), 256, 0, st>>>(g.A, g.M, g.lda, g.K, p.MT, p.KB,
-                                                                                     (uint4*)(w + p.off_ea));
-    k_expand_rows<<<elementwise_grid((long long)p.NT * p.KB * 512, sms), 256, 0, st>>>(g.W, g.N, g.ldw, g.K, p.NT, p.KB,
-                                                                                     (uint4*)(w + p.off_ew));
+    k_expand_rows<<<elementwise_grid((long long)(p.MT + p.NT) * p.KB * 256, sms), 256, 0, st>>>(
+        g.A, g.M, g.lda, p.MT, g.W, g.N, g.ldw, p.NT, g.K, p.KB, (uint4*)(w + p.off_ea), (uint4*)(w + p.off_ew));
     if (launch_check("gemm (operand expansion)")) return 1;
     umma::GemmUmmaArgs a;
     a.ea = (const unsigned char*)(w + p.off_ea); a.ew = (const unsigned char*)(w + p.off_ew);
     a.M = g.M; a.N = g.N; a.KB = p.KB; a.MT = p.MT; a.NT = p.NT; a.splits = p.splits; a.per = p.per;
-    a.partial = (int32_t*)(w + p.off_partial);
+    a.partial = p.splits > 1 ? (int32_t*)(w + p.off_partial) : nullptr;
+    a.mode = g.mode; a.out = g.out; a.ldo = g.ldo; a.p0 = g.p0; a.p1 = g.p1;
+    a.trace = g_conv_trace;
+    a.nst = p.stages;
     {
         static int* status_addr[64] = {nullptr};
         int dev = 0;
@@ -206,8 +243,12 @@ int run_gemm_umma(const GemmArgs& g, const GemmUmmaPlan& p, void* workspace, int
             a.status = status_addr[dev];
         }
     }
-    k_gemm_umma<<<((p.MT + 1) / 2) * p.NT * p.splits, umma::kGemmThreads, umma::kGemmSmem, st>>>(a);
+    if (p.pair)
+        k_gemm_umma<true><<<((p.MT + 1) / 2) * p.NT * p.splits, umma::kGemmThreads, umma::gemm_smem(true, p.stages), st>>>(a);
+    else
+        k_gemm_umma<false><<<p.MT * p.NT * p.splits, umma::kGemmThreads, umma::gemm_smem(false, p.stages), st>>>(a);
     if (launch_check("gemm (tcgen05)")) return 1;
+    if (p.splits == 1) return 0;                         // the GEMM's epilogue finished the layer
     GemmArgs f = g;
     f.K = 0;                                             // the partial sums are already K - 2*popc
     f.splits = p.splits;
@@ -424,7 +465,6 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
     return launch_check("inconv_layer (tiled)");
 }
 
-long long* g_conv_trace = nullptr;   // device buffer for per-role cycle counters, or null
 int g_conv_two_ctas = 1;  // loader-fed kernel, n-tile 64: two CTAs of eight epilogue warps per SM when they fit
 int g_conv_res_stage = 1; // loader-fed kernel: stage int16 residual rows in shared memory when possible
 int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible), 3 = 2 without the activation-stationary kernel
@@ -868,6 +908,45 @@ __global__ void __launch_bounds__(128) k_wait_probe(int polls, int* status, int*
     if (threadIdx.x < 32) umma::tmem_dealloc(tm, 32);
 }
 
+// ---- how fast one SM pulls bulk copies out of L2 ---------------------------------------------
+// Each CTA runs `iters` rounds over its own part of an L2-resident buffer: lane 0 of each of its
+// `warps` warps issues `depth` bulk copies of `bytes` back to back into that warp's ring in shared
+// memory, then waits for all of them.  Reports per CTA the clocks warp 0 spent issuing and its
+// clocks in total.  Every wait is bounded.
+__global__ void __launch_bounds__(128) k_bulk_probe(const unsigned char* src, int bytes, int depth, int warps,
+                                                    int iters, long long* clocks, int* status) {
+    extern __shared__ __align__(128) unsigned char probe_smem[];
+    __shared__ uint64_t bars[4][16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < 4; w++)
+            for (int s = 0; s < 16; s++) umma::mbar_init(umma::smem_u32(&bars[w][s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    umma::fence_proxy_async();
+    __syncthreads();
+    if (warp < warps && lane == 0) {
+        const size_t span = (size_t)bytes * depth * 8;                 // this warp's window of the buffer
+        const unsigned char* mine = src + ((size_t)blockIdx.x * warps + warp) * span;
+        unsigned char* ring = probe_smem + (size_t)warp * depth * bytes;
+        bool ok = true;
+        long long issue = 0, total = 0;
+        for (int i = 0; i < iters && ok; i++) {
+            const long long t0 = clock64();
+            for (int s = 0; s < depth; s++) {
+                umma::mbar_expect_tx(umma::smem_u32(&bars[warp][s]), (uint32_t)bytes);
+                umma::bulk_g2s(umma::smem_u32(ring + (size_t)s * bytes), mine + (size_t)((i & 7) * depth + s) * bytes,
+                               (uint32_t)bytes, umma::smem_u32(&bars[warp][s]));
+            }
+            const long long t1 = clock64();
+            for (int s = 0; s < depth && ok; s++) ok = umma::mbar_wait(umma::smem_u32(&bars[warp][s]), i & 1, status);
+            issue += t1 - t0;
+            total += clock64() - t0;
+        }
+        if (warp == 0) { clocks[2 * blockIdx.x] = issue; clocks[2 * blockIdx.x + 1] = total; }
+    }
+}
+
 // ---- fixed scratch for callers that cannot allocate ---------------------------------------
 // Split-K partial sums for tcbnn_fc_layer_noalloc live in this array instead of a caller
 // workspace.  It is part of the loaded module: every GPU that loads the library keeps these
@@ -971,7 +1050,7 @@ int tcbnn_gemm_launches(int M, int N, int K, size_t workspace_bytes) {
     int sms;
     if (M <= 0 || N <= 0 || K <= 0 || sm_count(&sms)) return 0;
     const GemmUmmaPlan plan = gemm_umma_plan(M, N, K, sms);
-    if (plan.use && g_gemm_path != 1 && workspace_bytes >= plan.bytes) return 4;   // 2 expansions, GEMM, finish
+    if (plan.use && g_gemm_path != 1 && workspace_bytes >= plan.bytes) return plan.splits > 1 ? 3 : 2;   // expansion, GEMM, finish
     const int s = gemm_splits(M, N, K, sms);
     return (s > 1 && workspace_bytes >= (size_t)s * M * N * sizeof(int32_t)) ? 2 : 1;
 }
@@ -979,6 +1058,14 @@ int tcbnn_gemm_launches(int M, int N, int K, size_t workspace_bytes) {
 int tcbnn_set_gemm_path(int path) {
     if (path < 0 || path > 1) return fail("set_gemm_path: 0 = automatic, 1 = warp-level b1 MMA only");
     g_gemm_path = path;
+    return 0;
+}
+
+int tcbnn_set_gemm_plan(int pair, int splits) {
+    if (pair < -1 || pair > 1 || splits < -1 || splits == 0 || splits > 32)
+        return fail("set_gemm_plan: pair is -1, 0 or 1; splits is -1 or 1..32");
+    g_gemm_force_pair = pair;
+    g_gemm_force_splits = splits;
     return 0;
 }
 
@@ -1610,6 +1697,43 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops) {
     cudaFree(sink);
     const double ops = (kind == 2 ? 2.0 * 16 * 8 * 32 : 2.0 * 16 * 8 * 256);
     *tops = (double)ctas * (threads / 32) * iters * 8 * ops / (best * 1e-3) / 1e12;
+    return 0;
+}
+
+int tcbnn_bulk_copy_rate(int bytes, int depth, int warps, int ctas, int iters, double* issue_clocks_per_copy,
+                         double* bytes_per_clock) {
+    if (!bytes_per_clock || !issue_clocks_per_copy || bytes < 16 || bytes % 16 != 0 || depth < 1 || depth > 16 ||
+        warps < 1 || warps > 4 || ctas < 1 || iters < 1 || iters > (1 << 20) ||
+        (size_t)bytes * depth * warps > 200 * 1024)
+        return fail("bulk_copy_rate: bytes a multiple of 16, depth 1..16, warps 1..4, bytes*depth*warps <= 200 KB, "
+                    "iters <= 2^20");
+    const size_t span = (size_t)bytes * depth * 8, total = span * (size_t)ctas * warps;
+    if (total > ((size_t)1 << 30)) return fail("bulk_copy_rate: buffer would exceed 1 GB");
+    unsigned char* src = nullptr;
+    long long* clocks = nullptr;
+    const size_t nclk = sizeof(long long) * (2 * (size_t)ctas + 1);
+    CUDA_TRY(cudaMalloc(&src, total));
+    if (cudaMalloc(&clocks, nclk) != cudaSuccess) { cudaFree(src); return fail("bulk_copy_rate: out of memory"); }
+    cudaMemset(src, 1, total);
+    cudaMemset(clocks, 0, nclk);
+    int* status = (int*)(clocks + 2 * ctas);
+    cudaError_t e = cudaFuncSetAttribute(k_bulk_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    for (int rep = 0; rep < 2 && e == cudaSuccess; rep++) {   // the first pass warms L2
+        k_bulk_probe<<<ctas, 128, (size_t)bytes * depth * warps>>>(src, bytes, depth, warps, iters, clocks, status);
+        e = cudaDeviceSynchronize();
+    }
+    std::vector<long long> h(2 * (size_t)ctas + 1);
+    if (e == cudaSuccess) e = cudaMemcpy(h.data(), clocks, nclk, cudaMemcpyDeviceToHost);
+    cudaFree(src);
+    cudaFree(clocks);
+    if (e != cudaSuccess) return fail("bulk_copy_rate: %s", cudaGetErrorString(e));
+    if (*(int*)&h[2 * (size_t)ctas]) return fail("bulk_copy_rate: a bounded wait gave up");
+    long long worst = 1, issue = 0;
+    for (int i = 0; i < ctas; i++) {
+        if (h[2 * i + 1] > worst) { worst = h[2 * i + 1]; issue = h[2 * i]; }
+    }
+    *bytes_per_clock = (double)bytes * depth * warps * iters / (double)worst;
+    *issue_clocks_per_copy = (double)issue / ((double)depth * iters);
     return 0;
 }
 

@@ -44,6 +44,8 @@ SIGNATURES = {
     "tcbnn_conv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_set_conv_path": (_I, [_I]),
     "tcbnn_conv_set_trace": (_I, [_P]),
+    "tcbnn_set_gemm_plan": (_I, [_I, _I]),
+    "tcbnn_bulk_copy_rate": (_I, [_I, _I, _I, _I, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "tcbnn_conv_status": (_I, [C.POINTER(ConvDesc), _P, C.POINTER(C.c_int)]),
     "tcbnn_inconv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
     "tcbnn_noalloc_scratch_bytes": (_SZ, []),

@@ -26,10 +26,29 @@ def _words(shape, seed, dev):
     return torch.randint(-2**31, 2**31 - 1, shape, dtype=torch.int32, device=dev, generator=g)
 
 
+_GRAPH = False
+
+
 def _time(fn, iters, warmup=3):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if _GRAPH:
+        # the calls recorded once and replayed: device time without the host's launch cost
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(iters):
+                    fn()
+            graph.replay()
+            side.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            graph.replay()
+            e1.record(side)
+            side.synchronize()
+        return e0.elapsed_time(e1) / iters
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
@@ -61,9 +80,19 @@ def main():
     ap.add_argument("--residual", action="store_true", help="c2: also save the int32 residual")
     ap.add_argument("--chunked", action="store_true",
                     help="conv --residual: int16 residuals in the chunk-major layout (TCBNN_RES_INT16_CHUNKED)")
+    ap.add_argument("--mnk", default="1024,1024,4096", help="c1: M,N,K of the bit GEMM")
+    ap.add_argument("--gemm-path", type=int, default=0, help="c1: 0 automatic, 1 warp-level b1 MMA only")
+    ap.add_argument("--gemm-plan", default="-1,-1", help="c1: pair,splits forced on the tcgen05 GEMM (-1 automatic)")
+    ap.add_argument("--trace", action="store_true", help="c1: print the kernel's cycle counters")
+    ap.add_argument("--gemm-mode", default="int32", choices=["int32", "fc", "out"],
+                    help="c1: int32 sums, threshold bits (Fc layer) or scale + bias (Out layer)")
+    ap.add_argument("--graph", action="store_true",
+                    help="time the calls as one replayed CUDA graph (small kernels: the host cannot launch fast enough)")
     ap.add_argument("--no-peak", action="store_true")
     ap.add_argument("--specialized", action="store_true", help="stem: the kernel compiled for the filter")
     a = ap.parse_args()
+    global _GRAPH
+    _GRAPH = a.graph
     dev = torch.device("cuda", 0)
     if a.case == "net":
         import numpy as np
@@ -104,14 +133,39 @@ def main():
                           "bytes": nbytes, "gb_per_s": nbytes / (ms * 1e-3) / 1e9}))
         return
     if a.case == "c1":
-        M = N = 1024
-        K = 4096
-        A, B = _words((M, K // 32), 1, dev), _words((N, K // 32), 2, dev)
-        out = torch.empty((M, N), dtype=torch.int32, device=dev)
+        M, N, K = (int(v) for v in a.mnk.split(","))
+        ld = ops.step128_words(K)
+        A, B = _words((M, ld), 1, dev), _words((N, ld), 2, dev)
+        ops.set_gemm_plan(*(int(v) for v in a.gemm_plan.split(",")))
         ws = ops.gemm_workspace(M, N, K, dev)
-        ms = _time(lambda: ops.bgemm(A, B, K, out=out, workspace=ws), a.iters)
+        ops.set_gemm_path(a.gemm_path)
+        if a.gemm_mode == "int32":
+            out = torch.empty((M, N), dtype=torch.int32, device=dev)
+            fn = lambda: ops.bgemm(A, B, K, out=out, workspace=ws)
+        elif a.gemm_mode == "fc":
+            thr = torch.randn(N, device=dev) * K ** 0.5
+            out = torch.zeros((M, ops.step128_words(N)), dtype=torch.int32, device=dev)
+            fn = lambda: ops.fc_layer(A, B, thr, K, out=out, workspace=ws)
+        else:
+            sc, bi = torch.randn(N, device=dev), torch.randn(N, device=dev)
+            out = torch.empty((M, N), dtype=torch.float32, device=dev)
+            fn = lambda: ops.out_layer(A, B, sc, bi, K, out=out, workspace=ws)
+        ms = _time(fn, a.iters)
+        if a.trace:
+            from . import lib as _lib
+            import ctypes as C
+            tb = torch.zeros(16, dtype=torch.int64, device=dev)
+            _lib.call("tcbnn_conv_set_trace", C.c_void_p(tb.data_ptr()))
+            fn()
+            torch.cuda.synchronize()
+            _lib.call("tcbnn_conv_set_trace", C.c_void_p(0))
+            t = tb.tolist()
+            print(json.dumps({"trace": {"loader_wait_free": t[10], "mma_total": t[11], "mma_wait_full": t[12],
+                                        "epilogue_wait": t[13], "kblocks": t[14], "epilogue": t[15], "cta_total": t[9]}}))
+        ops.set_gemm_path(0)
         work = 2.0 * M * N * K
-        desc = "bit GEMM %dx%dx%d" % (M, N, K)
+        desc = "bit GEMM %dx%dx%d (%s, %d launches)" % (M, N, K, a.gemm_mode,
+                                                       1 if a.gemm_path else ops.gemm_launches(M, N, K, ws))
     elif a.case == "stem":
         Bn = a.batch
         d = ops.conv_desc(Bn, 224, 224, 3, 64, 7, 7, 4, 4)

@@ -325,6 +325,11 @@ def set_gemm_path(path):
     _l.call("tcbnn_set_gemm_path", int(path))
 
 
+def set_gemm_plan(pair=-1, splits=-1):
+    """Force the tcgen05 GEMM's tile shape (1: 256 x 128, 0: 128 x 128) and split count; -1 = automatic."""
+    _l.call("tcbnn_set_gemm_plan", int(pair), int(splits))
+
+
 def gemm_status():
     s = C.c_int(0)
     _l.call("tcbnn_gemm_status", C.byref(s))

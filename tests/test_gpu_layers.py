@@ -70,17 +70,37 @@ def test_bgemm_fc_out(cuda, M, N, K, split):
 
 
 UMMA_GEMM_CASES = [
-    # M, N, K: large enough for the tcgen05 int8 GEMM (M*N*K >= 2^31), ragged on purpose
-    (300, 200, 40010),       # partial row tiles, K not a multiple of 16
-    (1024, 512, 25088),      # the ResNet-18 FC layer
-    (129, 64, 300000),       # one full + one almost empty row tile, very long K
-    (512, 1000, 4200),       # N not a multiple of 128
-    (256, 130, 65536),       # N not a multiple of 4: scalar stores of the partial sums
+    # M, N, K, pair, splits: large enough for the tcgen05 GEMM (M*N*K >= 2^30, less with a forced
+    # plan), ragged on purpose.
+    # pair / splits force the tile shape (1: 256 x 128, 0: 128 x 128) and the number of K slices
+    # (1: the GEMM's own epilogue finishes the layer; more: partial sums and a finishing pass);
+    # -1 leaves the choice to the library's cost model.
+    (300, 200, 40010, -1, -1),      # partial row tiles, K not a multiple of 32
+    (300, 200, 40010, 1, 1),
+    (300, 200, 40010, 0, 7),
+    (1024, 512, 25088, -1, -1),     # the ResNet-18 FC layer
+    (129, 64, 300000, -1, -1),      # one full + one almost empty row tile, very long K
+    (129, 64, 300000, 1, 32),
+    (512, 1000, 4200, -1, -1),      # N not a multiple of 128
+    (256, 130, 65536, -1, -1),      # N not a multiple of 4: scalar stores
+    (256, 130, 65536, 0, 1),
+    (256, 130, 65536, 1, 5),
+    (1024, 1024, 4096, -1, -1),     # the standalone bit-GEMM benchmark shape
+    (8192, 1024, 1024, -1, -1),     # an MLP hidden layer
+    (2100, 1000, 1030, 0, 1),       # ragged in M, N (not a multiple of 32) and K
+    (2100, 1000, 1030, 1, 1),
+    (2100, 1000, 1030, 1, 2),
+    (2050, 130, 1500, 0, 1),
+    (140, 66, 30000, 1, 1),         # a 256-row tile whose second half is nearly empty
+    (128, 64, 32768, 0, 3),         # a single tile
+    (128, 64, 32768, 1, 1),         # a pair tile without a second half
+    (1000, 520, 576, 0, 1),         # K = 9 k-blocks: stages of 4, 4 and 1
+    (1000, 520, 576, 1, 2),         # splits of 5 and 4 k-blocks
 ]
 
 
-@pytest.mark.parametrize("M,N,K", UMMA_GEMM_CASES)
-def test_gemm_family_on_tcgen05_matches_oracle_and_b1_kernel(cuda, M, N, K):
+@pytest.mark.parametrize("M,N,K,pair,splits", UMMA_GEMM_CASES)
+def test_gemm_family_on_tcgen05_matches_oracle_and_b1_kernel(cuda, M, N, K, pair, splits):
     g = util.rng(M + 3 * N + 7 * K)
     ld = orc.step128_words(K)
     A = util.mask_row_pad(util.rand_words(g, (M, ld)), K)
@@ -89,10 +109,15 @@ def test_gemm_family_on_tcgen05_matches_oracle_and_b1_kernel(cuda, M, N, K):
     scale = g.standard_normal(N).astype(np.float32)
     bias = g.standard_normal(N).astype(np.float32)
     dA, dW = dev(A, cuda), dev(W, cuda)
-    ws = ops.gemm_workspace(M, N, K, cuda)
-    assert ws is not None and ws.numel() * 4 >= (M + N) * K          # room for both operands as bytes
     ref = orc.bgemm(A, W, K)
     try:
+        ops.set_gemm_plan(pair, splits)
+        ws = ops.gemm_workspace(M, N, K, cuda)
+        assert ws is not None and ws.numel() * 4 >= (M + N) * K // 2     # room for both operands as nibbles
+        launches = ops.gemm_launches(M, N, K, ws)
+        assert launches in (2, 3)                                        # i.e. the tcgen05 path
+        if splits > 0:
+            assert launches == (2 if splits == 1 else 3)
         for path in (0, 1):
             ops.set_gemm_path(path)
             assert np.array_equal(ops.bgemm(dA, dW, K, workspace=ws).cpu().numpy(), ref), path
@@ -103,6 +128,7 @@ def test_gemm_family_on_tcgen05_matches_oracle_and_b1_kernel(cuda, M, N, K):
             assert ops.gemm_status() == 0
     finally:
         ops.set_gemm_path(0)
+        ops.set_gemm_plan(-1, -1)
 
 
 def test_gemm_kat_srand4(cuda):
