@@ -113,10 +113,15 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
  * narrow channel counts are bound by.  It is read and written only by the loader-fed tcgen05
  * kernel (layers with tcbnn_conv_planes_bytes != 0 called with their workspace, pool == 1, channel
  * counts in multiples of 8; other calls fail) and written by tcbnn_inconv_specialized_layer;
- * tcbnn_conv_prefers_chunked_residual says for which layers it is the faster choice. */
+ * tcbnn_conv_prefers_chunked_residual says for which layers it is the faster choice.
+ * TCBNN_RES_PROVEN, ORed into the res_out_bytes of an int16 format, says that the caller has
+ * proven the bound |value| <= 32767 (e.g. C*R*S + the bound of res_in, the way the drop-in classes
+ * choose int16): the layer then skips the per-value range check that sets status 2, which costs
+ * the residual layers' epilogues about a fifth of their instructions. */
 #define TCBNN_RES_INT32 4
 #define TCBNN_RES_INT16 2
 #define TCBNN_RES_INT16_CHUNKED 18
+#define TCBNN_RES_PROVEN 32
 int tcbnn_conv_prefers_chunked_residual(const tcbnn_conv_desc* d);
 
 /* Binary conv layer with threshold / OR-pool / residual / repack fused.

@@ -596,14 +596,18 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 const size_t idx = q.opix * a.O + o0;
                 if (a.res_out_bytes == 2) {
                     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<short*>(a.res_out) + idx);
-                    uint32_t ovf = 0;                      // |v| of every value ORed together
+                    if (!a.res_out_proven) {               // a real branch: two instructions per value
+                        uint32_t ovf = 0;                  // |v| of every value ORed together
+#pragma unroll
+                        for (int j = 0; j < COLS; j++) ovf |= (uint32_t)(v[j] ^ (v[j] >> 31));
+                        overflow |= ovf > 32767u;          // some value outside [-32768, 32767]
+                    }
 #pragma unroll
                     for (int j = 0; j < NQ; j++) {
                         uint32_t w[4];
 #pragma unroll
                         for (int kk = 0; kk < 4; kk++) {
                             const int lo = v[8 * j + 2 * kk], hi = v[8 * j + 2 * kk + 1];
-                            ovf |= (uint32_t)(lo ^ (lo >> 31)) | (uint32_t)(hi ^ (hi >> 31));
                             w[kk] = ((uint32_t)lo & 0xFFFFu) | ((uint32_t)hi << 16);
                         }
                         if (RSTAGE)                        // into the staged row, in place of what was read
@@ -615,7 +619,6 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                         else
                             dst[j] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    overflow |= ovf > 32767u;              // some value outside [-32768, 32767]
                 } else {
                     int4* dst = reinterpret_cast<int4*>(reinterpret_cast<int*>(a.res_out) + idx);
 #pragma unroll

@@ -55,6 +55,7 @@ struct ConvWsArgs {
     int res_in_chunked, res_out_chunked; long long res_in_npix, res_out_npix;
     uint32_t* out; long long out_image_stride;
     void* res_out; int res_out_bytes; int32_t* acc_out;
+    int res_out_proven;       // the caller vouches that every saved int16 value fits: no range check
     int* err_flag;
     long long* trace;         // optional: block 0 writes per-role cycle counters (see tcbnn_conv_set_trace)
 };

@@ -588,10 +588,13 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
 
 // The *_bytes arguments of the conv entry points name the residual's element format: 4 = int32
 // NHWC, 2 = int16 NHWC, TCBNN_RES_INT16_CHUNKED = int16 laid out by 8-channel chunk.
-bool residual_format(int code, int* bytes, int* chunked) {
-    *chunked = code == TCBNN_RES_INT16_CHUNKED;
-    *bytes = *chunked ? 2 : code;
-    return code == 2 || code == 4 || code == TCBNN_RES_INT16_CHUNKED;
+// TCBNN_RES_PROVEN on an int16 format: the caller vouches for the range, no check per value.
+bool residual_format(int code, int* bytes, int* chunked, int* proven = nullptr) {
+    const int fmt = code & ~TCBNN_RES_PROVEN;
+    if (proven) *proven = (code & TCBNN_RES_PROVEN) != 0 && fmt != 4;
+    *chunked = fmt == TCBNN_RES_INT16_CHUNKED;
+    *bytes = *chunked ? 2 : fmt;
+    return fmt == 2 || fmt == 4 || fmt == TCBNN_RES_INT16_CHUNKED;
 }
 
 // 2x2 max of a chunked int16 residual [ch/8][B*2P*2Q][8] -> NHWC [B][P][Q][ch].  A block takes 32
@@ -1234,10 +1237,10 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
     if (out_image_stride < (long long)d->OH * d->OW * Ow) return fail("conv_layer: out_image_stride too small");
     if ((res_out || res_in) && d->pool != 1) return fail("conv_layer: residuals need pool == 1");
     if (res_in && (res_in_ch <= 0 || residual_channels <= 0)) return fail("conv_layer: residual channel counts must be positive");
-    int res_in_chunked = 0, res_out_chunked = 0;
+    int res_in_chunked = 0, res_out_chunked = 0, res_out_proven = 0;
     if (res_in && !residual_format(res_in_bytes, &res_in_bytes, &res_in_chunked))
         return fail("conv_layer: res_in_bytes must be 2, 4 or TCBNN_RES_INT16_CHUNKED");
-    if (res_out && !residual_format(res_out_bytes, &res_out_bytes, &res_out_chunked))
+    if (res_out && !residual_format(res_out_bytes, &res_out_bytes, &res_out_chunked, &res_out_proven))
         return fail("conv_layer: res_out_bytes must be 2, 4 or TCBNN_RES_INT16_CHUNKED");
     if (!res_in) res_in_chunked = 0;
     if (!res_out) res_out_chunked = 0;
@@ -1289,6 +1292,7 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         umma::fastdiv_setup(a.VH, &a.vh_mul, &a.vh_sh);
         a.res_in = res_in; a.res_in_bytes = res_in_bytes; a.res_in_ch = res_in_ch;
         a.res_in_chunked = res_in_chunked; a.res_out_chunked = res_out_chunked;
+        a.res_out_proven = res_out ? res_out_proven : 0;
         a.res_in_npix = (long long)d->B * d->OH * d->OW * (residual_pool ? 4 : 1);
         a.res_out_npix = (long long)d->B * d->OH * d->OW;
         a.residual_channels = residual_channels; a.residual_pool = residual_pool;

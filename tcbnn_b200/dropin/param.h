@@ -767,7 +767,9 @@ public:
                                            fast_res_in_chunked ? TCBNN_RES_INT16_CHUNKED : fast_res_in_bytes,
                                            fast_res_in_ch, residual_channels, residual_pool ? 1 : 0, output_gpu,
                                            (long long)image_words(), save_residual ? (void*)output_residual_gpu : NULL,
-                                           fast_res_chunked ? TCBNN_RES_INT16_CHUNKED : fast_res_bytes, NULL, ws, wsb,
+                                           // int16 follows from the bound chain in fast_setup: no range check needed
+                                           (fast_res_chunked ? TCBNN_RES_INT16_CHUNKED : fast_res_bytes) | (fast_res_bytes == 2 ? TCBNN_RES_PROVEN : 0),
+                                           NULL, ws, wsb,
                                            fast_planes ? 1 : 0, fast_next, fast_next_planes, fast_next_planes_bytes, stream));
     }
     // 2 after a forward pass in which a residual value did not fit the int16 rows chosen above

@@ -67,7 +67,7 @@ SIGNATURES = {
     "tcbnn_conv_prefers_chunked_residual": (_I, [C.POINTER(ConvDesc)]),
 }
 
-RES_INT32, RES_INT16, RES_INT16_CHUNKED = 4, 2, 18      # TCBNN_RES_* of the header
+RES_INT32, RES_INT16, RES_INT16_CHUNKED, RES_PROVEN = 4, 2, 18, 32      # TCBNN_RES_* of the header
 
 _lib = None
 

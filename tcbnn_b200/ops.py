@@ -163,10 +163,11 @@ def conv_workspace(d, device):
 def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_pool=False,
                out=None, out_image_stride=None, save_residual=False, want_acc=False,
                res_out_buf=None, residual_dtype=torch.int32, workspace=None, workspace_ready=False,
-               next_layer=None, res_in_chunked=False, res_out_chunked=False):
+               next_layer=None, res_in_chunked=False, res_out_chunked=False, res_out_proven=False):
     """x: [B][H][W][Cw] int32 words.  Returns (out_bits, res_out, acc_out).
     Residual tensors may be torch.int32 or torch.int16; res_in_chunked / res_out_chunked: the
     int16 tensor is laid out by 8-channel chunk (TCBNN_RES_INT16_CHUNKED, see chunked_to_nhwc).
+    res_out_proven: the caller has proven that every saved int16 value fits (TCBNN_RES_PROVEN).
     workspace: uint8 scratch tensor for tcbnn_conv_layer_w; None = the shared one of
     conv_workspace(); False = none (tcbnn_conv_layer).
     next_layer: (descriptor, planes tensor) of the layer consuming this output: the layer also
@@ -191,7 +192,7 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
             _residual_code(res_in, res_in_chunked),
             res_in_ch, residual_channels, int(bool(residual_pool)), _ptr(out),
             C.c_longlong(stride), _ptr(res_out),
-            _residual_code(res_out, res_out_chunked), _ptr(acc_out))
+            _residual_code(res_out, res_out_chunked, res_out_proven), _ptr(acc_out))
     if next_layer is not None or workspace_ready:
         nd, npl = next_layer if next_layer is not None else (None, None)
         _l.call("tcbnn_conv_layer_x", *args, _ptr(workspace),
@@ -205,15 +206,16 @@ def conv_layer(d, x, prepared, thr, res_in=None, residual_channels=0, residual_p
     return out, res_out, acc_out
 
 
-def _residual_code(t, chunked):
+def _residual_code(t, chunked, proven=False):
     """The *_bytes argument of the conv entry points for a residual tensor."""
     if t is None:
         return 4
+    flag = _l.RES_PROVEN if (proven and t.dtype == torch.int16) else 0
     if chunked:
         if t.dtype != torch.int16:
             raise _l.TcbnnError("chunked residuals are int16")
-        return _l.RES_INT16_CHUNKED
-    return t.element_size()
+        return _l.RES_INT16_CHUNKED | flag
+    return t.element_size() | flag
 
 
 def conv_prefers_chunked_residual(d):

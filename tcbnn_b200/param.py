@@ -451,7 +451,9 @@ class Conv128LayerParam:
                        workspace=self.input_planes, workspace_ready=self.input_planes is not None,
                        next_layer=self.next_layer,
                        res_in_chunked=self.input_residual_chunked and self.inject_residual,
-                       res_out_chunked=self.residual_chunked)
+                       res_out_chunked=self.residual_chunked,
+                       # int16 was chosen from the bound fan-in + bound of the injected residual
+                       res_out_proven=self.residual_bound is not None and self.residual_bound <= 32767)
 
     def get_output_gpu(self):
         return self.output_gpu
