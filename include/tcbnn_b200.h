@@ -113,7 +113,9 @@ int tcbnn_conv_prepare(const tcbnn_conv_desc* d, const uint32_t* filter_bits, vo
  * narrow channel counts are bound by.  It is read and written only by the loader-fed tcgen05
  * kernel (layers with tcbnn_conv_planes_bytes != 0 called with their workspace, pool == 1, channel
  * counts in multiples of 8; other calls fail) and written by tcbnn_inconv_specialized_layer;
- * tcbnn_conv_prefers_chunked_residual says for which layers it is the faster choice.
+ * tcbnn_conv_prefers_chunked_residual says for which layers it is the faster choice (every layer
+ * the loader-fed kernel takes: its tile-per-group epilogue handles no other residual layout, and
+ * it reads a pooled chunk-major residual in place, without the pooling pass NHWC tensors get).
  * TCBNN_RES_PROVEN, ORed into the res_out_bytes of an int16 format, says that the caller has
  * proven the bound |value| <= 32767 (e.g. C*R*S + the bound of res_in, the way the drop-in classes
  * choose int16): the layer then skips the per-value range check that sets status 2, which costs
@@ -189,7 +191,10 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
  * rows straight between registers and global memory, never staging them in shared memory, 5 = as 0
  * but staging them wherever the tensors allow (0 stages them where that measured faster), 6 = as
  * 0 but the loader-fed kernel always runs one CTA per SM (0 runs layers with an n-tile of 64 as
- * two smaller CTAs per SM when they fit).
+ * two smaller CTAs per SM when they fit), 7 = as 0 but without the loader-fed kernel's
+ * tile-per-group epilogues (0 uses them for layers without residuals and for chunk-major int16
+ * residuals), 8 = as 0 but two CTAs per SM also for the all-warps-per-tile residual epilogues at an
+ * n-tile of 64.
  * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);

@@ -102,17 +102,34 @@ __device__ __forceinline__ void expand_raster(const ConvWsArgs& a, uint4* planes
 // the fp32 accumulator is compared with the fp32 threshold as it is), 1 = residual rows moved
 // directly between registers and global memory (any element size, pooled residuals, partial
 // channel ranges), 2 = staged int16 residual rows as described above.
-constexpr int kEpiPlain = 0, kEpiDirect = 1, kEpiStaged = 2;
+//
+// Tile-per-group epilogues (3 = no residual, 4 = chunk-major int16 residuals in and / or out): the
+// forms above put all 16 epilogue warps on every tile, so that a thread holds 16 or 32 of its
+// pixel's columns and pays the per-tile bookkeeping (raster position -> pixel, addresses, barrier
+// waits: some 200 instructions) for that few outputs -- most of what these warps issue.  Here a
+// group of 4 warps (8 at an n-tile of 128) owns a whole tile and the groups take tiles in turn: a
+// thread walks 64 columns of its pixel in passes of 32, the bookkeeping is paid once per 64
+// outputs, and the groups work on different accumulators at the same time (NT = 64: 4 groups on
+// 7 accumulators; NT = 128: 2 groups on 3).  With one thread per pixel every tensor is touched in
+// whole lines: chunk-major residuals, 16-byte plane slots, 8 bytes of packed bits -- so nothing is
+// staged, and a pooled residual is read in place (four lines per chunk) instead of by a pass of
+// its own.
+constexpr int kEpiPlain = 0, kEpiDirect = 1, kEpiStaged = 2, kEpiTile = 3, kEpiTileRes = 4;
 template <int NT, int EPI, int EPIW>
 __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     constexpr bool RSTAGE = EPI == kEpiStaged;
     constexpr int kEpiThreads = EPIW * 32, kThreadsCta = pre_threads(EPIW);
     static_assert(EPIW == 16 || (EPIW == 8 && NT == 64 && EPI != kEpiStaged), "8 epilogue warps: n-tile 64, no staging");
+    constexpr bool TILE = EPI == kEpiTile || EPI == kEpiTileRes;
+    constexpr int CPT = NT < 64 ? NT : 64;            // tile-per-group: columns of a tile per thread
+    constexpr int WPG = 4 * (NT / CPT);               // ... warps of a group (all rows x all columns of a tile)
+    constexpr int NG = EPIW / WPG;                    // ... groups, each on a tile of its own
     // Tensor memory: accumulators (7 at NT = 64) below column 480, the unit block scales of the
     // 4-bit MMA above it; the patch ring is as deep as shared memory allows, so that no role waits
     // on another's latency.
     constexpr uint32_t TM_COLS = EPIW == 16 ? 512 : 256, SF_COL = TM_COLS - 32;
-    constexpr int NACC = NT >= 128 ? 2 : ((SF_COL / NT) > 8 ? 8 : (SF_COL / NT));   // measured: deeper does not pay at NT = 128
+    constexpr int NACC = NT >= 128 ? (TILE ? 3 : 2)   // measured: deeper does not pay at NT = 128 when all warps share a tile
+                                   : ((SF_COL / NT) > 8 ? 8 : (SF_COL / NT));
     const int NSTAGE = a.pre_stages;
     constexpr int COLS = NT / (EPIW / 4);             // accumulator columns per epilogue thread
     static_assert(COLS == 8 || COLS == 16 || COLS == 32, "n-tile of 32, 64 or 128");
@@ -149,7 +166,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
 
     if (tid == 0) {
         for (int s = 0; s < 8; s++) { mbar_init(BAR_AFULL(s), 1); mbar_init(BAR_AEMPTY(s), 1); }
-        for (int b = 0; b < 8; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), EPIW); }
+        for (int b = 0; b < 8; b++) { mbar_init(BAR_CFULL(b), 1); mbar_init(BAR_CEMPTY(b), TILE ? WPG : EPIW); }
         for (int g = 0; g < 4; g++) mbar_init(BAR_EPI(g), EPIW / 4);
         mbar_init(BAR_DRAIN, 1);
         *sAbort = 0;
@@ -305,7 +322,151 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             if (a.trace && blockIdx.x == 0 && leader && w2 == 0) { a.trace[3] = clock64() - tr_t0; a.trace[4] = tr_wc; a.trace[5] = tr_wa; a.trace[2] = it; }
         }
         __syncwarp();
-    } else if (tid < kEpiThreads) {
+    } else if (TILE && tid < kEpiThreads) {
+        // =============================== epilogue, a tile per group ==========================
+        constexpr bool RES = EPI == kEpiTileRes;
+        constexpr int PASSES = CPT / 32;
+        const int grp = warp / WPG, quad = warp & 3, half = (warp % WPG) >> 2;
+        const int row = quad * 32 + lane;
+        const int Ow = (a.O + 31) >> 5;
+        const int o0 = obase + half * CPT;                 // this thread's first output channel
+        const int lim = (RES && a.res_in) ? min(a.residual_channels, a.res_in_ch) : 0;
+        const bool has_in = RES && a.res_in && o0 < lim;
+        const uint4* rin = reinterpret_cast<const uint4*>(a.res_in) + (size_t)(o0 >> 3) * a.res_in_npix;
+        uint4* rout = reinterpret_cast<uint4*>(a.res_out) + (size_t)(o0 >> 3) * a.res_out_npix;
+        bool ok = true, overflow = false;
+        uint32_t done = 0;
+        long long tr_w = 0;
+        const long long tr_t0 = clock64();
+        for (uint32_t tc = grp; (long long)mfirst + (long long)tc * mstep < mtiles && ok; tc += NG, done++) {
+            const int m = mfirst + (int)tc * mstep;
+            const int b = (int)(tc % NACC);
+            const uint32_t bph = (tc / NACC) & 1u;
+            // raster position -> output pixel
+            const int p = m * 128 + row;
+            bool live = false;
+            int n = 0, y = 0, x = 0;
+            if (p < NV) {
+                const int vy = fastdiv(p, a.pw_mul, a.pw_sh);
+                x = p - vy * a.PW;
+                n = fastdiv(vy, a.vh_mul, a.vh_sh);
+                y = vy - n * a.VH;
+                live = x < a.OWg && y < a.OHg;
+            }
+            const size_t opix = ((size_t)n * a.OHg + y) * a.OWg + x;
+            // injected residual of pass k (channels o0 + 32k ..): zeros where nothing is injected;
+            // 2x2 max for pooled residuals (kernel.cuh:773-783)
+            uint4 r[4];
+            auto fetch = [&](int k) {
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                if (a.residual_pool) {
+                    const size_t i00 = ((size_t)n * 2 * a.OHg + 2 * y) * 2 * a.OWg + 2 * x, rw = (size_t)2 * a.OWg;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        r[j] = z;
+                        if (live && o0 + 32 * k + 8 * j < lim) {
+                            const uint4* q = rin + (size_t)(4 * k + j) * a.res_in_npix + i00;
+                            const uint4 w0 = __ldg(q), w1 = __ldg(q + 1), w2 = __ldg(q + rw), w3 = __ldg(q + rw + 1);
+                            r[j].x = __vmaxs2(__vmaxs2(w0.x, w1.x), __vmaxs2(w2.x, w3.x));
+                            r[j].y = __vmaxs2(__vmaxs2(w0.y, w1.y), __vmaxs2(w2.y, w3.y));
+                            r[j].z = __vmaxs2(__vmaxs2(w0.z, w1.z), __vmaxs2(w2.z, w3.z));
+                            r[j].w = __vmaxs2(__vmaxs2(w0.w, w1.w), __vmaxs2(w2.w, w3.w));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        r[j] = (live && o0 + 32 * k + 8 * j < lim) ? __ldg(rin + (size_t)(4 * k + j) * a.res_in_npix + opix) : z;
+                }
+            };
+            if (RES && has_in) fetch(0);                   // flies while the accumulator is awaited
+            ok = (a.trace && blockIdx.x == 0) ? wait.timed(BAR_CFULL(b), bph, tr_w) : wait.relaxed(BAR_CFULL(b), bph);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t words[PASSES];
+#pragma unroll
+            for (int k = 0; k < PASSES; k++) {
+                int v[32];
+                tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * NT + half * CPT + k * 32, v);
+                tmem_ld_wait();
+                if (k == PASSES - 1) {
+                    tc_fence_before();                     // this warp is done with the accumulator
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR_CEMPTY(b));
+                }
+                uint32_t word = 0;                         // channel c of the pass at bit 31 - c
+                if (!RES) {
+                    // the reference's comparison as it stands, !((float)value < threshold)
+                    // (kernel.cuh:795-796), on the fp32 accumulator
+                    const float4* tf4 = reinterpret_cast<const float4*>(sThrF + half * CPT + k * 32);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const float4 th = tf4[j];
+                        if (!(__int_as_float(v[4 * j]) < th.x)) word |= 0x80000000u >> (4 * j);
+                        if (!(__int_as_float(v[4 * j + 1]) < th.y)) word |= 0x80000000u >> (4 * j + 1);
+                        if (!(__int_as_float(v[4 * j + 2]) < th.z)) word |= 0x80000000u >> (4 * j + 2);
+                        if (!(__int_as_float(v[4 * j + 3]) < th.w)) word |= 0x80000000u >> (4 * j + 3);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = f4_acc_to_int(v[j]);   // fp32 accumulators, exact integers
+                    if (has_in) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            v[8 * j] += (int)(short)(r[j].x & 0xFFFFu);
+                            v[8 * j + 1] += (int)(short)(r[j].x >> 16);
+                            v[8 * j + 2] += (int)(short)(r[j].y & 0xFFFFu);
+                            v[8 * j + 3] += (int)(short)(r[j].y >> 16);
+                            v[8 * j + 4] += (int)(short)(r[j].z & 0xFFFFu);
+                            v[8 * j + 5] += (int)(short)(r[j].z >> 16);
+                            v[8 * j + 6] += (int)(short)(r[j].w & 0xFFFFu);
+                            v[8 * j + 7] += (int)(short)(r[j].w >> 16);
+                        }
+                        if (k + 1 < PASSES) fetch(k + 1);  // the next pass's residual flies during this one's arithmetic
+                    }
+                    const int4* th4 = reinterpret_cast<const int4*>(sThr + half * CPT + k * 32);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int4 th = th4[j];
+                        if (v[4 * j] >= th.x) word |= 0x80000000u >> (4 * j);
+                        if (v[4 * j + 1] >= th.y) word |= 0x80000000u >> (4 * j + 1);
+                        if (v[4 * j + 2] >= th.z) word |= 0x80000000u >> (4 * j + 2);
+                        if (v[4 * j + 3] >= th.w) word |= 0x80000000u >> (4 * j + 3);
+                    }
+                    if (a.res_out && live) {
+                        if (!a.res_out_proven) {           // a real branch: two instructions per value
+                            uint32_t ovf = 0;              // |v| of every value ORed together
+#pragma unroll
+                            for (int j = 0; j < 32; j++) ovf |= (uint32_t)(v[j] ^ (v[j] >> 31));
+                            overflow |= ovf > 32767u;      // some value outside [-32768, 32767]
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int kk = 0; kk < 4; kk++)
+                                w[kk] = ((uint32_t)v[8 * j + 2 * kk] & 0xFFFFu) | ((uint32_t)v[8 * j + 2 * kk + 1] << 16);
+                            rout[(size_t)(4 * k + j) * a.res_out_npix + opix] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+                words[k] = word;
+                if (a.nxt && live) store_next_planes(a, n, y, x, o0 + 32 * k, word, 32);
+            }
+            if (live) {
+                // bits of channel o live at bit 31 - o%32 of word o/32
+                uint32_t* wp = a.out + (size_t)n * a.out_image_stride + ((size_t)y * a.OWg + x) * Ow + (o0 >> 5);
+                if (PASSES == 2 && (reinterpret_cast<uintptr_t>(wp) & 7) == 0) {
+                    *reinterpret_cast<uint2*>(wp) = make_uint2(words[0], words[PASSES - 1]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < PASSES; k++) wp[k] = words[k];
+                }
+            }
+        }
+        if (overflow) atomicExch(a.err_flag, 2);
+        if (a.trace && blockIdx.x == 0 && tid == 0) { a.trace[6] = clock64() - tr_t0; a.trace[7] = tr_w; a.trace[8] = done; }
+    } else if (!TILE && tid < kEpiThreads) {
         // =============================== epilogue ===========================================
         constexpr int NQ = COLS / 8;                       // 8-channel groups (one uint4 of int16) per thread
         const int row = tid & 127, quad = warp & 3, cg = warp >> 2;

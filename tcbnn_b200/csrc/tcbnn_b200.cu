@@ -467,6 +467,15 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
 
 int g_conv_two_ctas = 1;  // loader-fed kernel, n-tile 64: two CTAs of eight epilogue warps per SM when they fit
 int g_conv_res_stage = 1; // loader-fed kernel: stage int16 residual rows in shared memory when possible
+int g_conv_tile = 1;      // loader-fed kernel: the tile-per-group epilogues where the tensors allow them
+
+// The tile-per-group epilogues of the loader-fed kernel take residuals only in the chunk-major
+// int16 layout and write no int32 accumulators.
+bool pre_tile_ok(const void* res_in, int res_in_bytes, int res_in_chunked, const void* res_out, int res_out_bytes,
+                 int res_out_chunked, const void* acc_out) {
+    return g_conv_tile && !acc_out && (!res_in || (res_in_chunked && res_in_bytes == 2)) &&
+           (!res_out || (res_out_chunked && res_out_bytes == 2));
+}
 int g_conv_path = 0;     // 0 auto, 1 warp-level b1 MMA, 2 tcgen05 (error if not eligible), 3 = 2 without the activation-stationary kernel
 
 template <int NT, int STRIDE>
@@ -524,14 +533,14 @@ int launch_conv_umma_pre_k(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream
     return launch_check("conv_layer (tcgen05, pre-expanded input)");
 }
 
-// n-tile 64, plain epilogue: two CTAs of eight epilogue warps per SM when the filter block and a
-// patch ring of at least three stages fit half of the shared memory.  Measured at batch 1024,
-// 56 x 56 x 64 -> 64: 0.119 ms against 0.154 with one CTA; with residual rows moved directly the
-// two-CTA form loses (0.40 against 0.33: 32 columns of residual per thread spill), so those
-// layers stay on one CTA of sixteen epilogue warps.
+// n-tile 64: two CTAs of eight epilogue warps per SM when the filter block and a patch ring of at
+// least three stages fit half of the shared memory.  Measured at batch 1024, 56 x 56 x 64 -> 64
+// (two CTAs / one): all-warps-per-tile epilogues 0.119 / 0.154 ms plain and 0.40 / 0.33 with
+// residual rows moved directly (32 columns of residual per thread spill), so those stay on one
+// CTA; tile-per-group epilogues 0.105 / 0.143 plain and 0.223 / 0.255 with chunk-major residuals.
 template <int EPI>
 int launch_conv_umma_pre_64(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
-    if (g_conv_two_ctas && (EPI == umma::kEpiPlain || g_conv_two_ctas == 2)) {
+    if (g_conv_two_ctas && (EPI == umma::kEpiPlain || EPI == umma::kEpiTile || EPI == umma::kEpiTileRes || g_conv_two_ctas == 2)) {
         int stages = a.pre_stages;
         const int nplane = a.stride == 2 ? 4 : 1;
         while (stages > 3 && umma::pre_smem_bytes(a.NPOS, a.C, a.R * a.S, 64, stages, nplane) > 113 * 1024) stages--;
@@ -552,6 +561,16 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
         k_expand_raster<<<elementwise_grid(units, sms), 256, 0, st>>>(a, const_cast<uint4*>(a.pre), a.pre_positions,
                                                                    a.pre_front);
         if (launch_check("conv_layer (input expansion)")) return 1;
+    }
+    if (pre_tile_ok(a.res_in, a.res_in_bytes, a.res_in_chunked, a.res_out, a.res_out_bytes, a.res_out_chunked, a.acc_out)) {
+        const bool plain = !a.res_in && !a.res_out;
+        if constexpr (NT == 64) {
+            return plain ? launch_conv_umma_pre_64<umma::kEpiTile>(a, smem, sms, st)
+                         : launch_conv_umma_pre_64<umma::kEpiTileRes>(a, smem, sms, st);
+        } else {
+            return plain ? launch_conv_umma_pre_k<NT, umma::kEpiTile, 16>(a, smem, sms, st)
+                         : launch_conv_umma_pre_k<NT, umma::kEpiTileRes, 16>(a, smem, sms, st);
+        }
     }
     if constexpr (NT >= 64) {
         // int16 residual rows through shared memory (see conv_umma_pre_cta) when the tensors allow
@@ -1335,7 +1354,9 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
             // a pooled int16 residual is reduced by a streaming pass first when the workspace has
             // the room behind the planes: four scattered loads per value in the epilogue cost more
             const size_t pooled_res_bytes = (size_t)d->B * d->OH * d->OW * (size_t)res_in_ch * 2;
+            // (the tile-per-group epilogues read a pooled chunk-major residual in place: whole lines)
             if (res_in && residual_pool && res_in_bytes == 2 && res_in_ch % 8 == 0 && !pooled &&
+                !pre_tile_ok(res_in, res_in_bytes, res_in_chunked, res_out, res_out_bytes, res_out_chunked, acc_out) &&
                 (!res_in_chunked || res_in_ch / 8 <= kPoolChunkedMaxCh8) &&
                 pooled_res_bytes <= L.pool_bytes && workspace_bytes >= planes_padded(L) + pooled_res_bytes) {
                 char* pooled_res = (char*)workspace + planes_padded(L);
@@ -1421,17 +1442,19 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
 int tcbnn_conv_prefers_chunked_residual(const tcbnn_conv_desc* d) {
     if (conv_check(d, true)) return 0;
     const PreparedLayout L = prepared_layout(d);
-    // the layers whose epilogue moves residual rows directly: n-tile 64 (wider ones stage NHWC rows)
-    return L.pre_nt == 64 && d->pool == 1 && d->O % 8 == 0 ? 1 : 0;
+    // the loader-fed kernel's tile-per-group epilogue: one thread per pixel, whole lines per warp
+    return L.pre_nt != 0 && d->pool == 1 && d->O % 8 == 0 ? 1 : 0;
 }
 
 int tcbnn_set_conv_path(int path) {
-    if (path < 0 || path > 6)
+    if (path < 0 || path > 8)
         return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05, 3 = tcgen05 filter-stationary kernel only, "
-                    "4 / 5 = automatic with residual staging never / wherever possible, 6 = automatic, one CTA per SM only");
+                    "4 / 5 = automatic with residual staging never / wherever possible, 6 = automatic, one CTA per SM only, "
+                    "7 = automatic without the tile-per-group epilogues, 8 = automatic, two CTAs per SM wherever they fit");
     g_conv_path = path >= 4 ? 0 : path;
     g_conv_res_stage = path == 4 ? 0 : path == 5 ? 2 : 1;
-    g_conv_two_ctas = path == 6 ? 0 : 1;
+    g_conv_two_ctas = path == 6 ? 0 : path == 8 ? 2 : 1;
+    g_conv_tile = path == 7 ? 0 : 1;
     return 0;
 }
 

@@ -437,8 +437,13 @@ class Conv128LayerParam:
         expansion pass too unless its producer filled the planes."""
         has_ws = ops.conv_workspace(self.desc, self.input_gpu.device) is not None
         own_expand = self.input_planes is None and ops.new_planes_bytes(self.desc) > 0
+        # a pooled NHWC int16 residual is reduced by a pass of its own; the chunk-major layout is
+        # read in place by the kernel's tile-per-group epilogue (which also needs the saved
+        # residual, if any, chunk-major)
+        in_place = self.input_residual_chunked and (self.output_residual_gpu is None or self.residual_chunked)
         pools_residual = (self.inject_residual and self.residual_pool and has_ws and self.desc.pool == 1 and
-                          self.input_residual_gpu is not None and self.input_residual_gpu.dtype == torch.int16)
+                          self.input_residual_gpu is not None and self.input_residual_gpu.dtype == torch.int16 and
+                          not in_place)
         pools_output = self.desc.pool != 1 and has_ws          # tcgen05 on the pre-pool grid + OR-pooling pass
         return 1 + int(own_expand) + int(pools_residual) + int(pools_output)
 

@@ -542,58 +542,106 @@ def test_bounded_wait_gives_up_and_the_context_stays_usable(cuda):
 
 
 CHUNKED_CASES = [
-    # B, H, W, C, O, residual: "plain" (same grid) or "pool" (2x2 max of a [2H][2W][O/2] tensor)
-    (3, 9, 11, 64, 64, "plain"),        # n-tile 64: the direct epilogue, two images straddle tiles
+    # B, H, W, C, O, residual: "plain" (same grid), "pool" (2x2 max of a [2H][2W][O/2] tensor) or
+    # "none" (no residual in; the layer still saves one)
+    (3, 9, 11, 64, 64, "plain"),        # n-tile 64, two images straddle tiles
     (2, 56, 56, 64, 64, "plain"),
     (5, 6, 6, 128, 64, "plain"),
-    (2, 8, 8, 128, 128, "pool"),        # pooled chunked input through the pooling pass, NHWC output
-    (2, 7, 9, 64, 64, "pool"),          # pooled chunked input read in the epilogue when there is no room ... or the pass
+    (2, 8, 8, 128, 128, "pool"),        # n-tile 128: groups of 8 warps, half of the columns injected
+    (2, 7, 9, 64, 64, "pool"),
+    (130, 3, 5, 64, 64, "plain"),       # many tiny images per tile
+    (9, 28, 28, 128, 128, "plain"),     # n-tile 128, several tiles per group
+    (7, 14, 14, 256, 256, "pool"),      # two n-tiles of 128, four channel blocks
+    (40, 7, 7, 512, 512, "plain"),      # n-tile 64 of a wide layer: eight n-tiles, eight channel blocks
+    (3, 7, 7, 512, 64, "none"),
+    (2, 8, 8, 256, 96, "plain"),        # n-tile 32: one pass per thread
+    (4, 12, 10, 64, 128, "none"),
 ]
 
 
 @pytest.mark.parametrize("case", CHUNKED_CASES)
 def test_conv_layer_chunked_int16_residuals(cuda, case):
     """int16 residual tensors laid out by 8-channel chunk (TCBNN_RES_INT16_CHUNKED) in and out of
-    the loader-fed kernel: same values as the oracle's NHWC tensors; calls that cannot honour the
-    layout fail instead of misreading it."""
+    the loader-fed kernel -- its tile-per-group epilogue (one or two CTAs per SM) and, with an
+    NHWC tensor on the other side or path 7, the all-warps-per-tile epilogues: same values as the
+    oracle's NHWC tensors; calls that cannot honour the layout fail instead of misreading it."""
     B, H, W, C, O, mode = case
     g = util.rng(sum(case[:5]) + 5)
     Cw = C // 32
     x = util.rand_words(g, (B, H, W, Cw))
     f = util.rand_words(g, (O, 9, Cw))
     thr = (g.standard_normal(O) * np.sqrt(C * 9) * 0.5).astype(np.float32)
+    res_in, rc, rpool = None, 0, False
     if mode == "plain":
         res_in = g.integers(-300, 300, size=(B, H, W, O)).astype(np.int32)
-        rc, rpool = O, False
-    else:
+        rc = O
+    elif mode == "pool":
         res_in = g.integers(-300, 300, size=(B, 2 * H, 2 * W, O // 2)).astype(np.int32)
         rc, rpool = O // 2, True
     eo, er, _ = orc.conv_layer(x, f, thr, C, 3, 3, 1, 1, True, 1, res_in=res_in, residual_channels=rc,
                                residual_pool=rpool, save_residual=True)
+    eo_plain, _, _ = orc.conv_layer(x, f, thr, C, 3, 3, 1, 1, True, 1)
     d = ops.conv_desc(B, H, W, C, O, 3, 3)
+    assert ops.conv_prefers_chunked_residual(d)
     prep = ops.conv_prepare(d, dev(f, cuda))
-    r16 = ops.nhwc_to_chunked(dev(res_in.astype(np.int16), cuda))
-    out_chunked = ops.conv_prefers_chunked_residual(d)
-    go, gr, _ = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16, residual_channels=rc,
-                               residual_pool=rpool, save_residual=True, residual_dtype=torch.int16,
-                               res_in_chunked=True, res_out_chunked=out_chunked)
-    assert ops.conv_status(d, prep) == 0
-    if out_chunked:
-        gr = ops.chunked_to_nhwc(gr)
-    assert np.array_equal(gr.cpu().numpy().astype(np.int32), er)
-    assert np.array_equal(host_u32(go), eo)
+    r16 = ops.nhwc_to_chunked(dev(res_in.astype(np.int16), cuda)) if res_in is not None else None
+    dx, dthr = dev(x, cuda), dev(thr, cuda)
+    try:
+        for path in (0, 6, 8, 7):
+            ops.set_conv_path(path)
+            for out_chunked in (True, False):
+                for proven in (False, True):
+                    go, gr, _ = ops.conv_layer(d, dx, prep, dthr, res_in=r16, residual_channels=rc,
+                                               residual_pool=rpool, save_residual=True, residual_dtype=torch.int16,
+                                               res_in_chunked=r16 is not None, res_out_chunked=out_chunked,
+                                               res_out_proven=proven)
+                    assert ops.conv_status(d, prep) == 0
+                    if out_chunked:
+                        gr = ops.chunked_to_nhwc(gr)
+                    assert np.array_equal(gr.cpu().numpy().astype(np.int32), er), (path, out_chunked, proven)
+                    assert np.array_equal(host_u32(go), eo), (path, out_chunked, proven)
+            # no residual saved: chunked in only
+            if r16 is not None:
+                go, _, _ = ops.conv_layer(d, dx, prep, dthr, res_in=r16, residual_channels=rc, residual_pool=rpool,
+                                          res_in_chunked=True)
+                assert np.array_equal(host_u32(go), eo), path
+            # no residual at all: the fp32 comparison of the plain epilogues
+            go, _, _ = ops.conv_layer(d, dx, prep, dthr)
+            assert np.array_equal(host_u32(go), eo_plain), path
+            assert ops.conv_status(d, prep) == 0
+    finally:
+        ops.set_conv_path(0)
     if rpool:
-        # a workspace with room for the planes only: no pooling pass, the epilogue takes the 2x2
-        # maximum from the chunked tensor itself
+        # a workspace with room for the planes only (no pooling pass possible on any path)
         ws = torch.zeros((ops.new_planes_bytes(d),), dtype=torch.uint8, device=cuda)
-        go, gr, _ = ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16, residual_channels=rc,
+        go, gr, _ = ops.conv_layer(d, dx, prep, dthr, res_in=r16, residual_channels=rc,
                                    residual_pool=True, save_residual=True, residual_dtype=torch.int16,
                                    res_in_chunked=True, workspace=ws)
         assert np.array_equal(gr.cpu().numpy().astype(np.int32), er) and np.array_equal(host_u32(go), eo)
-    # without its workspace the layer runs on a kernel that does not know the layout: refused
-    with pytest.raises(Exception):
-        ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16, residual_channels=rc, residual_pool=rpool,
-                       workspace=False, res_in_chunked=True)
+    if r16 is not None:
+        # without its workspace the layer runs on a kernel that does not know the layout: refused
+        with pytest.raises(Exception):
+            ops.conv_layer(d, dx, prep, dthr, res_in=r16, residual_channels=rc, residual_pool=rpool,
+                           workspace=False, res_in_chunked=True)
+
+
+def test_conv_layer_reports_int16_overflow_on_tile_epilogue(cuda):
+    """A saved int16 residual that does not fit sets status 2 on the tile-per-group epilogue too,
+    unless the caller claimed to have proven the bound."""
+    g = util.rng(77)
+    B, H, W, C, O = 2, 6, 6, 64, 64
+    x = util.rand_words(g, (B, H, W, 2))
+    f = util.rand_words(g, (O, 9, 2))
+    thr = np.zeros(O, np.float32)
+    res_in = np.full((B, H, W, O), 32700, np.int16)
+    res_in[:, :, :, 1::2] = -32700
+    d = ops.conv_desc(B, H, W, C, O, 3, 3)
+    prep = ops.conv_prepare(d, dev(f, cuda))
+    r16 = ops.nhwc_to_chunked(dev(res_in, cuda))
+    ops.conv_layer(d, dev(x, cuda), prep, dev(thr, cuda), res_in=r16, residual_channels=O, save_residual=True,
+                   residual_dtype=torch.int16, res_in_chunked=True, res_out_chunked=True)
+    assert ops.conv_status(d, prep) == 2
+    assert ops.conv_status(d, prep) == 0          # reading clears it
 
 
 def test_specialized_first_layer_writes_chunked_residual(cuda):
