@@ -313,6 +313,11 @@ int tcbnn_mma_peak(int kind, int warps_per_sm, int iters, double* tops);
  * Synchronises.  The device context stays usable (the next call works as usual).  The reference has
  * no counterpart: its error handling is exit() on a failed CUDA call (utility.h:57-101). */
 int tcbnn_wait_probe(int polls, int* status);
+/* Measurement aid: clocks per tcgen05.mma kind::mxf4 of 128 x n x 64 (operands resident in shared
+ * memory, K-major without swizzle, issued back to back on every SM) when the A operand's
+ * descriptor starts `a_off16` 16-byte rows into its buffer -- the conv kernels address a filter
+ * tap by such an offset.  No reference counterpart. */
+int tcbnn_mma_operand_probe(int n, int a_off16, int iters, double* clocks_per_mma);
 /* Measurement aid: `ctas` CTAs (one per SM up to the SM count) each run `iters` rounds in which
  * one thread of each of `warps` warps issues `depth` bulk copies (cp.async.bulk, global -> shared,
  * completion on an mbarrier) of `bytes` back to back over an L2-resident buffer and then waits for

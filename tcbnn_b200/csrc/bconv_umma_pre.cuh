@@ -252,7 +252,6 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         __syncwarp();
     } else if (warp >= MMA_WARP && warp < MMA_WARP + kPreMmaWarps) {
         // =============================== MMA issuer =========================================
-        // (ring slot, accumulator and their barrier phases follow from the tile's index tc)
         // The whole warp runs the control flow converged and polls the barriers, and one elected
         // lane issues: what the issuing thread executes between two MMAs is time the tensor pipe
         // idles, and a lone lane in a diverged warp pays far more per branch and per wait.
@@ -277,19 +276,19 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             bool ok = true;
             long long tr_wc = 0, tr_wa = 0;
             const long long tr_t0 = clock64();
+            // ring slot, accumulator and their phases as running counters: a division by the
+            // ring depth per stage would sit between two groups of MMAs
+            static_assert(kPreMmaWarps == 1, "the counters below assume one issuing warp");
+            int s = 0, b = 0;
+            uint32_t sph = 0, bph = 0;
             for (uint32_t tc = w2; (long long)mfirst + (long long)tc * mstep < mtiles && ok; tc += kPreMmaWarps) {
-                const int b = (int)(tc % NACC);
-                const uint32_t bph = (tc / NACC) & 1u;
                 ok = a.trace ? wait.timed(BAR_CEMPTY(b), bph ^ 1, tr_wc) : wait.spin(BAR_CEMPTY(b), bph ^ 1);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d = tmem + b * NT;
                 uint32_t acc = 0;
                 uint32_t bLo = bLo0;
-                it = tc * NCB;
                 for (int cb = 0; cb < NCB && ok; cb++, it++) {
-                    const int s = (int)(it % (uint32_t)NSTAGE);
-                    const uint32_t sph = (it / (uint32_t)NSTAGE) & 1u;
                     ok = a.trace ? wait.timed(BAR_AFULL(s), sph, tr_wa) : wait.spin(BAR_AFULL(s), sph);
                     if (!ok) break;
                     tc_fence_after();
@@ -310,8 +309,10 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                     acc = 1;
                     mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
                     }
+                    if (++s == NSTAGE) { s = 0; sph ^= 1u; }
                 }
                 if (ok && leader) mma_commit(BAR_CFULL(b));       // accumulator complete
+                if (++b == NACC) { b = 0; bph ^= 1u; }
             }
             if (!ok && leader) {
                 // giving up: the MMAs already issued must have finished before tensor memory is freed

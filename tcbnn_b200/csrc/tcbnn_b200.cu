@@ -852,6 +852,47 @@ __global__ void __launch_bounds__(128) k_umma_peak_mxf4(int iters, long long* cy
     if (threadIdx.x < 32) umma::tmem_dealloc(tmem, 512);
 }
 
+// What the position of the A operand costs: 128 x n x 64 MMAs (kind::mxf4, K-major without swizzle)
+// back to back, A's descriptor starting `a_off16` 16-byte rows into its buffer -- the conv kernels
+// address a filter tap by such an offset, so most of their operands start in the middle of an
+// 8-row core matrix.  CTA 0 reports its clocks.
+__global__ void __launch_bounds__(128) k_umma_operand_probe(int n, int a_off16, int iters, long long* cycles, int* err) {
+    extern __shared__ __align__(1024) unsigned char peak_smem[];
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tm;
+    if (threadIdx.x < 32) umma::tmem_alloc(umma::smem_u32(&tm), 512);
+    if (threadIdx.x == 0) umma::mbar_init(umma::smem_u32(&bar), 1);
+    for (int i = threadIdx.x; i < 49152 / 4; i += blockDim.x) ((uint32_t*)peak_smem)[i] = 0x22222222u;
+    umma::fence_proxy_async();
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    const uint32_t tmem = tm;
+    umma::tmem_fill_unit_scales(tmem, 480);
+    umma::tc_fence_before();
+    __syncthreads();
+    umma::tc_fence_after();
+    if (threadIdx.x == 0) {
+        // A: two chunk planes of 320 rows (room for the offset), B behind them: two planes of n rows
+        const uint64_t da = umma::smem_desc(umma::smem_u32(peak_smem) + 16u * (uint32_t)a_off16, 320 * 16, 128);
+        const uint64_t db = umma::smem_desc(umma::smem_u32(peak_smem + 16384), (uint32_t)n * 16, 128);
+        const uint32_t idesc = umma::idesc_f4(n);
+        const long long t0 = clock64();
+        for (int i = 0; i < iters; i += 8) {
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                umma::mma_f4_split(tmem, (uint32_t)da, (uint32_t)(da >> 32), (uint32_t)db, (uint32_t)(db >> 32), idesc,
+                                   (i | u) ? 1u : 0u, tmem + 480u, tmem + 496u);
+        }
+        umma::mma_commit(umma::smem_u32(&bar));
+        if (!umma::mbar_wait(umma::smem_u32(&bar), 0, err)) { /* status already recorded */ }
+        if (blockIdx.x == 0) cycles[0] = clock64() - t0;
+    }
+    umma::tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) umma::tmem_dealloc(tmem, 512);
+}
+
 // What the issuing thread's bookkeeping costs: 128x128x32 MMAs in groups of `group`, with per
 // group nothing (MODE 0), a try_wait on a completed barrier plus a commit by a lone lane inside
 // `if (threadIdx.x == 0)` (MODE 1), or a test_wait by the converged warp plus a commit by the lane
@@ -1761,6 +1802,29 @@ int tcbnn_bulk_copy_rate(int bytes, int depth, int warps, int ctas, int iters, d
     }
     *bytes_per_clock = (double)bytes * depth * warps * iters / (double)worst;
     *issue_clocks_per_copy = (double)issue / ((double)depth * iters);
+    return 0;
+}
+
+int tcbnn_mma_operand_probe(int n, int a_off16, int iters, double* clocks_per_mma) {
+    if (!clocks_per_mma || n < 16 || n > 256 || n % 16 || a_off16 < 0 || a_off16 > 128 || iters < 8 || iters > (1 << 18))
+        return fail("mma_operand_probe: n a multiple of 16 up to 256, offset 0..128 rows, 8..2^18 iterations");
+    int sms;
+    if (sm_count(&sms)) return 1;
+    long long* buf = nullptr;
+    CUDA_TRY(cudaMalloc(&buf, 16));
+    CUDA_TRY(cudaMemset(buf, 0, 16));
+    cudaError_t e = cudaFuncSetAttribute(k_umma_operand_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024);
+    iters &= ~7;
+    for (int rep = 0; rep < 2 && e == cudaSuccess; rep++) {
+        k_umma_operand_probe<<<sms, 128, 48 * 1024>>>(n, a_off16, iters, buf, (int*)(buf + 1));
+        e = cudaDeviceSynchronize();
+    }
+    long long host[2] = {0, 0};
+    if (e == cudaSuccess) e = cudaMemcpy(host, buf, sizeof host, cudaMemcpyDeviceToHost);
+    cudaFree(buf);
+    if (e != cudaSuccess) return fail("mma_operand_probe: %s", cudaGetErrorString(e));
+    if ((int)host[1]) return fail("mma_operand_probe: a bounded wait gave up");
+    *clocks_per_mma = (double)host[0] / iters;
     return 0;
 }
 

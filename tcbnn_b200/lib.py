@@ -45,6 +45,7 @@ SIGNATURES = {
     "tcbnn_set_conv_path": (_I, [_I]),
     "tcbnn_conv_set_trace": (_I, [_P]),
     "tcbnn_set_gemm_plan": (_I, [_I, _I]),
+    "tcbnn_mma_operand_probe": (_I, [_I, _I, _I, C.POINTER(C.c_double)]),
     "tcbnn_bulk_copy_rate": (_I, [_I, _I, _I, _I, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "tcbnn_conv_status": (_I, [C.POINTER(ConvDesc), _P, C.POINTER(C.c_int)]),
     "tcbnn_inconv_layer": (_I, [C.POINTER(ConvDesc), _P, _P, _P, _P, _LL, _P, _I, _P, _P]),
