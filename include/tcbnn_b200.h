@@ -194,7 +194,8 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
  * two smaller CTAs per SM when they fit), 7 = as 0 but without the loader-fed kernel's
  * tile-per-group epilogues (0 uses them for layers without residuals and for chunk-major int16
  * residuals), 8 = as 0 but two CTAs per SM also for the all-warps-per-tile residual epilogues at an
- * n-tile of 64.
+ * n-tile of 64, 9 = as 0 but the loader-fed kernel's stages hold one 64-channel block each (0
+ * puts four or two in a stage where three such stages fit).
  * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);

@@ -138,7 +138,11 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     const int RS = a.R * a.S, NCB = a.C >> 6;
     const int NPLANE = a.stride == 2 ? 4 : 1;
     const uint32_t plane_bytes = 2u * a.NPOS * 16u;           // two 32-channel chunk planes
-    const uint32_t stage_bytes = NPLANE * plane_bytes;
+    const uint32_t block_bytes = NPLANE * plane_bytes;        // one 64-channel block of a tile's patch
+    // A stage holds one, two or four blocks: the issuing thread's wait / commit round per stage is
+    // time the tensor pipe idles, so layers with several blocks pay it once per 2 or 4 x RS MMAs.
+    const int CBS = a.pre_cbs;
+    const uint32_t stage_bytes = (uint32_t)CBS * block_bytes;
 
     unsigned char* sAraw = smem;
     uint4* sB = reinterpret_cast<uint4*>(smem + (size_t)NSTAGE * stage_bytes);
@@ -222,19 +226,20 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             bool ok = true;
             for (int m = mfirst; m < mtiles && ok; m += mstep) {
                 const long long slot0 = (long long)m * 128 - back + a.pre_front;
-                for (int cb = 0; cb < NCB; cb++, it++) {
+                for (int cb = 0; cb < NCB; cb += CBS, it++) {
                     // the ring is several tiles deep: this lane mostly waits for a slot, and sleeps
                     // between polls so that it does not take issue slots from the epilogue warps
                     ok = wait.relaxed(BAR_AEMPTY(s), sph ^ 1);
                     if (!ok) break;
                     mbar_expect_tx(BAR_AFULL(s), stage_bytes);
                     const uint32_t dst = smem_u32(sAraw + (size_t)s * stage_bytes);
-                    for (int pl = 0; pl < NPLANE; pl++)
+                    for (int sub = 0; sub < CBS; sub++)
+                        for (int pl = 0; pl < NPLANE; pl++)
 #pragma unroll
-                        for (int c = 0; c < 2; c++)
-                            bulk_g2s(dst + (uint32_t)(pl * 2 + c) * (uint32_t)a.NPOS * 16u,
-                                     a.pre + ((size_t)(cb * 2 + c) * NPLANE + pl) * a.pre_positions + slot0,
-                                     (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
+                            for (int c = 0; c < 2; c++)
+                                bulk_g2s(dst + (uint32_t)sub * block_bytes + (uint32_t)(pl * 2 + c) * (uint32_t)a.NPOS * 16u,
+                                         a.pre + ((size_t)((cb + sub) * 2 + c) * NPLANE + pl) * a.pre_positions + slot0,
+                                         (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
                     if (++s == NSTAGE) { s = 0; sph ^= 1; }
                 }
             }
@@ -265,6 +270,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
             const uint32_t aHi = (uint32_t)(descA0 >> 32), bHi = (uint32_t)(descB0 >> 32);
             const uint32_t aLo0 = (uint32_t)descA0, bLo0 = (uint32_t)descB0;
             const uint32_t stepB = (2u * lboB) >> 4, stepStage = stage_bytes >> 4;   // one tap = two chunks of B
+            const uint32_t stepBlock = block_bytes >> 4;
             constexpr uint32_t IDESC = idesc_f4(NT);
             const uint32_t sfa = tmem + SF_COL, sfb = tmem + SF_COL + 16;
             const bool rs9 = RS == 9;
@@ -288,25 +294,27 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 const uint32_t d = tmem + b * NT;
                 uint32_t acc = 0;
                 uint32_t bLo = bLo0;
-                for (int cb = 0; cb < NCB && ok; cb++, it++) {
+                for (int cb = 0; cb < NCB && ok; cb += CBS, it++) {
                     ok = a.trace ? wait.timed(BAR_AFULL(s), sph, tr_wa) : wait.spin(BAR_AFULL(s), sph);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t aLo = aLo0 + s * stepStage;
                     if (leader) {
-                    if (rs9) {
+                    for (int sub = 0; sub < CBS; sub++) {
+                        const uint32_t aLo = aLo0 + s * stepStage + sub * stepBlock;
+                        if (rs9) {
 #pragma unroll
-                        for (int t = 0; t < 9; t++)
-                            mma_f4_split(d, aLo + tapk[t], aHi, bLo + t * stepB, bHi, IDESC, t == 0 ? acc : 1u, sfa, sfb);
-                        bLo += 9 * stepB;
-                    } else {
-                        for (int t = 0; t < RS; t++) {
-                            mma_f4_split(d, aLo + sTapK[t], aHi, bLo, bHi, IDESC, acc, sfa, sfb);
-                            acc = 1;
-                            bLo += stepB;
+                            for (int t = 0; t < 9; t++)
+                                mma_f4_split(d, aLo + tapk[t], aHi, bLo + t * stepB, bHi, IDESC, t == 0 ? acc : 1u, sfa, sfb);
+                            bLo += 9 * stepB;
+                        } else {
+                            for (int t = 0; t < RS; t++) {
+                                mma_f4_split(d, aLo + sTapK[t], aHi, bLo, bHi, IDESC, acc, sfa, sfb);
+                                acc = 1;
+                                bLo += stepB;
+                            }
                         }
+                        acc = 1;
                     }
-                    acc = 1;
                     mma_commit(BAR_AEMPTY(s));          // stage free once these MMAs have read it
                     }
                     if (++s == NSTAGE) { s = 0; sph ^= 1u; }

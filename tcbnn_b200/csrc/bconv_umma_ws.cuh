@@ -45,6 +45,7 @@ struct ConvWsArgs {
     const uint4* pre;         // pre-expanded input planes (bconv_umma_pre.cuh), else null
     long long pre_positions, pre_front;
     int pre_stages;           // patch ring depth of that kernel
+    int pre_cbs;              // 64-channel blocks per stage of that ring (1, 2 or 4)
     // optional: also write the output as +-1 nibbles into the next layer's input planes
     // (bconv_umma_pre.cuh layout over THAT layer's raster; dead slots stay as the caller zeroed them)
     uint4* nxt; long long nxt_positions, nxt_front; int nxt_PW, nxt_VH;

@@ -468,6 +468,7 @@ int launch_inconv_tiled(const InConvArgs& c, size_t smem, int sms, cudaStream_t 
 int g_conv_two_ctas = 1;  // loader-fed kernel, n-tile 64: two CTAs of eight epilogue warps per SM when they fit
 int g_conv_res_stage = 1; // loader-fed kernel: stage int16 residual rows in shared memory when possible
 int g_conv_tile = 1;      // loader-fed kernel: the tile-per-group epilogues where the tensors allow them
+int g_conv_cbs = 1;       // loader-fed kernel: four or two 64-channel blocks per stage where they fit
 
 // The tile-per-group epilogues of the loader-fed kernel take residuals only in the chunk-major
 // int16 layout and write no int32 accumulators.
@@ -542,7 +543,7 @@ template <int EPI>
 int launch_conv_umma_pre_64(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t st) {
     if (g_conv_two_ctas && (EPI == umma::kEpiPlain || EPI == umma::kEpiTile || EPI == umma::kEpiTileRes || g_conv_two_ctas == 2)) {
         int stages = a.pre_stages;
-        const int nplane = a.stride == 2 ? 4 : 1;
+        const int nplane = (a.stride == 2 ? 4 : 1) * a.pre_cbs;
         while (stages > 3 && umma::pre_smem_bytes(a.NPOS, a.C, a.R * a.S, 64, stages, nplane) > 113 * 1024) stages--;
         const size_t need = umma::pre_smem_bytes(a.NPOS, a.C, a.R * a.S, 64, stages, nplane);
         if (need <= 113 * 1024) {
@@ -585,7 +586,7 @@ int launch_conv_umma_pre(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream_t
         if ((a.res_in || a.res_out) && in_ok && out_ok && g_conv_res_stage && (NT >= 128 || g_conv_res_stage == 2)) {
             int stages = a.pre_stages;
             const int RS = a.R * a.S;
-            const int nplane = a.stride == 2 ? 4 : 1;
+            const int nplane = (a.stride == 2 ? 4 : 1) * a.pre_cbs;
             while (stages > 2 && umma::pre_smem_bytes(a.NPOS, a.C, RS, NT, stages, nplane) + umma::pre_res_stage_bytes(NT) > 227 * 1024)
                 stages--;
             const size_t need = umma::pre_smem_bytes(a.NPOS, a.C, RS, NT, stages, nplane) + umma::pre_res_stage_bytes(NT);
@@ -1363,7 +1364,7 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
         a.err_flag = (int*)(p + L.off_err);
         a.trace = g_conv_trace;
         a.pre = nullptr; a.pre_positions = 0; a.pre_front = 0;
-        a.pre_stages = 0;
+        a.pre_stages = 0; a.pre_cbs = 1;
         a.nxt = nullptr; a.nxt_positions = 0; a.nxt_front = 0; a.nxt_PW = 0; a.nxt_VH = 0; a.nxt_nplane = 1;
         if (nx && !use_as && !pooled) {     // (a pooled layer's kernel sees the pre-pool grid)
             a.nxt = nx->planes; a.nxt_positions = nx->positions; a.nxt_front = nx->front;
@@ -1392,6 +1393,20 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
             if ((uintptr_t)workspace & 255) return fail("conv_layer: workspace must be 256-byte aligned");
             a.pre = (const uint4*)workspace; a.pre_positions = L.pre_positions; a.pre_front = L.pre_front;
             a.pre_stages = L.pre_stages;
+            a.pre_cbs = 1;
+            size_t pre_smem = L.pre_smem;
+            if (g_conv_cbs) {
+                // four or two 64-channel blocks per stage where at least three such stages fit
+                const int RS = d->R * d->S;
+                for (int cbs = 4; cbs >= 2 && a.pre_cbs == 1; cbs >>= 1) {
+                    if ((d->C / 64) % cbs) continue;
+                    const int np = (d->stride_h == 2 ? 4 : 1) * cbs;
+                    int stages = 6;
+                    while (stages > 3 && umma::pre_smem_bytes(L.umma_npos, d->C, RS, L.pre_nt, stages, np) > 227 * 1024) stages--;
+                    const size_t need = umma::pre_smem_bytes(L.umma_npos, d->C, RS, L.pre_nt, stages, np);
+                    if (need <= 227 * 1024) { a.pre_cbs = cbs; a.pre_stages = stages; pre_smem = need; }
+                }
+            }
             // a pooled int16 residual is reduced by a streaming pass first when the workspace has
             // the room behind the planes: four scattered loads per value in the epilogue cost more
             const size_t pooled_res_bytes = (size_t)d->B * d->OH * d->OW * (size_t)res_in_ch * 2;
@@ -1412,9 +1427,9 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
                 a.res_in = pooled_res; a.residual_pool = 0;
                 a.res_in_chunked = 0; a.res_in_npix = (long long)d->B * d->OH * d->OW;     // the pooled copy is NHWC
             }
-            if (L.pre_nt == 32) return launch_conv_umma_pre<32>(a, L.pre_smem, sms, st, !workspace_ready);
-            if (L.pre_nt == 64) return launch_conv_umma_pre<64>(a, L.pre_smem, sms, st, !workspace_ready);
-            if (L.pre_nt == 128) return launch_conv_umma_pre<128>(a, L.pre_smem, sms, st, !workspace_ready);
+            if (L.pre_nt == 32) return launch_conv_umma_pre<32>(a, pre_smem, sms, st, !workspace_ready);
+            if (L.pre_nt == 64) return launch_conv_umma_pre<64>(a, pre_smem, sms, st, !workspace_ready);
+            if (L.pre_nt == 128) return launch_conv_umma_pre<128>(a, pre_smem, sms, st, !workspace_ready);
         }
 #define TCBNN_WS_CASE(NN, SS) \
         if (L.umma_nt == NN && d->stride_h == SS) return launch_conv_umma_ws<NN, SS>(a, L.umma_smem, sms, st);
@@ -1488,14 +1503,16 @@ int tcbnn_conv_prefers_chunked_residual(const tcbnn_conv_desc* d) {
 }
 
 int tcbnn_set_conv_path(int path) {
-    if (path < 0 || path > 8)
+    if (path < 0 || path > 9)
         return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05, 3 = tcgen05 filter-stationary kernel only, "
                     "4 / 5 = automatic with residual staging never / wherever possible, 6 = automatic, one CTA per SM only, "
-                    "7 = automatic without the tile-per-group epilogues, 8 = automatic, two CTAs per SM wherever they fit");
+                    "7 = automatic without the tile-per-group epilogues, 8 = automatic, two CTAs per SM wherever they fit, "
+                    "9 = automatic, one 64-channel block per stage");
     g_conv_path = path >= 4 ? 0 : path;
     g_conv_res_stage = path == 4 ? 0 : path == 5 ? 2 : 1;
     g_conv_two_ctas = path == 6 ? 0 : path == 8 ? 2 : 1;
     g_conv_tile = path == 7 ? 0 : 1;
+    g_conv_cbs = path == 9 ? 0 : 1;
     return 0;
 }
 
