@@ -338,7 +338,11 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
         const int grp = warp / WPG, quad = warp & 3, half = (warp % WPG) >> 2;
         const int row = quad * 32 + lane;
         const int Ow = (a.O + 31) >> 5;
-        const int o0 = obase + half * CPT;                 // this thread's first output channel
+        // Pass k of a thread covers the tile's 32-column block k (groups of 4 warps) or 2k + half
+        // (groups of 8: the two halves interleave, so that a residual injected into the first
+        // channels only -- the first block of a stage -- is shared between them).
+        constexpr int HSTEP = WPG / 4;                     // 32-column blocks between a thread's passes
+        const int o0 = obase + half * 32;                  // this thread's first output channel
         const int lim = (RES && a.res_in) ? min(a.residual_channels, a.res_in_ch) : 0;
         const bool has_in = RES && a.res_in && o0 < lim;
         const uint4* rin = reinterpret_cast<const uint4*>(a.res_in) + (size_t)(o0 >> 3) * a.res_in_npix;
@@ -373,8 +377,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         r[j] = z;
-                        if (live && o0 + 32 * k + 8 * j < lim) {
-                            const uint4* q = rin + (size_t)(4 * k + j) * a.res_in_npix + i00;
+                        if (live && o0 + 32 * HSTEP * k + 8 * j < lim) {
+                            const uint4* q = rin + (size_t)(4 * HSTEP * k + j) * a.res_in_npix + i00;
                             const uint4 w0 = __ldg(q), w1 = __ldg(q + 1), w2 = __ldg(q + rw), w3 = __ldg(q + rw + 1);
                             r[j].x = __vmaxs2(__vmaxs2(w0.x, w1.x), __vmaxs2(w2.x, w3.x));
                             r[j].y = __vmaxs2(__vmaxs2(w0.y, w1.y), __vmaxs2(w2.y, w3.y));
@@ -385,7 +389,8 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; j++)
-                        r[j] = (live && o0 + 32 * k + 8 * j < lim) ? __ldg(rin + (size_t)(4 * k + j) * a.res_in_npix + opix) : z;
+                        r[j] = (live && o0 + 32 * HSTEP * k + 8 * j < lim)
+                                   ? __ldg(rin + (size_t)(4 * HSTEP * k + j) * a.res_in_npix + opix) : z;
                 }
             };
             if (RES && has_in) fetch(0);                   // flies while the accumulator is awaited
@@ -396,7 +401,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
 #pragma unroll
             for (int k = 0; k < PASSES; k++) {
                 int v[32];
-                tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * NT + half * CPT + k * 32, v);
+                tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * NT + (HSTEP * k + half) * 32, v);
                 tmem_ld_wait();
                 if (k == PASSES - 1) {
                     tc_fence_before();                     // this warp is done with the accumulator
@@ -407,7 +412,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                 if (!RES) {
                     // the reference's comparison as it stands, !((float)value < threshold)
                     // (kernel.cuh:795-796), on the fp32 accumulator
-                    const float4* tf4 = reinterpret_cast<const float4*>(sThrF + half * CPT + k * 32);
+                    const float4* tf4 = reinterpret_cast<const float4*>(sThrF + (HSTEP * k + half) * 32);
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         const float4 th = tf4[j];
@@ -433,7 +438,7 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
                         }
                         if (k + 1 < PASSES) fetch(k + 1);  // the next pass's residual flies during this one's arithmetic
                     }
-                    const int4* th4 = reinterpret_cast<const int4*>(sThr + half * CPT + k * 32);
+                    const int4* th4 = reinterpret_cast<const int4*>(sThr + (HSTEP * k + half) * 32);
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         const int4 th = th4[j];
@@ -455,21 +460,21 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
 #pragma unroll
                             for (int kk = 0; kk < 4; kk++)
                                 w[kk] = ((uint32_t)v[8 * j + 2 * kk] & 0xFFFFu) | ((uint32_t)v[8 * j + 2 * kk + 1] << 16);
-                            rout[(size_t)(4 * k + j) * a.res_out_npix + opix] = make_uint4(w[0], w[1], w[2], w[3]);
+                            rout[(size_t)(4 * HSTEP * k + j) * a.res_out_npix + opix] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     }
                 }
                 words[k] = word;
-                if (a.nxt && live) store_next_planes(a, n, y, x, o0 + 32 * k, word, 32);
+                if (a.nxt && live) store_next_planes(a, n, y, x, o0 + 32 * HSTEP * k, word, 32);
             }
             if (live) {
                 // bits of channel o live at bit 31 - o%32 of word o/32
                 uint32_t* wp = a.out + (size_t)n * a.out_image_stride + ((size_t)y * a.OWg + x) * Ow + (o0 >> 5);
-                if (PASSES == 2 && (reinterpret_cast<uintptr_t>(wp) & 7) == 0) {
+                if (PASSES == 2 && HSTEP == 1 && (reinterpret_cast<uintptr_t>(wp) & 7) == 0) {
                     *reinterpret_cast<uint2*>(wp) = make_uint2(words[0], words[PASSES - 1]);
                 } else {
 #pragma unroll
-                    for (int k = 0; k < PASSES; k++) wp[k] = words[k];
+                    for (int k = 0; k < PASSES; k++) wp[HSTEP * k] = words[k];
                 }
             }
         }
