@@ -12,13 +12,14 @@
 //   fc N
 //   out N
 // A weights name ending in ".bin" is raw fp32 in launch_array order, anything else the
-// reference's text format.  TCBNN_RESIDUAL16=1 keeps the saved residuals as int16 (the caller's
+// reference's text format.  TCBNN_RESIDUAL16=1 (or =chunked, the chunk-major layout) keeps the saved residuals as int16 (the caller's
 // promise that they fit; an overflow is reported and fails the run).  TCBNN_RUNS=n runs the forward pass n times (the last one is timed);
 // TCBNN_DUMP_DIR=<dir> also writes every layer's download_full_output() as layerNN.bin.
 // TCBNN_TEXT_SIGNATURES=1 (text weights) builds the layers through the reference's own
 // initialize(FILE*, ...) signatures.  TCBNN_LIVE_BATCH=n: after the first runs on the full batch the
 // same objects are switched to the first n images (set_batch) for the last, timed run; logits and
 // dumps then hold n images.
+#include <cstring>
 #include <string>
 #include <vector>
 #include "tcbnn_host.hpp"
@@ -62,7 +63,10 @@ int main(int argc, char** argv) {
     std::vector<float> images;
     uin32* prev = NULL;
     int H = 0, W = 0, K = 0;
-    const int res_bytes = getenv("TCBNN_RESIDUAL16") ? 2 : 4;
+    // TCBNN_RESIDUAL16=1: int16 residual tensors; =chunked: int16 in the chunk-major layout the
+    // tcgen05 conv kernel's epilogue is fastest on (every conv layer has its workspace here)
+    const char* r16 = getenv("TCBNN_RESIDUAL16");
+    const int res_bytes = !r16 ? 4 : (strcmp(r16, "chunked") == 0 ? TCBNN_RES_INT16_CHUNKED : 2);
     const bool text_sig = getenv("TCBNN_TEXT_SIGNATURES") != NULL && !binary;
     while (fscanf(spec, "%63s", word) == 1) {
         const std::string t(word);

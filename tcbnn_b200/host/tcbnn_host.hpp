@@ -60,6 +60,13 @@ inline T* dev_alloc(size_t count, bool zero = true) {
     return p;
 }
 
+// set_residual_bytes takes a residual format of the C header: 4 (int32, the reference's), 2 (int16)
+// or TCBNN_RES_INT16_CHUNKED (int16 by 8-channel chunk, the layout the tcgen05 conv kernel's
+// epilogue is fastest on; every layer that injects the tensor must then run that kernel, i.e. have
+// its workspace, or its call fails).  Anything else means int32.
+inline int residual_code(int code) { return (code == 2 || code == TCBNN_RES_INT16_CHUNKED) ? code : 4; }
+inline int residual_elem_bytes(int code) { return code == 4 ? 4 : 2; }
+
 // What a layer that saves its residual tells the layers that inject it: the reference hands over
 // a bare int* (param.h:944), so channel count and element size travel through this table.
 struct ResidualInfo { const void* ptr; int channels; int bytes; };
@@ -353,7 +360,7 @@ public:
     // Extension: keep the saved residual as int16 instead of the reference's int (call before
     // initialize()).  The caller vouches that R*S*3*max|pixel| < 32768; the residual layers are
     // bound by this tensor's traffic, which it halves.
-    void set_residual_bytes(int bytes) { residual_bytes = bytes == 2 ? 2 : 4; }
+    void set_residual_bytes(int bytes) { residual_bytes = residual_code(bytes); }
     size_t input_size() const { return (size_t)desc.B * 3 * desc.H * desc.W; }
     size_t output_size() const { return (size_t)batch * desc.OH * desc.OW * desc.O; }   // at the constructor's batch
     // the following passes process the first n images (n <= the constructor's batch)
@@ -383,7 +390,7 @@ public:
         output_gpu = dev_alloc<uin32>((size_t)desc.B * desc.OH * desc.OW * Ow());
         if (save_residual) {
             output_residual_gpu = (int*)dev_alloc<char>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O *
-                                                        residual_bytes);
+                                                        residual_elem_bytes(residual_bytes));
             publish_residual(output_residual_gpu, desc.O, residual_bytes);
         }
         // the layer compiled for its filter, where the library offers it (at most 128 output channels)
@@ -458,7 +465,7 @@ public:
     // Extension: save this layer's residual as int16 (call before initialize()).  The caller vouches
     // that the running sum fits: |value| <= C*R*S + bound of the injected residual.  A value that
     // does not fit raises status 2 (overflowed()).
-    void set_residual_bytes(int bytes) { residual_bytes = bytes == 2 ? 2 : 4; }
+    void set_residual_bytes(int bytes) { residual_bytes = residual_code(bytes); }
     bool overflowed() {
         int st = 0;
         TCBNN_HOST_CALL(tcbnn_conv_status(&desc, prepared_gpu, &st));
@@ -501,7 +508,7 @@ public:
         output_gpu = dev_alloc<uin32>((size_t)desc.B * out_image_stride);
         if (save_residual) {
             output_residual_gpu = (int*)dev_alloc<char>((size_t)desc.B * desc.pool * desc.OH * desc.pool * desc.OW * desc.O *
-                                                        residual_bytes);
+                                                        residual_elem_bytes(residual_bytes));
             publish_residual(output_residual_gpu, desc.O, residual_bytes);
         }
         input_gpu = prev_layer_gpu;
@@ -512,7 +519,7 @@ public:
             }
             input_residual_gpu = _input_residual_gpu;
             input_residual_channels = input_residual_channels_;
-            input_residual_bytes = input_residual_bytes_ == 2 ? 2 : 4;
+            input_residual_bytes = residual_code(input_residual_bytes_);
         }
         return this;
     }

@@ -195,7 +195,8 @@ def main():
             rout = torch.empty((Bn, d.OH, d.OW, O), dtype=torch.int16, device=dev)
         ch = bool(a.chunked and a.residual)
         ms = _time(lambda: ops.conv_layer(d, x, prep, thr, res_in=rin, residual_channels=O if rin is not None else 0,
-                                          out=out, res_out_buf=rout, res_in_chunked=ch, res_out_chunked=ch), a.iters)
+                                          out=out, res_out_buf=rout, res_in_chunked=ch, res_out_chunked=ch,
+                                          res_out_proven=ch), a.iters)
         work = 2.0 * Bn * d.OH * d.OW * O * 9 * C
         desc = "bit conv %dx%dx%dx%d -> %d, 3x3 stride %d%s%s" % (Bn, H, H, C, O, st, " + int16 residual in/out" if a.residual else "",
                                                                 " (chunk-major)" if ch else "")

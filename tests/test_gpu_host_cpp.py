@@ -40,6 +40,14 @@ def test_host_cpp_int16_residuals(cuda, tmp_path, monkeypatch):
     _run(models.resnet18_spec(4, image=64, classes=100), 85, tmp_path, cuda, runner=hbuild.build_fast_runner())
 
 
+def test_host_cpp_chunked_int16_residuals(cuda, tmp_path, monkeypatch):
+    """set_residual_bytes(TCBNN_RES_INT16_CHUNKED) on every layer: the conv layers run the
+    tile-per-group epilogue on chunk-major residual tensors; same activations and logits."""
+    monkeypatch.setenv("TCBNN_RESIDUAL16", "chunked")
+    _run(models.resnet18_spec(4, image=64, classes=100), 89, tmp_path, cuda, runner=hbuild.build_fast_runner())
+    _run(models.resnet18_spec(3), 90, tmp_path, cuda, runner=hbuild.build_fast_runner(), runs=2)
+
+
 def test_host_cpp_reference_signatures_and_ragged_batch(cuda, tmp_path):
     """The layer lines of a reference driver compile against the host classes as they are:
     initialize(FILE*, prev [, residual]) with the residual's channel count and element size looked
