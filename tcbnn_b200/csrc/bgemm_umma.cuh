@@ -62,34 +62,53 @@ __device__ __forceinline__ uint32_t nibble_mask8(uint32_t b) {
 }
 
 // packed bits [rows][ld words] (bit k of a row at bit 31 - k%32 of word k/32) -> units; one launch
-// expands both operands: units [0, RT_a*KB) belong to A, the rest to W
+// expands both operands.  A task is (128-row tile, group of four k-blocks): 256 threads, two per
+// row, each reading the 16 bytes (four 32-bit chunks) of its row that fall into its half of the
+// group -- a whole 32-byte sector per row -- and writing four 16-byte slots; for a given chunk the
+// threads of a warp write two runs of 256 contiguous bytes.  Tasks [0, RT_a * KG) belong to A, the
+// rest to W (KG = groups per row tile).  lda / ldw are even, so the 8-byte loads are aligned.
 __device__ __forceinline__ void expand_rows_pair(const uint32_t* a_bits, int a_rows, int a_ld, int RT_a,
                                                  const uint32_t* w_bits, int w_rows, int w_ld, int RT_w,
                                                  int K, int KB, uint4* out_a, uint4* out_w) {
-    const long long na = (long long)RT_a * KB * 2 * 128, total = na + (long long)RT_w * KB * 2 * 128;
-    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total;
-         i0 += (long long)gridDim.x * blockDim.x) {
-        const bool isw = i0 >= na;
-        const long long i = isw ? i0 - na : i0;
+    // the GEMM that consumes these units may be set up meanwhile (it waits before its first copy)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int KG = (KB + 3) >> 2;
+    const int tasks = (RT_a + RT_w) * KG;
+    const int t = threadIdx.x, row = t >> 1, half = t & 1;
+    for (int task = blockIdx.x; task < tasks; task += gridDim.x) {
+        const bool isw = task >= RT_a * KG;
+        const int tk = isw ? task - RT_a * KG : task;
+        const int rt = tk / KG, kg = tk - rt * KG;
         const uint32_t* bits = isw ? w_bits : a_bits;
         const int rows = isw ? w_rows : a_rows, ld = isw ? w_ld : a_ld;
-        const int row = (int)(i & 127);
-        const int chunk = (int)((i >> 7) & 1);
-        const long long u = i >> 8;
-        const int kb = (int)(u % KB), rt = (int)(u / KB);
-        const int r = rt * 128 + row, k0 = kb * 64 + chunk * 32;
-        uint4 e = make_uint4(0u, 0u, 0u, 0u);
-        if (r < rows && k0 < K) {
-            const uint32_t w = __ldg(bits + (size_t)r * ld + (k0 >> 5));
-            e = expand32_f4(w);
-            const int valid = K - k0;                   // elements of this word that exist
-            if (valid < 32) {                           // the rest is padding: 0, not -1
-                const uint32_t m = 0xFFFFFFFFu << (32 - valid);
-                e.x &= nibble_mask8(m >> 24); e.y &= nibble_mask8(m >> 16);
-                e.z &= nibble_mask8(m >> 8);  e.w &= nibble_mask8(m);
-            }
+        uint4* out = (isw ? out_w : out_a) + (size_t)rt * KB * 256;      // 256 slots of 16 bytes per unit
+        const int r = rt * 128 + row;
+        const int w0 = kg * 8 + half * 4;                                // first 32-bit chunk of this thread
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (r < rows) {
+            const uint32_t* src = bits + (size_t)r * ld + w0;
+            if (w0 + 1 < ld) { const uint2 q = __ldg(reinterpret_cast<const uint2*>(src)); w[0] = q.x; w[1] = q.y; }
+            else if (w0 < ld) w[0] = __ldg(src);
+            if (w0 + 3 < ld) { const uint2 q = __ldg(reinterpret_cast<const uint2*>(src + 2)); w[2] = q.x; w[3] = q.y; }
+            else if (w0 + 2 < ld) w[2] = __ldg(src + 2);
         }
-        (isw ? out_w : out_a)[i] = e;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int c = w0 + j, kb = c >> 1;                           // chunk -> k-block
+            if (kb >= KB) break;
+            const int k0 = c * 32;
+            uint4 e = make_uint4(0u, 0u, 0u, 0u);
+            if (r < rows && k0 < K) {
+                e = expand32_f4(w[j]);
+                const int valid = K - k0;                                // elements of this chunk that exist
+                if (valid < 32) {                                        // the rest is padding: 0, not -1
+                    const uint32_t m = 0xFFFFFFFFu << (32 - valid);
+                    e.x &= nibble_mask8(m >> 24); e.y &= nibble_mask8(m >> 16);
+                    e.z &= nibble_mask8(m >> 8);  e.w &= nibble_mask8(m);
+                }
+            }
+            out[(size_t)kb * 256 + (c & 1) * 128 + row] = e;
+        }
     }
 }
 
@@ -136,6 +155,9 @@ __device__ __forceinline__ void gemm_umma_cta(const GemmUmmaArgs& g, unsigned ch
     __syncthreads();
     tc_fence_after();
     const WsWait wait{sAbort, g.status};
+    // Launched as a programmatic dependent of the expansion pass, the CTA has come this far while
+    // that pass was still running; its units are complete (and visible) once this returns.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     constexpr uint32_t OFF_W = (PAIR ? 2u : 1u) * kGemmKU * kGemmUnit;     // W's place inside a stage
     const bool tr = g.trace != nullptr && blockIdx.x == 0;
 

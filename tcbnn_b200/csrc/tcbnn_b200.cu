@@ -219,8 +219,12 @@ int run_gemm_umma(const GemmArgs& g, const GemmUmmaPlan& p, void* workspace, int
         }))
         return 1;
     char* w = (char*)workspace;
-    k_expand_rows<<<elementwise_grid((long long)(p.MT + p.NT) * p.KB * 256, sms), 256, 0, st>>>(
-        g.A, g.M, g.lda, p.MT, g.W, g.N, g.ldw, p.NT, g.K, p.KB, (uint4*)(w + p.off_ea), (uint4*)(w + p.off_ew));
+    {
+        const long long tasks = (long long)(p.MT + p.NT) * ((p.KB + 3) / 4);   // one CTA per task, up to 8 per SM
+        const int grid = (int)(tasks < (long long)sms * 8 ? tasks : (long long)sms * 8);
+        k_expand_rows<<<grid, 256, 0, st>>>(g.A, g.M, g.lda, p.MT, g.W, g.N, g.ldw, p.NT, g.K, p.KB,
+                                            (uint4*)(w + p.off_ea), (uint4*)(w + p.off_ew));
+    }
     if (launch_check("gemm (operand expansion)")) return 1;
     umma::GemmUmmaArgs a;
     a.ea = (const unsigned char*)(w + p.off_ea); a.ew = (const unsigned char*)(w + p.off_ew);
@@ -243,10 +247,23 @@ int run_gemm_umma(const GemmArgs& g, const GemmUmmaPlan& p, void* workspace, int
             a.status = status_addr[dev];
         }
     }
-    if (p.pair)
-        k_gemm_umma<true><<<((p.MT + 1) / 2) * p.NT * p.splits, umma::kGemmThreads, umma::gemm_smem(true, p.stages), st>>>(a);
-    else
-        k_gemm_umma<false><<<p.MT * p.NT * p.splits, umma::kGemmThreads, umma::gemm_smem(false, p.stages), st>>>(a);
+    {
+        // a programmatic dependent of the expansion launch: set-up (barriers, tensor memory, unit
+        // scales) overlaps the expansion pass, the kernel waits for it before its first copy
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((p.pair ? (p.MT + 1) / 2 : p.MT) * p.NT * p.splits));
+        cfg.blockDim = dim3(umma::kGemmThreads);
+        cfg.dynamicSmemBytes = umma::gemm_smem(p.pair, p.stages);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = p.pair ? cudaLaunchKernelEx(&cfg, k_gemm_umma<true>, a)
+                                     : cudaLaunchKernelEx(&cfg, k_gemm_umma<false>, a);
+        if (e != cudaSuccess) return fail("gemm (tcgen05): %s", cudaGetErrorString(e));
+    }
     if (launch_check("gemm (tcgen05)")) return 1;
     if (p.splits == 1) return 0;                         // the GEMM's epilogue finished the layer
     GemmArgs f = g;
