@@ -181,9 +181,21 @@ def main():
     sys.stdout.flush()
     json_fd = os.dup(1)
     os.dup2(2, 1)
+    # Should the run stall, every rank writes where it stands to stderr (every 3 minutes), and a
+    # collective that does not complete raises after 5 minutes instead of waiting for ten.
+    import faulthandler
+    faulthandler.dump_traceback_later(180, repeat=True, file=sys.stderr)
+    t_start = time.time()
+
+    def progress(what):
+        if rank == 0:
+            sys.stderr.write("[bench %6.1f s] %s\n" % (time.time() - t_start, what))
+            sys.stderr.flush()
+
     # before any pinned buffer exists: this rank's share of the cores next to its GPU
     cores = tdist.pin_to_gpu_node(local, int(os.environ.get("LOCAL_WORLD_SIZE", world)))
-    tdist.init("nccl", dev)
+    tdist.init("nccl", dev, timeout_s=300)
+    progress("process group up, %d rank(s), cores of rank 0: %s" % (world, len(cores) if cores else "all"))
 
     B = args.batch
     spec = models.resnet18_spec(B)
@@ -219,9 +231,11 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    progress("network built")
     for _ in range(max(args.warmup, 3)):
         step()
     sync()
+    progress("warm-up done")
 
     # ---- device-resident throughput ------------------------------------------------------
     mark0 = sampler.mark()
@@ -242,6 +256,7 @@ def main():
         step(events)
     sync()
     clocks = sampler.summary(mark0, sampler.mark()) if rank == 0 else None
+    progress("timed region and per-layer pass done")
     logits_resident = net.layers[-1].get_output_gpu().cpu().numpy()
 
     # ---- the same step for at least three seconds ----------------------------------------
@@ -290,12 +305,15 @@ def main():
         sync()
         return e0.elapsed_time(e1)
 
+    progress("sustained loop done")
     ms_e2e_f32 = timed_feed(net, x_host)
+    progress("end-to-end (fp32 images) done")
     u8_np, lut = models.synthetic_input_u8(spec, tdist.shard_seed(4321, rank))
     x8_host = torch.from_numpy(u8_np).pin_memory()
     net8 = models.Network(spec, weights, x8_host,
                           input_abs_bound=models.SYNTHETIC_IMAGE_ABS_BOUND, input_lut=lut)
     ms_e2e = timed_feed(net8, x8_host)
+    progress("end-to-end (uint8 images) done")
     logits_e2e = logits_host.numpy().copy()
 
     # ---- what the end-to-end figure is bounded by: the plain host-to-device copy ----------
@@ -320,6 +338,8 @@ def main():
         checked = check_logits(spec, weights, x_np, args.check_images,
                                {"device_resident": logits_resident, "e2e_uint8": logits_e2e})
     sampler.stop()
+    progress("checks done")
+    faulthandler.cancel_dump_traceback_later()
 
     if rank == 0:
         conv_ms, launches = 0.0, 0

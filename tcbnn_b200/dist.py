@@ -8,9 +8,10 @@ import torch
 import torch.distributed as dist
 
 
-def init(backend=None, device=None):
+def init(backend=None, device=None, timeout_s=None):
     """Join the process group described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT.
-    Returns (rank, world).  A single process needs no group."""
+    Returns (rank, world).  A single process needs no group.  timeout_s: how long a collective may
+    take before it raises (the backend's default otherwise)."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 and not dist.is_initialized():
@@ -18,6 +19,9 @@ def init(backend=None, device=None):
         os.environ.setdefault("MASTER_PORT", "29511")
         backend = backend or ("nccl" if torch.cuda.is_available() else "gloo")
         kw = {"device_id": device} if (backend == "nccl" and device is not None) else {}
+        if timeout_s:
+            import datetime
+            kw["timeout"] = datetime.timedelta(seconds=float(timeout_s))
         dist.init_process_group(backend, rank=rank, world_size=world, **kw)
     return rank, world
 
