@@ -269,8 +269,14 @@ def main():
         sync()
         mark_s = sampler.mark()
         s0.record()
-        for _ in range(n_sus):
+        for i in range(n_sus):
             step()
+            # N > 1: the host stays at most 16 steps (and all-gathers) ahead of the device; with
+            # more than a thousand steps queued behind one another the 4-rank run stalled in the
+            # first barrier after this loop, the 2-rank run did not
+            if world > 1 and (i & 15) == 15:
+                gather.finish()
+                torch.cuda.current_stream().synchronize()
         gather.finish()
         s1.record()
         sync()
