@@ -195,7 +195,8 @@ int tcbnn_conv_layer_x(const tcbnn_conv_desc* d, const uint32_t* in, const void*
  * tile-per-group epilogues (0 uses them for layers without residuals and for chunk-major int16
  * residuals), 8 = as 0 but two CTAs per SM also for the all-warps-per-tile residual epilogues at an
  * n-tile of 64, 9 = as 0 but the loader-fed kernel's stages hold one 64-channel block each (0
- * puts four or two in a stage where three such stages fit).
+ * puts four or two in a stage where three such stages fit), 10 = as 0 but every n-tile of a layer
+ * gets the same number of CTAs (0 gives the n-tiles that carry a pooled residual more).
  * Process-wide; meant for tests and measurements.  No reference counterpart (the reference has one
  * kernel per layer type). */
 int tcbnn_set_conv_path(int path);

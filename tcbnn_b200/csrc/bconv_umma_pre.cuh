@@ -162,8 +162,21 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
     auto BAR_CFULL = [&](int b) { return bar0 + 8u * (16 + b); };
     auto BAR_CEMPTY = [&](int b) { return bar0 + 8u * (24 + b); };
 
-    const int nt = blockIdx.x % a.ntiles_n;
-    const int mfirst = blockIdx.x / a.ntiles_n, mstep = gridDim.x / a.ntiles_n;
+    // CTA -> (n-tile, first m-tile, stride over m-tiles).  Normally every n-tile gets the same
+    // share of the grid; where only the first n-tiles carry the epilogue's expensive part (a pooled
+    // residual injected into the first channels) the host gives those more CTAs each.
+    int nt, mfirst, mstep;
+    if (a.nt_heavy > 0) {
+        const int nh = a.nt_heavy * a.per_heavy;
+        if ((int)blockIdx.x < nh) {
+            nt = blockIdx.x % a.nt_heavy; mfirst = blockIdx.x / a.nt_heavy; mstep = a.per_heavy;
+        } else {
+            const int r = blockIdx.x - nh, nl = a.ntiles_n - a.nt_heavy;
+            nt = a.nt_heavy + r % nl; mfirst = r / nl; mstep = a.per_light;
+        }
+    } else {
+        nt = blockIdx.x % a.ntiles_n; mfirst = blockIdx.x / a.ntiles_n; mstep = gridDim.x / a.ntiles_n;
+    }
     const int NV = (int)a.NV;
     const int mtiles = (NV + 127) / 128;
     const int obase = nt * NT;

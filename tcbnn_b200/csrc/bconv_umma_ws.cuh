@@ -40,6 +40,9 @@ struct ConvWsArgs {
     int back_y, back_x;       // patch origin = tile start - (back_y*PW + back_x)
     long long NV;             // raster positions over the batch
     int ntiles_n;
+    // loader-fed kernel: the first nt_heavy n-tiles (those an injected, pooled residual falls into)
+    // get per_heavy CTAs each, the others per_light; 0 = every n-tile the same share of the grid
+    int nt_heavy, per_heavy, per_light;
     int as_split;             // activation-stationary kernel: parts the n-tiles of a task are split into
     int as_slots;             // ... and units in its filter ring (9 or 18)
     const uint4* pre;         // pre-expanded input planes (bconv_umma_pre.cuh), else null

@@ -486,6 +486,7 @@ int g_conv_two_ctas = 1;  // loader-fed kernel, n-tile 64: two CTAs of eight epi
 int g_conv_res_stage = 1; // loader-fed kernel: stage int16 residual rows in shared memory when possible
 int g_conv_tile = 1;      // loader-fed kernel: the tile-per-group epilogues where the tensors allow them
 int g_conv_cbs = 1;       // loader-fed kernel: four or two 64-channel blocks per stage where they fit
+int g_conv_uneven = 1;    // loader-fed kernel: more CTAs for the n-tiles that carry a pooled residual
 
 // The tile-per-group epilogues of the loader-fed kernel take residuals only in the chunk-major
 // int16 layout and write no int32 accumulators.
@@ -545,9 +546,31 @@ int launch_conv_umma_pre_k(umma::ConvWsArgs& a, size_t smem, int sms, cudaStream
     a.ntiles_n = a.O / NT;
     if (a.ntiles_n > sms) return fail("conv_layer: more n-tiles than SMs");
     const long long mtiles = (a.NV + 127) / 128;
-    long long per = (long long)(EPIW == 8 ? 2 : 1) * sms / a.ntiles_n;    // CTAs per n-tile: one or two per SM
+    const long long budget = (long long)(EPIW == 8 ? 2 : 1) * sms;        // one or two CTAs per SM
+    long long per = budget / a.ntiles_n;                                  // CTAs per n-tile
     if (per > mtiles) per = mtiles;
-    k_conv_umma_pre<NT, EPI, EPIW><<<(int)(per * a.ntiles_n), umma::pre_threads(EPIW), smem, st>>>(a);
+    long long grid = per * a.ntiles_n;
+    a.nt_heavy = 0; a.per_heavy = a.per_light = (int)per;
+    if (EPI == umma::kEpiTileRes && g_conv_uneven && a.res_in && a.residual_pool) {
+        // A pooled residual injected into the first channels only (the first block of a stage):
+        // the n-tiles it falls into take about 1.75 times as long per tile as the others when the
+        // tile's own MMAs are few (measured at 14 x 14 x 256: 0.141 ms against 0.081 for the same
+        // layer without pooling), so they get that many more CTAs each.
+        const int lim = a.residual_channels < a.res_in_ch ? a.residual_channels : a.res_in_ch;
+        const int heavy = (lim + NT - 1) / NT, light = a.ntiles_n - heavy;
+        if (heavy > 0 && light > 0 && (a.C >> 6) * a.R * a.S <= 36) {
+            long long pl = (long long)((double)budget / (1.75 * heavy + light));
+            if (pl < 1) pl = 1;
+            long long ph = (budget - light * pl) / heavy;
+            if (ph > mtiles) ph = mtiles;
+            if (pl > mtiles) pl = mtiles;
+            if (ph >= 1) {
+                a.nt_heavy = heavy; a.per_heavy = (int)ph; a.per_light = (int)pl;
+                grid = heavy * ph + light * pl;
+            }
+        }
+    }
+    k_conv_umma_pre<NT, EPI, EPIW><<<(int)grid, umma::pre_threads(EPIW), smem, st>>>(a);
     return launch_check("conv_layer (tcgen05, pre-expanded input)");
 }
 
@@ -1520,16 +1543,17 @@ int tcbnn_conv_prefers_chunked_residual(const tcbnn_conv_desc* d) {
 }
 
 int tcbnn_set_conv_path(int path) {
-    if (path < 0 || path > 9)
+    if (path < 0 || path > 10)
         return fail("set_conv_path: 0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05, 3 = tcgen05 filter-stationary kernel only, "
                     "4 / 5 = automatic with residual staging never / wherever possible, 6 = automatic, one CTA per SM only, "
                     "7 = automatic without the tile-per-group epilogues, 8 = automatic, two CTAs per SM wherever they fit, "
-                    "9 = automatic, one 64-channel block per stage");
+                    "9 = automatic, one 64-channel block per stage, 10 = automatic, every n-tile the same number of CTAs");
     g_conv_path = path >= 4 ? 0 : path;
     g_conv_res_stage = path == 4 ? 0 : path == 5 ? 2 : 1;
     g_conv_two_ctas = path == 6 ? 0 : path == 8 ? 2 : 1;
     g_conv_tile = path == 7 ? 0 : 1;
     g_conv_cbs = path == 9 ? 0 : 1;
+    g_conv_uneven = path == 10 ? 0 : 1;
     return 0;
 }
 

@@ -342,7 +342,8 @@ def set_conv_path(path):
     """0 = automatic, 1 = warp-level b1 MMA, 2 = tcgen05 (error when a layer is not eligible),
     3 = tcgen05 without the activation-stationary kernel, 4 / 5 = residual rows never / always
     staged in shared memory, 6 = one CTA per SM only, 7 = without the tile-per-group epilogues,
-    8 = two CTAs per SM wherever they fit, 9 = one 64-channel block per stage (tcbnn_set_conv_path)."""
+    8 = two CTAs per SM wherever they fit, 9 = one 64-channel block per stage, 10 = every n-tile the same number of CTAs
+    (tcbnn_set_conv_path)."""
     _l.call("tcbnn_set_conv_path", int(path))
 
 

@@ -587,7 +587,7 @@ def test_conv_layer_chunked_int16_residuals(cuda, case):
     r16 = ops.nhwc_to_chunked(dev(res_in.astype(np.int16), cuda)) if res_in is not None else None
     dx, dthr = dev(x, cuda), dev(thr, cuda)
     try:
-        for path in (0, 6, 8, 7, 9):
+        for path in (0, 6, 8, 7, 9, 10):
             ops.set_conv_path(path)
             for out_chunked in (True, False):
                 for proven in (False, True):
