@@ -232,31 +232,40 @@ __device__ void conv_umma_pre_cta(const ConvWsArgs& a, unsigned char* smem) {
 
     if (warp == LOAD_WARP) {
         // =============================== patch loader =======================================
-        if (lane == 0) {
+        // Lane 0 waits for a free stage and announces the bytes; up to eight lanes then issue the
+        // stage's bulk copies between them.  A thread is busy 100-200 clocks per copy whatever its
+        // size, and a stage of a stride-2 layer is 8 to 32 copies (four parity planes x two chunks
+        // per 64-channel block): one lane issuing them all took longer than the stage's MMAs.
+        {
+            constexpr int kIssueLanes = 8;
             const long long back = (long long)a.back_y * a.PW + a.back_x;
+            const int ncopy = CBS * NPLANE * 2;
             uint32_t it = 0, sph = 0;
             int s = 0;
             bool ok = true;
             for (int m = mfirst; m < mtiles && ok; m += mstep) {
                 const long long slot0 = (long long)m * 128 - back + a.pre_front;
                 for (int cb = 0; cb < NCB; cb += CBS, it++) {
-                    // the ring is several tiles deep: this lane mostly waits for a slot, and sleeps
+                    // the ring is several tiles deep: lane 0 mostly waits for a slot, and sleeps
                     // between polls so that it does not take issue slots from the epilogue warps
-                    ok = wait.relaxed(BAR_AEMPTY(s), sph ^ 1);
+                    if (lane == 0) ok = wait.relaxed(BAR_AEMPTY(s), sph ^ 1);
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                     if (!ok) break;
-                    mbar_expect_tx(BAR_AFULL(s), stage_bytes);
+                    if (lane == 0) mbar_expect_tx(BAR_AFULL(s), stage_bytes);
+                    __syncwarp();
                     const uint32_t dst = smem_u32(sAraw + (size_t)s * stage_bytes);
-                    for (int sub = 0; sub < CBS; sub++)
-                        for (int pl = 0; pl < NPLANE; pl++)
-#pragma unroll
-                            for (int c = 0; c < 2; c++)
-                                bulk_g2s(dst + (uint32_t)sub * block_bytes + (uint32_t)(pl * 2 + c) * (uint32_t)a.NPOS * 16u,
-                                         a.pre + ((size_t)((cb + sub) * 2 + c) * NPLANE + pl) * a.pre_positions + slot0,
-                                         (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
+                    if (lane < kIssueLanes) {
+                        for (int i = lane; i < ncopy; i += kIssueLanes) {
+                            const int c = i & 1, pl = (i >> 1) % NPLANE, sub = (i >> 1) / NPLANE;
+                            bulk_g2s(dst + (uint32_t)sub * block_bytes + (uint32_t)(pl * 2 + c) * (uint32_t)a.NPOS * 16u,
+                                     a.pre + ((size_t)((cb + sub) * 2 + c) * NPLANE + pl) * a.pre_positions + slot0,
+                                     (uint32_t)a.NPOS * 16u, BAR_AFULL(s));
+                        }
+                    }
                     if (++s == NSTAGE) { s = 0; sph ^= 1; }
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 // giving up: wait (bounded) for the copies still in flight before the CTA exits;
                 // stages below `s` were last filled in this pass over the ring, the others in the one before
                 for (int s2 = 0; s2 < NSTAGE; s2++) {
