@@ -1446,6 +1446,12 @@ static int conv_layer_impl(const tcbnn_conv_desc* d, const uint32_t* in, const v
                     const size_t need = umma::pre_smem_bytes(L.umma_npos, d->C, RS, L.pre_nt, stages, np);
                     if (need <= 227 * 1024) { a.pre_cbs = cbs; a.pre_stages = stages; pre_smem = need; }
                 }
+                // (a stride-2 layer next to a 147 KB filter block: two stages of two blocks still
+                // halve the issuing thread's wait / commit rounds)
+                if (a.pre_cbs == 1 && (d->C / 64) % 2 == 0) {
+                    const size_t need = umma::pre_smem_bytes(L.umma_npos, d->C, RS, L.pre_nt, 2, (d->stride_h == 2 ? 4 : 1) * 2);
+                    if (need <= 227 * 1024) { a.pre_cbs = 2; a.pre_stages = 2; pre_smem = need; }
+                }
             }
             // a pooled int16 residual is reduced by a streaming pass first when the workspace has
             // the room behind the planes: four scattered loads per value in the epilogue cost more
